@@ -1,0 +1,740 @@
+// Grouped GEMMs of the MoE expert path on tcgen05 tensor cores.
+//
+// One persistent, warp-specialised kernel template covers the five GEMMs of a forward + backward
+// pass.  Rows of every activation matrix live in the "padded grouped" layout produced by ck_route:
+// the rows routed to expert e occupy [padded_off[e], padded_off[e+1]), a multiple of 128 rows, pad
+// rows are zero.  A 128-row tile therefore belongs to exactly one expert and needs no row masks on
+// the operand side.
+//
+//   CTA (192 threads, one per SM, 128x256 output tile, fp32 accumulators in TMEM, double buffered)
+//     warp 0     : TMA producer  -- global -> 128B-swizzled shared memory, 4-stage mbarrier ring
+//     warp 1     : MMA issuer    -- tcgen05.mma (cta_group::1, M=128, N=256, K=32 bytes per instruction)
+//     warps 2..5 : epilogue      -- tcgen05.ld of the finished accumulator + the fused tail:
+//                                   activation, SwiGLU backward, router-weight grad, scatter-add
+//                                   combine, or a plain store (wgrad / generic grouped linear)
+//
+// Every mbarrier wait is bounded by wall-clock time; when one runs out the CTA raises
+// CK_DEV_TIMEOUT in the caller's status word, lets in-flight copies land, frees TMEM and returns.
+#include <cuda.h>
+
+#include "ck_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace ck {
+
+enum { MODE_STORE = 0, MODE_UP_ACT = 1, MODE_SCATTER_ADD = 2, MODE_ACT_BWD = 3, MODE_WGRAD = 4 };
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int kStages = 4;
+constexpr int kRowBytes = 128;                       // one swizzle row
+constexpr int kAStageBytes = BM * kRowBytes;         // 16 KiB
+constexpr int kBStageBytes = BN * kRowBytes;         // 32 KiB
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;                       // 2 accumulators x 256 fp32 columns
+constexpr uint64_t kWaitLimitNs = 4000000000ull;     // 4 s per wait, far above any legitimate stall
+constexpr int kMaxSchedExperts = CK_ROUTE_MAX_EXPERTS;
+
+struct GemmParams {
+    CUtensorMap tmA;
+    CUtensorMap tmB;
+    const int32_t *mtile_off;   // [E+1] (all modes but WGRAD)
+    const int32_t *padded_off;  // [E+1] (WGRAD)
+    const int32_t *row_map;     // [cap]
+    const void *gate_w;         // router weights, flat [T*k], dtype T (may be NULL)
+    const void *h_in;           // ACT_BWD: saved [cap, 2I] pre-activation
+    void *out0;                 // STORE/WGRAD: y | UP_ACT: act | ACT_BWD: dh
+    void *out1;                 // UP_ACT: h (may be NULL)
+    float *out32;               // SCATTER_ADD target [T, N]
+    float *dgates;              // ACT_BWD: [T*k] fp32
+    int32_t *dev_status;
+    int E;
+    int n_tiles;   // tiles along N
+    int m_tiles_w; // WGRAD: tiles along M
+    int N;         // valid output columns (UP_ACT / ACT_BWD: I)
+    int K;         // contraction length in elements (not WGRAD)
+    int M;         // WGRAD: output rows
+    int top_k;
+    int act_kind;
+    int n_fastest; // WGRAD tile order
+    int64_t cap;   // rows allocated for the padded layout
+};
+
+struct TileCoord {
+    int e;       // expert
+    int m_tile;  // global padded m-tile (not WGRAD) or m-tile of dW (WGRAD)
+    int n_tile;
+    int k_row0;  // WGRAD: first padded row of the expert
+    int k_iters;
+};
+
+template <typename T>
+struct GemmTraits {
+    static constexpr int kElem = sizeof(T);
+    static constexpr int BK = kRowBytes / kElem;       // elements of K per stage (64 or 32)
+    static constexpr int UMMA_K = 32 / kElem;          // elements of K per instruction (16 or 8)
+    static constexpr int kSteps = BK / UMMA_K;         // 4
+    static constexpr bool kTf32 = (kElem == 4);
+    static constexpr int kMnBoxElems = kRowBytes / kElem;  // MN elements per 128-byte swizzle row
+    static constexpr int kMnBoxBytes = BK * kRowBytes;     // one {128 B of MN} x {BK rows of K} box
+};
+
+template <typename T>
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn) {
+    const uint32_t fmt = (sizeof(T) == 4) ? 2u : (DT<T>::code == CK_BF16 ? 1u : 0u);
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+           (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+}
+
+struct SmemCtl {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_ptr;
+    volatile int abort_flag;
+    int32_t sched[kMaxSchedExperts + 1];
+};
+
+constexpr size_t kGemmSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * (kAStageBytes + kBStageBytes) + sizeof(SmemCtl);
+
+// bounded wait: false when the CTA is aborting or the time limit ran out
+__device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, SmemCtl *ctl, int32_t *dev_status) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 63u) == 0) {
+            if (ctl->abort_flag) return false;
+            if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
+                ctl->abort_flag = 1;
+                if (dev_status) atomicOr(dev_status, CK_DEV_TIMEOUT);
+                return false;
+            }
+        }
+    }
+}
+
+template <int MODE>
+__device__ __forceinline__ int total_tiles(const GemmParams &p, const SmemCtl *ctl) {
+    if constexpr (MODE == MODE_WGRAD) return p.E * p.m_tiles_w * p.n_tiles;
+    return ctl->sched[p.E] * p.n_tiles;
+}
+
+template <int MODE, int BK>
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, const SmemCtl *ctl, int t) {
+    TileCoord c;
+    if constexpr (MODE == MODE_WGRAD) {
+        const int per_e = p.m_tiles_w * p.n_tiles;
+        c.e = t / per_e;
+        const int local = t - c.e * per_e;
+        if (p.n_fastest) {
+            c.m_tile = local / p.n_tiles;
+            c.n_tile = local - c.m_tile * p.n_tiles;
+        } else {
+            c.n_tile = local / p.m_tiles_w;
+            c.m_tile = local - c.n_tile * p.m_tiles_w;
+        }
+        c.k_row0 = ctl->sched[c.e];
+        c.k_iters = (ctl->sched[c.e + 1] - c.k_row0) / BK;
+    } else {
+        // experts in order; inside an expert n-major with the m-tiles fastest, so that concurrently
+        // running CTAs share one weight panel and the expert's activation rows stay L2 resident
+        int lo = 0, hi = p.E;  // find e with sched[e]*n_tiles <= t < sched[e+1]*n_tiles
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (ctl->sched[mid] * p.n_tiles <= t) lo = mid; else hi = mid;
+        }
+        c.e = lo;
+        const int m0 = ctl->sched[lo];
+        const int mt = ctl->sched[lo + 1] - m0;
+        const int local = t - m0 * p.n_tiles;
+        c.n_tile = local / mt;
+        c.m_tile = m0 + (local - c.n_tile * mt);
+        c.k_row0 = 0;
+        c.k_iters = (p.K + BK - 1) / BK;
+    }
+    return c;
+}
+
+// ---- epilogue helpers ----------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void store8(T *ptr, const float *v) {
+    if constexpr (sizeof(T) == 4) {
+        reinterpret_cast<float4 *>(ptr)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4 *>(ptr)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+        Vec16<T> o;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o.v[i] = DT<T>::down(v[i]);
+        *reinterpret_cast<int4 *>(ptr) = *reinterpret_cast<const int4 *>(&o);
+    }
+}
+template <typename T>
+__device__ __forceinline__ void load8(const T *ptr, float *v) {
+    if constexpr (sizeof(T) == 4) {
+        const float4 a = reinterpret_cast<const float4 *>(ptr)[0];
+        const float4 b = reinterpret_cast<const float4 *>(ptr)[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        Vec16<T> o;
+        *reinterpret_cast<int4 *>(&o) = *reinterpret_cast<const int4 *>(ptr);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = DT<T>::up(o.v[i]);
+    }
+}
+
+__device__ __forceinline__ float act_fwd(int kind, float u, float g) {
+    const float s = sigmoid_fast(g);
+    return kind == CK_ACT_SWIGLU ? u * g * s : u * s;
+}
+// returns a = act(u, g); d(out)/du and d(out)/dg multipliers
+__device__ __forceinline__ void act_bwd(int kind, float u, float g, float &a, float &du_m, float &dg_m) {
+    const float s = sigmoid_fast(g);
+    if (kind == CK_ACT_SWIGLU) {
+        const float silu = g * s;
+        a = u * silu;
+        du_m = silu;
+        dg_m = u * (s + silu * (1.0f - s));
+    } else {
+        a = u * s;
+        du_m = s;
+        dg_m = u * s * (1.0f - s);
+    }
+}
+
+// ---- the kernel ------------------------------------------------------------------------------------
+template <typename T, int MODE, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
+    using TR = GemmTraits<T>;
+    constexpr bool A_MN = (MODE == MODE_WGRAD);
+    static_assert(MODE != MODE_WGRAD || B_MN, "wgrad contracts over rows: both operands are MN-major");
+    constexpr int BK = TR::BK;
+    constexpr uint32_t kIdesc = make_idesc<T>(A_MN, B_MN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_u32 & 1023u)) & 1023u;
+    uint8_t *smem = smem_raw + pad;
+    const uint32_t smem_a = raw_u32 + pad;
+    const uint32_t smem_b = smem_a + kStages * kAStageBytes;
+    SmemCtl *ctl = reinterpret_cast<SmemCtl *>(smem + kStages * (kAStageBytes + kBStageBytes));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // ---- setup -------------------------------------------------------------------------------------
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&ctl->tmem_full[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[b]), 4);
+        }
+        ctl->abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&p.tmA);
+        ptx::prefetch_tensormap(&p.tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(&ctl->tmem_ptr), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    {
+        const int32_t *src = (MODE == MODE_WGRAD) ? p.padded_off : p.mtile_off;
+        for (int i = threadIdx.x; i <= p.E; i += kGemmThreads) ctl->sched[i] = src[i];
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_ptr;
+    int ntiles = total_tiles<MODE>(p, ctl);
+    {
+        // the tile tables come from device memory: never walk past the rows the caller allocated
+        const int64_t rows = (MODE == MODE_WGRAD) ? int64_t(ctl->sched[p.E]) : int64_t(ctl->sched[p.E]) * BM;
+        if (rows > p.cap || rows < 0) {
+            ntiles = 0;
+            if (threadIdx.x == 0 && p.dev_status) atomicOr(p.dev_status, CK_DEV_META);
+        }
+    }
+
+    if (warp == 0) {
+        // =================================== TMA producer ===================================
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
+                for (int kb = 0; kb < c.k_iters; ++kb) {
+                    if (!wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status)) { ok = false; break; }
+                    const uint32_t full = ptx::smem_u32(&ctl->full[stage]);
+                    ptx::mbar_expect_tx(full, kAStageBytes + kBStageBytes);
+                    const uint32_t sa = smem_a + stage * kAStageBytes;
+                    const uint32_t sb = smem_b + stage * kBStageBytes;
+                    if constexpr (MODE == MODE_WGRAD) {
+                        const int krow = c.k_row0 + kb * BK;
+#pragma unroll
+                        for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
+                            ptx::tma_load_2d(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
+#pragma unroll
+                        for (int j = 0; j < BN / TR::kMnBoxElems; ++j)
+                            ptx::tma_load_2d(sb + j * TR::kMnBoxBytes, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, krow);
+                    } else {
+                        const int k0 = kb * BK;
+                        ptx::tma_load_2d(sa, &p.tmA, full, k0, c.m_tile * BM);
+                        if constexpr (B_MN) {
+#pragma unroll
+                            for (int j = 0; j < BN / TR::kMnBoxElems; ++j)
+                                ptx::tma_load_3d(sb + j * TR::kMnBoxBytes, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, k0, c.e);
+                        } else if constexpr (MODE == MODE_UP_ACT) {
+                            // 128 rows of W_up followed by the matching 128 rows of W_gate
+                            ptx::tma_load_3d(sb, &p.tmB, full, k0, c.n_tile * (BN / 2), c.e);
+                            ptx::tma_load_3d(sb + kBStageBytes / 2, &p.tmB, full, k0, p.N + c.n_tile * (BN / 2), c.e);
+                        } else {
+                            ptx::tma_load_3d(sb, &p.tmB, full, k0, c.n_tile * BN, c.e);
+                        }
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // aborting: give copies already in flight time to land before the CTA exits
+                for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // =================================== MMA issuer =====================================
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++it) {
+                const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
+                const int buf = it & 1;
+                if (!wait_barrier(ptx::smem_u32(&ctl->tmem_empty[buf]), ((uint32_t(it) >> 1) & 1u) ^ 1u, ctl, p.dev_status)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + uint32_t(buf) * BN;
+                for (int kb = 0; kb < c.k_iters; ++kb) {
+                    if (!wait_barrier(ptx::smem_u32(&ctl->full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = smem_a + stage * kAStageBytes;
+                    const uint32_t sb = smem_b + stage * kBStageBytes;
+#pragma unroll
+                    for (int k = 0; k < TR::kSteps; ++k) {
+                        uint64_t adesc, bdesc;
+                        if constexpr (A_MN) adesc = ptx::umma_desc_mnmajor(sa + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
+                        else adesc = ptx::umma_desc_kmajor(sa + k * 32);
+                        if constexpr (B_MN) bdesc = ptx::umma_desc_mnmajor(sb + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
+                        else bdesc = ptx::umma_desc_kmajor(sb + k * 32);
+                        ptx::umma_ss<TR::kTf32>(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit(ptx::smem_u32(&ctl->empty[stage]));  // frees the stage when these MMAs retire
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                ptx::tc_commit(ptx::smem_u32(&ctl->tmem_full[buf]));  // accumulator complete
+            }
+            if (!ok) {
+                for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            }
+        }
+        __syncwarp();
+    } else {
+        // =================================== epilogue =======================================
+        const int quarter = warp & 3;              // TMEM lanes this warp may read
+        const int row_in_tile = quarter * 32 + lane;
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++it) {
+            const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
+            const int buf = it & 1;
+            if (!wait_barrier(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t tbase = tmem_base + uint32_t(buf) * BN + (uint32_t(quarter * 32) << 16);
+            const bool have_acc = c.k_iters > 0;
+
+            if constexpr (MODE == MODE_STORE || MODE == MODE_WGRAD) {
+                T *out;
+                bool row_ok;
+                if constexpr (MODE == MODE_WGRAD) {
+                    const int m = c.m_tile * BM + row_in_tile;
+                    row_ok = m < p.M;
+                    out = reinterpret_cast<T *>(p.out0) + (int64_t(c.e) * p.M + m) * int64_t(p.N);
+                } else {
+                    row_ok = true;
+                    out = reinterpret_cast<T *>(p.out0) + (int64_t(c.m_tile) * BM + row_in_tile) * int64_t(p.N);
+                }
+                const int n0 = c.n_tile * BN;
+#pragma unroll 1
+                for (int cc = 0; cc < BN; cc += 32) {
+                    uint32_t r[32];
+                    if (have_acc) {
+                        ptx::tmem_ld32(tbase + cc, r);
+                        ptx::tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = 0u;
+                    }
+                    if (row_ok) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const int n = n0 + cc + g * 8;
+                            if (n < p.N) {
+                                float v[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+                                store8<T>(out + n, v);
+                            }
+                        }
+                    }
+                }
+            } else if constexpr (MODE == MODE_UP_ACT) {
+                const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
+                const int32_t src = p.row_map[prow];
+                float w = 1.0f;
+                if (p.gate_w) w = (src >= 0) ? DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]) : 0.0f;
+                T *act = reinterpret_cast<T *>(p.out0) + prow * int64_t(p.N);
+                T *h = p.out1 ? reinterpret_cast<T *>(p.out1) + prow * int64_t(2 * p.N) : nullptr;
+                const int n0 = c.n_tile * (BN / 2);
+#pragma unroll 1
+                for (int cc = 0; cc < BN / 2; cc += 32) {
+                    uint32_t ru[32], rg[32];
+                    ptx::tmem_ld32(tbase + cc, ru);
+                    ptx::tmem_ld32(tbase + BN / 2 + cc, rg);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const int n = n0 + cc + g * 8;
+                        if (n < p.N) {
+                            float vu[8], vg[8], va[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                vu[i] = __uint_as_float(ru[g * 8 + i]);
+                                vg[i] = __uint_as_float(rg[g * 8 + i]);
+                                va[i] = w * act_fwd(p.act_kind, vu[i], vg[i]);
+                            }
+                            store8<T>(act + n, va);
+                            if (h) {
+                                store8<T>(h + n, vu);
+                                store8<T>(h + p.N + n, vg);
+                            }
+                        }
+                    }
+                }
+            } else if constexpr (MODE == MODE_SCATTER_ADD) {
+                const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
+                const int32_t src = p.row_map[prow];
+                float *out = p.out32 + int64_t(src >= 0 ? src / p.top_k : 0) * int64_t(p.N);
+                const int n0 = c.n_tile * BN;
+#pragma unroll 1
+                for (int cc = 0; cc < BN; cc += 32) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(tbase + cc, r);
+                    ptx::tmem_ld_wait();
+                    if (src >= 0) {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            const int n = n0 + cc + g * 4;
+                            if (n < p.N)
+                                ptx::red_add_v4(out + n, __uint_as_float(r[g * 4 + 0]), __uint_as_float(r[g * 4 + 1]),
+                                                __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+                        }
+                    }
+                }
+            } else if constexpr (MODE == MODE_ACT_BWD) {
+                const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
+                const int32_t src = p.row_map[prow];
+                float w = (src >= 0) ? 1.0f : 0.0f;
+                if (p.gate_w && src >= 0) w = DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]);
+                const T *h = reinterpret_cast<const T *>(p.h_in) + prow * int64_t(2 * p.N);
+                T *dh = reinterpret_cast<T *>(p.out0) + prow * int64_t(2 * p.N);
+                const int n0 = c.n_tile * BN;
+                float dgate_w = 0.0f;
+#pragma unroll 1
+                for (int cc = 0; cc < BN; cc += 32) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(tbase + cc, r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const int n = n0 + cc + g * 8;
+                        if (n < p.N) {
+                            float vu[8], vg[8], du[8], dg[8];
+                            load8<T>(h + n, vu);
+                            load8<T>(h + p.N + n, vg);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float acc = __uint_as_float(r[g * 8 + i]);
+                                float a, du_m, dg_m;
+                                act_bwd(p.act_kind, vu[i], vg[i], a, du_m, dg_m);
+                                dgate_w += a * acc;
+                                const float da = w * acc;
+                                du[i] = da * du_m;
+                                dg[i] = da * dg_m;
+                            }
+                            store8<T>(dh + n, du);
+                            store8<T>(dh + p.N + n, dg);
+                        }
+                    }
+                }
+                if (p.dgates && src >= 0) atomicAdd(p.dgates + src, dgate_w);
+            }
+            // release the accumulator buffer
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->tmem_empty[buf]));
+        }
+    }
+
+    // ---- teardown ------------------------------------------------------------------------------------
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &ptr, 12000, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !ptr) {
+        set_last_cuda_error(e, "cudaGetDriverEntryPointByVersion(cuTensorMapEncodeTiled)");
+        return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    return fn;
+}
+
+template <typename T>
+static CUtensorMapDataType tm_dtype() {
+    if (sizeof(T) == 4) return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    return DT<T>::code == CK_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+
+// rank-2 or rank-3 row-major tensor; dims innermost first; box innermost first
+template <typename T>
+static int encode_map(CUtensorMap *tm, const void *base, int rank, const uint64_t *dims, const uint32_t *box) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return CK_ERR_CUDA;
+    cuuint64_t gdims[3];
+    cuuint64_t gstrides[2];
+    cuuint32_t gbox[3];
+    cuuint32_t estr[3] = {1, 1, 1};
+    uint64_t stride = sizeof(T);
+    for (int i = 0; i < rank; ++i) {
+        gdims[i] = dims[i];
+        gbox[i] = box[i];
+        stride *= dims[i];
+        if (i < rank - 1) gstrides[i] = stride;
+    }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (dims[0] * sizeof(T)) % 16 != 0) return CK_ERR_SHAPE;
+    CUresult r = fn(tm, tm_dtype<T>(), (cuuint32_t)rank, const_cast<void *>(base), gdims, gstrides, gbox, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+        return CK_ERR_CUDA;
+    }
+    return CK_OK;
+}
+
+template <typename T, int MODE, bool B_MN>
+static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t stream) {
+    auto kern = grouped_gemm_kernel<T, MODE, B_MN>;
+    CK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes));
+    int64_t grid = num_sms();
+    if (grid > max_tiles) grid = max_tiles;
+    if (grid < 1) return CK_OK;
+    kern<<<dim3((unsigned)grid), kGemmThreads, kGemmSmemBytes, stream>>>(p);
+    CK_LAUNCH_CHECK("grouped_gemm_kernel");
+    return CK_OK;
+}
+
+// activations [cap, K] as K-major A: box {BK, 128}
+template <typename T>
+static int map_a_kmajor(CUtensorMap *tm, const void *a, int64_t cap, int K) {
+    const uint64_t dims[2] = {uint64_t(K), uint64_t(cap)};
+    const uint32_t box[2] = {uint32_t(GemmTraits<T>::BK), uint32_t(BM)};
+    return encode_map<T>(tm, a, 2, dims, box);
+}
+// weights [E, rows, K] as K-major B: box {BK, box_rows, 1}
+template <typename T>
+static int map_w_kmajor(CUtensorMap *tm, const void *w, int E, int rows, int K, int box_rows) {
+    const uint64_t dims[3] = {uint64_t(K), uint64_t(rows), uint64_t(E)};
+    const uint32_t box[3] = {uint32_t(GemmTraits<T>::BK), uint32_t(box_rows), 1};
+    return encode_map<T>(tm, w, 3, dims, box);
+}
+// weights [E, K, N] as MN-major B: box {128 bytes of N, BK rows of K, 1}
+template <typename T>
+static int map_w_mnmajor(CUtensorMap *tm, const void *w, int E, int K, int N) {
+    const uint64_t dims[3] = {uint64_t(N), uint64_t(K), uint64_t(E)};
+    const uint32_t box[3] = {uint32_t(GemmTraits<T>::kMnBoxElems), uint32_t(GemmTraits<T>::BK), 1};
+    return encode_map<T>(tm, w, 3, dims, box);
+}
+// activations [cap, cols] as MN-major operand of wgrad: box {128 bytes of cols, BK rows}
+template <typename T>
+static int map_act_mnmajor(CUtensorMap *tm, const void *a, int64_t cap, int cols) {
+    const uint64_t dims[2] = {uint64_t(cols), uint64_t(cap)};
+    const uint32_t box[2] = {uint32_t(GemmTraits<T>::kMnBoxElems), uint32_t(GemmTraits<T>::BK)};
+    return encode_map<T>(tm, a, 2, dims, box);
+}
+
+static bool dims_ok(int64_t cap, int a, int b) { return cap > 0 && cap % BM == 0 && a > 0 && b > 0 && a % 8 == 0 && b % 8 == 0; }
+
+template <typename T>
+static int up_act_fwd_t(const void *xg, const void *wfc, const void *gate_w, const int32_t *row_map,
+                        const int32_t *mtile_off, void *act, void *h, int E, int64_t cap, int H, int I, int act_kind,
+                        int32_t *dev_status, cudaStream_t stream) {
+    GemmParams p = {};
+    p.cap = cap;
+    int rc;
+    if ((rc = map_a_kmajor<T>(&p.tmA, xg, cap, H)) != CK_OK) return rc;
+    if ((rc = map_w_kmajor<T>(&p.tmB, wfc, E, 2 * I, H, BN / 2)) != CK_OK) return rc;
+    p.mtile_off = mtile_off; p.row_map = row_map; p.gate_w = gate_w; p.out0 = act; p.out1 = h; p.dev_status = dev_status;
+    p.E = E; p.n_tiles = (I + BN / 2 - 1) / (BN / 2); p.N = I; p.K = H; p.act_kind = act_kind; p.top_k = 1;
+    return launch_gemm<T, MODE_UP_ACT, false>(p, (cap / BM) * p.n_tiles, stream);
+}
+
+template <typename T>
+static int down_combine_fwd_t(const void *act, const void *wproj, const int32_t *row_map, const int32_t *mtile_off,
+                              float *out32, int E, int64_t cap, int H, int I, int top_k, int32_t *dev_status,
+                              cudaStream_t stream) {
+    GemmParams p = {};
+    p.cap = cap;
+    int rc;
+    if ((rc = map_a_kmajor<T>(&p.tmA, act, cap, I)) != CK_OK) return rc;
+    if ((rc = map_w_kmajor<T>(&p.tmB, wproj, E, H, I, BN)) != CK_OK) return rc;
+    p.mtile_off = mtile_off; p.row_map = row_map; p.out32 = out32; p.dev_status = dev_status;
+    p.E = E; p.n_tiles = (H + BN - 1) / BN; p.N = H; p.K = I; p.top_k = top_k;
+    return launch_gemm<T, MODE_SCATTER_ADD, false>(p, (cap / BM) * p.n_tiles, stream);
+}
+
+template <typename T>
+static int dgrad_down_t(const void *dyg, const void *wproj, const void *h, const void *gate_w, const int32_t *row_map,
+                        const int32_t *mtile_off, void *dh, float *dgates, int E, int64_t cap, int H, int I, int act_kind,
+                        int32_t *dev_status, cudaStream_t stream) {
+    GemmParams p = {};
+    p.cap = cap;
+    int rc;
+    if ((rc = map_a_kmajor<T>(&p.tmA, dyg, cap, H)) != CK_OK) return rc;
+    if ((rc = map_w_mnmajor<T>(&p.tmB, wproj, E, H, I)) != CK_OK) return rc;
+    p.mtile_off = mtile_off; p.row_map = row_map; p.gate_w = gate_w; p.h_in = h; p.out0 = dh; p.dgates = dgates;
+    p.dev_status = dev_status;
+    p.E = E; p.n_tiles = (I + BN - 1) / BN; p.N = I; p.K = H; p.act_kind = act_kind; p.top_k = 1;
+    return launch_gemm<T, MODE_ACT_BWD, true>(p, (cap / BM) * p.n_tiles, stream);
+}
+
+template <typename T>
+static int dgrad_up_t(const void *dh, const void *wfc, const int32_t *row_map, const int32_t *mtile_off, float *dx32,
+                      int E, int64_t cap, int H, int I2, int top_k, int32_t *dev_status, cudaStream_t stream) {
+    GemmParams p = {};
+    p.cap = cap;
+    int rc;
+    if ((rc = map_a_kmajor<T>(&p.tmA, dh, cap, I2)) != CK_OK) return rc;
+    if ((rc = map_w_mnmajor<T>(&p.tmB, wfc, E, I2, H)) != CK_OK) return rc;
+    p.mtile_off = mtile_off; p.row_map = row_map; p.out32 = dx32; p.dev_status = dev_status;
+    p.E = E; p.n_tiles = (H + BN - 1) / BN; p.N = H; p.K = I2; p.top_k = top_k;
+    return launch_gemm<T, MODE_SCATTER_ADD, true>(p, (cap / BM) * p.n_tiles, stream);
+}
+
+template <typename T>
+static int wgrad_t(const void *a, const void *b, const int32_t *padded_off, void *dw, int E, int64_t cap, int M, int N,
+                   int32_t *dev_status, cudaStream_t stream) {
+    GemmParams p = {};
+    p.cap = cap;
+    int rc;
+    if ((rc = map_act_mnmajor<T>(&p.tmA, a, cap, M)) != CK_OK) return rc;
+    if ((rc = map_act_mnmajor<T>(&p.tmB, b, cap, N)) != CK_OK) return rc;
+    p.padded_off = padded_off; p.out0 = dw; p.dev_status = dev_status;
+    p.E = E; p.m_tiles_w = (M + BM - 1) / BM; p.n_tiles = (N + BN - 1) / BN; p.M = M; p.N = N;
+    // keep the smaller operand panel set L2 resident: iterate the shorter output dimension fastest
+    p.n_fastest = (N <= M) ? 1 : 0;
+    return launch_gemm<T, MODE_WGRAD, true>(p, int64_t(E) * p.m_tiles_w * p.n_tiles, stream);
+}
+
+template <typename T>
+static int grouped_linear_t(const void *x, const void *w, const int32_t *mtile_off, void *y, int E, int64_t cap, int N,
+                            int K, int trans_w, int32_t *dev_status, cudaStream_t stream) {
+    GemmParams p = {};
+    p.cap = cap;
+    int rc;
+    if ((rc = map_a_kmajor<T>(&p.tmA, x, cap, K)) != CK_OK) return rc;
+    p.mtile_off = mtile_off; p.out0 = y; p.dev_status = dev_status;
+    p.E = E; p.n_tiles = (N + BN - 1) / BN; p.N = N; p.K = K; p.top_k = 1;
+    if (trans_w) {
+        if ((rc = map_w_mnmajor<T>(&p.tmB, w, E, K, N)) != CK_OK) return rc;
+        return launch_gemm<T, MODE_STORE, true>(p, (cap / BM) * p.n_tiles, stream);
+    }
+    if ((rc = map_w_kmajor<T>(&p.tmB, w, E, N, K, BN)) != CK_OK) return rc;
+    return launch_gemm<T, MODE_STORE, false>(p, (cap / BM) * p.n_tiles, stream);
+}
+
+}  // namespace ck
+
+using namespace ck;
+
+#define CK_DISPATCH_DTYPE(dtype, CALL)                              \
+    switch (dtype) {                                                \
+        case CK_BF16: { using T = __nv_bfloat16; return CALL; }     \
+        case CK_F16: { using T = __half; return CALL; }             \
+        case CK_F32: { using T = float; return CALL; }              \
+        default: return CK_ERR_UNSUPPORTED;                         \
+    }
+
+extern "C" int ck_moe_up_act_fwd(const void *xg, const void *wfc, const void *gate_w, const int32_t *row_map,
+                                 const int32_t *mtile_off, void *act, void *h, int E, int64_t cap, int H, int I,
+                                 int act_kind, int dtype, int32_t *dev_status, void *stream) {
+    if (!xg || !wfc || !row_map || !mtile_off || !act || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
+    if (act_kind != CK_ACT_SWIGLU && act_kind != CK_ACT_GLU) return CK_ERR_UNSUPPORTED;
+    CK_DISPATCH_DTYPE(dtype, (up_act_fwd_t<T>(xg, wfc, gate_w, row_map, mtile_off, act, h, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream)));
+}
+
+extern "C" int ck_moe_down_combine_fwd(const void *act, const void *wproj, const int32_t *row_map,
+                                       const int32_t *mtile_off, float *out32, int E, int64_t cap, int H, int I,
+                                       int top_k, int dtype, int32_t *dev_status, void *stream) {
+    if (!act || !wproj || !row_map || !mtile_off || !out32 || E <= 0 || E > kMaxSchedExperts || top_k <= 0 || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
+    CK_DISPATCH_DTYPE(dtype, (down_combine_fwd_t<T>(act, wproj, row_map, mtile_off, out32, E, cap, H, I, top_k, dev_status, (cudaStream_t)stream)));
+}
+
+extern "C" int ck_moe_dgrad_down(const void *dyg, const void *wproj, const void *h, const void *gate_w,
+                                 const int32_t *row_map, const int32_t *mtile_off, void *dh, float *dgates, int E,
+                                 int64_t cap, int H, int I, int act_kind, int dtype, int32_t *dev_status, void *stream) {
+    if (!dyg || !wproj || !h || !row_map || !mtile_off || !dh || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
+    if (act_kind != CK_ACT_SWIGLU && act_kind != CK_ACT_GLU) return CK_ERR_UNSUPPORTED;
+    CK_DISPATCH_DTYPE(dtype, (dgrad_down_t<T>(dyg, wproj, h, gate_w, row_map, mtile_off, dh, dgates, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream)));
+}
+
+extern "C" int ck_moe_dgrad_up(const void *dh, const void *wfc, const int32_t *row_map, const int32_t *mtile_off,
+                               float *dx32, int E, int64_t cap, int H, int I2, int top_k, int dtype,
+                               int32_t *dev_status, void *stream) {
+    if (!dh || !wfc || !row_map || !mtile_off || !dx32 || E <= 0 || E > kMaxSchedExperts || top_k <= 0 || !dims_ok(cap, H, I2)) return CK_ERR_SHAPE;
+    CK_DISPATCH_DTYPE(dtype, (dgrad_up_t<T>(dh, wfc, row_map, mtile_off, dx32, E, cap, H, I2, top_k, dev_status, (cudaStream_t)stream)));
+}
+
+extern "C" int ck_moe_wgrad(const void *a, const void *b, const int32_t *padded_off, void *dw, int E, int64_t cap, int M,
+                            int N, int dtype, int32_t *dev_status, void *stream) {
+    if (!a || !b || !padded_off || !dw || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, M, N)) return CK_ERR_SHAPE;
+    CK_DISPATCH_DTYPE(dtype, (wgrad_t<T>(a, b, padded_off, dw, E, cap, M, N, dev_status, (cudaStream_t)stream)));
+}
+
+extern "C" int ck_moe_grouped_linear(const void *x, const void *w, const int32_t *mtile_off, void *y, int E, int64_t cap,
+                                     int N, int K, int trans_w, int dtype, int32_t *dev_status, void *stream) {
+    if (!x || !w || !mtile_off || !y || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, N, K)) return CK_ERR_SHAPE;
+    CK_DISPATCH_DTYPE(dtype, (grouped_linear_t<T>(x, w, mtile_off, y, E, cap, N, K, trans_w, dev_status, (cudaStream_t)stream)));
+}

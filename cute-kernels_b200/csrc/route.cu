@@ -1,0 +1,343 @@
+// Routing kernels: continuous_count (histogram) and route (count + scan + stable scatter).
+//
+// Both are HBM-bound integer passes over the expert ids.  The histogram aggregates equal ids
+// inside a warp with __match_any_sync / __popc so that a skewed (Zipf) id distribution costs one
+// shared-memory update per distinct id per warp step instead of one contended atomic per element.
+// The stable scatter gives every warp a contiguous slice of the ids; a slice's position in the
+// output is (exclusive scan over experts) + (exclusive scan over earlier warps for that expert) +
+// (running count inside the warp), which is exactly the order torch.sort(stable=True) produces.
+#include "ck_common.cuh"
+
+namespace ck {
+
+constexpr int kRouteMaxWarps = 148 * 32;  // upper bound on id slices (fixed so workspace size is device independent)
+constexpr int kRouteWarpsPerBlock = 8;
+constexpr int kStep = 128;  // ids per warp per unrolled step (4 coalesced loads of 32)
+
+__device__ __forceinline__ unsigned lanemask_lt() {
+    unsigned m;
+    asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+    return m;
+}
+
+// ------------------------------------------------------------------------------------------------
+// continuous_count: counts[v] += #ids == v.  counts is zeroed by the host wrapper beforehand.
+// ------------------------------------------------------------------------------------------------
+template <typename IdT>
+__global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids, int64_t n, int size,
+                                                   uint32_t *__restrict__ counts) {
+    extern __shared__ uint32_t hist[];
+    for (int i = threadIdx.x; i < size; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_id = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    const int64_t nchunks = (n + kStep - 1) / kStep;
+
+    for (int64_t c = warp_id; c < nchunks; c += nwarps) {
+        const int64_t b = c * kStep + lane;
+        int key[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t idx = b + 32 * j;
+            long long v = -1;
+            if (idx < n) v = (long long)ids[idx];
+            key[j] = (v >= 0 && v < size) ? int(v) : -1;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const unsigned m = __match_any_sync(0xffffffffu, key[j]);
+            if (key[j] >= 0 && lane == __ffs(m) - 1) atomicAdd(&hist[key[j]], __popc(m));
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const uint32_t v = hist[i];
+        if (v) atomicAdd(&counts[i], v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// route pass 1: per-warp histogram of a contiguous slice of ids -> whist[w][E]
+// ------------------------------------------------------------------------------------------------
+template <typename IdT>
+__global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
+    route_hist_kernel(const IdT *__restrict__ ids, int64_t n, int E, int64_t slice, int W,
+                      int32_t *__restrict__ whist, int32_t *dev_status) {
+    extern __shared__ int32_t smem_i[];
+    const int lane = threadIdx.x & 31;
+    const int wib = threadIdx.x >> 5;
+    const int w = blockIdx.x * kRouteWarpsPerBlock + wib;
+    int32_t *wh = smem_i + wib * E;
+    if (w >= W) return;  // whole warp leaves together (no block-level sync below)
+    for (int e = lane; e < E; e += 32) wh[e] = 0;
+    __syncwarp();
+
+    const int64_t begin = int64_t(w) * slice;
+    const int64_t end = min(begin + slice, n);
+    bool bad = false;
+    for (int64_t off = begin; off < end; off += kStep) {
+        int key[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t idx = off + 32 * j + lane;
+            long long v = -1;
+            bool have = idx < end;
+            if (have) v = (long long)ids[idx];
+            const bool ok = (v >= 0 && v < E);
+            bad |= (have && !ok);
+            key[j] = ok ? int(v) : -1;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const unsigned m = __match_any_sync(0xffffffffu, key[j]);
+            if (key[j] >= 0 && lane == __ffs(m) - 1) wh[key[j]] += __popc(m);
+            __syncwarp();
+        }
+    }
+    for (int e = lane; e < E; e += 32) whist[int64_t(w) * E + e] = wh[e];
+    if (__any_sync(0xffffffffu, bad) && lane == 0 && dev_status) atomicOr(dev_status, CK_DEV_RANGE);
+}
+
+// block-wide exclusive scan of one int per thread (blockDim.x == 1024); returns the exclusive
+// prefix, writes the block total to *total.
+__device__ __forceinline__ int block_excl_scan_1024(int v, int *total, int *warp_sums /*[32]*/) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += t;
+    }
+    if (lane == 31) warp_sums[wid] = incl;
+    __syncthreads();
+    if (wid == 0) {
+        int s = warp_sums[lane];
+        int si = s;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, si, d);
+            if (lane >= d) si += t;
+        }
+        warp_sums[lane] = si - s;  // exclusive prefix of warp sums
+        if (lane == 31) *total = si;
+    }
+    __syncthreads();
+    const int res = warp_sums[wid] + incl - v;
+    __syncthreads();  // warp_sums / total may be reused by the caller
+    return res;
+}
+
+// ------------------------------------------------------------------------------------------------
+// route pass 2: one block per expert scans whist[:, e] over the slices (in place: whist[w][e]
+// becomes the number of ids == e in earlier slices); the last block to finish scans the E counts
+// into the exclusive / end / padded offsets.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+    route_scan_kernel(int32_t *__restrict__ whist, int W, int E, uint32_t *__restrict__ counts,
+                      int32_t *__restrict__ excl_off, int32_t *__restrict__ end_off,
+                      int32_t *__restrict__ padded_off, int32_t *__restrict__ mtile_off, int *ticket) {
+    __shared__ int warp_sums[32];
+    __shared__ int total_s;
+    __shared__ int is_last;
+    const int e = blockIdx.x;
+    int carry = 0;
+    for (int base = 0; base < W; base += 1024) {
+        const int w = base + threadIdx.x;
+        const int v = (w < W) ? whist[int64_t(w) * E + e] : 0;
+        const int ex = block_excl_scan_1024(v, &total_s, warp_sums);
+        if (w < W) whist[int64_t(w) * E + e] = carry + ex;
+        carry += total_s;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        counts[e] = uint32_t(carry);
+        __threadfence();
+        const int t = atomicAdd(ticket, 1);
+        is_last = (t == E - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // E <= 1024: one expert per thread
+    const int c = (threadIdx.x < E) ? int(__ldcg(&counts[threadIdx.x])) : 0;
+    const int ex = block_excl_scan_1024(c, &total_s, warp_sums);
+    if (threadIdx.x < E) {
+        excl_off[threadIdx.x] = ex;
+        end_off[threadIdx.x] = ex + c;
+    }
+    if (padded_off) {
+        const int tiles = (c + CK_TILE_M - 1) / CK_TILE_M;
+        const int tex = block_excl_scan_1024(tiles, &total_s, warp_sums);
+        if (threadIdx.x < E) {
+            mtile_off[threadIdx.x] = tex;
+            padded_off[threadIdx.x] = tex * CK_TILE_M;
+        }
+        if (threadIdx.x == 0) {
+            mtile_off[E] = total_s;
+            padded_off[E] = total_s * CK_TILE_M;
+        }
+    }
+    if (threadIdx.x == 0) *ticket = 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// route pass 3: stable scatter.  Each warp walks its slice in order; an id's output position is
+// excl_off[e] + whist[w][e] + (ids == e seen so far in this slice).
+// ------------------------------------------------------------------------------------------------
+template <typename IdT>
+__global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
+    route_scatter_kernel(const IdT *__restrict__ ids, int64_t n, int E, int64_t slice, int W,
+                         const int32_t *__restrict__ whist, const int32_t *__restrict__ excl_off,
+                         const int32_t *__restrict__ padded_off, int32_t *__restrict__ sorted_idx,
+                         int32_t *__restrict__ sorted_expert, int32_t *__restrict__ row_map) {
+    extern __shared__ int32_t smem_i[];
+    const int lane = threadIdx.x & 31;
+    const int wib = threadIdx.x >> 5;
+    const int w = blockIdx.x * kRouteWarpsPerBlock + wib;
+    int32_t *delta = smem_i;                       // [E] padded_off - excl_off (block shared)
+    int32_t *wbase = smem_i + E + wib * E;         // [E] next output position per expert (warp private)
+    for (int e = threadIdx.x; e < E; e += blockDim.x) delta[e] = padded_off ? padded_off[e] - excl_off[e] : 0;
+    __syncthreads();
+    if (w >= W) return;
+    for (int e = lane; e < E; e += 32) wbase[e] = excl_off[e] + whist[int64_t(w) * E + e];
+    __syncwarp();
+
+    const unsigned lt = lanemask_lt();
+    const int64_t begin = int64_t(w) * slice;
+    const int64_t end = min(begin + slice, n);
+    for (int64_t off = begin; off < end; off += kStep) {
+        int key[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t idx = off + 32 * j + lane;
+            long long v = -1;
+            if (idx < end) v = (long long)ids[idx];
+            key[j] = (v >= 0 && v < E) ? int(v) : -1;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = key[j];
+            const unsigned m = __match_any_sync(0xffffffffu, k);
+            int b = 0;
+            if (k >= 0) b = wbase[k];
+            __syncwarp();
+            if (k >= 0 && lane == __ffs(m) - 1) wbase[k] = b + __popc(m);
+            __syncwarp();
+            if (k >= 0) {
+                const int pos = b + __popc(m & lt);
+                const int32_t src = int32_t(off + 32 * j + lane);
+                sorted_idx[pos] = src;
+                if (sorted_expert) sorted_expert[pos] = k;
+                if (row_map) row_map[pos + delta[k]] = src;
+            }
+        }
+    }
+}
+
+static void route_plan(int64_t n, int64_t *slice, int *W) {
+    if (n <= 0) {
+        *slice = kStep;
+        *W = 0;
+        return;
+    }
+    int64_t s = ceil_div64(n, kRouteMaxWarps);
+    s = ceil_div64(s, kStep) * kStep;
+    if (s < 2 * kStep) s = 2 * kStep;
+    *slice = s;
+    *W = int(ceil_div64(n, s));
+}
+
+}  // namespace ck
+
+using namespace ck;
+
+extern "C" int ck_continuous_count(const void *ids, int ids_is_i64, int64_t n, int size, uint32_t *counts,
+                                   void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (size <= 0 || n < 0 || counts == nullptr) return CK_ERR_SHAPE;
+    if (size > CK_COUNT_MAX_SIZE) return CK_ERR_RANGE;
+    if (n > 0 && ids == nullptr) return CK_ERR_SHAPE;
+    CK_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(uint32_t) * size, stream));
+    if (n == 0) return CK_OK;
+    const int threads = 512;
+    const size_t smem = sizeof(uint32_t) * size;
+    const int64_t nchunks = ceil_div64(n, kStep);
+    const int blocks_per_sm = smem > 48 * 1024 ? 3 : 4;
+    int64_t grid = ceil_div64(nchunks, threads / 32);
+    const int64_t cap = int64_t(num_sms()) * blocks_per_sm;
+    if (grid > cap) grid = cap;
+    if (ids_is_i64) {
+        if (smem > 48 * 1024)
+            CK_CUDA_TRY(cudaFuncSetAttribute(count_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        count_kernel<int64_t><<<dim3((unsigned)grid), threads, smem, stream>>>((const int64_t *)ids, n, size, counts);
+    } else {
+        if (smem > 48 * 1024)
+            CK_CUDA_TRY(cudaFuncSetAttribute(count_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        count_kernel<int32_t><<<dim3((unsigned)grid), threads, smem, stream>>>((const int32_t *)ids, n, size, counts);
+    }
+    CK_LAUNCH_CHECK("count_kernel");
+    return CK_OK;
+}
+
+extern "C" int64_t ck_route_workspace_bytes(int64_t n, int E) {
+    if (n < 0 || E <= 0 || E > CK_ROUTE_MAX_EXPERTS) return CK_ERR_SHAPE;
+    int64_t slice;
+    int W;
+    route_plan(n, &slice, &W);
+    return 256 + int64_t(W > 0 ? W : 1) * E * int64_t(sizeof(int32_t));
+}
+
+extern "C" int64_t ck_route_padded_capacity(int64_t n, int E) {
+    if (n < 0 || E <= 0) return CK_ERR_SHAPE;
+    return (n / CK_TILE_M + E) * CK_TILE_M;
+}
+
+extern "C" int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint32_t *counts, int32_t *excl_off,
+                        int32_t *end_off, int32_t *sorted_idx, int32_t *sorted_expert, int32_t *padded_off,
+                        int32_t *mtile_off, int32_t *row_map, void *workspace, int64_t workspace_bytes,
+                        int32_t *dev_status, void *stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (E <= 0 || E > CK_ROUTE_MAX_EXPERTS || n < 0) return CK_ERR_SHAPE;
+    if (n > int64_t(INT32_MAX) - int64_t(E) * CK_TILE_M) return CK_ERR_SHAPE;
+    if (!counts || !excl_off || !end_off || (n > 0 && (!ids || !sorted_idx))) return CK_ERR_SHAPE;
+    const int meta = (padded_off != nullptr) + (mtile_off != nullptr) + (row_map != nullptr);
+    if (meta != 0 && meta != 3) return CK_ERR_SHAPE;
+    const int64_t need = ck_route_workspace_bytes(n, E);
+    if (!workspace || workspace_bytes < need) return CK_ERR_WORKSPACE;
+
+    int64_t slice;
+    int W;
+    route_plan(n, &slice, &W);
+    int *ticket = (int *)workspace;
+    int32_t *whist = (int32_t *)((char *)workspace + 256);
+    CK_CUDA_TRY(cudaMemsetAsync(ticket, 0, 256, stream));
+    if (row_map) CK_CUDA_TRY(cudaMemsetAsync(row_map, 0xFF, sizeof(int32_t) * ck_route_padded_capacity(n, E), stream));
+
+    const int threads = kRouteWarpsPerBlock * 32;
+    const int blocks = (W + kRouteWarpsPerBlock - 1) / kRouteWarpsPerBlock;
+    if (W > 0) {
+        const size_t smem = sizeof(int32_t) * kRouteWarpsPerBlock * E;
+        if (ids_is_i64)
+            route_hist_kernel<int64_t><<<blocks, threads, smem, stream>>>((const int64_t *)ids, n, E, slice, W, whist, dev_status);
+        else
+            route_hist_kernel<int32_t><<<blocks, threads, smem, stream>>>((const int32_t *)ids, n, E, slice, W, whist, dev_status);
+        CK_LAUNCH_CHECK("route_hist_kernel");
+    }
+    route_scan_kernel<<<E, 1024, 0, stream>>>(whist, W, E, counts, excl_off, end_off, padded_off, mtile_off, ticket);
+    CK_LAUNCH_CHECK("route_scan_kernel");
+    if (W > 0) {
+        const size_t smem = sizeof(int32_t) * (kRouteWarpsPerBlock + 1) * E;
+        if (ids_is_i64)
+            route_scatter_kernel<int64_t><<<blocks, threads, smem, stream>>>((const int64_t *)ids, n, E, slice, W, whist,
+                                                                            excl_off, padded_off, sorted_idx,
+                                                                            sorted_expert, row_map);
+        else
+            route_scatter_kernel<int32_t><<<blocks, threads, smem, stream>>>((const int32_t *)ids, n, E, slice, W, whist,
+                                                                            excl_off, padded_off, sorted_idx,
+                                                                            sorted_expert, row_map);
+        CK_LAUNCH_CHECK("route_scatter_kernel");
+    }
+    return CK_OK;
+}

@@ -1,0 +1,178 @@
+/*
+ * ck_b200.h -- C ABI of the B200 (sm_100a) MoE expert path.
+ *
+ * One ahead-of-time built shared library (libck_b200.so) replaces the JIT-built pybind modules and
+ * the Triton launches of the reference for this path.  Every entry point
+ *   - takes plain device pointers, sizes and a cudaStream_t passed as void*,
+ *   - never allocates or frees device memory (outputs and workspaces are caller-owned),
+ *   - launches on the given stream and returns without synchronising,
+ *   - returns a ck_status (0 = ok, negative = error) for everything the host can check,
+ *   - reports device-side findings (out-of-range expert id, a bounded wait that ran out) by
+ *     OR-ing a CK_DEV_* bit into the caller's `dev_status` word (device memory, may be NULL).
+ *
+ * Citations name files of the reference project (cute_kernels/...).
+ */
+#ifndef CK_B200_H
+#define CK_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define CK_API __attribute__((visibility("default")))
+#else
+#define CK_API
+#endif
+
+/* ---- status ------------------------------------------------------------------------------ */
+enum {
+    CK_OK = 0,
+    CK_ERR_SHAPE = -1,       /* a size / stride / alignment the kernel cannot take            */
+    CK_ERR_RANGE = -2,       /* value out of the accepted range (e.g. size > CK_COUNT_MAX_SIZE)*/
+    CK_ERR_TIMEOUT = -3,     /* reserved for hosts that translate CK_DEV_TIMEOUT               */
+    CK_ERR_CUDA = -4,        /* a CUDA runtime / driver call failed (see ck_last_cuda_error)   */
+    CK_ERR_UNSUPPORTED = -5, /* dtype / mode not built                                         */
+    CK_ERR_WORKSPACE = -6    /* workspace pointer NULL or too small                            */
+};
+
+/* bits OR-ed into *dev_status by kernels */
+enum {
+    CK_DEV_RANGE = 1,   /* an expert id outside [0, E) was seen (the element was skipped)        */
+    CK_DEV_TIMEOUT = 2, /* a bounded mbarrier wait ran out; the kernel backed out, output invalid */
+    CK_DEV_META = 4     /* tile metadata inconsistent with the launch (capacity too small)        */
+};
+
+/* element types of activations / weights */
+enum { CK_F32 = 0, CK_F16 = 1, CK_BF16 = 2 };
+
+/* fused activation of the up projection */
+enum {
+    CK_ACT_SWIGLU = 0, /* up * silu(gate)     (swiglu_packed: [up | gate] along the last dim)   */
+    CK_ACT_GLU = 1     /* up * sigmoid(gate)  (torch.nn.GLU on the same packing)                 */
+};
+
+#define CK_COUNT_MAX_SIZE 16384 /* same bound as kernels/continuous_count/cuda_implementation/forward.cu:12 */
+#define CK_ROUTE_MAX_EXPERTS 1024
+#define CK_TILE_M 128 /* rows of one grouped-GEMM tile; expert segments are padded to this */
+
+CK_API const char *ck_status_string(int status);
+CK_API const char *ck_last_cuda_error(void);
+CK_API int ck_abi_version(void);
+
+/* ---- continuous_count --------------------------------------------------------------------
+ * Replaces continuous_count_cuda (kernels/continuous_count/cuda_implementation/ops.cpp:7-15,
+ * forward.cu:110-178): counts[v] = #{i : ids[i] == v} for v in [0, size); values outside the
+ * range are ignored, as kernels/continuous_count/__init__.py:15-16 promises.
+ * ids: int32 or int64 device array of n elements (any alignment of the element type).
+ * counts: uint32[size], fully overwritten.  size <= CK_COUNT_MAX_SIZE. */
+CK_API int ck_continuous_count(const void *ids, int ids_is_i64, int64_t n, int size, uint32_t *counts,
+                        void *stream);
+
+/* ---- routing: count + scan + stable scatter ----------------------------------------------
+ * Replaces the three torch calls of MoE_Triton._compute_experts
+ * (kernels/scattermoe/triton_implementation/__init__.py:82-83: sort(), bincount(), cumsum())
+ * and MoE_Torch._compute_expert_assignment (kernels/scattermoe/torch_implementation.py:171-193).
+ *
+ *   counts[e]      = bincount(ids, minlength=E)
+ *   excl_off[e]    = sum_{e'<e} counts[e']            (exclusive scan)
+ *   end_off[e]     = excl_off[e] + counts[e]          (the reference's expert_offsets)
+ *   sorted_idx[j]  = torch.sort(ids, stable=True).indices[j]   (int32)
+ *   sorted_expert[j] = ids[sorted_idx[j]]             (optional, may be NULL)
+ *
+ * Optional grouped-GEMM metadata (all three NULL, or all three non-NULL): expert segments padded
+ * to CK_TILE_M rows so that one GEMM tile never spans two experts.
+ *   padded_off[E+1] : start row of each expert in the padded layout; padded_off[E] = total rows
+ *   mtile_off[E+1]  : padded_off / CK_TILE_M
+ *   row_map[cap]    : row_map[padded_off[e] + r] = sorted_idx[excl_off[e] + r]; -1 on pad rows.
+ *                     cap = ck_route_padded_capacity(n, E).
+ * n <= 2^31 - 1 - E*CK_TILE_M; E <= CK_ROUTE_MAX_EXPERTS.  Out-of-range ids are skipped and flagged
+ * with CK_DEV_RANGE (the outputs then describe the in-range ids only). */
+CK_API int64_t ck_route_workspace_bytes(int64_t n, int E);
+CK_API int64_t ck_route_padded_capacity(int64_t n, int E);
+CK_API int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint32_t *counts, int32_t *excl_off,
+             int32_t *end_off, int32_t *sorted_idx, int32_t *sorted_expert, int32_t *padded_off,
+             int32_t *mtile_off, int32_t *row_map, void *workspace, int64_t workspace_bytes,
+             int32_t *dev_status, void *stream);
+
+/* ---- SwiGLU ------------------------------------------------------------------------------
+ * Replace swiglu_forward_cuda / swiglu_backward_cuda
+ * (kernels/swiglu/cuda_implementation/ops.cpp:7-22, forward.cu:31-93, backward.cu:44-128) and
+ * the strided Triton kernels used by swiglu_packed_cute (kernels/swiglu/__init__.py:114-138).
+ *   out = up * gate * sigmoid(gate)                      (fp32 math, round-to-nearest downcast)
+ *   dgate = dy * up * (s + gate*s*(1-s)), dup = dy * gate * s,   s = sigmoid(gate)
+ * sigmoid clamps its argument to +-88.3762626647949 (include/activations.h:9-22).
+ * Tensors are rows x cols with a row stride in elements (contiguous: rows=1, cols=numel).
+ * The packed form passes up = x, gate = x + cols, stride = 2*cols. */
+CK_API int ck_swiglu_fwd(const void *gate, const void *up, void *out, int64_t rows, int64_t cols,
+                  int64_t in_stride, int64_t out_stride, int dtype, void *stream);
+CK_API int ck_swiglu_bwd(const void *gate, const void *up, const void *dy, void *dgate, void *dup,
+                  int64_t rows, int64_t cols, int64_t in_stride, int64_t dy_stride,
+                  int64_t grad_stride, int dtype, void *stream);
+
+/* ---- grouped rows: gather / cast ----------------------------------------------------------
+ * ck_moe_gather_rows replaces `group` (kernels/scattermoe/triton_implementation/ops.py:108-140,
+ * kernels.py:225-280) for the padded layout: dst[p, :] = src[row_map[p] / fan_out, :] for
+ * p < padded_off[E], zeros on pad rows (row_map[p] < 0).  cap rows are scanned. */
+CK_API int ck_moe_gather_rows(const void *src, void *dst, const int32_t *row_map, const int32_t *padded_off,
+                       int E, int64_t cap, int fan_out, int64_t cols, int dtype, void *stream);
+/* dst[i] = (T) src[i] for fp32 staging buffers of the fused combine */
+CK_API int ck_cast_from_f32(const float *src, void *dst, int64_t n, int dtype, void *stream);
+
+/* ---- grouped GEMMs (tcgen05 / TMEM / TMA) -------------------------------------------------
+ * Together these replace scatter2scatter, group_bwd_W and the bmm / sum combines of
+ * _ScatteredExperts (kernels/scattermoe/triton_implementation/ops.py:31-105,143-292,
+ * kernels.py:12-222).  Notation: Rp = padded_off[E] rows (capacity `cap` allocated), H hidden,
+ * I intermediate, T tokens, k top-k.  All matrices row-major, 16-byte aligned, leading dimensions
+ * equal to the logical widths.  H % 8 == 0 and I % 8 == 0.
+ * `tmap_cache` is reserved (pass NULL). */
+
+/* up projection + fused activation:  h[p, :] = xg[p, :] @ Wfc[e]^T  ([up | gate], 2I wide),
+ * act[p, :] = w[p] * up * silu(gate), with w[p] = gate_w[row_map[p]] (1 if gate_w is NULL).
+ * Wfc: [E, 2I, H] (c_fc.weight).  h may be NULL (inference: gate/up never reach HBM). */
+CK_API int ck_moe_up_act_fwd(const void *xg, const void *wfc, const void *gate_w, const int32_t *row_map,
+                      const int32_t *mtile_off, void *act, void *h, int E, int64_t cap, int H, int I,
+                      int act_kind, int dtype, int32_t *dev_status, void *stream);
+
+/* down projection + fused gather-back and top-k combine:
+ * out32[row_map[p] / k, :] += act[p, :] @ Wproj[e]^T   (fp32 red.add into a zeroed [T, H] buffer).
+ * Wproj: [E, H, I] (c_proj.weight). */
+CK_API int ck_moe_down_combine_fwd(const void *act, const void *wproj, const int32_t *row_map,
+                            const int32_t *mtile_off, float *out32, int E, int64_t cap, int H, int I,
+                            int top_k, int dtype, int32_t *dev_status, void *stream);
+
+/* dgrad of the down projection fused with the activation backward and the router-weight grad:
+ *   g[p, :]   = dyg[p, :] @ Wproj[e]                      (dyg = gathered, un-weighted grad_out)
+ *   dgates[row_map[p]] += sum_n a[p, n] * g[p, n],  a = up * silu(gate) recomputed from h
+ *   dh[p, :]  = activation_backward(h[p, :], w[p] * g[p, :])      ([dup | dgate], 2I wide)   */
+CK_API int ck_moe_dgrad_down(const void *dyg, const void *wproj, const void *h, const void *gate_w,
+                      const int32_t *row_map, const int32_t *mtile_off, void *dh, float *dgates, int E,
+                      int64_t cap, int H, int I, int act_kind, int dtype, int32_t *dev_status,
+                      void *stream);
+
+/* dgrad of the up projection fused with the k-way sum:
+ *   dx32[row_map[p] / k, :] += dh[p, :] @ Wfc[e]          (fp32 red.add into a zeroed [T, H])  */
+CK_API int ck_moe_dgrad_up(const void *dh, const void *wfc, const int32_t *row_map, const int32_t *mtile_off,
+                    float *dx32, int E, int64_t cap, int H, int I2, int top_k, int dtype,
+                    int32_t *dev_status, void *stream);
+
+/* wgrad: dW[e] = A_e^T @ B_e over the padded rows of expert e (pad rows must be zero in A or B and
+ * finite in both).  A: [cap, M], B: [cap, N], dW: [E, M, N], fully overwritten (zeros for experts
+ * without rows, so the caller needs no memset -- ops.py:252 zero-fills instead). */
+CK_API int ck_moe_wgrad(const void *a, const void *b, const int32_t *padded_off, void *dw, int E, int64_t cap,
+                 int M, int N, int dtype, int32_t *dev_status, void *stream);
+
+/* plain grouped linear on padded rows (used when the activation is an arbitrary callable and for
+ * expert-parallel shards whose rows travel back before the combine):
+ *   trans_w == 0: y[p, :] = x[p, :] @ W[e]^T,  W: [E, N, K]     (forward)
+ *   trans_w == 1: y[p, :] = x[p, :] @ W[e],    W: [E, K, N]     (dgrad)                        */
+CK_API int ck_moe_grouped_linear(const void *x, const void *w, const int32_t *mtile_off, void *y, int E,
+                          int64_t cap, int N, int K, int trans_w, int dtype, int32_t *dev_status,
+                          void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CK_B200_H */
