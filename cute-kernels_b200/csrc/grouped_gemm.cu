@@ -329,9 +329,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 #pragma unroll
                     for (int k = 0; k < TR::kSteps; ++k) {
                         uint64_t adesc, bdesc;
-                        if constexpr (A_MN) adesc = ptx::umma_desc_mnmajor(sa + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
+                        if constexpr (A_MN) adesc = ptx::umma_desc_mnmajor<TR::kTf32>(sa + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
                         else adesc = ptx::umma_desc_kmajor(sa + k * 32);
-                        if constexpr (B_MN) bdesc = ptx::umma_desc_mnmajor(sb + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
+                        if constexpr (B_MN) bdesc = ptx::umma_desc_mnmajor<TR::kTf32>(sb + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
                         else bdesc = ptx::umma_desc_kmajor(sb + k * 32);
                         ptx::umma_ss<TR::kTf32>(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
                     }
@@ -529,7 +529,8 @@ static CUtensorMapDataType tm_dtype() {
 
 // rank-2 or rank-3 row-major tensor; dims innermost first; box innermost first
 template <typename T>
-static int encode_map(CUtensorMap *tm, const void *base, int rank, const uint64_t *dims, const uint32_t *box) {
+static int encode_map(CUtensorMap *tm, const void *base, int rank, const uint64_t *dims, const uint32_t *box,
+                      bool mn_major = false) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return CK_ERR_CUDA;
     cuuint64_t gdims[3];
@@ -544,8 +545,10 @@ static int encode_map(CUtensorMap *tm, const void *base, int rank, const uint64_
         if (i < rank - 1) gstrides[i] = stride;
     }
     if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (dims[0] * sizeof(T)) % 16 != 0) return CK_ERR_SHAPE;
+    // 32-bit MN-major operands are read by the MMA in the 128-byte swizzle with 32-byte atomicity
+    const CUtensorMapSwizzle swz = (mn_major && sizeof(T) == 4) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B;
     CUresult r = fn(tm, tm_dtype<T>(), (cuuint32_t)rank, const_cast<void *>(base), gdims, gstrides, gbox, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
@@ -585,14 +588,14 @@ template <typename T>
 static int map_w_mnmajor(CUtensorMap *tm, const void *w, int E, int K, int N) {
     const uint64_t dims[3] = {uint64_t(N), uint64_t(K), uint64_t(E)};
     const uint32_t box[3] = {uint32_t(GemmTraits<T>::kMnBoxElems), uint32_t(GemmTraits<T>::BK), 1};
-    return encode_map<T>(tm, w, 3, dims, box);
+    return encode_map<T>(tm, w, 3, dims, box, true);
 }
 // activations [cap, cols] as MN-major operand of wgrad: box {128 bytes of cols, BK rows}
 template <typename T>
 static int map_act_mnmajor(CUtensorMap *tm, const void *a, int64_t cap, int cols) {
     const uint64_t dims[2] = {uint64_t(cols), uint64_t(cap)};
     const uint32_t box[2] = {uint32_t(GemmTraits<T>::kMnBoxElems), uint32_t(GemmTraits<T>::BK)};
-    return encode_map<T>(tm, a, 2, dims, box);
+    return encode_map<T>(tm, a, 2, dims, box, true);
 }
 
 static bool dims_ok(int64_t cap, int a, int b) { return cap > 0 && cap % BM == 0 && a > 0 && b > 0 && a % 8 == 0 && b % 8 == 0; }

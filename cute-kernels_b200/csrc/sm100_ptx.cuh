@@ -126,11 +126,16 @@ __device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t saddr) {
     const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
     return (uint64_t(hi) << 32) | lo;
 }
-// MN-major operand: 128 bytes of MN contiguous per K row, 8 K rows per 1024-byte swizzle atom
-// (stride-byte-offset), the next 128-byte MN block `mn_block_bytes` further (leading-byte-offset).
+// MN-major operand: 128 bytes of MN contiguous per K row; the next 128-byte MN block lies
+// `mn_block_bytes` further (leading-byte-offset).  16-bit types use the plain 128-byte swizzle
+// (8 K rows per 1024-byte atom).  32-bit (tf32) MN-major operands only exist in the 128-byte swizzle
+// with 32-byte atomicity (layout type 1): 4 K rows per 512-byte atom.
+template <bool ATOM_32B>
 __device__ __forceinline__ uint64_t umma_desc_mnmajor(uint32_t saddr, uint32_t mn_block_bytes) {
+    constexpr uint32_t sbo = ATOM_32B ? 512u : 1024u;
+    constexpr uint32_t layout = ATOM_32B ? 1u : 2u;
     const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | (((mn_block_bytes >> 4) & 0x3FFFu) << 16);
-    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    const uint32_t hi = (sbo >> 4) | (1u << 14) | (layout << 29);
     return (uint64_t(hi) << 32) | lo;
 }
 

@@ -122,3 +122,44 @@ def check_device_status(device: torch.device | None = None) -> None:
                               (CK_DEV_TIMEOUT, "CK_DEV_TIMEOUT (a bounded device wait ran out)"),
                               (CK_DEV_META, "CK_DEV_META (tile metadata exceeds the allocated rows)")) if v & bit]
     raise RuntimeError("device status: " + ", ".join(names))
+
+
+# ---- launch accounting ------------------------------------------------------------------------------
+class LaunchLog:
+    """Counts this library's kernel launches and, when enabled, brackets each with CUDA events on the
+    launching stream so a harness can attribute device time to kernels inside its own timed region."""
+
+    def __init__(self) -> None:
+        self.count = 0
+        self.record_events = False
+        self.events: list[tuple[str, float, "torch.cuda.Event", "torch.cuda.Event"]] = []
+
+    def reset(self) -> None:
+        self.count = 0
+        self.events = []
+
+
+launch_log = LaunchLog()
+
+
+class launch:
+    """``with launch("kernel", n_kernels, work): lib.ck_...`` -- bookkeeping around one C-ABI call."""
+
+    __slots__ = ("name", "n", "work", "e0")
+
+    def __init__(self, name: str, n_kernels: int = 1, work: float = 0.0) -> None:
+        self.name, self.n, self.work, self.e0 = name, n_kernels, work, None
+
+    def __enter__(self):
+        if launch_log.record_events:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
+        return self
+
+    def __exit__(self, *exc):
+        launch_log.count += self.n
+        if self.e0 is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            launch_log.events.append((self.name, self.work, self.e0, e1))
+        return False

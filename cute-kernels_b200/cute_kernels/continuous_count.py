@@ -7,7 +7,7 @@ from . import _lib
 
 def _continuous_count_impl(x: torch.Tensor, output: torch.Tensor, size: int) -> None:
     _lib.require_cuda(x, output)
-    with torch.cuda.device(x.device):
+    with torch.cuda.device(x.device), _lib.launch("continuous_count", 1 if x.numel() else 0):
         st = _lib.lib.ck_continuous_count(
             x.data_ptr(), int(x.dtype == torch.int64), x.numel(), size, output.data_ptr(), _lib.stream_ptr()
         )

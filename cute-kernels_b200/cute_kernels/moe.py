@@ -44,7 +44,7 @@ def _make_op(name: str, impl: Callable, mutates: set[str]) -> Callable:
 def _gather_rows_impl(src: torch.Tensor, dst: torch.Tensor, row_map: torch.Tensor, padded_off: torch.Tensor,
                       fan_out: int) -> None:
     _lib.require_cuda(src, dst)
-    with torch.cuda.device(src.device):
+    with torch.cuda.device(src.device), _lib.launch("gather_rows", 1, 0.0):
         st = _lib.lib.ck_moe_gather_rows(src.data_ptr(), dst.data_ptr(), row_map.data_ptr(), padded_off.data_ptr(),
                                          padded_off.numel() - 1, dst.size(0), fan_out, src.size(1),
                                          _lib.dtype_code(src.dtype), _lib.stream_ptr())
@@ -53,7 +53,7 @@ def _gather_rows_impl(src: torch.Tensor, dst: torch.Tensor, row_map: torch.Tenso
 
 def _cast_from_f32_impl(src: torch.Tensor, dst: torch.Tensor) -> None:
     _lib.require_cuda(src, dst)
-    with torch.cuda.device(src.device):
+    with torch.cuda.device(src.device), _lib.launch("cast_from_f32", 1, 0.0):
         st = _lib.lib.ck_cast_from_f32(src.data_ptr(), dst.data_ptr(), src.numel(), _lib.dtype_code(dst.dtype),
                                        _lib.stream_ptr())
     _lib.check(st, "ck_cast_from_f32")
@@ -64,7 +64,7 @@ def _up_act_fwd_impl(xg: torch.Tensor, wfc: torch.Tensor, gate_w: torch.Tensor |
                      status: torch.Tensor) -> None:
     _lib.require_cuda(xg, wfc, act)
     E, two_i, H = wfc.shape
-    with torch.cuda.device(xg.device):
+    with torch.cuda.device(xg.device), _lib.launch("up_act_fwd", 1, 2.0 * xg.size(0) * two_i * H):
         st = _lib.lib.ck_moe_up_act_fwd(xg.data_ptr(), wfc.data_ptr(), _lib.ptr(gate_w), row_map.data_ptr(),
                                         mtile_off.data_ptr(), act.data_ptr(), _lib.ptr(h), E, xg.size(0), H,
                                         two_i // 2, act_kind, _lib.dtype_code(xg.dtype), status.data_ptr(),
@@ -76,7 +76,7 @@ def _down_combine_fwd_impl(act: torch.Tensor, wproj: torch.Tensor, row_map: torc
                            out32: torch.Tensor, top_k: int, status: torch.Tensor) -> None:
     _lib.require_cuda(act, wproj, out32)
     E, H, I = wproj.shape
-    with torch.cuda.device(act.device):
+    with torch.cuda.device(act.device), _lib.launch("down_combine_fwd", 1, 2.0 * act.size(0) * H * I):
         st = _lib.lib.ck_moe_down_combine_fwd(act.data_ptr(), wproj.data_ptr(), row_map.data_ptr(),
                                               mtile_off.data_ptr(), out32.data_ptr(), E, act.size(0), H, I, top_k,
                                               _lib.dtype_code(act.dtype), status.data_ptr(), _lib.stream_ptr())
@@ -88,7 +88,7 @@ def _dgrad_down_impl(dyg: torch.Tensor, wproj: torch.Tensor, h: torch.Tensor, ga
                      act_kind: int, status: torch.Tensor) -> None:
     _lib.require_cuda(dyg, wproj, h, dh, dgates)
     E, H, I = wproj.shape
-    with torch.cuda.device(dyg.device):
+    with torch.cuda.device(dyg.device), _lib.launch("dgrad_down", 1, 2.0 * dyg.size(0) * H * I):
         st = _lib.lib.ck_moe_dgrad_down(dyg.data_ptr(), wproj.data_ptr(), h.data_ptr(), _lib.ptr(gate_w),
                                         row_map.data_ptr(), mtile_off.data_ptr(), dh.data_ptr(), dgates.data_ptr(), E,
                                         dyg.size(0), H, I, act_kind, _lib.dtype_code(dyg.dtype), status.data_ptr(),
@@ -100,7 +100,7 @@ def _dgrad_up_impl(dh: torch.Tensor, wfc: torch.Tensor, row_map: torch.Tensor, m
                    dx32: torch.Tensor, top_k: int, status: torch.Tensor) -> None:
     _lib.require_cuda(dh, wfc, dx32)
     E, i2, H = wfc.shape
-    with torch.cuda.device(dh.device):
+    with torch.cuda.device(dh.device), _lib.launch("dgrad_up", 1, 2.0 * dh.size(0) * H * i2):
         st = _lib.lib.ck_moe_dgrad_up(dh.data_ptr(), wfc.data_ptr(), row_map.data_ptr(), mtile_off.data_ptr(),
                                       dx32.data_ptr(), E, dh.size(0), H, i2, top_k, _lib.dtype_code(dh.dtype),
                                       status.data_ptr(), _lib.stream_ptr())
@@ -112,7 +112,7 @@ def _wgrad_impl(a: torch.Tensor, b: torch.Tensor, padded_off: torch.Tensor, dw: 
     _lib.require_cuda(a, b, dw)
     E, M, N = dw.shape
     assert a.size(1) == M and b.size(1) == N and a.size(0) == b.size(0)
-    with torch.cuda.device(a.device):
+    with torch.cuda.device(a.device), _lib.launch("wgrad", 1, 2.0 * a.size(0) * M * N):
         st = _lib.lib.ck_moe_wgrad(a.data_ptr(), b.data_ptr(), padded_off.data_ptr(), dw.data_ptr(), E, a.size(0), M, N,
                                    _lib.dtype_code(a.dtype), status.data_ptr(), _lib.stream_ptr())
     _lib.check(st, "ck_moe_wgrad")
@@ -124,7 +124,7 @@ def _grouped_linear_impl(x: torch.Tensor, w: torch.Tensor, mtile_off: torch.Tens
     E = w.size(0)
     N, K = (w.size(2), w.size(1)) if trans_w else (w.size(1), w.size(2))
     assert x.size(1) == K and y.size(1) == N and x.size(0) == y.size(0)
-    with torch.cuda.device(x.device):
+    with torch.cuda.device(x.device), _lib.launch("grouped_linear", 1, 2.0 * x.size(0) * N * K):
         st = _lib.lib.ck_moe_grouped_linear(x.data_ptr(), w.data_ptr(), mtile_off.data_ptr(), y.data_ptr(), E,
                                             x.size(0), N, K, int(trans_w), _lib.dtype_code(x.dtype),
                                             status.data_ptr(), _lib.stream_ptr())

@@ -61,7 +61,7 @@ def _route_impl(
     status: torch.Tensor,
 ) -> None:
     _lib.require_cuda(ids, counts, sorted_idx, workspace)
-    with torch.cuda.device(ids.device):
+    with torch.cuda.device(ids.device), _lib.launch("route", 3 if ids.numel() else 1):
         st = _lib.lib.ck_route(
             ids.data_ptr(), int(ids.dtype == torch.int64), ids.numel(), num_experts,
             counts.data_ptr(), excl.data_ptr(), end.data_ptr(), sorted_idx.data_ptr(), _lib.ptr(sorted_expert),

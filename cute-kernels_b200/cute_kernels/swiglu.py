@@ -10,7 +10,7 @@ from .utils import divide_if_divisible, ensure_contiguous
 def _swiglu_forward_impl(gate: torch.Tensor, up: torch.Tensor, output: torch.Tensor, rows: int, cols: int,
                          in_stride: int, out_stride: int) -> None:
     _lib.require_cuda(gate, up, output)
-    with torch.cuda.device(gate.device):
+    with torch.cuda.device(gate.device), _lib.launch("swiglu_fwd"):
         st = _lib.lib.ck_swiglu_fwd(gate.data_ptr(), up.data_ptr(), output.data_ptr(), rows, cols, in_stride,
                                     out_stride, _lib.dtype_code(gate.dtype), _lib.stream_ptr())
     _lib.check(st, "ck_swiglu_fwd")
@@ -20,7 +20,7 @@ def _swiglu_backward_impl(gate: torch.Tensor, up: torch.Tensor, output_grad: tor
                           up_grad: torch.Tensor, rows: int, cols: int, in_stride: int, dy_stride: int,
                           grad_stride: int) -> None:
     _lib.require_cuda(gate, up, output_grad, gate_grad, up_grad)
-    with torch.cuda.device(gate.device):
+    with torch.cuda.device(gate.device), _lib.launch("swiglu_bwd"):
         st = _lib.lib.ck_swiglu_bwd(gate.data_ptr(), up.data_ptr(), output_grad.data_ptr(), gate_grad.data_ptr(),
                                     up_grad.data_ptr(), rows, cols, in_stride, dy_stride, grad_stride,
                                     _lib.dtype_code(gate.dtype), _lib.stream_ptr())
@@ -31,7 +31,7 @@ def _swiglu_packed_forward_impl(x: torch.Tensor, output: torch.Tensor, rows: int
     # up = x[:, :cols], gate = x[:, cols:]; both are passed as pointers into the one packed buffer
     _lib.require_cuda(x, output)
     esz = x.element_size()
-    with torch.cuda.device(x.device):
+    with torch.cuda.device(x.device), _lib.launch("swiglu_fwd"):
         st = _lib.lib.ck_swiglu_fwd(x.data_ptr() + cols * esz, x.data_ptr(), output.data_ptr(), rows, cols, 2 * cols,
                                     cols, _lib.dtype_code(x.dtype), _lib.stream_ptr())
     _lib.check(st, "ck_swiglu_fwd")
@@ -41,7 +41,7 @@ def _swiglu_packed_backward_impl(x: torch.Tensor, output_grad: torch.Tensor, x_g
                                  cols: int) -> None:
     _lib.require_cuda(x, output_grad, x_grad)
     esz = x.element_size()
-    with torch.cuda.device(x.device):
+    with torch.cuda.device(x.device), _lib.launch("swiglu_bwd"):
         st = _lib.lib.ck_swiglu_bwd(x.data_ptr() + cols * esz, x.data_ptr(), output_grad.data_ptr(),
                                     x_grad.data_ptr() + cols * esz, x_grad.data_ptr(), rows, cols, 2 * cols, cols,
                                     2 * cols, _lib.dtype_code(x.dtype), _lib.stream_ptr())

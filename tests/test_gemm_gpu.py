@@ -1,0 +1,250 @@
+"""Each grouped-GEMM entry point of the C ABI against an fp32 torch reference of the same op."""
+
+import numpy as np
+import pytest
+import torch
+
+import ck_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.bfloat16: dict(rtol=2e-2, atol=2e-2), torch.float16: dict(rtol=4e-3, atol=4e-3),
+       torch.float32: dict(rtol=6e-3, atol=6e-3)}  # fp32 runs as TF32 on the tensor cores, like the reference's tl.dot
+
+
+def _routing(counts, k, seed=0):
+    """ids with the given per-expert counts, shuffled; returns the device Routing and the oracle dict."""
+    from cute_kernels import route
+
+    ids = np.concatenate([np.full(c, e, dtype=np.int64) for e, c in enumerate(counts)])
+    np.random.default_rng(seed).shuffle(ids)
+    pad = (-ids.size) % k
+    if pad:
+        ids = np.concatenate([ids, np.zeros(pad, dtype=np.int64)])
+    r = route(torch.from_numpy(ids).cuda(), len(counts))
+    return ids, r, orc.route_ref(ids, len(counts))
+
+
+def _row_expert(ref, E):
+    cap = ref["row_map"].size
+    re = np.full(cap, -1, dtype=np.int64)
+    for e in range(E):
+        re[ref["padded_off"][e] : ref["padded_off"][e + 1]] = e
+    return re
+
+
+def _padded_rows(ref, cols, dtype, seed, scale=1.0):
+    """[cap, cols] activations: random on valid rows, zero on pad rows."""
+    cap = ref["row_map"].size
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(cap, cols, generator=g) * scale
+    x[torch.from_numpy(ref["row_map"] < 0)] = 0
+    return x.to(dtype).cuda()
+
+
+CASES = [
+    # counts per expert, K, N
+    ([130, 0, 5], 64, 256),
+    ([1, 1, 1, 1], 192, 8),
+    ([300, 17, 128, 0, 256], 136, 264),
+    ([700, 900], 512, 1024),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("trans_w", [False, True])
+@pytest.mark.parametrize("case", CASES)
+def test_grouped_linear(dtype, trans_w, case):
+    from cute_kernels import _lib
+    from cute_kernels.moe import grouped_linear
+
+    counts, K, N = case
+    E = len(counts)
+    ids, r, ref = _routing(counts, 1)
+    x = _padded_rows(ref, K, dtype, 1)
+    g = torch.Generator().manual_seed(2)
+    w = (torch.randn(E, K, N, generator=g) if trans_w else torch.randn(E, N, K, generator=g)).mul(0.1).to(dtype).cuda()
+    y = torch.full((x.size(0), N), float("nan"), dtype=dtype, device="cuda")
+    grouped_linear(x, w, r.mtile_off, y, trans_w, _lib.status_word(x.device))
+    re = _row_expert(ref, E)
+    total = int(ref["padded_off"][-1])
+    xf, wf = x.float().cpu(), w.float().cpu()
+    for e in range(E):
+        rows = np.nonzero(re[:total] == e)[0]
+        if rows.size == 0:
+            continue
+        exp = xf[rows] @ (wf[e] if trans_w else wf[e].t())
+        torch.testing.assert_close(y[rows].float().cpu(), exp, **TOL[dtype])
+    assert torch.isnan(y[total:].float()).all()  # rows past the padded total are never written
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("case", [([130, 0, 5], 64, 256), ([300, 17, 128, 0, 256], 136, 264), ([700, 900], 512, 384)])
+def test_wgrad(dtype, case):
+    from cute_kernels import _lib
+    from cute_kernels.moe import wgrad
+
+    counts, M, N = case
+    E = len(counts)
+    ids, r, ref = _routing(counts, 1)
+    a = _padded_rows(ref, M, dtype, 3)
+    b = _padded_rows(ref, N, dtype, 4)
+    dw = torch.full((E, M, N), float("nan"), dtype=dtype, device="cuda")
+    wgrad(a, b, r.padded_off, dw, _lib.status_word(a.device))
+    re = _row_expert(ref, E)
+    af, bf = a.float().cpu(), b.float().cpu()
+    for e in range(E):
+        rows = np.nonzero(re == e)[0]
+        exp = af[rows].t() @ bf[rows] if rows.size else torch.zeros(M, N)
+        scale = max(1.0, float(rows.size) ** 0.5)
+        tol = {k: v * scale for k, v in TOL[dtype].items()}
+        torch.testing.assert_close(dw[e].float().cpu(), exp, **tol)
+
+
+def _moe_problem(counts, H, I, k, dtype, seed=0):
+    E = len(counts)
+    ids, r, ref = _routing(counts, k, seed)
+    T = ids.size // k
+    g = torch.Generator().manual_seed(seed + 10)
+    x = torch.randn(T, H, generator=g).to(dtype).cuda()
+    w_fc = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(dtype).cuda()
+    w_proj = (torch.randn(E, H, I, generator=g) * 0.05).to(dtype).cuda()
+    gate_w = torch.rand(T * k, generator=g).to(dtype).cuda()
+    return dict(E=E, T=T, H=H, I=I, k=k, ids=ids, r=r, ref=ref, x=x, w_fc=w_fc, w_proj=w_proj, gate_w=gate_w)
+
+
+MOE_CASES = [([130, 0, 5, 9], 64, 128, 2), ([300, 17, 128, 0, 255], 136, 72, 2), ([513, 700, 64, 3], 256, 320, 4)]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("act_kind", [0, 1])
+@pytest.mark.parametrize("case", MOE_CASES)
+def test_fused_forward_pieces(dtype, act_kind, case):
+    """gather -> up projection + activation -> down projection + combine, each checked separately."""
+    from cute_kernels import _lib
+    from cute_kernels.moe import down_combine_fwd, gather_rows, up_act_fwd
+
+    counts, H, I, k = case
+    p = _moe_problem(counts, H, I, k, dtype)
+    r, ref, E, T = p["r"], p["ref"], p["E"], p["T"]
+    cap = r.capacity
+    st = _lib.status_word(p["x"].device)
+    xg = torch.full((cap, H), float("nan"), dtype=dtype, device="cuda")
+    gather_rows(p["x"], xg, r.row_map, r.padded_off, k)
+    total = int(ref["padded_off"][-1])
+    rm = torch.from_numpy(ref["row_map"][:total].astype(np.int64))
+    valid = rm >= 0
+    exp_xg = torch.zeros(total, H)
+    exp_xg[valid] = p["x"].float().cpu()[rm[valid] // k]
+    assert torch.equal(xg[:total].float().cpu(), exp_xg)
+
+    act = torch.full((cap, I), float("nan"), dtype=dtype, device="cuda")
+    h = torch.full((cap, 2 * I), float("nan"), dtype=dtype, device="cuda")
+    up_act_fwd(xg, p["w_fc"], p["gate_w"], r.row_map, r.mtile_off, act, h, act_kind, st)
+    re = torch.from_numpy(_row_expert(ref, E)[:total])
+    wf = p["w_fc"].float().cpu()
+    exp_h = torch.zeros(total, 2 * I)
+    for e in range(E):
+        rows = re == e
+        exp_h[rows] = exp_xg[rows] @ wf[e].t()
+    torch.testing.assert_close(h[:total].float().cpu(), exp_h, **TOL[dtype])
+    gw = torch.zeros(total)
+    gw[valid] = p["gate_w"].float().cpu()[rm[valid]]
+    up_, gate_ = exp_h[:, :I], exp_h[:, I:]
+    exp_act = gw[:, None] * up_ * (torch.nn.functional.silu(gate_) if act_kind == 0 else torch.sigmoid(gate_))
+    torch.testing.assert_close(act[:total].float().cpu(), exp_act, **TOL[dtype])
+
+    out32 = torch.zeros(T, H, dtype=torch.float32, device="cuda")
+    down_combine_fwd(act, p["w_proj"], r.row_map, r.mtile_off, out32, k, st)
+    af = act[:total].float().cpu()
+    wp = p["w_proj"].float().cpu()
+    exp_out = torch.zeros(T, H)
+    for e in range(E):
+        rows = (re == e) & valid
+        exp_out.index_add_(0, rm[rows] // k, af[rows] @ wp[e].t())
+    torch.testing.assert_close(out32.cpu(), exp_out, **TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("act_kind", [0, 1])
+@pytest.mark.parametrize("case", MOE_CASES)
+def test_fused_backward_pieces(dtype, act_kind, case):
+    from cute_kernels import _lib
+    from cute_kernels.moe import dgrad_down, dgrad_up
+
+    counts, H, I, k = case
+    p = _moe_problem(counts, H, I, k, dtype, seed=1)
+    r, ref, E, T = p["r"], p["ref"], p["E"], p["T"]
+    st = _lib.status_word(p["x"].device)
+    total = int(ref["padded_off"][-1])
+    rm = torch.from_numpy(ref["row_map"][:total].astype(np.int64))
+    valid = rm >= 0
+    re = torch.from_numpy(_row_expert(ref, E)[:total])
+    dyg = _padded_rows(ref, H, dtype, 5)
+    h = _padded_rows(ref, 2 * I, dtype, 6)
+    dh = torch.full((r.capacity, 2 * I), float("nan"), dtype=dtype, device="cuda")
+    dgates = torch.zeros(T * k, dtype=torch.float32, device="cuda")
+    dgrad_down(dyg, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh, dgates, act_kind, st)
+
+    wp = p["w_proj"].float().cpu()
+    g = torch.zeros(total, I)
+    for e in range(E):
+        rows = re == e
+        g[rows] = dyg[:total].float().cpu()[rows] @ wp[e]
+    hf = h[:total].float().cpu()
+    up_, gate_ = hf[:, :I], hf[:, I:]
+    s = torch.sigmoid(gate_)
+    if act_kind == 0:
+        a = up_ * gate_ * s
+        du_m, dg_m = gate_ * s, up_ * (s + gate_ * s * (1 - s))
+    else:
+        a = up_ * s
+        du_m, dg_m = s, up_ * s * (1 - s)
+    gw = torch.zeros(total)
+    gw[valid] = p["gate_w"].float().cpu()[rm[valid]]
+    exp_dh = torch.cat([gw[:, None] * g * du_m, gw[:, None] * g * dg_m], dim=1)
+    torch.testing.assert_close(dh[:total].float().cpu(), exp_dh, **TOL[dtype])
+    exp_dg = torch.zeros(T * k)
+    exp_dg[rm[valid]] = (a * g).sum(-1)[valid]
+    tol = {k_: v * max(1.0, I**0.5 / 4) for k_, v in TOL[dtype].items()}
+    torch.testing.assert_close(dgates.cpu(), exp_dg, **tol)
+
+    dh_in = _padded_rows(ref, 2 * I, dtype, 7)
+    dx32 = torch.zeros(T, H, dtype=torch.float32, device="cuda")
+    dgrad_up(dh_in, p["w_fc"], r.row_map, r.mtile_off, dx32, k, st)
+    wf = p["w_fc"].float().cpu()
+    exp_dx = torch.zeros(T, H)
+    dhf = dh_in[:total].float().cpu()
+    for e in range(E):
+        rows = (re == e) & valid
+        exp_dx.index_add_(0, rm[rows] // k, dhf[rows] @ wf[e])
+    tol = {k_: v * max(1.0, (2 * I) ** 0.5 / 4) for k_, v in TOL[dtype].items()}
+    torch.testing.assert_close(dx32.cpu(), exp_dx, **tol)
+
+
+def test_bad_arguments_are_rejected():
+    from cute_kernels import _lib
+
+    x = torch.zeros(128, 60, dtype=torch.bfloat16, device="cuda")  # K not a multiple of 8
+    w = torch.zeros(1, 64, 60, dtype=torch.bfloat16, device="cuda")
+    off = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    y = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    st = _lib.lib.ck_moe_grouped_linear(x.data_ptr(), w.data_ptr(), off.data_ptr(), y.data_ptr(), 1, 128, 64, 60, 0, 2,
+                                        None, None)
+    assert st == -1
+
+
+@pytest.mark.expects_dev_status
+def test_capacity_guard_flags_instead_of_overrunning():
+    """Tile tables that describe more rows than were allocated: the kernel refuses and flags CK_DEV_META."""
+    import cute_kernels
+    from cute_kernels import _lib
+    from cute_kernels.moe import grouped_linear
+
+    x = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(1, 64, 64, dtype=torch.bfloat16, device="cuda")
+    off = torch.tensor([0, 5], dtype=torch.int32, device="cuda")  # claims 5 tiles, only 1 allocated
+    y = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    grouped_linear(x, w, off, y, False, _lib.status_word(x.device))
+    with pytest.raises(RuntimeError, match="CK_DEV_META"):
+        cute_kernels.check_device_status()
