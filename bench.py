@@ -37,6 +37,8 @@ import torch  # noqa: E402
 WORKLOADS = {
     "c4": dict(name="c4_mixtral_moe_fwd_bwd", T=16384, H=4096, I=14336, E=8, k=2, expert_bias=False),
     "c5": dict(name="c5_finegrained_moe_fwd_bwd", T=32768, H=2048, I=1408, E=64, k=8, expert_bias=True),
+    # profiling-sized slice of c4: same hidden / intermediate sizes, 4 experts, 2048 tokens (weights > L2, ~4 GB held)
+    "c4s": dict(name="c4_slice_moe_fwd_bwd", T=2048, H=4096, I=14336, E=4, k=2, expert_bias=False),
     "c1": dict(name="c1_small_moe_fwd_bwd", T=512, H=256, I=512, E=8, k=2, expert_bias=False),
 }
 METRIC = "moe_fwd_bwd_tokens_per_s"

@@ -136,11 +136,17 @@ class MoERef(torch.nn.Module):
         self.c_proj = self._Experts(num_experts, intermediate_size, hidden_size, add_bias, std)
         self.act = activation_function
 
-    def forward(self, hidden_states):
+    def forward(self, hidden_states, forced_selection=None):
+        """``forced_selection`` [T, k] pins the chosen experts (a 16-bit router can break near-ties differently
+        from this fp32 one); the router weights are still the softmax of this module's own logits."""
         shape = hidden_states.shape
         x = hidden_states.view(-1, self.hidden_size)
         logits = self.gate(x)
-        w, idx = routing_weights_ref(logits, self.top_k, x.dtype)
+        if forced_selection is None:
+            w, idx = routing_weights_ref(logits, self.top_k, x.dtype)
+        else:
+            idx = forced_selection
+            w = F.softmax(logits.gather(1, idx).float(), dim=-1).to(x.dtype)
         y = moe_experts_ref(x, w, idx, self.c_fc.weight, self.c_proj.weight, self.act, self.c_fc.bias, self.c_proj.bias)
         return y.view(shape), logits
 
