@@ -6,6 +6,8 @@
 // The stable scatter gives every warp a contiguous slice of the ids; a slice's position in the
 // output is (exclusive scan over experts) + (exclusive scan over earlier warps for that expert) +
 // (running count inside the warp), which is exactly the order torch.sort(stable=True) produces.
+#include <mutex>
+
 #include "ck_common.cuh"
 
 namespace ck {
@@ -340,4 +342,57 @@ extern "C" int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint3
         CK_LAUNCH_CHECK("route_scatter_kernel");
     }
     return CK_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// ck_route_static: the routing pass for callers that cannot bring a workspace.
+//
+// Some hosts of this library have no way to allocate device memory at the moment they need the routing
+// tables: a serving loop whose memory pool is sealed after start-up, a plug-in living inside an engine
+// that owns every byte of the device and hands out only the input and output buffers, a real-time step
+// that must not run into the device-wide synchronisation cudaMalloc / cudaFree imply.  For them the
+// per-slice histograms and the ticket counter live in the fixed array below instead of a caller-owned
+// workspace.  The array is part of the loaded module: every GPU that loads the library holds these
+// CK_ROUTE_STATIC_SCRATCH_BYTES until the process exits, whether or not this entry point is ever called.
+//
+// The array's name is only a host-side handle; the device address comes from cudaGetSymbolAddress, asked
+// once per device with that device current (the first call on a device does this set-up, so make that
+// first call outside any stream capture).  Nothing here calls cudaMalloc, cudaFree or an allocating
+// library routine.  All calls share the one array and it keeps whatever the previous call left: the
+// ticket counter is cleared on every call, the histogram slots in use are fully rewritten before they
+// are read.  Two calls whose kernels overlap on the same GPU (different streams, or different host
+// threads) race on the array; serialise them.
+// ------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_route_static_scratch[CK_ROUTE_STATIC_SCRATCH_BYTES];
+
+static int route_static_scratch_ptr(void **out) {
+    static std::mutex mu;
+    static void *ptrs[64];  // per device, nullptr = not looked up yet
+    int dev = -1;
+    CK_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return CK_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        void *p = nullptr;
+        CK_CUDA_TRY(cudaGetSymbolAddress(&p, g_route_static_scratch));
+        if (p == nullptr) return CK_ERR_CUDA;
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return CK_OK;
+}
+
+extern "C" int64_t ck_route_static_max_bytes(void) { return CK_ROUTE_STATIC_SCRATCH_BYTES; }
+
+extern "C" int ck_route_static(const void *ids, int ids_is_i64, int64_t n, int E, uint32_t *counts, int32_t *excl_off,
+                               int32_t *end_off, int32_t *sorted_idx, int32_t *sorted_expert, int32_t *padded_off,
+                               int32_t *mtile_off, int32_t *row_map, int32_t *dev_status, void *stream_) {
+    const int64_t need = ck_route_workspace_bytes(n, E);
+    if (need < 0) return CK_ERR_SHAPE;
+    if (need > CK_ROUTE_STATIC_SCRATCH_BYTES) return CK_ERR_RANGE;  // n * E beyond the built-in scratch
+    void *scratch = nullptr;
+    const int rc = route_static_scratch_ptr(&scratch);
+    if (rc != CK_OK) return rc;
+    return ck_route(ids, ids_is_i64, n, E, counts, excl_off, end_off, sorted_idx, sorted_expert, padded_off, mtile_off,
+                    row_map, scratch, CK_ROUTE_STATIC_SCRATCH_BYTES, dev_status, stream_);
 }

@@ -34,6 +34,8 @@ PROTOTYPES = {
     "ck_route_workspace_bytes": (_i64, [_i64, _i]),
     "ck_route_padded_capacity": (_i64, [_i64, _i]),
     "ck_route": (_i, [_vp, _i, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
+    "ck_route_static_max_bytes": (_i64, []),
+    "ck_route_static": (_i, [_vp, _i, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "ck_swiglu_fwd": (_i, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i, _vp]),
     "ck_swiglu_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _vp]),
     "ck_moe_gather_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i64, _i, _vp]),

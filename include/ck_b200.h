@@ -97,6 +97,22 @@ CK_API int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint32_t 
              int32_t *mtile_off, int32_t *row_map, void *workspace, int64_t workspace_bytes,
              int32_t *dev_status, void *stream);
 
+/* ck_route without a caller workspace.  No counterpart in the reference (its routing goes through torch
+ * ops that allocate freely); added for hosts that cannot allocate device memory where they call this:
+ * a sealed memory pool, an engine that owns the device and passes only inputs and outputs, a step that
+ * must not meet the device-wide synchronisation of cudaMalloc / cudaFree.  The scratch is a fixed
+ * CK_ROUTE_STATIC_SCRATCH_BYTES array inside the library, held by every GPU that loads it until exit.
+ * Same outputs, bit for bit, as ck_route.  Limits: ck_route_workspace_bytes(n, E) must not exceed
+ * CK_ROUTE_STATIC_SCRATCH_BYTES (any n at E <= 32; n <= 606,208 ids at E = 64; n <= 303,104 at E = 128), otherwise
+ * CK_ERR_RANGE and nothing is launched.  The first call on a device looks up the array's device address
+ * (make it outside stream capture).  Calls share the array: do not let two of them overlap on one GPU. */
+#define CK_ROUTE_STATIC_SCRATCH_BYTES (256 + 148 * 32 * 32 * 4)
+CK_API int64_t ck_route_static_max_bytes(void);
+CK_API int ck_route_static(const void *ids, int ids_is_i64, int64_t n, int E, uint32_t *counts,
+                           int32_t *excl_off, int32_t *end_off, int32_t *sorted_idx, int32_t *sorted_expert,
+                           int32_t *padded_off, int32_t *mtile_off, int32_t *row_map, int32_t *dev_status,
+                           void *stream);
+
 /* ---- SwiGLU ------------------------------------------------------------------------------
  * Replace swiglu_forward_cuda / swiglu_backward_cuda
  * (kernels/swiglu/cuda_implementation/ops.cpp:7-22, forward.cu:31-93, backward.cu:44-128) and
