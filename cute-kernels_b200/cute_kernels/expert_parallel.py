@@ -1,0 +1,196 @@
+"""Expert parallelism for the MoE expert path: experts block-partitioned over the ranks of a process
+group, tokens data-parallel, rows exchanged with all-to-all-v (NCCL over NVLink on GPUs).
+
+The reference has no multi-GPU path; the contract is the single-process layer on the concatenated
+batch.  Rank g owns experts [g*E/G, (g+1)*E/G) and only those slices of ``c_fc.weight`` /
+``c_proj.weight`` (so expert weight gradients need no all-reduce).
+
+  forward   local route by global expert id (sorted by expert == sorted by destination rank)
+            -> exchange the per-(rank, expert) counts            (all_to_all_single, int64[G * E/G])
+            -> gather the token rows in sorted order              (send buffer)
+            -> all-to-all-v of the rows                           (dispatch)
+            -> local expert computation on the received rows      (the fused grouped-GEMM path, top_k = 1)
+            -> all-to-all-v back                                  (return)
+            -> router-weighted k-way combine on the source rank
+  backward  the mirror image; every exchange step is an autograd function whose backward is the
+            reverse exchange.
+
+Receive sizes are data dependent: one device-to-host read of the count matrix per call.
+``expert_fn`` / ``route_fn`` are injectable so the permutation and exchange logic can run on CPU ranks
+(gloo) with a CPU expert function in tests.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+
+def _all_to_all_rows(inp: torch.Tensor, out_rows: int, in_splits: list[int], out_splits: list[int], group) -> torch.Tensor:
+    out = torch.empty((out_rows,) + tuple(inp.shape[1:]), dtype=inp.dtype, device=inp.device)
+    if inp.is_cuda:
+        dist.all_to_all_single(out, inp.contiguous(), output_split_sizes=out_splits, input_split_sizes=in_splits, group=group)
+    else:
+        # gloo has no all_to_all_single with uneven splits on every build: pairwise send / recv
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        ins = list(inp.contiguous().split(in_splits))
+        outs = list(out.split(out_splits))
+        outs[rank].copy_(ins[rank])
+        ops = []
+        for peer in range(world):
+            if peer == rank:
+                continue
+            gpeer = dist.get_global_rank(group, peer) if group is not None else peer
+            if in_splits[peer] > 0:
+                ops.append(dist.P2POp(dist.isend, ins[peer].contiguous(), gpeer, group))
+            if out_splits[peer] > 0:
+                ops.append(dist.P2POp(dist.irecv, outs[peer], gpeer, group))
+        if ops:
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
+    return out
+
+
+class _AllToAllRows(torch.autograd.Function):
+    """Rows [sum(in_splits), ...] -> [sum(out_splits), ...]; the gradient travels the reverse way."""
+
+    @staticmethod
+    def forward(ctx, inp, in_splits, out_splits, group):
+        ctx.in_splits, ctx.out_splits, ctx.group = in_splits, out_splits, group
+        return _all_to_all_rows(inp, sum(out_splits), in_splits, out_splits, group)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return _all_to_all_rows(grad.contiguous(), sum(ctx.in_splits), ctx.out_splits, ctx.in_splits, ctx.group), None, None, None
+
+
+class _GatherSorted(torch.autograd.Function):
+    """rows[j] = x[tok[j]]; backward sums the k copies of every token in fp32."""
+
+    @staticmethod
+    def forward(ctx, x, tok):
+        ctx.save_for_backward(tok)
+        ctx.tokens = x.size(0)
+        return x.index_select(0, tok)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (tok,) = ctx.saved_tensors
+        acc = torch.zeros(ctx.tokens, grad.size(1), dtype=torch.float32, device=grad.device)
+        acc.index_add_(0, tok, grad.float())
+        return acc.to(grad.dtype), None
+
+
+class _CombineSorted(torch.autograd.Function):
+    """y[t] = sum_j w[flat_j] * rows[j] over the sorted rows of token t (fp32 accumulation)."""
+
+    @staticmethod
+    def forward(ctx, rows, w_flat_sorted, tok, tokens: int):
+        ctx.save_for_backward(rows, w_flat_sorted, tok)
+        acc = torch.zeros(tokens, rows.size(1), dtype=torch.float32, device=rows.device)
+        acc.index_add_(0, tok, rows.float() * w_flat_sorted.float().unsqueeze(1))
+        return acc.to(rows.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        rows, w, tok = ctx.saved_tensors
+        dyg = dy.index_select(0, tok)
+        d_rows = (dyg.float() * w.float().unsqueeze(1)).to(rows.dtype)
+        d_w = (dyg.float() * rows.float()).sum(dim=1).to(w.dtype)
+        return d_rows, d_w, None, None
+
+
+def _default_route(ids: torch.Tensor, num_experts: int):
+    from .routing import route
+
+    r = route(ids, num_experts, with_tile_metadata=False)
+    return r.sorted_idx, r.counts
+
+
+def _default_expert_fn(rows, local_ids, w_fc, w_proj, act_kind):
+    from .moe import fused_experts
+
+    ones = torch.ones(rows.size(0), 1, dtype=rows.dtype, device=rows.device)
+    return fused_experts(rows, ones, local_ids.view(-1, 1), w_fc, w_proj, 1, act_kind)
+
+
+class ExpertParallelMoE:
+    """Callable: ``y = ep(x, router_weights, selected_experts, w_fc_local, w_proj_local)``.
+
+    x [T_local, H]; router_weights / selected_experts [T_local, k] with GLOBAL expert ids;
+    w_fc_local [E/G, 2I, H], w_proj_local [E/G, H, I]: this rank's experts."""
+
+    def __init__(self, num_experts: int, top_k: int, group=None, act_kind: int = 0,
+                 expert_fn: Callable | None = None, route_fn: Callable | None = None) -> None:
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if num_experts % self.world != 0:
+            raise ValueError("num_experts must be divisible by the number of ranks")
+        self.num_experts = num_experts
+        self.local_experts = num_experts // self.world
+        self.top_k = top_k
+        self.act_kind = act_kind
+        self.expert_fn = expert_fn or _default_expert_fn
+        self.route_fn = route_fn or _default_route
+
+    def __call__(self, x, router_weights, selected_experts, w_fc_local, w_proj_local):
+        G, epr, k = self.world, self.local_experts, self.top_k
+        T = x.size(0)
+        dev = x.device
+        flat_ids = selected_experts.reshape(-1)
+        sorted_idx, counts = self.route_fn(flat_ids, self.num_experts)
+        sorted_idx = sorted_idx.long()
+        tok = sorted_idx // k
+
+        # per-(destination rank, local expert) counts -> what every source sends us
+        send_counts = counts.to(torch.int64).view(G, epr)
+        recv_counts = torch.empty_like(send_counts)
+        if dev.type == "cuda":
+            dist.all_to_all_single(recv_counts, send_counts.contiguous(), group=self.group)
+        else:
+            gathered = [torch.empty_like(send_counts) for _ in range(G)]
+            dist.all_gather(gathered, send_counts.contiguous(), group=self.group)
+            recv_counts = torch.stack([g[self.rank] for g in gathered])
+        both = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).cpu()  # the one host sync of the layer
+        in_splits, out_splits = both[0].tolist(), both[1].tolist()
+        n_recv = sum(out_splits)
+
+        rows = _GatherSorted.apply(x, tok)
+        recv = _AllToAllRows.apply(rows, in_splits, out_splits, self.group)
+        # received rows are (source rank major, local expert minor): their local expert ids
+        local_ids = torch.repeat_interleave(
+            torch.arange(epr, device=dev, dtype=torch.int64).repeat(G), recv_counts.reshape(-1), output_size=n_recv)
+        y_recv = self.expert_fn(recv, local_ids, w_fc_local, w_proj_local, self.act_kind)
+        y_back = _AllToAllRows.apply(y_recv, out_splits, in_splits, self.group)
+        w_sorted = router_weights.reshape(-1).index_select(0, sorted_idx)
+        return _CombineSorted.apply(y_back, w_sorted, tok, T)
+
+
+def shard_expert_state_dict(full: dict[str, torch.Tensor], rank: int, world: int) -> dict[str, torch.Tensor]:
+    """Slices ``c_fc.*`` / ``c_proj.*`` of a full MoE state_dict to the experts rank ``rank`` owns;
+    ``gate.weight`` (the router) is replicated."""
+    out = {}
+    for key, v in full.items():
+        if key.startswith(("c_fc.", "c_proj.")):
+            epr = v.size(0) // world
+            out[key] = v[rank * epr : (rank + 1) * epr].clone()
+        else:
+            out[key] = v.clone()
+    return out
+
+
+def gather_expert_state_dict(local: dict[str, torch.Tensor], group=None) -> dict[str, torch.Tensor]:
+    """Inverse of :func:`shard_expert_state_dict`: all-gathers the expert slices into a full state_dict."""
+    world = dist.get_world_size(group)
+    out = {}
+    for key, v in local.items():
+        if key.startswith(("c_fc.", "c_proj.")):
+            parts = [torch.empty_like(v) for _ in range(world)]
+            dist.all_gather(parts, v.contiguous(), group=group)
+            out[key] = torch.cat(parts, dim=0)
+        else:
+            out[key] = v.clone()
+    return out

@@ -60,9 +60,9 @@ def _cast_from_f32_impl(src: torch.Tensor, dst: torch.Tensor) -> None:
 
 
 def _up_act_fwd_impl(xg: torch.Tensor, wfc: torch.Tensor, gate_w: torch.Tensor | None, row_map: torch.Tensor,
-                     mtile_off: torch.Tensor, act: torch.Tensor, h: torch.Tensor | None, act_kind: int,
-                     status: torch.Tensor) -> None:
+                     mtile_off: torch.Tensor, act: torch.Tensor, h: torch.Tensor | None, act_kind: int) -> None:
     _lib.require_cuda(xg, wfc, act)
+    status = _lib.status_word(xg.device)
     E, two_i, H = wfc.shape
     with torch.cuda.device(xg.device), _lib.launch("up_act_fwd", 1, 2.0 * xg.size(0) * two_i * H):
         st = _lib.lib.ck_moe_up_act_fwd(xg.data_ptr(), wfc.data_ptr(), _lib.ptr(gate_w), row_map.data_ptr(),
@@ -73,8 +73,9 @@ def _up_act_fwd_impl(xg: torch.Tensor, wfc: torch.Tensor, gate_w: torch.Tensor |
 
 
 def _down_combine_fwd_impl(act: torch.Tensor, wproj: torch.Tensor, row_map: torch.Tensor, mtile_off: torch.Tensor,
-                           out32: torch.Tensor, top_k: int, status: torch.Tensor) -> None:
+                           out32: torch.Tensor, top_k: int) -> None:
     _lib.require_cuda(act, wproj, out32)
+    status = _lib.status_word(act.device)
     E, H, I = wproj.shape
     with torch.cuda.device(act.device), _lib.launch("down_combine_fwd", 1, 2.0 * act.size(0) * H * I):
         st = _lib.lib.ck_moe_down_combine_fwd(act.data_ptr(), wproj.data_ptr(), row_map.data_ptr(),
@@ -85,8 +86,9 @@ def _down_combine_fwd_impl(act: torch.Tensor, wproj: torch.Tensor, row_map: torc
 
 def _dgrad_down_impl(dyg: torch.Tensor, wproj: torch.Tensor, h: torch.Tensor, gate_w: torch.Tensor | None,
                      row_map: torch.Tensor, mtile_off: torch.Tensor, dh: torch.Tensor, dgates: torch.Tensor,
-                     act_kind: int, status: torch.Tensor) -> None:
+                     act_kind: int) -> None:
     _lib.require_cuda(dyg, wproj, h, dh, dgates)
+    status = _lib.status_word(dyg.device)
     E, H, I = wproj.shape
     with torch.cuda.device(dyg.device), _lib.launch("dgrad_down", 1, 2.0 * dyg.size(0) * H * I):
         st = _lib.lib.ck_moe_dgrad_down(dyg.data_ptr(), wproj.data_ptr(), h.data_ptr(), _lib.ptr(gate_w),
@@ -97,8 +99,9 @@ def _dgrad_down_impl(dyg: torch.Tensor, wproj: torch.Tensor, h: torch.Tensor, ga
 
 
 def _dgrad_up_impl(dh: torch.Tensor, wfc: torch.Tensor, row_map: torch.Tensor, mtile_off: torch.Tensor,
-                   dx32: torch.Tensor, top_k: int, status: torch.Tensor) -> None:
+                   dx32: torch.Tensor, top_k: int) -> None:
     _lib.require_cuda(dh, wfc, dx32)
+    status = _lib.status_word(dh.device)
     E, i2, H = wfc.shape
     with torch.cuda.device(dh.device), _lib.launch("dgrad_up", 1, 2.0 * dh.size(0) * H * i2):
         st = _lib.lib.ck_moe_dgrad_up(dh.data_ptr(), wfc.data_ptr(), row_map.data_ptr(), mtile_off.data_ptr(),
@@ -107,9 +110,9 @@ def _dgrad_up_impl(dh: torch.Tensor, wfc: torch.Tensor, row_map: torch.Tensor, m
     _lib.check(st, "ck_moe_dgrad_up")
 
 
-def _wgrad_impl(a: torch.Tensor, b: torch.Tensor, padded_off: torch.Tensor, dw: torch.Tensor,
-                status: torch.Tensor) -> None:
+def _wgrad_impl(a: torch.Tensor, b: torch.Tensor, padded_off: torch.Tensor, dw: torch.Tensor) -> None:
     _lib.require_cuda(a, b, dw)
+    status = _lib.status_word(a.device)
     E, M, N = dw.shape
     assert a.size(1) == M and b.size(1) == N and a.size(0) == b.size(0)
     with torch.cuda.device(a.device), _lib.launch("wgrad", 1, 2.0 * a.size(0) * M * N):
@@ -118,9 +121,9 @@ def _wgrad_impl(a: torch.Tensor, b: torch.Tensor, padded_off: torch.Tensor, dw: 
     _lib.check(st, "ck_moe_wgrad")
 
 
-def _grouped_linear_impl(x: torch.Tensor, w: torch.Tensor, mtile_off: torch.Tensor, y: torch.Tensor, trans_w: bool,
-                         status: torch.Tensor) -> None:
+def _grouped_linear_impl(x: torch.Tensor, w: torch.Tensor, mtile_off: torch.Tensor, y: torch.Tensor, trans_w: bool) -> None:
     _lib.require_cuda(x, w, y)
+    status = _lib.status_word(x.device)
     E = w.size(0)
     N, K = (w.size(2), w.size(1)) if trans_w else (w.size(1), w.size(2))
     assert x.size(1) == K and y.size(1) == N and x.size(0) == y.size(0)
@@ -133,12 +136,12 @@ def _grouped_linear_impl(x: torch.Tensor, w: torch.Tensor, mtile_off: torch.Tens
 
 gather_rows = _make_op("moe_gather_rows", _gather_rows_impl, {"dst"})
 cast_from_f32 = _make_op("cast_from_f32", _cast_from_f32_impl, {"dst"})
-up_act_fwd = _make_op("moe_up_act_fwd", _up_act_fwd_impl, {"act", "h", "status"})
-down_combine_fwd = _make_op("moe_down_combine_fwd", _down_combine_fwd_impl, {"out32", "status"})
-dgrad_down = _make_op("moe_dgrad_down", _dgrad_down_impl, {"dh", "dgates", "status"})
-dgrad_up = _make_op("moe_dgrad_up", _dgrad_up_impl, {"dx32", "status"})
-wgrad = _make_op("moe_wgrad", _wgrad_impl, {"dw", "status"})
-grouped_linear = _make_op("moe_grouped_linear", _grouped_linear_impl, {"y", "status"})
+up_act_fwd = _make_op("moe_up_act_fwd", _up_act_fwd_impl, {"act", "h"})
+down_combine_fwd = _make_op("moe_down_combine_fwd", _down_combine_fwd_impl, {"out32"})
+dgrad_down = _make_op("moe_dgrad_down", _dgrad_down_impl, {"dh", "dgates"})
+dgrad_up = _make_op("moe_dgrad_up", _dgrad_up_impl, {"dx32"})
+wgrad = _make_op("moe_wgrad", _wgrad_impl, {"dw"})
+grouped_linear = _make_op("moe_grouped_linear", _grouped_linear_impl, {"y"})
 
 
 def _from_f32(src32: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
@@ -163,7 +166,6 @@ class _FusedExperts(torch.autograd.Function):
         I = two_i // 2
         cap = row_map.numel()
         dev, dt = x.device, x.dtype
-        status = _lib.status_word(dev)
         need_grad = any(ctx.needs_input_grad[:4])
 
         x = x.contiguous()
@@ -172,9 +174,9 @@ class _FusedExperts(torch.autograd.Function):
         gather_rows(x, xg, row_map, padded_off, top_k)
         act = torch.empty(cap, I, dtype=dt, device=dev)
         h = torch.empty(cap, two_i, dtype=dt, device=dev) if need_grad else None
-        up_act_fwd(xg, w_fc, gate_w, row_map, mtile_off, act, h, act_kind, status)
+        up_act_fwd(xg, w_fc, gate_w, row_map, mtile_off, act, h, act_kind)
         out32 = torch.zeros(T, H, dtype=torch.float32, device=dev)
-        down_combine_fwd(act, w_proj, row_map, mtile_off, out32, top_k, status)
+        down_combine_fwd(act, w_proj, row_map, mtile_off, out32, top_k)
         y = _from_f32(out32, dt)
 
         if need_grad:
@@ -191,7 +193,6 @@ class _FusedExperts(torch.autograd.Function):
         E, two_i, H = w_fc.shape
         cap = row_map.numel()
         dev, dt = dy.device, xg.dtype
-        status = _lib.status_word(dev)
         need_x, need_rw, need_wfc, need_wproj = ctx.needs_input_grad[:4]
 
         dy = dy.contiguous().to(dt)
@@ -199,19 +200,19 @@ class _FusedExperts(torch.autograd.Function):
         gather_rows(dy, dyg, row_map, padded_off, top_k)
         dh = torch.empty(cap, two_i, dtype=dt, device=dev)
         dgates = torch.zeros(T * top_k, dtype=torch.float32, device=dev)
-        dgrad_down(dyg, w_proj, h, gate_w, row_map, mtile_off, dh, dgates, act_kind, status)
+        dgrad_down(dyg, w_proj, h, gate_w, row_map, mtile_off, dh, dgates, act_kind)
 
         d_wproj = d_wfc = dx = d_rw = None
         if need_wproj:
             d_wproj = torch.empty_like(w_proj)
-            wgrad(dyg, act, padded_off, d_wproj, status)
+            wgrad(dyg, act, padded_off, d_wproj)
         if need_x:
             dx32 = torch.zeros(T, H, dtype=torch.float32, device=dev)
-            dgrad_up(dh, w_fc, row_map, mtile_off, dx32, top_k, status)
+            dgrad_up(dh, w_fc, row_map, mtile_off, dx32, top_k)
             dx = _from_f32(dx32, dt)
         if need_wfc:
             d_wfc = torch.empty_like(w_fc)
-            wgrad(dh, xg, padded_off, d_wfc, status)
+            wgrad(dh, xg, padded_off, d_wfc)
         if need_rw:
             d_rw = dgates.view(T, top_k).to(dt)
         return dx, d_rw, d_wfc, d_wproj, None, None, None, None, None
@@ -239,24 +240,22 @@ class _GroupedLinear(torch.autograd.Function):
     def forward(ctx, x, w, mtile_off, padded_off):
         x = x.contiguous()
         w = w.contiguous()
-        status = _lib.status_word(x.device)
         y = torch.zeros(x.size(0), w.size(1), dtype=x.dtype, device=x.device)
-        grouped_linear(x, w, mtile_off, y, False, status)
+        grouped_linear(x, w, mtile_off, y, False)
         ctx.save_for_backward(x, w, mtile_off, padded_off)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, w, mtile_off, padded_off = ctx.saved_tensors
-        status = _lib.status_word(x.device)
         dy = dy.contiguous()
         dx = dw = None
         if ctx.needs_input_grad[0]:
             dx = torch.zeros_like(x)
-            grouped_linear(dy, w, mtile_off, dx, True, status)
+            grouped_linear(dy, w, mtile_off, dx, True)
         if ctx.needs_input_grad[1]:
             dw = torch.empty_like(w)
-            wgrad(dy, x, padded_off, dw, status)
+            wgrad(dy, x, padded_off, dw)
         return dx, dw, None, None
 
 

@@ -46,6 +46,15 @@ def padded_capacity(n: int, num_experts: int) -> int:
     return (n // _lib.CK_TILE_M + num_experts) * _lib.CK_TILE_M
 
 
+def route_workspace_bytes(n: int, num_experts: int) -> int:
+    """Python mirror of ck_route_workspace_bytes (kept out of ctypes so torch.compile can trace callers)."""
+    if n <= 0:
+        return 256 + num_experts * 4
+    slice_len = -(-n // (148 * 32))
+    slice_len = max(256, -(-slice_len // 128) * 128)
+    return 256 + -(-n // slice_len) * num_experts * 4
+
+
 def _route_impl(
     ids: torch.Tensor,
     num_experts: int,
@@ -58,9 +67,9 @@ def _route_impl(
     mtile_off: torch.Tensor | None,
     row_map: torch.Tensor | None,
     workspace: torch.Tensor,
-    status: torch.Tensor,
 ) -> None:
     _lib.require_cuda(ids, counts, sorted_idx, workspace)
+    status = _lib.status_word(ids.device)
     with torch.cuda.device(ids.device), _lib.launch("route", 3 if ids.numel() else 1):
         st = _lib.lib.ck_route(
             ids.data_ptr(), int(ids.dtype == torch.int64), ids.numel(), num_experts,
@@ -75,7 +84,7 @@ _route_op = torch.library.custom_op(
     "cute_kernels_b200::route",
     _route_impl,
     mutates_args={"counts", "excl", "end", "sorted_idx", "sorted_expert", "padded_off", "mtile_off", "row_map",
-                  "workspace", "status"},
+                  "workspace"},
 )
 
 
@@ -102,9 +111,7 @@ def route(ids: torch.Tensor, num_experts: int, *, with_tile_metadata: bool = Tru
         row_map = torch.empty(padded_capacity(n, num_experts), **i32)
     else:
         padded_off = mtile_off = row_map = None
-    ws_bytes = _lib.lib.ck_route_workspace_bytes(n, num_experts)
-    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-    status = _lib.status_word(dev)
+    workspace = torch.empty(route_workspace_bytes(n, num_experts), dtype=torch.uint8, device=dev)
     fn = _route_op if torch.compiler.is_compiling() else _route_impl
-    fn(ids, num_experts, counts, excl, end, sorted_idx, sorted_expert, padded_off, mtile_off, row_map, workspace, status)
+    fn(ids, num_experts, counts, excl, end, sorted_idx, sorted_expert, padded_off, mtile_off, row_map, workspace)
     return Routing(counts, excl, end, sorted_idx, sorted_expert, padded_off, mtile_off, row_map)

@@ -65,7 +65,7 @@ def test_grouped_linear(dtype, trans_w, case):
     g = torch.Generator().manual_seed(2)
     w = (torch.randn(E, K, N, generator=g) if trans_w else torch.randn(E, N, K, generator=g)).mul(0.1).to(dtype).cuda()
     y = torch.full((x.size(0), N), float("nan"), dtype=dtype, device="cuda")
-    grouped_linear(x, w, r.mtile_off, y, trans_w, _lib.status_word(x.device))
+    grouped_linear(x, w, r.mtile_off, y, trans_w)
     re = _row_expert(ref, E)
     total = int(ref["padded_off"][-1])
     xf, wf = x.float().cpu(), w.float().cpu()
@@ -90,7 +90,7 @@ def test_wgrad(dtype, case):
     a = _padded_rows(ref, M, dtype, 3)
     b = _padded_rows(ref, N, dtype, 4)
     dw = torch.full((E, M, N), float("nan"), dtype=dtype, device="cuda")
-    wgrad(a, b, r.padded_off, dw, _lib.status_word(a.device))
+    wgrad(a, b, r.padded_off, dw)
     re = _row_expert(ref, E)
     af, bf = a.float().cpu(), b.float().cpu()
     for e in range(E):
@@ -128,7 +128,6 @@ def test_fused_forward_pieces(dtype, act_kind, case):
     p = _moe_problem(counts, H, I, k, dtype)
     r, ref, E, T = p["r"], p["ref"], p["E"], p["T"]
     cap = r.capacity
-    st = _lib.status_word(p["x"].device)
     xg = torch.full((cap, H), float("nan"), dtype=dtype, device="cuda")
     gather_rows(p["x"], xg, r.row_map, r.padded_off, k)
     total = int(ref["padded_off"][-1])
@@ -140,7 +139,7 @@ def test_fused_forward_pieces(dtype, act_kind, case):
 
     act = torch.full((cap, I), float("nan"), dtype=dtype, device="cuda")
     h = torch.full((cap, 2 * I), float("nan"), dtype=dtype, device="cuda")
-    up_act_fwd(xg, p["w_fc"], p["gate_w"], r.row_map, r.mtile_off, act, h, act_kind, st)
+    up_act_fwd(xg, p["w_fc"], p["gate_w"], r.row_map, r.mtile_off, act, h, act_kind)
     re = torch.from_numpy(_row_expert(ref, E)[:total])
     wf = p["w_fc"].float().cpu()
     exp_h = torch.zeros(total, 2 * I)
@@ -155,7 +154,7 @@ def test_fused_forward_pieces(dtype, act_kind, case):
     torch.testing.assert_close(act[:total].float().cpu(), exp_act, **TOL[dtype])
 
     out32 = torch.zeros(T, H, dtype=torch.float32, device="cuda")
-    down_combine_fwd(act, p["w_proj"], r.row_map, r.mtile_off, out32, k, st)
+    down_combine_fwd(act, p["w_proj"], r.row_map, r.mtile_off, out32, k)
     af = act[:total].float().cpu()
     wp = p["w_proj"].float().cpu()
     exp_out = torch.zeros(T, H)
@@ -175,7 +174,6 @@ def test_fused_backward_pieces(dtype, act_kind, case):
     counts, H, I, k = case
     p = _moe_problem(counts, H, I, k, dtype, seed=1)
     r, ref, E, T = p["r"], p["ref"], p["E"], p["T"]
-    st = _lib.status_word(p["x"].device)
     total = int(ref["padded_off"][-1])
     rm = torch.from_numpy(ref["row_map"][:total].astype(np.int64))
     valid = rm >= 0
@@ -184,7 +182,7 @@ def test_fused_backward_pieces(dtype, act_kind, case):
     h = _padded_rows(ref, 2 * I, dtype, 6)
     dh = torch.full((r.capacity, 2 * I), float("nan"), dtype=dtype, device="cuda")
     dgates = torch.zeros(T * k, dtype=torch.float32, device="cuda")
-    dgrad_down(dyg, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh, dgates, act_kind, st)
+    dgrad_down(dyg, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh, dgates, act_kind)
 
     wp = p["w_proj"].float().cpu()
     g = torch.zeros(total, I)
@@ -211,7 +209,7 @@ def test_fused_backward_pieces(dtype, act_kind, case):
 
     dh_in = _padded_rows(ref, 2 * I, dtype, 7)
     dx32 = torch.zeros(T, H, dtype=torch.float32, device="cuda")
-    dgrad_up(dh_in, p["w_fc"], r.row_map, r.mtile_off, dx32, k, st)
+    dgrad_up(dh_in, p["w_fc"], r.row_map, r.mtile_off, dx32, k)
     wf = p["w_fc"].float().cpu()
     exp_dx = torch.zeros(T, H)
     dhf = dh_in[:total].float().cpu()
@@ -245,6 +243,6 @@ def test_capacity_guard_flags_instead_of_overrunning():
     w = torch.zeros(1, 64, 64, dtype=torch.bfloat16, device="cuda")
     off = torch.tensor([0, 5], dtype=torch.int32, device="cuda")  # claims 5 tiles, only 1 allocated
     y = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
-    grouped_linear(x, w, off, y, False, _lib.status_word(x.device))
+    grouped_linear(x, w, off, y, False)
     with pytest.raises(RuntimeError, match="CK_DEV_META"):
         cute_kernels.check_device_status()

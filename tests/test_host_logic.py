@@ -129,3 +129,28 @@ def test_padded_capacity_bounds_every_routing():
         ids = rng.integers(0, E, size=n)
         r = orc.route_ref(ids, E)
         assert r["padded_off"][-1] <= ck.padded_capacity(n, E) == r["row_map"].size
+
+
+def test_route_workspace_bytes_mirror_matches_the_library():
+    from cute_kernels import _lib
+    from cute_kernels.routing import route_workspace_bytes
+
+    for n in (0, 1, 255, 256, 257, 4096, 32768, 262144, 1 << 20, (1 << 24) + 5):
+        for E in (1, 8, 64, 72, 1024):
+            assert route_workspace_bytes(n, E) == _lib.lib.ck_route_workspace_bytes(n, E), (n, E)
+
+
+def test_module_traces_under_fullgraph_compile_without_graph_breaks():
+    """Dynamo must trace MoE_Cute end to end (custom ops stay opaque).  On a CPU-only machine the trace
+    succeeds and the first kernel call then refuses the CPU tensors."""
+    import cute_kernels as ck
+
+    m = ck.MoE_Cute(4, 2, 64, 64, ck.swiglu_packed_cute, True, False, 0.02)
+    mod = torch.compile(m, fullgraph=True, backend="eager")
+    x = torch.randn(16, 64, requires_grad=True)
+    if torch.cuda.is_available():
+        y, _ = mod.cuda()(x.cuda())
+        assert y.shape == (16, 64)
+    else:
+        with pytest.raises(RuntimeError, match="CUDA tensors only"):
+            mod(x)
