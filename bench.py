@@ -212,6 +212,8 @@ def gpu_arm(args, w: dict) -> dict | None:
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=device)
 
     T, H, I, E, k = w["T"], w["H"], w["I"], w["E"], w["k"]

@@ -368,8 +368,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                     row_ok = m < p.M;
                     out = reinterpret_cast<T *>(p.out0) + (int64_t(c.e) * p.M + m) * int64_t(p.N);
                 } else {
+                    int64_t orow = int64_t(c.m_tile) * BM + row_in_tile;
                     row_ok = true;
-                    out = reinterpret_cast<T *>(p.out0) + (int64_t(c.m_tile) * BM + row_in_tile) * int64_t(p.N);
+                    if (p.row_map) {  // scatter store: padded row -> caller's row order (each row written once)
+                        const int32_t src = p.row_map[orow];
+                        row_ok = src >= 0;
+                        orow = row_ok ? src : 0;
+                    }
+                    out = reinterpret_cast<T *>(p.out0) + orow * int64_t(p.N);
                 }
                 const int n0 = c.n_tile * BN;
 #pragma unroll 1
@@ -672,13 +678,13 @@ static int wgrad_t(const void *a, const void *b, const int32_t *padded_off, void
 }
 
 template <typename T>
-static int grouped_linear_t(const void *x, const void *w, const int32_t *mtile_off, void *y, int E, int64_t cap, int N,
-                            int K, int trans_w, int32_t *dev_status, cudaStream_t stream) {
+static int grouped_linear_t(const void *x, const void *w, const int32_t *mtile_off, const int32_t *row_map, void *y, int E,
+                            int64_t cap, int N, int K, int trans_w, int32_t *dev_status, cudaStream_t stream) {
     GemmParams p = {};
     p.cap = cap;
     int rc;
     if ((rc = map_a_kmajor<T>(&p.tmA, x, cap, K)) != CK_OK) return rc;
-    p.mtile_off = mtile_off; p.out0 = y; p.dev_status = dev_status;
+    p.mtile_off = mtile_off; p.row_map = row_map; p.out0 = y; p.dev_status = dev_status;
     p.E = E; p.n_tiles = (N + BN - 1) / BN; p.N = N; p.K = K; p.top_k = 1;
     if (trans_w) {
         if ((rc = map_w_mnmajor<T>(&p.tmB, w, E, K, N)) != CK_OK) return rc;
@@ -739,5 +745,12 @@ extern "C" int ck_moe_wgrad(const void *a, const void *b, const int32_t *padded_
 extern "C" int ck_moe_grouped_linear(const void *x, const void *w, const int32_t *mtile_off, void *y, int E, int64_t cap,
                                      int N, int K, int trans_w, int dtype, int32_t *dev_status, void *stream) {
     if (!x || !w || !mtile_off || !y || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, N, K)) return CK_ERR_SHAPE;
-    CK_DISPATCH_DTYPE(dtype, (grouped_linear_t<T>(x, w, mtile_off, y, E, cap, N, K, trans_w, dev_status, (cudaStream_t)stream)));
+    CK_DISPATCH_DTYPE(dtype, (grouped_linear_t<T>(x, w, mtile_off, nullptr, y, E, cap, N, K, trans_w, dev_status, (cudaStream_t)stream)));
+}
+
+extern "C" int ck_moe_grouped_linear_scatter(const void *x, const void *w, const int32_t *mtile_off, const int32_t *row_map,
+                                             void *y, int E, int64_t cap, int N, int K, int trans_w, int dtype,
+                                             int32_t *dev_status, void *stream) {
+    if (!x || !w || !mtile_off || !row_map || !y || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, N, K)) return CK_ERR_SHAPE;
+    CK_DISPATCH_DTYPE(dtype, (grouped_linear_t<T>(x, w, mtile_off, row_map, y, E, cap, N, K, trans_w, dev_status, (cudaStream_t)stream)));
 }

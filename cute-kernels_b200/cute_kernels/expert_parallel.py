@@ -102,6 +102,57 @@ class _CombineSorted(torch.autograd.Function):
         return d_rows, d_w, None, None
 
 
+class _GatherSortedCuda(torch.autograd.Function):
+    """rows[j] = x[sorted_idx[j] // k] (one streaming kernel); backward = deterministic k-way sum."""
+
+    @staticmethod
+    def forward(ctx, x, sorted_idx32, pos32, k: int):
+        from .moe import gather_rows_scaled
+
+        ctx.save_for_backward(pos32)
+        ctx.k, ctx.tokens = k, x.size(0)
+        rows = torch.empty(sorted_idx32.numel(), x.size(1), dtype=x.dtype, device=x.device)
+        gather_rows_scaled(x.contiguous(), rows, sorted_idx32, None, k)
+        return rows
+
+    @staticmethod
+    def backward(ctx, grad):
+        from .moe import combine_rows
+
+        (pos32,) = ctx.saved_tensors
+        dx = torch.empty(ctx.tokens, grad.size(1), dtype=grad.dtype, device=grad.device)
+        combine_rows(grad.contiguous(), pos32, None, dx, ctx.k)
+        return dx, None, None, None
+
+
+class _CombineSortedCuda(torch.autograd.Function):
+    """y[t] = sum_j w[t, j] * rows[pos[t*k+j]] with fp32 accumulation; backward = scaled gather + row dots."""
+
+    @staticmethod
+    def forward(ctx, rows, w, sorted_idx32, pos32, k: int):
+        from .moe import combine_rows
+
+        rows = rows.contiguous()
+        w = w.contiguous()
+        ctx.save_for_backward(rows, w, sorted_idx32, pos32)
+        ctx.k = k
+        y = torch.empty(w.size(0), rows.size(1), dtype=rows.dtype, device=rows.device)
+        combine_rows(rows, pos32, w.view(-1), y, k)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .moe import gather_rows_scaled, row_dots
+
+        rows, w, sorted_idx32, pos32 = ctx.saved_tensors
+        dy = dy.contiguous()
+        d_rows = torch.empty_like(rows)
+        gather_rows_scaled(dy, d_rows, sorted_idx32, w.view(-1), ctx.k)
+        d_w = torch.empty_like(w)
+        row_dots(rows, pos32, dy, d_w.view(-1), ctx.k)
+        return d_rows, d_w, None, None, None
+
+
 def _default_route(ids: torch.Tensor, num_experts: int):
     from .routing import route
 
@@ -110,10 +161,9 @@ def _default_route(ids: torch.Tensor, num_experts: int):
 
 
 def _default_expert_fn(rows, local_ids, w_fc, w_proj, act_kind):
-    from .moe import fused_experts
+    from .moe import expert_shard
 
-    ones = torch.ones(rows.size(0), 1, dtype=rows.dtype, device=rows.device)
-    return fused_experts(rows, ones, local_ids.view(-1, 1), w_fc, w_proj, 1, act_kind)
+    return expert_shard(rows, local_ids, w_fc, w_proj, act_kind)
 
 
 class ExpertParallelMoE:
@@ -141,9 +191,14 @@ class ExpertParallelMoE:
         T = x.size(0)
         dev = x.device
         flat_ids = selected_experts.reshape(-1)
-        sorted_idx, counts = self.route_fn(flat_ids, self.num_experts)
-        sorted_idx = sorted_idx.long()
-        tok = sorted_idx // k
+        sorted_idx32, counts = self.route_fn(flat_ids, self.num_experts)
+        sorted_idx = sorted_idx32.long()
+        on_gpu = dev.type == "cuda"
+        if on_gpu:  # inverse permutation: position of flat slot (t*k + j) in the sorted order
+            pos32 = torch.empty_like(sorted_idx32)
+            pos32[sorted_idx] = torch.arange(sorted_idx32.numel(), device=dev, dtype=torch.int32)
+        else:
+            tok = sorted_idx // k
 
         # per-(destination rank, local expert) counts -> what every source sends us
         send_counts = counts.to(torch.int64).view(G, epr)
@@ -158,13 +213,15 @@ class ExpertParallelMoE:
         in_splits, out_splits = both[0].tolist(), both[1].tolist()
         n_recv = sum(out_splits)
 
-        rows = _GatherSorted.apply(x, tok)
+        rows = _GatherSortedCuda.apply(x, sorted_idx32, pos32, k) if on_gpu else _GatherSorted.apply(x, tok)
         recv = _AllToAllRows.apply(rows, in_splits, out_splits, self.group)
         # received rows are (source rank major, local expert minor): their local expert ids
         local_ids = torch.repeat_interleave(
             torch.arange(epr, device=dev, dtype=torch.int64).repeat(G), recv_counts.reshape(-1), output_size=n_recv)
         y_recv = self.expert_fn(recv, local_ids, w_fc_local, w_proj_local, self.act_kind)
         y_back = _AllToAllRows.apply(y_recv, out_splits, in_splits, self.group)
+        if on_gpu:
+            return _CombineSortedCuda.apply(y_back, router_weights, sorted_idx32, pos32, k)
         w_sorted = router_weights.reshape(-1).index_select(0, sorted_idx)
         return _CombineSorted.apply(y_back, w_sorted, tok, T)
 

@@ -85,14 +85,14 @@ def _down_combine_fwd_impl(act: torch.Tensor, wproj: torch.Tensor, row_map: torc
 
 
 def _dgrad_down_impl(dyg: torch.Tensor, wproj: torch.Tensor, h: torch.Tensor, gate_w: torch.Tensor | None,
-                     row_map: torch.Tensor, mtile_off: torch.Tensor, dh: torch.Tensor, dgates: torch.Tensor,
+                     row_map: torch.Tensor, mtile_off: torch.Tensor, dh: torch.Tensor, dgates: torch.Tensor | None,
                      act_kind: int) -> None:
     _lib.require_cuda(dyg, wproj, h, dh, dgates)
     status = _lib.status_word(dyg.device)
     E, H, I = wproj.shape
     with torch.cuda.device(dyg.device), _lib.launch("dgrad_down", 1, 2.0 * dyg.size(0) * H * I):
         st = _lib.lib.ck_moe_dgrad_down(dyg.data_ptr(), wproj.data_ptr(), h.data_ptr(), _lib.ptr(gate_w),
-                                        row_map.data_ptr(), mtile_off.data_ptr(), dh.data_ptr(), dgates.data_ptr(), E,
+                                        row_map.data_ptr(), mtile_off.data_ptr(), dh.data_ptr(), _lib.ptr(dgates), E,
                                         dyg.size(0), H, I, act_kind, _lib.dtype_code(dyg.dtype), status.data_ptr(),
                                         _lib.stream_ptr())
     _lib.check(st, "ck_moe_dgrad_down")
@@ -134,6 +134,46 @@ def _grouped_linear_impl(x: torch.Tensor, w: torch.Tensor, mtile_off: torch.Tens
     _lib.check(st, "ck_moe_grouped_linear")
 
 
+def _grouped_linear_scatter_impl(x: torch.Tensor, w: torch.Tensor, mtile_off: torch.Tensor, row_map: torch.Tensor,
+                                 y: torch.Tensor, trans_w: bool) -> None:
+    _lib.require_cuda(x, w, y)
+    status = _lib.status_word(x.device)
+    E = w.size(0)
+    N, K = (w.size(2), w.size(1)) if trans_w else (w.size(1), w.size(2))
+    assert x.size(1) == K and y.size(1) == N
+    with torch.cuda.device(x.device), _lib.launch("grouped_linear_scatter", 1, 2.0 * x.size(0) * N * K):
+        st = _lib.lib.ck_moe_grouped_linear_scatter(x.data_ptr(), w.data_ptr(), mtile_off.data_ptr(), row_map.data_ptr(),
+                                                    y.data_ptr(), E, x.size(0), N, K, int(trans_w),
+                                                    _lib.dtype_code(x.dtype), status.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_grouped_linear_scatter")
+
+
+def _gather_rows_scaled_impl(src: torch.Tensor, dst: torch.Tensor, idx: torch.Tensor, coeff: torch.Tensor | None,
+                             fan_out: int) -> None:
+    _lib.require_cuda(src, dst, idx)
+    with torch.cuda.device(src.device), _lib.launch("gather_rows_scaled"):
+        st = _lib.lib.ck_moe_gather_rows_scaled(src.data_ptr(), dst.data_ptr(), idx.data_ptr(), _lib.ptr(coeff),
+                                                dst.size(0), fan_out, src.size(1), _lib.dtype_code(src.dtype),
+                                                _lib.stream_ptr())
+    _lib.check(st, "ck_moe_gather_rows_scaled")
+
+
+def _combine_rows_impl(src: torch.Tensor, pos: torch.Tensor, w: torch.Tensor | None, out: torch.Tensor, k: int) -> None:
+    _lib.require_cuda(src, pos, out)
+    with torch.cuda.device(src.device), _lib.launch("combine_rows"):
+        st = _lib.lib.ck_moe_combine_rows(src.data_ptr(), pos.data_ptr(), _lib.ptr(w), out.data_ptr(), out.size(0), k,
+                                          src.size(1), _lib.dtype_code(src.dtype), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_combine_rows")
+
+
+def _row_dots_impl(a: torch.Tensor, pos: torch.Tensor, b: torch.Tensor, dots: torch.Tensor, k: int) -> None:
+    _lib.require_cuda(a, pos, b, dots)
+    with torch.cuda.device(a.device), _lib.launch("row_dots"):
+        st = _lib.lib.ck_moe_row_dots(a.data_ptr(), pos.data_ptr(), b.data_ptr(), dots.data_ptr(), dots.numel(), k,
+                                      a.size(1), _lib.dtype_code(a.dtype), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_row_dots")
+
+
 gather_rows = _make_op("moe_gather_rows", _gather_rows_impl, {"dst"})
 cast_from_f32 = _make_op("cast_from_f32", _cast_from_f32_impl, {"dst"})
 up_act_fwd = _make_op("moe_up_act_fwd", _up_act_fwd_impl, {"act", "h"})
@@ -142,6 +182,10 @@ dgrad_down = _make_op("moe_dgrad_down", _dgrad_down_impl, {"dh", "dgates"})
 dgrad_up = _make_op("moe_dgrad_up", _dgrad_up_impl, {"dx32"})
 wgrad = _make_op("moe_wgrad", _wgrad_impl, {"dw"})
 grouped_linear = _make_op("moe_grouped_linear", _grouped_linear_impl, {"y"})
+grouped_linear_scatter = _make_op("moe_grouped_linear_scatter", _grouped_linear_scatter_impl, {"y"})
+gather_rows_scaled = _make_op("moe_gather_rows_scaled", _gather_rows_scaled_impl, {"dst"})
+combine_rows = _make_op("moe_combine_rows", _combine_rows_impl, {"out"})
+row_dots = _make_op("moe_row_dots", _row_dots_impl, {"dots"})
 
 
 def _from_f32(src32: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
@@ -216,6 +260,62 @@ class _FusedExperts(torch.autograd.Function):
         if need_rw:
             d_rw = dgates.view(T, top_k).to(dt)
         return dx, d_rw, d_wfc, d_wproj, None, None, None, None, None
+
+
+class _ExpertShard(torch.autograd.Function):
+    """Expert computation on rows that already belong to this rank's experts (expert parallelism): every row is
+    computed once, un-weighted, and returned in the caller's row order (scatter store, no fp32 staging)."""
+
+    @staticmethod
+    def forward(ctx, rows, w_fc, w_proj, row_map, mtile_off, padded_off, act_kind: int):
+        n, H = rows.shape
+        two_i = w_fc.size(1)
+        cap = row_map.numel()
+        dev, dt = rows.device, rows.dtype
+        need_grad = any(ctx.needs_input_grad[:3])
+        rows = rows.contiguous()
+        xg = torch.empty(cap, H, dtype=dt, device=dev)
+        gather_rows(rows, xg, row_map, padded_off, 1)
+        act = torch.empty(cap, two_i // 2, dtype=dt, device=dev)
+        h = torch.empty(cap, two_i, dtype=dt, device=dev) if need_grad else None
+        up_act_fwd(xg, w_fc, None, row_map, mtile_off, act, h, act_kind)
+        y = torch.empty(n, H, dtype=dt, device=dev)
+        grouped_linear_scatter(act, w_proj, mtile_off, row_map, y, False)
+        if need_grad:
+            ctx.save_for_backward(xg, act, h, w_fc, w_proj, row_map, mtile_off, padded_off)
+        ctx.act_kind = act_kind
+        ctx.rows = n
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xg, act, h, w_fc, w_proj, row_map, mtile_off, padded_off = ctx.saved_tensors
+        E, two_i, H = w_fc.shape
+        cap = row_map.numel()
+        dev, dt = dy.device, xg.dtype
+        dy = dy.contiguous().to(dt)
+        dyg = torch.empty(cap, H, dtype=dt, device=dev)
+        gather_rows(dy, dyg, row_map, padded_off, 1)
+        dh = torch.empty(cap, two_i, dtype=dt, device=dev)
+        dgrad_down(dyg, w_proj, h, None, row_map, mtile_off, dh, None, ctx.act_kind)
+        d_rows = d_wfc = d_wproj = None
+        if ctx.needs_input_grad[2]:
+            d_wproj = torch.empty_like(w_proj)
+            wgrad(dyg, act, padded_off, d_wproj)
+        if ctx.needs_input_grad[0]:
+            d_rows = torch.empty(ctx.rows, H, dtype=dt, device=dev)
+            grouped_linear_scatter(dh, w_fc, mtile_off, row_map, d_rows, True)
+        if ctx.needs_input_grad[1]:
+            d_wfc = torch.empty_like(w_fc)
+            wgrad(dh, xg, padded_off, d_wfc)
+        return d_rows, d_wfc, d_wproj, None, None, None, None
+
+
+def expert_shard(rows: torch.Tensor, local_expert_ids: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor,
+                 act_kind: int = _lib.CK_ACT_SWIGLU) -> torch.Tensor:
+    """y[i] = W_proj[e_i] @ act(W_fc[e_i] @ rows[i]) for rows already dispatched to this rank's experts."""
+    r = route(local_expert_ids.reshape(-1), w_fc.size(0))
+    return _ExpertShard.apply(rows, w_fc.contiguous(), w_proj.contiguous(), r.row_map, r.mtile_off, r.padded_off, act_kind)
 
 
 def fused_experts(x: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor, w_fc: torch.Tensor,

@@ -188,6 +188,27 @@ CK_API int ck_moe_grouped_linear(const void *x, const void *w, const int32_t *mt
                           int64_t cap, int N, int K, int trans_w, int dtype, int32_t *dev_status,
                           void *stream);
 
+/* same as ck_moe_grouped_linear, but row p of the result is stored at y[row_map[p], :] (pad rows dropped):
+ * scatter2scatter with y_grouped=False and FAN_OUT=1 (ops.py:31-78) -- used by expert-parallel shards, where
+ * every routed row is produced exactly once and travels back before the combine. */
+CK_API int ck_moe_grouped_linear_scatter(const void *x, const void *w, const int32_t *mtile_off,
+                                         const int32_t *row_map, void *y, int E, int64_t cap, int N, int K,
+                                         int trans_w, int dtype, int32_t *dev_status, void *stream);
+
+/* ---- row permutations around the expert-parallel exchange ---------------------------------------
+ * ck_moe_gather_rows_scaled: dst[j, :] = c * src[idx[j] / fan_out, :], c = coeff ? coeff[idx[j]] : 1, zeros
+ *   where idx[j] < 0 -- `group` with its optional coefficient (ops.py:108-140, kernels.py:225-280).
+ * ck_moe_combine_rows: out[t, :] = sum_{j<k} (w ? w[t*k+j] : 1) * src[pos[t*k+j], :] -- the bmm(gates, out)
+ *   combine (ops.py:170-174) and the sum(-2) of the input grad (ops.py:276), deterministic, fp32 accumulate.
+ * ck_moe_row_dots: dots[f] = <a[pos[f], :], b[f / k, :]> -- d_gates = bmm(output_expanded, grad_out) (ops.py:214).
+ * cols must be a multiple of 16 bytes of elements; pointers 16-byte aligned. */
+CK_API int ck_moe_gather_rows_scaled(const void *src, void *dst, const int32_t *idx, const void *coeff,
+                                     int64_t n_rows, int fan_out, int64_t cols, int dtype, void *stream);
+CK_API int ck_moe_combine_rows(const void *src, const int32_t *pos, const void *w, void *out, int64_t tokens,
+                               int k, int64_t cols, int dtype, void *stream);
+CK_API int ck_moe_row_dots(const void *a, const int32_t *pos, const void *b, void *dots, int64_t n, int k,
+                           int64_t cols, int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

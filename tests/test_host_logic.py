@@ -152,5 +152,9 @@ def test_module_traces_under_fullgraph_compile_without_graph_breaks():
         y, _ = mod.cuda()(x.cuda())
         assert y.shape == (16, 64)
     else:
-        with pytest.raises(RuntimeError, match="CUDA tensors only"):
-            mod(x)
+        try:
+            with pytest.raises(RuntimeError, match="CUDA tensors only"):
+                mod(x)
+        finally:
+            # the refusal interrupts the traced graph inside route()'s no_grad region: restore grad mode
+            torch.set_grad_enabled(True)
