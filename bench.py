@@ -43,7 +43,8 @@ WORKLOADS = {
 }
 METRIC = "moe_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
-GEMM_KERNELS = ("up_act_fwd", "down_combine_fwd", "dgrad_down", "dgrad_up", "wgrad", "grouped_linear")
+GEMM_KERNELS = ("up_act_fwd", "down_combine_fwd", "dgrad_down", "dgrad_up", "wgrad", "grouped_linear",
+                "grouped_linear_scatter")
 
 
 def measured_peaks() -> dict:
@@ -329,6 +330,7 @@ def gpu_arm(args, w: dict) -> dict | None:
     algo = {  # algorithmic FLOPs per launch: 2 * rows * N * K with un-padded rows
         "up_act_fwd": 2.0 * R * (2 * I) * H, "down_combine_fwd": 2.0 * R * H * I, "dgrad_down": 2.0 * R * H * I,
         "dgrad_up": 2.0 * R * (2 * I) * H, "wgrad": 2.0 * R * H * I * 1.5,  # two launches per step: (H x I) and (2I x H)
+        "grouped_linear_scatter": 2.0 * R * H * I * 1.5,  # expert-parallel shards: down (H x I) and dgrad-up (2I x H)
     }
     kernels = {}
     for name, ts in per_kernel.items():
@@ -371,15 +373,104 @@ def gpu_arm(args, w: dict) -> dict | None:
     return line
 
 
+# ---------------------------------------------------------------------------------------------------
+# HBM-bound pieces: routing (count + scan + stable scatter) and stand-alone SwiGLU
+# ---------------------------------------------------------------------------------------------------
+def _time_each(fn, steps: int, warmup: int, flush: torch.Tensor | None) -> list[float]:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(steps):
+        if flush is not None:
+            flush.add_(1)  # 512 MB written: evicts the 126 MB L2 between timed launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return out
+
+
+def micro_arm(args, which: str) -> dict:
+    import numpy as np
+
+    import ck_oracle as orc
+    import cute_kernels as ck
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    peaks = measured_peaks()
+    peak = float(peaks["hbm_gbs"])
+    sampler = ClockSampler(0)
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    results = {}
+    if which == "c2":
+        n, E = 1 << 24, 64
+        for dist_name in ("uniform", "zipf"):
+            ids = torch.from_numpy(orc.gen_ids(0, n, E, dist_name, np.int32)).to(dev)
+            t_route = _time_each(lambda: ck.route(ids, E, with_tile_metadata=False), args.steps, args.warmup, flush)
+            t_count = _time_each(lambda: ck.continuous_count_cute(ids, E), args.steps, args.warmup, flush)
+            results[dist_name] = dict(
+                route_ms=statistics.median(t_route), route_gbs=12.0 * n / (statistics.median(t_route) * 1e-3) / 1e9,
+                count_ms=statistics.median(t_count), count_gbs=4.0 * n / (statistics.median(t_count) * 1e-3) / 1e9)
+        sampler.mark_begin(); sampler.mark_end()
+        head = results["uniform"]
+        line = dict(metric="route_hbm_gb_per_s", value=head["route_gbs"], unit="GB/s", ms_per_step=head["route_ms"],
+                    config=dict(workload="c2_count_scan_stable_scatter", n_ids=n, experts=E, ids_dtype="int32",
+                                l2_policy="l2_flushed_between_launches", draws=["uniform", "zipf(1.2)"]),
+                    roofline=dict(bound="hbm", kernel="route_hist + route_scan + route_scatter (3 launches)",
+                                  achieved=head["route_gbs"], peak=peak, unit="GB/s", frac=head["route_gbs"] / peak,
+                                  traffic=None, algorithmic_bytes=12 * n, peak_source=f"hbm_gbs of {peaks['source']}"),
+                    detail=results)
+    else:
+        rows, cols = 16384, 14336
+        g = torch.Generator(device=dev).manual_seed(0)
+        gate = torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32).bfloat16().requires_grad_()
+        up = torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32).bfloat16().requires_grad_()
+        dy = torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32).bfloat16()
+        nel = rows * cols
+        with torch.no_grad():
+            t_fwd = _time_each(lambda: ck.swiglu_cute(gate, up), args.steps, args.warmup, None)
+        out = ck.swiglu_cute(gate, up)
+
+        def bwd():
+            gate.grad = None
+            up.grad = None
+            out.backward(dy, retain_graph=True)
+
+        t_bwd = _time_each(bwd, args.steps, args.warmup, None)
+        sampler.mark_begin(); sampler.mark_end()
+        f_ms, b_ms = statistics.median(t_fwd), statistics.median(t_bwd)
+        results = dict(fwd_ms=f_ms, fwd_gbs=6.0 * nel / (f_ms * 1e-3) / 1e9, bwd_ms=b_ms, bwd_gbs=10.0 * nel / (b_ms * 1e-3) / 1e9)
+        both = 16.0 * nel / ((f_ms + b_ms) * 1e-3) / 1e9
+        line = dict(metric="swiglu_fwd_bwd_hbm_gb_per_s", value=both, unit="GB/s", ms_per_step=f_ms + b_ms,
+                    config=dict(workload="c3_swiglu_fwd_bwd", shape=[rows, cols], l2_policy="inputs_exceed_l2"),
+                    roofline=dict(bound="hbm", kernel="swiglu_bwd_vec_kernel<bf16>", achieved=results["bwd_gbs"], peak=peak,
+                                  unit="GB/s", frac=results["bwd_gbs"] / peak, traffic=None, algorithmic_bytes=10 * nel,
+                                  peak_source=f"hbm_gbs of {peaks['source']}"),
+                    detail=results)
+    ck.check_device_status()
+    line.update(n_gpus=1, steps=args.steps, warmup=args.warmup, higher_is_better=True, scaling="weak", vs_baseline=None,
+                dtype="int32" if which == "c2" else "bf16", data="synthetic", clocks=sampler.stop(), gpu_launches=None)
+    return line
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c2", "c3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.workload in ("c2", "c3"):
+        if args.warmup < 3:
+            args.warmup = 3
+        print(json.dumps(micro_arm(args, args.workload)))
+        return
     w = WORKLOADS[args.workload]
 
     if args.impl == "reference":

@@ -6,7 +6,9 @@
 // The stable scatter gives every warp a contiguous slice of the ids; a slice's position in the
 // output is (exclusive scan over experts) + (exclusive scan over earlier warps for that expert) +
 // (running count inside the warp), which is exactly the order torch.sort(stable=True) produces.
+#include <algorithm>
 #include <mutex>
+#include <type_traits>
 
 #include "ck_common.cuh"
 
@@ -22,83 +24,143 @@ __device__ __forceinline__ unsigned lanemask_lt() {
     return m;
 }
 
+// Peer mask of the lanes holding the same key, built from one ballot per key bit.  __match_any_sync
+// gives the same mask but its cost grows with the number of distinct keys in the warp (about 26 of 32
+// lanes differ for uniform ids over 64 experts); log2(range) ballots cost the same for every input.
+// Lanes with key < 0 (out of range / past the end) get 0.
+__device__ __forceinline__ unsigned match_key_bits(int key, int nbits) {
+    unsigned m = __ballot_sync(0xffffffffu, key >= 0);
+    for (int b = 0; b < nbits; ++b) {
+        const bool bit = (key >> b) & 1;
+        const unsigned bal = __ballot_sync(0xffffffffu, bit);
+        m &= bit ? bal : ~bal;
+    }
+    return key >= 0 ? m : 0u;
+}
+
+template <typename IdT>
+__device__ __forceinline__ int load_key(const IdT *__restrict__ ids, int64_t idx, int64_t end, int range, bool &bad) {
+    if (idx >= end) return -1;
+    const IdT v = ids[idx];
+    using U = typename std::make_unsigned<IdT>::type;
+    if (U(v) < U(range)) return int(v);
+    bad = true;
+    return -1;
+}
+
+constexpr int kLanePrivateMax = 128;  // largest id range that gets a per-lane histogram (16 KiB per warp)
+
 // ------------------------------------------------------------------------------------------------
 // continuous_count: counts[v] += #ids == v.  counts is zeroed by the host wrapper beforehand.
+// Small ranges (the MoE case) count into per-lane histograms laid out [value][lane]: bank == lane, so
+// the read-modify-write needs neither atomics nor conflict replays; larger ranges aggregate equal ids in
+// the warp first and issue one shared-memory atomic per distinct id.
 // ------------------------------------------------------------------------------------------------
-template <typename IdT>
-__global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids, int64_t n, int size,
+template <typename IdT, bool LANE_PRIVATE>
+__global__ void __launch_bounds__(256) count_kernel(const IdT *__restrict__ ids, int64_t n, int size, int nbits,
                                                    uint32_t *__restrict__ counts) {
     extern __shared__ uint32_t hist[];
-    for (int i = threadIdx.x; i < size; i += blockDim.x) hist[i] = 0;
-    __syncthreads();
-
     const int lane = threadIdx.x & 31;
+    const int wib = threadIdx.x >> 5;
     const int64_t warp_id = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
     const int64_t nchunks = (n + kStep - 1) / kStep;
+    bool bad = false;
 
-    for (int64_t c = warp_id; c < nchunks; c += nwarps) {
-        const int64_t b = c * kStep + lane;
-        int key[4];
+    if constexpr (LANE_PRIVATE) {
+        uint32_t *wh = hist + wib * size * 32;  // [size][32]
+        for (int i = lane; i < size * 32; i += 32) wh[i] = 0;
+        __syncwarp();
+        for (int64_t c = warp_id; c < nchunks; c += nwarps) {
+            const int64_t b = c * kStep + lane;
+            int key[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int64_t idx = b + 32 * j;
-            long long v = -1;
-            if (idx < n) v = (long long)ids[idx];
-            key[j] = (v >= 0 && v < size) ? int(v) : -1;
-        }
+            for (int j = 0; j < 4; ++j) key[j] = load_key(ids, b + 32 * j, n, size, bad);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const unsigned m = __match_any_sync(0xffffffffu, key[j]);
-            if (key[j] >= 0 && lane == __ffs(m) - 1) atomicAdd(&hist[key[j]], __popc(m));
+            for (int j = 0; j < 4; ++j)
+                if (key[j] >= 0) wh[key[j] * 32 + lane] += 1;
         }
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < size; i += blockDim.x) {
-        const uint32_t v = hist[i];
-        if (v) atomicAdd(&counts[i], v);
+        __syncwarp();
+        for (int v = 0; v < size; ++v) {
+            uint32_t c = wh[v * 32 + lane];
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
+            if (lane == 0 && c) atomicAdd(&counts[v], c);
+        }
+    } else {
+        for (int i = threadIdx.x; i < size; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        for (int64_t c = warp_id; c < nchunks; c += nwarps) {
+            const int64_t b = c * kStep + lane;
+            int key[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) key[j] = load_key(ids, b + 32 * j, n, size, bad);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const unsigned m = match_key_bits(key[j], nbits);
+                if (key[j] >= 0 && lane == __ffs(m) - 1) atomicAdd(&hist[key[j]], __popc(m));
+            }
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < size; i += blockDim.x) {
+            const uint32_t v = hist[i];
+            if (v) atomicAdd(&counts[i], v);
+        }
     }
 }
 
 // ------------------------------------------------------------------------------------------------
 // route pass 1: per-warp histogram of a contiguous slice of ids -> whist[w][E]
 // ------------------------------------------------------------------------------------------------
-template <typename IdT>
+template <typename IdT, bool LANE_PRIVATE>
 __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
-    route_hist_kernel(const IdT *__restrict__ ids, int64_t n, int E, int64_t slice, int W,
+    route_hist_kernel(const IdT *__restrict__ ids, int64_t n, int E, int nbits, int64_t slice, int W,
                       int32_t *__restrict__ whist, int32_t *dev_status) {
     extern __shared__ int32_t smem_i[];
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
     const int w = blockIdx.x * kRouteWarpsPerBlock + wib;
-    int32_t *wh = smem_i + wib * E;
     if (w >= W) return;  // whole warp leaves together (no block-level sync below)
-    for (int e = lane; e < E; e += 32) wh[e] = 0;
-    __syncwarp();
-
     const int64_t begin = int64_t(w) * slice;
     const int64_t end = min(begin + slice, n);
     bool bad = false;
-    for (int64_t off = begin; off < end; off += kStep) {
-        int key[4];
+
+    if constexpr (LANE_PRIVATE) {
+        int32_t *wh = smem_i + wib * E * 32;  // [E][32]
+        for (int i = lane; i < E * 32; i += 32) wh[i] = 0;
+        __syncwarp();
+        for (int64_t off = begin; off < end; off += kStep) {
+            int key[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int64_t idx = off + 32 * j + lane;
-            long long v = -1;
-            bool have = idx < end;
-            if (have) v = (long long)ids[idx];
-            const bool ok = (v >= 0 && v < E);
-            bad |= (have && !ok);
-            key[j] = ok ? int(v) : -1;
-        }
+            for (int j = 0; j < 4; ++j) key[j] = load_key(ids, off + 32 * j + lane, end, E, bad);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const unsigned m = __match_any_sync(0xffffffffu, key[j]);
-            if (key[j] >= 0 && lane == __ffs(m) - 1) wh[key[j]] += __popc(m);
-            __syncwarp();
+            for (int j = 0; j < 4; ++j)
+                if (key[j] >= 0) wh[key[j] * 32 + lane] += 1;
         }
+        __syncwarp();
+        for (int e = 0; e < E; ++e) {
+            int c = wh[e * 32 + lane];
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
+            if (lane == 0) whist[int64_t(w) * E + e] = c;
+        }
+    } else {
+        int32_t *wh = smem_i + wib * E;
+        for (int e = lane; e < E; e += 32) wh[e] = 0;
+        __syncwarp();
+        for (int64_t off = begin; off < end; off += kStep) {
+            int key[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) key[j] = load_key(ids, off + 32 * j + lane, end, E, bad);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const unsigned m = match_key_bits(key[j], nbits);
+                if (key[j] >= 0 && lane == __ffs(m) - 1) wh[key[j]] += __popc(m);
+                __syncwarp();
+            }
+        }
+        for (int e = lane; e < E; e += 32) whist[int64_t(w) * E + e] = wh[e];
     }
-    for (int e = lane; e < E; e += 32) whist[int64_t(w) * E + e] = wh[e];
     if (__any_sync(0xffffffffu, bad) && lane == 0 && dev_status) atomicOr(dev_status, CK_DEV_RANGE);
 }
 
@@ -190,7 +252,7 @@ __global__ void __launch_bounds__(1024)
 // ------------------------------------------------------------------------------------------------
 template <typename IdT>
 __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
-    route_scatter_kernel(const IdT *__restrict__ ids, int64_t n, int E, int64_t slice, int W,
+    route_scatter_kernel(const IdT *__restrict__ ids, int64_t n, int E, int nbits, int64_t slice, int W,
                          const int32_t *__restrict__ whist, const int32_t *__restrict__ excl_off,
                          const int32_t *__restrict__ padded_off, int32_t *__restrict__ sorted_idx,
                          int32_t *__restrict__ sorted_expert, int32_t *__restrict__ row_map) {
@@ -209,19 +271,15 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
     const unsigned lt = lanemask_lt();
     const int64_t begin = int64_t(w) * slice;
     const int64_t end = min(begin + slice, n);
+    bool bad = false;
     for (int64_t off = begin; off < end; off += kStep) {
         int key[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int64_t idx = off + 32 * j + lane;
-            long long v = -1;
-            if (idx < end) v = (long long)ids[idx];
-            key[j] = (v >= 0 && v < E) ? int(v) : -1;
-        }
+        for (int j = 0; j < 4; ++j) key[j] = load_key(ids, off + 32 * j + lane, end, E, bad);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int k = key[j];
-            const unsigned m = __match_any_sync(0xffffffffu, k);
+            const unsigned m = match_key_bits(k, nbits);
             int b = 0;
             if (k >= 0) b = wbase[k];
             __syncwarp();
@@ -263,22 +321,29 @@ extern "C" int ck_continuous_count(const void *ids, int ids_is_i64, int64_t n, i
     if (n > 0 && ids == nullptr) return CK_ERR_SHAPE;
     CK_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(uint32_t) * size, stream));
     if (n == 0) return CK_OK;
-    const int threads = 512;
-    const size_t smem = sizeof(uint32_t) * size;
+    const int threads = 256;
+    const bool lane_private = size <= kLanePrivateMax;
+    const int nbits = size > 1 ? 32 - __builtin_clz(unsigned(size - 1)) : 0;
+    const size_t smem = lane_private ? sizeof(uint32_t) * size * 32 * (threads / 32) : sizeof(uint32_t) * size;
     const int64_t nchunks = ceil_div64(n, kStep);
-    const int blocks_per_sm = smem > 48 * 1024 ? 3 : 4;
+    int blocks_per_sm = 8;
+    if (smem > 0) blocks_per_sm = int(std::min<size_t>(8, (200 * 1024) / smem));
+    if (blocks_per_sm < 1) blocks_per_sm = 1;
     int64_t grid = ceil_div64(nchunks, threads / 32);
     const int64_t cap = int64_t(num_sms()) * blocks_per_sm;
     if (grid > cap) grid = cap;
+#define CK_LAUNCH_COUNT(IDT, LP)                                                                                          \
+    do {                                                                                                                  \
+        if (smem > 48 * 1024)                                                                                             \
+            CK_CUDA_TRY(cudaFuncSetAttribute(count_kernel<IDT, LP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        count_kernel<IDT, LP><<<dim3((unsigned)grid), threads, smem, stream>>>((const IDT *)ids, n, size, nbits, counts);    \
+    } while (0)
     if (ids_is_i64) {
-        if (smem > 48 * 1024)
-            CK_CUDA_TRY(cudaFuncSetAttribute(count_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        count_kernel<int64_t><<<dim3((unsigned)grid), threads, smem, stream>>>((const int64_t *)ids, n, size, counts);
+        if (lane_private) CK_LAUNCH_COUNT(int64_t, true); else CK_LAUNCH_COUNT(int64_t, false);
     } else {
-        if (smem > 48 * 1024)
-            CK_CUDA_TRY(cudaFuncSetAttribute(count_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        count_kernel<int32_t><<<dim3((unsigned)grid), threads, smem, stream>>>((const int32_t *)ids, n, size, counts);
+        if (lane_private) CK_LAUNCH_COUNT(int32_t, true); else CK_LAUNCH_COUNT(int32_t, false);
     }
+#undef CK_LAUNCH_COUNT
     CK_LAUNCH_CHECK("count_kernel");
     return CK_OK;
 }
@@ -319,12 +384,22 @@ extern "C" int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint3
 
     const int threads = kRouteWarpsPerBlock * 32;
     const int blocks = (W + kRouteWarpsPerBlock - 1) / kRouteWarpsPerBlock;
+    const int nbits = E > 1 ? 32 - __builtin_clz(unsigned(E - 1)) : 0;
     if (W > 0) {
-        const size_t smem = sizeof(int32_t) * kRouteWarpsPerBlock * E;
-        if (ids_is_i64)
-            route_hist_kernel<int64_t><<<blocks, threads, smem, stream>>>((const int64_t *)ids, n, E, slice, W, whist, dev_status);
-        else
-            route_hist_kernel<int32_t><<<blocks, threads, smem, stream>>>((const int32_t *)ids, n, E, slice, W, whist, dev_status);
+        const bool lane_private = E <= kLanePrivateMax;
+        const size_t smem = sizeof(int32_t) * kRouteWarpsPerBlock * E * (lane_private ? 32 : 1);
+#define CK_LAUNCH_HIST(IDT, LP)                                                                                          \
+    do {                                                                                                                 \
+        if (smem > 48 * 1024)                                                                                            \
+            CK_CUDA_TRY(cudaFuncSetAttribute(route_hist_kernel<IDT, LP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        route_hist_kernel<IDT, LP><<<blocks, threads, smem, stream>>>((const IDT *)ids, n, E, nbits, slice, W, whist, dev_status); \
+    } while (0)
+        if (ids_is_i64) {
+            if (lane_private) CK_LAUNCH_HIST(int64_t, true); else CK_LAUNCH_HIST(int64_t, false);
+        } else {
+            if (lane_private) CK_LAUNCH_HIST(int32_t, true); else CK_LAUNCH_HIST(int32_t, false);
+        }
+#undef CK_LAUNCH_HIST
         CK_LAUNCH_CHECK("route_hist_kernel");
     }
     route_scan_kernel<<<E, 1024, 0, stream>>>(whist, W, E, counts, excl_off, end_off, padded_off, mtile_off, ticket);
@@ -332,11 +407,11 @@ extern "C" int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint3
     if (W > 0) {
         const size_t smem = sizeof(int32_t) * (kRouteWarpsPerBlock + 1) * E;
         if (ids_is_i64)
-            route_scatter_kernel<int64_t><<<blocks, threads, smem, stream>>>((const int64_t *)ids, n, E, slice, W, whist,
+            route_scatter_kernel<int64_t><<<blocks, threads, smem, stream>>>((const int64_t *)ids, n, E, nbits, slice, W, whist,
                                                                             excl_off, padded_off, sorted_idx,
                                                                             sorted_expert, row_map);
         else
-            route_scatter_kernel<int32_t><<<blocks, threads, smem, stream>>>((const int32_t *)ids, n, E, slice, W, whist,
+            route_scatter_kernel<int32_t><<<blocks, threads, smem, stream>>>((const int32_t *)ids, n, E, nbits, slice, W, whist,
                                                                             excl_off, padded_off, sorted_idx,
                                                                             sorted_expert, row_map);
         CK_LAUNCH_CHECK("route_scatter_kernel");

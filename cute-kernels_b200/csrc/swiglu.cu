@@ -21,42 +21,125 @@ __device__ __forceinline__ void stg16(T *p, const Vec16<T> &v) {
     *reinterpret_cast<int4 *>(p) = *reinterpret_cast<const int4 *>(&v);
 }
 
-__device__ __forceinline__ float swiglu_f(float g, float u) { return u * g * sigmoid_clamped(g); }
+// ---- 16 bytes <-> fp32 lanes with paired conversions (one instruction per two 16-bit elements) ----
+template <typename T>
+struct Lanes;  // N fp32 values per 16-byte vector
+template <>
+struct Lanes<float> {
+    static constexpr int N = 4;
+    __device__ __forceinline__ static void unpack(const int4 &r, float (&v)[4]) {
+        v[0] = __int_as_float(r.x); v[1] = __int_as_float(r.y); v[2] = __int_as_float(r.z); v[3] = __int_as_float(r.w);
+    }
+    __device__ __forceinline__ static int4 pack(const float (&v)[4]) {
+        return make_int4(__float_as_int(v[0]), __float_as_int(v[1]), __float_as_int(v[2]), __float_as_int(v[3]));
+    }
+};
+template <>
+struct Lanes<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ __forceinline__ static void unpack(const int4 &r, float (&v)[8]) {
+        const uint32_t w[4] = {uint32_t(r.x), uint32_t(r.y), uint32_t(r.z), uint32_t(r.w)};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // bf16 is the upper half of an fp32
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    __device__ __forceinline__ static int4 pack(const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        return make_int4(int(w[0]), int(w[1]), int(w[2]), int(w[3]));
+    }
+};
+template <>
+struct Lanes<__half> {
+    static constexpr int N = 8;
+    __device__ __forceinline__ static void unpack(const int4 &r, float (&v)[8]) {
+        const uint32_t w[4] = {uint32_t(r.x), uint32_t(r.y), uint32_t(r.z), uint32_t(r.w)};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+    __device__ __forceinline__ static int4 pack(const float (&v)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        return make_int4(int(w[0]), int(w[1]), int(w[2]), int(w[3]));
+    }
+};
+
+// sigmoid for the streaming kernels.  fp32 tensors keep the clamped expf form of the reference
+// (include/activations.h:9-22).  For 16-bit tensors a B200 at full HBM rate has to retire about one
+// element per SM per clock; two special-function ops per element (ex2 + rcp) would saturate the SFU
+// before the memory system, so sigmoid(x) = 0.5 + 0.5 * tanh(0.5 x) with the one-instruction tanh.approx
+// is used: its 2^-11 relative error is a few percent of a bf16 ulp and a quarter of an fp16 ulp.
+template <typename T>
+__device__ __forceinline__ float sigmoid_stream(float x) {
+    if constexpr (sizeof(T) == 4) {
+        return sigmoid_clamped(x);
+    } else {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+        return fmaf(t, 0.5f, 0.5f);
+    }
+}
+template <typename T>
+__device__ __forceinline__ float swiglu_f(float g, float u) { return u * (g * sigmoid_stream<T>(g)); }
+template <typename T>
 __device__ __forceinline__ void swiglu_b(float g, float u, float dy, float &dg, float &du) {
-    const float s = sigmoid_clamped(g);
+    const float s = sigmoid_stream<T>(g);
     const float silu = g * s;
-    dg = dy * u * (s + silu * (1.0f - s));
+    dg = (dy * u) * fmaf(silu, 1.0f - s, s);
     du = dy * silu;
 }
 
-// vectors are indexed v in [0, rows * vpr); vpr = cols / VEC
-template <typename T>
+// vectors are indexed v in [0, rows * vpr); vpr = cols / VEC.  CONTIG: one row, no index division.
+template <typename T, bool CONTIG>
 __global__ void __launch_bounds__(kEwThreads)
     swiglu_fwd_vec_kernel(const T *__restrict__ gate, const T *__restrict__ up, T *__restrict__ out, int64_t nvec,
                           int64_t vpr, int64_t in_stride, int64_t out_stride) {
-    constexpr int VEC = Vec16<T>::N;
+    constexpr int VEC = Lanes<T>::N;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t v0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * kEwUnroll) {
-        Vec16<T> g[kEwUnroll], u[kEwUnroll];
+        int4 g[kEwUnroll], u[kEwUnroll];
         int64_t oo[kEwUnroll];
 #pragma unroll
         for (int j = 0; j < kEwUnroll; ++j) {
             const int64_t v = v0 + j * stride;
             if (v < nvec) {
-                const int64_t r = v / vpr, c = (v - r * vpr) * VEC;
-                g[j] = ldg16(gate + r * in_stride + c);
-                u[j] = ldg16(up + r * in_stride + c);
-                oo[j] = r * out_stride + c;
+                int64_t io;
+                if constexpr (CONTIG) {
+                    io = v * VEC;
+                    oo[j] = io;
+                } else {
+                    const int64_t r = v / vpr, c = (v - r * vpr) * VEC;
+                    io = r * in_stride + c;
+                    oo[j] = r * out_stride + c;
+                }
+                g[j] = __ldg(reinterpret_cast<const int4 *>(gate + io));
+                u[j] = __ldg(reinterpret_cast<const int4 *>(up + io));
             }
         }
 #pragma unroll
         for (int j = 0; j < kEwUnroll; ++j) {
             const int64_t v = v0 + j * stride;
             if (v < nvec) {
-                Vec16<T> o;
+                float gf[VEC], uf[VEC], of[VEC];
+                Lanes<T>::unpack(g[j], gf);
+                Lanes<T>::unpack(u[j], uf);
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) o.v[i] = DT<T>::down(swiglu_f(DT<T>::up(g[j].v[i]), DT<T>::up(u[j].v[i])));
-                stg16(out + oo[j], o);
+                for (int i = 0; i < VEC; ++i) of[i] = swiglu_f<T>(gf[i], uf[i]);
+                *reinterpret_cast<int4 *>(out + oo[j]) = Lanes<T>::pack(of);
             }
         }
     }
@@ -69,46 +152,51 @@ __global__ void __launch_bounds__(kEwThreads)
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         const int64_t r = i / cols, c = i - r * cols;
-        out[r * out_stride + c] = DT<T>::down(swiglu_f(DT<T>::up(gate[r * in_stride + c]), DT<T>::up(up[r * in_stride + c])));
+        out[r * out_stride + c] = DT<T>::down(swiglu_f<T>(DT<T>::up(gate[r * in_stride + c]), DT<T>::up(up[r * in_stride + c])));
     }
 }
 
-template <typename T>
+template <typename T, bool CONTIG>
 __global__ void __launch_bounds__(kEwThreads)
     swiglu_bwd_vec_kernel(const T *__restrict__ gate, const T *__restrict__ up, const T *__restrict__ dy,
                           T *__restrict__ dgate, T *__restrict__ dup, int64_t nvec, int64_t vpr, int64_t in_stride,
                           int64_t dy_stride, int64_t grad_stride) {
-    constexpr int VEC = Vec16<T>::N;
+    constexpr int VEC = Lanes<T>::N;
     constexpr int U = 2;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t v0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * U) {
-        Vec16<T> g[U], u[U], d[U];
+        int4 g[U], u[U], d[U];
         int64_t oo[U];
 #pragma unroll
         for (int j = 0; j < U; ++j) {
             const int64_t v = v0 + j * stride;
             if (v < nvec) {
-                const int64_t r = v / vpr, c = (v - r * vpr) * VEC;
-                g[j] = ldg16(gate + r * in_stride + c);
-                u[j] = ldg16(up + r * in_stride + c);
-                d[j] = ldg16(dy + r * dy_stride + c);
-                oo[j] = r * grad_stride + c;
+                int64_t io, dyo;
+                if constexpr (CONTIG) {
+                    io = dyo = oo[j] = v * VEC;
+                } else {
+                    const int64_t r = v / vpr, c = (v - r * vpr) * VEC;
+                    io = r * in_stride + c;
+                    dyo = r * dy_stride + c;
+                    oo[j] = r * grad_stride + c;
+                }
+                g[j] = __ldg(reinterpret_cast<const int4 *>(gate + io));
+                u[j] = __ldg(reinterpret_cast<const int4 *>(up + io));
+                d[j] = __ldg(reinterpret_cast<const int4 *>(dy + dyo));
             }
         }
 #pragma unroll
         for (int j = 0; j < U; ++j) {
             const int64_t v = v0 + j * stride;
             if (v < nvec) {
-                Vec16<T> og, ou;
+                float gf[VEC], uf[VEC], df[VEC], og[VEC], ou[VEC];
+                Lanes<T>::unpack(g[j], gf);
+                Lanes<T>::unpack(u[j], uf);
+                Lanes<T>::unpack(d[j], df);
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) {
-                    float dg, du;
-                    swiglu_b(DT<T>::up(g[j].v[i]), DT<T>::up(u[j].v[i]), DT<T>::up(d[j].v[i]), dg, du);
-                    og.v[i] = DT<T>::down(dg);
-                    ou.v[i] = DT<T>::down(du);
-                }
-                stg16(dgate + oo[j], og);
-                stg16(dup + oo[j], ou);
+                for (int i = 0; i < VEC; ++i) swiglu_b<T>(gf[i], uf[i], df[i], og[i], ou[i]);
+                *reinterpret_cast<int4 *>(dgate + oo[j]) = Lanes<T>::pack(og);
+                *reinterpret_cast<int4 *>(dup + oo[j]) = Lanes<T>::pack(ou);
             }
         }
     }
@@ -123,8 +211,8 @@ __global__ void __launch_bounds__(kEwThreads)
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
         const int64_t r = i / cols, c = i - r * cols;
         float dg, du;
-        swiglu_b(DT<T>::up(gate[r * in_stride + c]), DT<T>::up(up[r * in_stride + c]), DT<T>::up(dy[r * dy_stride + c]),
-                 dg, du);
+        swiglu_b<T>(DT<T>::up(gate[r * in_stride + c]), DT<T>::up(up[r * in_stride + c]), DT<T>::up(dy[r * dy_stride + c]),
+                    dg, du);
         dgate[r * grad_stride + c] = DT<T>::down(dg);
         dup[r * grad_stride + c] = DT<T>::down(du);
     }
@@ -208,7 +296,7 @@ static int swiglu_fwd_t(const T *gate, const T *up, T *out, int64_t rows, int64_
     if (rows == 1) {
         const int64_t main = ptr_ok ? (cols / VEC) * VEC : 0;
         if (main > 0) {
-            swiglu_fwd_vec_kernel<T><<<ew_grid(main / VEC, kEwUnroll), kEwThreads, 0, stream>>>(gate, up, out, main / VEC,
+            swiglu_fwd_vec_kernel<T, true><<<ew_grid(main / VEC, kEwUnroll), kEwThreads, 0, stream>>>(gate, up, out, main / VEC,
                                                                                            main / VEC, main, main);
             CK_LAUNCH_CHECK("swiglu_fwd_vec_kernel");
         }
@@ -222,7 +310,7 @@ static int swiglu_fwd_t(const T *gate, const T *up, T *out, int64_t rows, int64_
     }
     if (ptr_ok && cols % VEC == 0 && in_stride % VEC == 0 && out_stride % VEC == 0) {
         const int64_t vpr = cols / VEC;
-        swiglu_fwd_vec_kernel<T><<<ew_grid(rows * vpr, kEwUnroll), kEwThreads, 0, stream>>>(gate, up, out, rows * vpr, vpr,
+        swiglu_fwd_vec_kernel<T, false><<<ew_grid(rows * vpr, kEwUnroll), kEwThreads, 0, stream>>>(gate, up, out, rows * vpr, vpr,
                                                                                        in_stride, out_stride);
         CK_LAUNCH_CHECK("swiglu_fwd_vec_kernel");
     } else {
@@ -246,7 +334,7 @@ static int swiglu_bwd_t(const T *gate, const T *up, const T *dy, T *dgate, T *du
     if (rows == 1) {
         const int64_t main = ptr_ok ? (cols / VEC) * VEC : 0;
         if (main > 0) {
-            swiglu_bwd_vec_kernel<T><<<ew_grid(main / VEC, 2), kEwThreads, 0, stream>>>(gate, up, dy, dgate, dup, main / VEC,
+            swiglu_bwd_vec_kernel<T, true><<<ew_grid(main / VEC, 2), kEwThreads, 0, stream>>>(gate, up, dy, dgate, dup, main / VEC,
                                                                                    main / VEC, main, main, main);
             CK_LAUNCH_CHECK("swiglu_bwd_vec_kernel");
         }
@@ -261,7 +349,7 @@ static int swiglu_bwd_t(const T *gate, const T *up, const T *dy, T *dgate, T *du
     }
     if (ptr_ok && cols % VEC == 0 && in_stride % VEC == 0 && dy_stride % VEC == 0 && grad_stride % VEC == 0) {
         const int64_t vpr = cols / VEC;
-        swiglu_bwd_vec_kernel<T><<<ew_grid(rows * vpr, 2), kEwThreads, 0, stream>>>(gate, up, dy, dgate, dup, rows * vpr, vpr,
+        swiglu_bwd_vec_kernel<T, false><<<ew_grid(rows * vpr, 2), kEwThreads, 0, stream>>>(gate, up, dy, dgate, dup, rows * vpr, vpr,
                                                                                in_stride, dy_stride, grad_stride);
         CK_LAUNCH_CHECK("swiglu_bwd_vec_kernel");
     } else {
