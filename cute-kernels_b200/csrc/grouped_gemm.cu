@@ -16,6 +16,7 @@
 // Every mbarrier wait is bounded by wall-clock time; when one runs out the CTA raises
 // CK_DEV_TIMEOUT in the caller's status word, lets in-flight copies land, frees TMEM and returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "ck_common.cuh"
 #include "sm100_ptx.cuh"
@@ -66,6 +67,7 @@ struct TileCoord {
     int n_tile;
     int k_row0;  // WGRAD: first padded row of the expert
     int k_iters;
+    bool valid;  // CTA-pair kernels: this CTA's half of the pair tile holds real rows
 };
 
 template <typename T>
@@ -80,10 +82,10 @@ struct GemmTraits {
 };
 
 template <typename T>
-__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn) {
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int mma_m = BM) {
     const uint32_t fmt = (sizeof(T) == 4) ? 2u : (DT<T>::code == CK_BF16 ? 1u : 0u);
     return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-           (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+           (uint32_t(BN >> 3) << 17) | (uint32_t(mma_m >> 4) << 24);
 }
 
 struct SmemCtl {
@@ -125,6 +127,7 @@ __device__ __forceinline__ int total_tiles(const GemmParams &p, const SmemCtl *c
 template <int MODE, int BK>
 __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, const SmemCtl *ctl, int t) {
     TileCoord c;
+    c.valid = true;
     if constexpr (MODE == MODE_WGRAD) {
         const int per_e = p.m_tiles_w * p.n_tiles;
         c.e = t / per_e;
@@ -202,6 +205,145 @@ __device__ __forceinline__ void act_bwd(int kind, float u, float g, float &a, fl
         a = u * s;
         du_m = s;
         dg_m = u * s * (1.0f - s);
+    }
+}
+
+// ---- fused tail of one 128 x 256 tile: executed by the four epilogue warps of a CTA --------------------
+template <typename T, int MODE>
+__device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoord &c, uint32_t tbase, int row_in_tile) {
+    const bool have_acc = c.k_iters > 0;
+
+    if constexpr (MODE == MODE_STORE || MODE == MODE_WGRAD) {
+        T *out;
+        bool row_ok;
+        if constexpr (MODE == MODE_WGRAD) {
+            const int m = c.m_tile * BM + row_in_tile;
+            row_ok = m < p.M;
+            out = reinterpret_cast<T *>(p.out0) + (int64_t(c.e) * p.M + m) * int64_t(p.N);
+        } else {
+            int64_t orow = int64_t(c.m_tile) * BM + row_in_tile;
+            row_ok = true;
+            if (p.row_map) {  // scatter store: padded row -> caller's row order (each row written once)
+                const int32_t src = p.row_map[orow];
+                row_ok = src >= 0;
+                orow = row_ok ? src : 0;
+            }
+            out = reinterpret_cast<T *>(p.out0) + orow * int64_t(p.N);
+        }
+        const int n0 = c.n_tile * BN;
+#pragma unroll 1
+        for (int cc = 0; cc < BN; cc += 32) {
+            uint32_t r[32];
+            if (have_acc) {
+                ptx::tmem_ld32(tbase + cc, r);
+                ptx::tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = 0u;
+            }
+            if (row_ok) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const int n = n0 + cc + g * 8;
+                    if (n < p.N) {
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+                        store8<T>(out + n, v);
+                    }
+                }
+            }
+        }
+    } else if constexpr (MODE == MODE_UP_ACT) {
+        const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
+        const int32_t src = p.row_map[prow];
+        float w = 1.0f;
+        if (p.gate_w) w = (src >= 0) ? DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]) : 0.0f;
+        T *act = reinterpret_cast<T *>(p.out0) + prow * int64_t(p.N);
+        T *h = p.out1 ? reinterpret_cast<T *>(p.out1) + prow * int64_t(2 * p.N) : nullptr;
+        const int n0 = c.n_tile * (BN / 2);
+#pragma unroll 1
+        for (int cc = 0; cc < BN / 2; cc += 32) {
+            uint32_t ru[32], rg[32];
+            ptx::tmem_ld32(tbase + cc, ru);
+            ptx::tmem_ld32(tbase + BN / 2 + cc, rg);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int n = n0 + cc + g * 8;
+                if (n < p.N) {
+                    float vu[8], vg[8], va[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        vu[i] = __uint_as_float(ru[g * 8 + i]);
+                        vg[i] = __uint_as_float(rg[g * 8 + i]);
+                        va[i] = w * act_fwd(p.act_kind, vu[i], vg[i]);
+                    }
+                    store8<T>(act + n, va);
+                    if (h) {
+                        store8<T>(h + n, vu);
+                        store8<T>(h + p.N + n, vg);
+                    }
+                }
+            }
+        }
+    } else if constexpr (MODE == MODE_SCATTER_ADD) {
+        const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
+        const int32_t src = p.row_map[prow];
+        float *out = p.out32 + int64_t(src >= 0 ? src / p.top_k : 0) * int64_t(p.N);
+        const int n0 = c.n_tile * BN;
+#pragma unroll 1
+        for (int cc = 0; cc < BN; cc += 32) {
+            uint32_t r[32];
+            ptx::tmem_ld32(tbase + cc, r);
+            ptx::tmem_ld_wait();
+            if (src >= 0) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const int n = n0 + cc + g * 4;
+                    if (n < p.N)
+                        ptx::red_add_v4(out + n, __uint_as_float(r[g * 4 + 0]), __uint_as_float(r[g * 4 + 1]),
+                                        __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+                }
+            }
+        }
+    } else if constexpr (MODE == MODE_ACT_BWD) {
+        const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
+        const int32_t src = p.row_map[prow];
+        float w = (src >= 0) ? 1.0f : 0.0f;
+        if (p.gate_w && src >= 0) w = DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]);
+        const T *h = reinterpret_cast<const T *>(p.h_in) + prow * int64_t(2 * p.N);
+        T *dh = reinterpret_cast<T *>(p.out0) + prow * int64_t(2 * p.N);
+        const int n0 = c.n_tile * BN;
+        float dgate_w = 0.0f;
+#pragma unroll 1
+        for (int cc = 0; cc < BN; cc += 32) {
+            uint32_t r[32];
+            ptx::tmem_ld32(tbase + cc, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int n = n0 + cc + g * 8;
+                if (n < p.N) {
+                    float vu[8], vg[8], du[8], dg[8];
+                    load8<T>(h + n, vu);
+                    load8<T>(h + p.N + n, vg);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float acc = __uint_as_float(r[g * 8 + i]);
+                        float a, du_m, dg_m;
+                        act_bwd(p.act_kind, vu[i], vg[i], a, du_m, dg_m);
+                        dgate_w += a * acc;
+                        const float da = w * acc;
+                        du[i] = da * du_m;
+                        dg[i] = da * dg_m;
+                    }
+                    store8<T>(dh + n, du);
+                    store8<T>(dh + p.N + n, dg);
+                }
+            }
+        }
+        if (p.dgates && src >= 0) atomicAdd(p.dgates + src, dgate_w);
     }
 }
 
@@ -358,140 +500,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             if (!wait_barrier(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
             ptx::tc_fence_after();
             const uint32_t tbase = tmem_base + uint32_t(buf) * BN + (uint32_t(quarter * 32) << 16);
-            const bool have_acc = c.k_iters > 0;
-
-            if constexpr (MODE == MODE_STORE || MODE == MODE_WGRAD) {
-                T *out;
-                bool row_ok;
-                if constexpr (MODE == MODE_WGRAD) {
-                    const int m = c.m_tile * BM + row_in_tile;
-                    row_ok = m < p.M;
-                    out = reinterpret_cast<T *>(p.out0) + (int64_t(c.e) * p.M + m) * int64_t(p.N);
-                } else {
-                    int64_t orow = int64_t(c.m_tile) * BM + row_in_tile;
-                    row_ok = true;
-                    if (p.row_map) {  // scatter store: padded row -> caller's row order (each row written once)
-                        const int32_t src = p.row_map[orow];
-                        row_ok = src >= 0;
-                        orow = row_ok ? src : 0;
-                    }
-                    out = reinterpret_cast<T *>(p.out0) + orow * int64_t(p.N);
-                }
-                const int n0 = c.n_tile * BN;
-#pragma unroll 1
-                for (int cc = 0; cc < BN; cc += 32) {
-                    uint32_t r[32];
-                    if (have_acc) {
-                        ptx::tmem_ld32(tbase + cc, r);
-                        ptx::tmem_ld_wait();
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = 0u;
-                    }
-                    if (row_ok) {
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            const int n = n0 + cc + g * 8;
-                            if (n < p.N) {
-                                float v[8];
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
-                                store8<T>(out + n, v);
-                            }
-                        }
-                    }
-                }
-            } else if constexpr (MODE == MODE_UP_ACT) {
-                const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
-                const int32_t src = p.row_map[prow];
-                float w = 1.0f;
-                if (p.gate_w) w = (src >= 0) ? DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]) : 0.0f;
-                T *act = reinterpret_cast<T *>(p.out0) + prow * int64_t(p.N);
-                T *h = p.out1 ? reinterpret_cast<T *>(p.out1) + prow * int64_t(2 * p.N) : nullptr;
-                const int n0 = c.n_tile * (BN / 2);
-#pragma unroll 1
-                for (int cc = 0; cc < BN / 2; cc += 32) {
-                    uint32_t ru[32], rg[32];
-                    ptx::tmem_ld32(tbase + cc, ru);
-                    ptx::tmem_ld32(tbase + BN / 2 + cc, rg);
-                    ptx::tmem_ld_wait();
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const int n = n0 + cc + g * 8;
-                        if (n < p.N) {
-                            float vu[8], vg[8], va[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                vu[i] = __uint_as_float(ru[g * 8 + i]);
-                                vg[i] = __uint_as_float(rg[g * 8 + i]);
-                                va[i] = w * act_fwd(p.act_kind, vu[i], vg[i]);
-                            }
-                            store8<T>(act + n, va);
-                            if (h) {
-                                store8<T>(h + n, vu);
-                                store8<T>(h + p.N + n, vg);
-                            }
-                        }
-                    }
-                }
-            } else if constexpr (MODE == MODE_SCATTER_ADD) {
-                const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
-                const int32_t src = p.row_map[prow];
-                float *out = p.out32 + int64_t(src >= 0 ? src / p.top_k : 0) * int64_t(p.N);
-                const int n0 = c.n_tile * BN;
-#pragma unroll 1
-                for (int cc = 0; cc < BN; cc += 32) {
-                    uint32_t r[32];
-                    ptx::tmem_ld32(tbase + cc, r);
-                    ptx::tmem_ld_wait();
-                    if (src >= 0) {
-#pragma unroll
-                        for (int g = 0; g < 8; ++g) {
-                            const int n = n0 + cc + g * 4;
-                            if (n < p.N)
-                                ptx::red_add_v4(out + n, __uint_as_float(r[g * 4 + 0]), __uint_as_float(r[g * 4 + 1]),
-                                                __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
-                        }
-                    }
-                }
-            } else if constexpr (MODE == MODE_ACT_BWD) {
-                const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
-                const int32_t src = p.row_map[prow];
-                float w = (src >= 0) ? 1.0f : 0.0f;
-                if (p.gate_w && src >= 0) w = DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]);
-                const T *h = reinterpret_cast<const T *>(p.h_in) + prow * int64_t(2 * p.N);
-                T *dh = reinterpret_cast<T *>(p.out0) + prow * int64_t(2 * p.N);
-                const int n0 = c.n_tile * BN;
-                float dgate_w = 0.0f;
-#pragma unroll 1
-                for (int cc = 0; cc < BN; cc += 32) {
-                    uint32_t r[32];
-                    ptx::tmem_ld32(tbase + cc, r);
-                    ptx::tmem_ld_wait();
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const int n = n0 + cc + g * 8;
-                        if (n < p.N) {
-                            float vu[8], vg[8], du[8], dg[8];
-                            load8<T>(h + n, vu);
-                            load8<T>(h + p.N + n, vg);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const float acc = __uint_as_float(r[g * 8 + i]);
-                                float a, du_m, dg_m;
-                                act_bwd(p.act_kind, vu[i], vg[i], a, du_m, dg_m);
-                                dgate_w += a * acc;
-                                const float da = w * acc;
-                                du[i] = da * du_m;
-                                dg[i] = da * dg_m;
-                            }
-                            store8<T>(dh + n, du);
-                            store8<T>(dh + p.N + n, dg);
-                        }
-                    }
-                }
-                if (p.dgates && src >= 0) atomicAdd(p.dgates + src, dgate_w);
-            }
+            epilogue_tile<T, MODE>(p, c, tbase, row_in_tile);
             // release the accumulator buffer
             ptx::tc_fence_before();
             __syncwarp();
@@ -505,6 +514,270 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- CTA-pair variant --------------------------------------------------------------------------------
+// Two CTAs on one TPC share a 256 x 256 tile: each owns 128 rows of it (its own A tile and accumulators)
+// and loads only half of the B tile; one tcgen05.mma.cta_group::2 issued by the leader CTA reads both
+// halves.  Per CTA and k-block that is 32 KiB instead of 48 KiB from L2 and leaves room for a 6-stage
+// ring, which is what keeps the tensor pipe fed.  TMA loads are plain (non-multicast) per CTA; the
+// leader's mbarrier collects the transaction bytes of both CTAs.
+constexpr int kPairStages = 6;
+constexpr int kBHalfStageBytes = kBStageBytes / 2;  // 16 KiB
+
+struct SmemCtlPair {
+    uint64_t full[kPairStages];
+    uint64_t empty[kPairStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_ptr;
+    volatile int abort_flag;
+    int32_t sched[kMaxSchedExperts + 1];   // m-tile offsets (or padded row offsets for WGRAD)
+    int32_t psched[kMaxSchedExperts + 1];  // pair-tile offsets per expert
+};
+
+constexpr size_t kGemmPairSmemBytes = 1024 + size_t(kPairStages) * (kAStageBytes + kBHalfStageBytes) + sizeof(SmemCtlPair);
+
+template <int MODE, int BK>
+__device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams &p, const SmemCtlPair *ctl, int t, int rank) {
+    TileCoord c;
+    if constexpr (MODE == MODE_WGRAD) {
+        const int mpairs = (p.m_tiles_w + 1) >> 1;
+        const int per_e = mpairs * p.n_tiles;
+        c.e = t / per_e;
+        const int local = t - c.e * per_e;
+        int pm;
+        if (p.n_fastest) {
+            pm = local / p.n_tiles;
+            c.n_tile = local - pm * p.n_tiles;
+        } else {
+            c.n_tile = local / mpairs;
+            pm = local - c.n_tile * mpairs;
+        }
+        c.m_tile = 2 * pm + rank;
+        c.valid = c.m_tile < p.m_tiles_w;
+        c.k_row0 = ctl->sched[c.e];
+        c.k_iters = (ctl->sched[c.e + 1] - c.k_row0) / BK;
+    } else {
+        int lo = 0, hi = p.E;
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (ctl->psched[mid] * p.n_tiles <= t) lo = mid; else hi = mid;
+        }
+        c.e = lo;
+        const int p0 = ctl->psched[lo];
+        const int pairs = ctl->psched[lo + 1] - p0;
+        const int local = t - p0 * p.n_tiles;
+        c.n_tile = local / pairs;
+        const int pm = local - c.n_tile * pairs;
+        const int m0 = ctl->sched[lo];
+        const int mt = ctl->sched[lo + 1] - m0;
+        c.valid = (2 * pm + rank) < mt;
+        c.m_tile = m0 + 2 * pm + (c.valid ? rank : 0);  // an odd tail repeats the leader's rows; its result is dropped
+        c.k_row0 = 0;
+        c.k_iters = (p.K + BK - 1) / BK;
+    }
+    return c;
+}
+
+__device__ __forceinline__ bool wait_barrier_pair(uint32_t bar, uint32_t parity, SmemCtlPair *ctl, int32_t *dev_status) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 63u) == 0) {
+            if (ctl->abort_flag) return false;
+            if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
+                ctl->abort_flag = 1;
+                if (dev_status) atomicOr(dev_status, CK_DEV_TIMEOUT);
+                return false;
+            }
+        }
+    }
+}
+
+template <typename T, int MODE, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p) {
+    using TR = GemmTraits<T>;
+    constexpr bool A_MN = (MODE == MODE_WGRAD);
+    constexpr int BK = TR::BK;
+    constexpr uint32_t kIdesc = make_idesc<T>(A_MN, B_MN, 2 * BM);
+    constexpr uint32_t kStageTx = 2 * (kAStageBytes + kBHalfStageBytes);  // both CTAs' bytes land on the leader's barrier
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
+    const uint32_t pad = (1024u - (raw_u32 & 1023u)) & 1023u;
+    uint8_t *smem = smem_raw + pad;
+    const uint32_t smem_a = raw_u32 + pad;
+    const uint32_t smem_b = smem_a + kPairStages * kAStageBytes;
+    SmemCtlPair *ctl = reinterpret_cast<SmemCtlPair *>(smem + kPairStages * (kAStageBytes + kBHalfStageBytes));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int rank = int(ptx::cluster_ctarank());  // 0 = leader
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&ctl->tmem_full[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[b]), 8);  // 4 epilogue warps of each CTA
+        }
+        ctl->abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&p.tmA);
+        ptx::prefetch_tensormap(&p.tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(&ctl->tmem_ptr), kTmemCols);
+        ptx::tmem_relinquish_pair();
+    }
+    {
+        const int32_t *src = (MODE == MODE_WGRAD) ? p.padded_off : p.mtile_off;
+        for (int i = threadIdx.x; i <= p.E; i += kGemmThreads) ctl->sched[i] = src[i];
+    }
+    __syncthreads();
+    if (MODE != MODE_WGRAD && threadIdx.x == 0) {
+        int acc = 0;
+        ctl->psched[0] = 0;
+        for (int e = 0; e < p.E; ++e) {
+            acc += (ctl->sched[e + 1] - ctl->sched[e] + 1) >> 1;
+            ctl->psched[e + 1] = acc;
+        }
+    }
+    ptx::tc_fence_before();
+    ptx::cluster_sync_all();  // barriers of both CTAs initialised and visible; TMEM address published
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_ptr;
+
+    int ntiles;
+    if constexpr (MODE == MODE_WGRAD) ntiles = p.E * ((p.m_tiles_w + 1) >> 1) * p.n_tiles;
+    else ntiles = ctl->psched[p.E] * p.n_tiles;
+    {
+        const int64_t rows = (MODE == MODE_WGRAD) ? int64_t(ctl->sched[p.E]) : int64_t(ctl->sched[p.E]) * BM;
+        if (rows > p.cap || rows < 0) {
+            ntiles = 0;
+            if (threadIdx.x == 0 && p.dev_status) atomicOr(p.dev_status, CK_DEV_META);
+        }
+    }
+
+    if (warp == 0) {
+        // ================= TMA producer (one per CTA: own A rows, own half of B) =================
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
+                const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
+                for (int kb = 0; kb < c.k_iters; ++kb) {
+                    if (!wait_barrier_pair(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status)) { ok = false; break; }
+                    if (rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), kStageTx);
+                    const uint32_t full = ptx::mapa_shared(ptx::smem_u32(&ctl->full[stage]), 0);  // the leader's barrier
+                    const uint32_t sa = smem_a + stage * kAStageBytes;
+                    const uint32_t sb = smem_b + stage * kBHalfStageBytes;
+                    const int nb0 = c.n_tile * BN + rank * (BN / 2);  // this CTA's half of the N range
+                    if constexpr (MODE == MODE_WGRAD) {
+                        const int krow = c.k_row0 + kb * BK;
+#pragma unroll
+                        for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
+                            ptx::tma_load_2d_pair(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
+#pragma unroll
+                        for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
+                            ptx::tma_load_2d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow);
+                    } else {
+                        const int k0 = kb * BK;
+                        ptx::tma_load_2d_pair(sa, &p.tmA, full, k0, c.m_tile * BM);
+                        if constexpr (B_MN) {
+#pragma unroll
+                            for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
+                                ptx::tma_load_3d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, k0, c.e);
+                        } else if constexpr (MODE == MODE_UP_ACT) {
+                            // leader: 128 rows of W_up, peer: the matching 128 rows of W_gate
+                            ptx::tma_load_3d_pair(sb, &p.tmB, full, k0, rank * p.N + c.n_tile * (BN / 2), c.e);
+                        } else {
+                            ptx::tma_load_3d_pair(sb, &p.tmB, full, k0, nb0, c.e);
+                        }
+                    }
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ================= MMA issuer: the leader CTA drives both tensor cores =================
+        if (lane == 0 && rank == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = pair_id; t < ntiles && ok; t += num_pairs, ++it) {
+                const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, 0);
+                const int buf = it & 1;
+                if (!wait_barrier_pair(ptx::smem_u32(&ctl->tmem_empty[buf]), ((uint32_t(it) >> 1) & 1u) ^ 1u, ctl, p.dev_status)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + uint32_t(buf) * BN;
+                for (int kb = 0; kb < c.k_iters; ++kb) {
+                    if (!wait_barrier_pair(ptx::smem_u32(&ctl->full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = smem_a + stage * kAStageBytes;
+                    const uint32_t sb = smem_b + stage * kBHalfStageBytes;
+#pragma unroll
+                    for (int k = 0; k < TR::kSteps; ++k) {
+                        uint64_t adesc, bdesc;
+                        if constexpr (A_MN) adesc = ptx::umma_desc_mnmajor<TR::kTf32>(sa + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
+                        else adesc = ptx::umma_desc_kmajor(sa + k * 32);
+                        if constexpr (B_MN) bdesc = ptx::umma_desc_mnmajor<TR::kTf32>(sb + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
+                        else bdesc = ptx::umma_desc_kmajor(sb + k * 32);
+                        ptx::umma_ss_pair<TR::kTf32>(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit_pair(ptx::smem_u32(&ctl->empty[stage]), 3);  // frees the stage in both CTAs
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                ptx::tc_commit_pair(ptx::smem_u32(&ctl->tmem_full[buf]), 3);  // accumulators of both CTAs complete
+            }
+            if (!ok) {
+                for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ================= epilogue: each CTA drains its own 128 rows =================
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const uint32_t leader_empty0 = ptx::mapa_shared(ptx::smem_u32(&ctl->tmem_empty[0]), 0);
+        const uint32_t leader_empty1 = ptx::mapa_shared(ptx::smem_u32(&ctl->tmem_empty[1]), 0);
+        int it = 0;
+        bool ok = true;
+        for (int t = pair_id; t < ntiles && ok; t += num_pairs, ++it) {
+            const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
+            const int buf = it & 1;
+            if (!wait_barrier_pair(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t tbase = tmem_base + uint32_t(buf) * BN + (uint32_t(quarter * 32) << 16);
+            if (c.valid) epilogue_tile<T, MODE>(p, c, tbase, row_in_tile);
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(buf ? leader_empty1 : leader_empty0);
+        }
+    }
+
+    // teardown: nobody leaves while the partner may still read its shared memory or signal its barriers
+    ptx::tc_fence_before();
+    ptx::cluster_sync_all();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
     }
 }
 
@@ -563,8 +836,28 @@ static int encode_map(CUtensorMap *tm, const void *base, int rank, const uint64_
     return CK_OK;
 }
 
+// 1 = CTA-pair kernels (cta_group::2), 0 = single-CTA kernels; initial value from CK_GEMM_CTA_PAIR
+static int g_cta_pair = -1;
+static bool use_cta_pair() {
+    if (g_cta_pair < 0) {
+        const char *e = getenv("CK_GEMM_CTA_PAIR");
+        g_cta_pair = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_cta_pair != 0;
+}
+
 template <typename T, int MODE, bool B_MN>
 static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t stream) {
+    if (use_cta_pair()) {
+        auto kern2 = grouped_gemm_pair_kernel<T, MODE, B_MN>;
+        CK_CUDA_TRY(cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmPairSmemBytes));
+        int64_t pairs = num_sms() / 2;
+        if (pairs > max_tiles) pairs = max_tiles;  // upper bound: a pair tile covers at least one single tile
+        if (pairs < 1) return CK_OK;
+        kern2<<<dim3((unsigned)(2 * pairs)), kGemmThreads, kGemmPairSmemBytes, stream>>>(p);
+        CK_LAUNCH_CHECK("grouped_gemm_pair_kernel");
+        return CK_OK;
+    }
     auto kern = grouped_gemm_kernel<T, MODE, B_MN>;
     CK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes));
     int64_t grid = num_sms();
@@ -628,7 +921,7 @@ static int down_combine_fwd_t(const void *act, const void *wproj, const int32_t 
     p.cap = cap;
     int rc;
     if ((rc = map_a_kmajor<T>(&p.tmA, act, cap, I)) != CK_OK) return rc;
-    if ((rc = map_w_kmajor<T>(&p.tmB, wproj, E, H, I, BN)) != CK_OK) return rc;
+    if ((rc = map_w_kmajor<T>(&p.tmB, wproj, E, H, I, use_cta_pair() ? BN / 2 : BN)) != CK_OK) return rc;
     p.mtile_off = mtile_off; p.row_map = row_map; p.out32 = out32; p.dev_status = dev_status;
     p.E = E; p.n_tiles = (H + BN - 1) / BN; p.N = H; p.K = I; p.top_k = top_k;
     return launch_gemm<T, MODE_SCATTER_ADD, false>(p, (cap / BM) * p.n_tiles, stream);
@@ -690,13 +983,19 @@ static int grouped_linear_t(const void *x, const void *w, const int32_t *mtile_o
         if ((rc = map_w_mnmajor<T>(&p.tmB, w, E, K, N)) != CK_OK) return rc;
         return launch_gemm<T, MODE_STORE, true>(p, (cap / BM) * p.n_tiles, stream);
     }
-    if ((rc = map_w_kmajor<T>(&p.tmB, w, E, N, K, BN)) != CK_OK) return rc;
+    if ((rc = map_w_kmajor<T>(&p.tmB, w, E, N, K, use_cta_pair() ? BN / 2 : BN)) != CK_OK) return rc;
     return launch_gemm<T, MODE_STORE, false>(p, (cap / BM) * p.n_tiles, stream);
 }
 
 }  // namespace ck
 
 using namespace ck;
+
+extern "C" int ck_set_gemm_cta_pair(int enable) {
+    const int prev = use_cta_pair() ? 1 : 0;
+    g_cta_pair = enable ? 1 : 0;
+    return prev;
+}
 
 #define CK_DISPATCH_DTYPE(dtype, CALL)                              \
     switch (dtype) {                                                \

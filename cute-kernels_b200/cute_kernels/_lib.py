@@ -46,6 +46,7 @@ PROTOTYPES = {
     "ck_moe_dgrad_up": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_moe_wgrad": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _vp, _vp]),
     "ck_moe_grouped_linear": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_set_gemm_cta_pair": (_i, [_i]),
     "ck_moe_grouped_linear_scatter": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_moe_gather_rows_scaled": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i, _vp]),
     "ck_moe_combine_rows": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i, _vp]),

@@ -188,6 +188,12 @@ CK_API int ck_moe_grouped_linear(const void *x, const void *w, const int32_t *mt
                           int64_t cap, int N, int K, int trans_w, int dtype, int32_t *dev_status,
                           void *stream);
 
+/* Kernel flavour of the grouped GEMMs: 1 (default) = CTA pairs (tcgen05 cta_group::2, 256 x 256 tile per pair,
+ * half of the weight tile per CTA), 0 = one CTA per 128 x 256 tile.  Returns the previous setting.  The initial
+ * value comes from the environment variable CK_GEMM_CTA_PAIR.  Takes the place of the reference's per-call
+ * cutotune knobs (cute_kernels/cutotune/): there is no runtime search, only this switch. */
+CK_API int ck_set_gemm_cta_pair(int enable);
+
 /* same as ck_moe_grouped_linear, but row p of the result is stored at y[row_map[p], :] (pad rows dropped):
  * scatter2scatter with y_grouped=False and FAN_OUT=1 (ops.py:31-78) -- used by expert-parallel shards, where
  * every routed row is produced exactly once and travels back before the combine. */

@@ -8,6 +8,16 @@ import ck_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
+@pytest.fixture(params=["cta_pair", "single_cta"], autouse=True)
+def gemm_flavour(request):
+    """Every test of this file runs on both grouped-GEMM kernel flavours."""
+    from cute_kernels import _lib
+
+    prev = _lib.lib.ck_set_gemm_cta_pair(1 if request.param == "cta_pair" else 0)
+    yield request.param
+    _lib.lib.ck_set_gemm_cta_pair(prev)
+
+
 TOL = {torch.bfloat16: dict(rtol=2e-2, atol=2e-2), torch.float16: dict(rtol=4e-3, atol=4e-3),
        torch.float32: dict(rtol=6e-3, atol=6e-3)}  # fp32 runs as TF32 on the tensor cores, like the reference's tl.dot
 
