@@ -16,7 +16,8 @@ namespace ck {
 
 constexpr int kRouteMaxWarps = 148 * 32;  // upper bound on id slices (fixed so workspace size is device independent)
 constexpr int kRouteWarpsPerBlock = 8;
-constexpr int kStep = 128;  // ids per warp per unrolled step (4 coalesced loads of 32)
+constexpr int kLoads = 16;          // coalesced 32-id loads in flight per warp: 2 KiB (int32) of reads per warp step
+constexpr int kStep = 32 * kLoads;  // ids per warp per unrolled step
 
 __device__ __forceinline__ unsigned lanemask_lt() {
     unsigned m;
@@ -31,6 +32,18 @@ __device__ __forceinline__ unsigned lanemask_lt() {
 __device__ __forceinline__ unsigned match_key_bits(int key, int nbits) {
     unsigned m = __ballot_sync(0xffffffffu, key >= 0);
     for (int b = 0; b < nbits; ++b) {
+        const bool bit = (key >> b) & 1;
+        const unsigned bal = __ballot_sync(0xffffffffu, bit);
+        m &= bit ? bal : ~bal;
+    }
+    return key >= 0 ? m : 0u;
+}
+
+template <int NBITS>
+__device__ __forceinline__ unsigned match_key_fixed(int key) {
+    unsigned m = __ballot_sync(0xffffffffu, key >= 0);
+#pragma unroll
+    for (int b = 0; b < NBITS; ++b) {
         const bool bit = (key >> b) & 1;
         const unsigned bal = __ballot_sync(0xffffffffu, bit);
         m &= bit ? bal : ~bal;
@@ -57,7 +70,7 @@ constexpr int kLanePrivateMax = 128;  // largest id range that gets a per-lane h
 // the warp first and issue one shared-memory atomic per distinct id.
 // ------------------------------------------------------------------------------------------------
 template <typename IdT, bool LANE_PRIVATE>
-__global__ void __launch_bounds__(256) count_kernel(const IdT *__restrict__ ids, int64_t n, int size, int nbits,
+__global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids, int64_t n, int size, int nbits,
                                                    uint32_t *__restrict__ counts) {
     extern __shared__ uint32_t hist[];
     const int lane = threadIdx.x & 31;
@@ -68,35 +81,46 @@ __global__ void __launch_bounds__(256) count_kernel(const IdT *__restrict__ ids,
     bool bad = false;
 
     if constexpr (LANE_PRIVATE) {
-        uint32_t *wh = hist + wib * size * 32;  // [size][32]
+        const int wpb = blockDim.x >> 5;
+        uint32_t *wh = hist + wib * size * 32;      // [size][32] per warp
+        uint32_t *bh = hist + wpb * size * 32;      // [size] block totals
         for (int i = lane; i < size * 32; i += 32) wh[i] = 0;
-        __syncwarp();
+        for (int i = threadIdx.x; i < size; i += blockDim.x) bh[i] = 0;
+        __syncthreads();
         for (int64_t c = warp_id; c < nchunks; c += nwarps) {
             const int64_t b = c * kStep + lane;
-            int key[4];
+            int key[kLoads];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) key[j] = load_key(ids, b + 32 * j, n, size, bad);
+            for (int j = 0; j < kLoads; ++j) key[j] = load_key(ids, b + 32 * j, n, size, bad);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < kLoads; ++j)
                 if (key[j] >= 0) wh[key[j] * 32 + lane] += 1;
         }
         __syncwarp();
+        // lanes -> warp -> block -> one global atomic per value per block (same-sector atomics serialise in L2,
+        // so the number of global atomics, not the histogram itself, would otherwise set the run time)
         for (int v = 0; v < size; ++v) {
             uint32_t c = wh[v * 32 + lane];
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
-            if (lane == 0 && c) atomicAdd(&counts[v], c);
+            if (lane == 0 && c) atomicAdd(&bh[v], c);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < size; i += blockDim.x) {
+            const int v = (i + blockIdx.x * 8) % size;  // blocks start on different 32-byte sectors
+            const uint32_t c = bh[v];
+            if (c) atomicAdd(&counts[v], c);
         }
     } else {
         for (int i = threadIdx.x; i < size; i += blockDim.x) hist[i] = 0;
         __syncthreads();
         for (int64_t c = warp_id; c < nchunks; c += nwarps) {
             const int64_t b = c * kStep + lane;
-            int key[4];
+            int key[kLoads];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) key[j] = load_key(ids, b + 32 * j, n, size, bad);
+            for (int j = 0; j < kLoads; ++j) key[j] = load_key(ids, b + 32 * j, n, size, bad);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < kLoads; ++j) {
                 const unsigned m = match_key_bits(key[j], nbits);
                 if (key[j] >= 0 && lane == __ffs(m) - 1) atomicAdd(&hist[key[j]], __popc(m));
             }
@@ -130,11 +154,11 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
         for (int i = lane; i < E * 32; i += 32) wh[i] = 0;
         __syncwarp();
         for (int64_t off = begin; off < end; off += kStep) {
-            int key[4];
+            int key[kLoads];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) key[j] = load_key(ids, off + 32 * j + lane, end, E, bad);
+            for (int j = 0; j < kLoads; ++j) key[j] = load_key(ids, off + 32 * j + lane, end, E, bad);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
+            for (int j = 0; j < kLoads; ++j)
                 if (key[j] >= 0) wh[key[j] * 32 + lane] += 1;
         }
         __syncwarp();
@@ -149,11 +173,11 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
         for (int e = lane; e < E; e += 32) wh[e] = 0;
         __syncwarp();
         for (int64_t off = begin; off < end; off += kStep) {
-            int key[4];
+            int key[kLoads];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) key[j] = load_key(ids, off + 32 * j + lane, end, E, bad);
+            for (int j = 0; j < kLoads; ++j) key[j] = load_key(ids, off + 32 * j + lane, end, E, bad);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < kLoads; ++j) {
                 const unsigned m = match_key_bits(key[j], nbits);
                 if (key[j] >= 0 && lane == __ffs(m) - 1) wh[key[j]] += __popc(m);
                 __syncwarp();
@@ -206,15 +230,26 @@ __global__ void __launch_bounds__(1024)
     __shared__ int total_s;
     __shared__ int is_last;
     const int e = blockIdx.x;
-    int carry = 0;
-    for (int base = 0; base < W; base += 1024) {
-        const int w = base + threadIdx.x;
-        const int v = (w < W) ? whist[int64_t(w) * E + e] : 0;
-        const int ex = block_excl_scan_1024(v, &total_s, warp_sums);
-        if (w < W) whist[int64_t(w) * E + e] = carry + ex;
-        carry += total_s;
-        __syncthreads();
+    // W <= 148*32 slices: at most kScanItems consecutive slices per thread, all loads issued before one block scan
+    constexpr int kScanItems = (kRouteMaxWarps + 1023) / 1024;
+    int v[kScanItems];
+    int tsum = 0;
+#pragma unroll
+    for (int i = 0; i < kScanItems; ++i) {
+        const int w = threadIdx.x * kScanItems + i;
+        v[i] = (w < W) ? whist[int64_t(w) * E + e] : 0;
     }
+#pragma unroll
+    for (int i = 0; i < kScanItems; ++i) tsum += v[i];
+    int run = block_excl_scan_1024(tsum, &total_s, warp_sums);
+    const int carry = total_s;
+#pragma unroll
+    for (int i = 0; i < kScanItems; ++i) {
+        const int w = threadIdx.x * kScanItems + i;
+        if (w < W) whist[int64_t(w) * E + e] = run;
+        run += v[i];
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         counts[e] = uint32_t(carry);
         __threadfence();
@@ -250,7 +285,7 @@ __global__ void __launch_bounds__(1024)
 // route pass 3: stable scatter.  Each warp walks its slice in order; an id's output position is
 // excl_off[e] + whist[w][e] + (ids == e seen so far in this slice).
 // ------------------------------------------------------------------------------------------------
-template <typename IdT>
+template <typename IdT, int NBITS>  // NBITS > 0: ids need exactly NBITS bits (unrolled ballots); 0: run-time bit count
 __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
     route_scatter_kernel(const IdT *__restrict__ ids, int64_t n, int E, int nbits, int64_t slice, int W,
                          const int32_t *__restrict__ whist, const int32_t *__restrict__ excl_off,
@@ -271,15 +306,18 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
     const unsigned lt = lanemask_lt();
     const int64_t begin = int64_t(w) * slice;
     const int64_t end = min(begin + slice, n);
+    const IdT *__restrict__ my_ids = ids + begin;
+    const int len = int(end - begin);              // a slice is far below 2^31 ids
+    const int32_t src0 = int32_t(begin) + lane;    // n < 2^31 is checked by the host wrapper
     bool bad = false;
-    for (int64_t off = begin; off < end; off += kStep) {
-        int key[4];
+    for (int off = 0; off < len; off += kStep) {
+        int key[kLoads];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) key[j] = load_key(ids, off + 32 * j + lane, end, E, bad);
+        for (int j = 0; j < kLoads; ++j) key[j] = load_key(my_ids, int64_t(off + 32 * j + lane), int64_t(len), E, bad);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < kLoads; ++j) {
             const int k = key[j];
-            const unsigned m = match_key_bits(k, nbits);
+            const unsigned m = NBITS > 0 ? match_key_fixed<NBITS>(k) : match_key_bits(k, nbits);
             int b = 0;
             if (k >= 0) b = wbase[k];
             __syncwarp();
@@ -287,7 +325,7 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
             __syncwarp();
             if (k >= 0) {
                 const int pos = b + __popc(m & lt);
-                const int32_t src = int32_t(off + 32 * j + lane);
+                const int32_t src = src0 + off + 32 * j;
                 sorted_idx[pos] = src;
                 if (sorted_expert) sorted_expert[pos] = k;
                 if (row_map) row_map[pos + delta[k]] = src;
@@ -304,7 +342,6 @@ static void route_plan(int64_t n, int64_t *slice, int *W) {
     }
     int64_t s = ceil_div64(n, kRouteMaxWarps);
     s = ceil_div64(s, kStep) * kStep;
-    if (s < 2 * kStep) s = 2 * kStep;
     *slice = s;
     *W = int(ceil_div64(n, s));
 }
@@ -321,16 +358,15 @@ extern "C" int ck_continuous_count(const void *ids, int ids_is_i64, int64_t n, i
     if (n > 0 && ids == nullptr) return CK_ERR_SHAPE;
     CK_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(uint32_t) * size, stream));
     if (n == 0) return CK_OK;
-    const int threads = 256;
     const bool lane_private = size <= kLanePrivateMax;
     const int nbits = size > 1 ? 32 - __builtin_clz(unsigned(size - 1)) : 0;
-    const size_t smem = lane_private ? sizeof(uint32_t) * size * 32 * (threads / 32) : sizeof(uint32_t) * size;
+    int wpb = 16;  // warps per block; one block per SM keeps the count of global atomics at num_sms * size
+    if (lane_private) wpb = std::max(1, std::min(16, int((200 * 1024) / (size_t(size) * 128))));
+    const int threads = wpb * 32;
+    const size_t smem = lane_private ? sizeof(uint32_t) * size * (32 * wpb + 1) : sizeof(uint32_t) * size;
     const int64_t nchunks = ceil_div64(n, kStep);
-    int blocks_per_sm = 8;
-    if (smem > 0) blocks_per_sm = int(std::min<size_t>(8, (200 * 1024) / smem));
-    if (blocks_per_sm < 1) blocks_per_sm = 1;
-    int64_t grid = ceil_div64(nchunks, threads / 32);
-    const int64_t cap = int64_t(num_sms()) * blocks_per_sm;
+    int64_t grid = ceil_div64(nchunks, wpb);
+    const int64_t cap = int64_t(num_sms()) * (lane_private ? 1 : 2);
     if (grid > cap) grid = cap;
 #define CK_LAUNCH_COUNT(IDT, LP)                                                                                          \
     do {                                                                                                                  \
@@ -406,14 +442,24 @@ extern "C" int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint3
     CK_LAUNCH_CHECK("route_scan_kernel");
     if (W > 0) {
         const size_t smem = sizeof(int32_t) * (kRouteWarpsPerBlock + 1) * E;
-        if (ids_is_i64)
-            route_scatter_kernel<int64_t><<<blocks, threads, smem, stream>>>((const int64_t *)ids, n, E, nbits, slice, W, whist,
-                                                                            excl_off, padded_off, sorted_idx,
-                                                                            sorted_expert, row_map);
-        else
-            route_scatter_kernel<int32_t><<<blocks, threads, smem, stream>>>((const int32_t *)ids, n, E, nbits, slice, W, whist,
-                                                                            excl_off, padded_off, sorted_idx,
-                                                                            sorted_expert, row_map);
+#define CK_LAUNCH_SCATTER(IDT, NB)                                                                                        \
+    route_scatter_kernel<IDT, NB><<<blocks, threads, smem, stream>>>((const IDT *)ids, n, E, nbits, slice, W, whist, excl_off, \
+                                                                     padded_off, sorted_idx, sorted_expert, row_map)
+#define CK_SCATTER_BY_BITS(IDT)                         \
+    switch (nbits) {                                    \
+        case 1: CK_LAUNCH_SCATTER(IDT, 1); break;       \
+        case 2: CK_LAUNCH_SCATTER(IDT, 2); break;       \
+        case 3: CK_LAUNCH_SCATTER(IDT, 3); break;       \
+        case 4: CK_LAUNCH_SCATTER(IDT, 4); break;       \
+        case 5: CK_LAUNCH_SCATTER(IDT, 5); break;       \
+        case 6: CK_LAUNCH_SCATTER(IDT, 6); break;       \
+        case 7: CK_LAUNCH_SCATTER(IDT, 7); break;       \
+        case 8: CK_LAUNCH_SCATTER(IDT, 8); break;       \
+        default: CK_LAUNCH_SCATTER(IDT, 0); break;      \
+    }
+        if (ids_is_i64) { CK_SCATTER_BY_BITS(int64_t) } else { CK_SCATTER_BY_BITS(int32_t) }
+#undef CK_SCATTER_BY_BITS
+#undef CK_LAUNCH_SCATTER
         CK_LAUNCH_CHECK("route_scatter_kernel");
     }
     return CK_OK;

@@ -51,7 +51,7 @@ def route_workspace_bytes(n: int, num_experts: int) -> int:
     if n <= 0:
         return 256 + num_experts * 4
     slice_len = -(-n // (148 * 32))
-    slice_len = max(256, -(-slice_len // 128) * 128)
+    slice_len = -(-slice_len // 512) * 512
     return 256 + -(-n // slice_len) * num_experts * 4
 
 
