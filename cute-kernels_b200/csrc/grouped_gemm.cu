@@ -98,7 +98,7 @@ struct SmemCtl {
     int32_t sched[kMaxSchedExperts + 1];
 };
 
-constexpr size_t kGemmSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * (kAStageBytes + kBStageBytes) + sizeof(SmemCtl);
+constexpr size_t kGemmSmemBytes_noepi = 1024 /*alignment slack*/ + size_t(kStages) * (kAStageBytes + kBStageBytes) + sizeof(SmemCtl);
 
 // bounded wait: false when the CTA is aborting or the time limit ran out
 __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, SmemCtl *ctl, int32_t *dev_status) {
@@ -209,27 +209,159 @@ __device__ __forceinline__ void act_bwd(int kind, float u, float g, float &a, fl
 }
 
 // ---- fused tail of one 128 x 256 tile: executed by the four epilogue warps of a CTA --------------------
+//
+// tcgen05.ld hands every thread one accumulator ROW.  Writing rows straight from registers makes each
+// warp-wide global access touch 32 different rows (32 LSU wavefronts of 16 bytes): on tiles with a short
+// K loop the load/store unit, not the tensor pipe, then sets the pace.  The tail therefore computes in the
+// row-per-thread domain and moves data between registers and global memory through a small per-warp
+// shared-memory stage, so that every global access is a run of 64 or 128 contiguous bytes of one row.
+constexpr int kStagePitchWords = 36;                           // 32 payload words + 4 pad: conflict-free v4 / v2 access
+constexpr int kStageWarpBytes = 32 * kStagePitchWords * 4;     // 4608 B per epilogue warp
+constexpr int kEpiWarps = 4;
+constexpr int kEpiSmemBytes = kEpiWarps * (kStageWarpBytes + 32 * 4);  // stages + per-row info
+
+struct EpiSmem {
+    uint32_t *stage;  // [32][kStagePitchWords] words, private to the warp
+    int32_t *rowinfo; // [32] per-row index (row_map entry), private to the warp
+};
+
+// thread `lane` (owner of tile row `lane` of this warp) writes / reads its WORDS consecutive words
+template <int WORDS>
+__device__ __forceinline__ void stage_put_row(uint32_t *stage, int lane, const uint32_t *w) {
+    uint4 *dst = reinterpret_cast<uint4 *>(stage + lane * kStagePitchWords);
+#pragma unroll
+    for (int q = 0; q < WORDS / 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+}
+template <int WORDS>
+__device__ __forceinline__ void stage_get_row(const uint32_t *stage, int lane, uint32_t *w) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(stage + lane * kStagePitchWords);
+#pragma unroll
+    for (int q = 0; q < WORDS / 4; ++q) {
+        const uint4 v = src[q];
+        w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
+    }
+}
+
+// 32 fp32 values -> WORDS words of T (16 words for 16-bit types, 32 for fp32)
+template <typename T>
+__device__ __forceinline__ void pack32(const float *v, uint32_t *w) {
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) w[i] = __float_as_uint(v[i]);
+    } else if constexpr (DT<T>::code == CK_BF16) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+    }
+}
+template <typename T>
+__device__ __forceinline__ void unpack32(const uint32_t *w, float *v) {
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(w[i]);
+    } else if constexpr (DT<T>::code == CK_BF16) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+            v[2 * i] = f.x;
+            v[2 * i + 1] = f.y;
+        }
+    }
+}
+
+// Geometry of one staged pass over 32 rows x 32 elements of T: each lane moves 8 bytes, LPR lanes cover a row.
+template <typename T>
+struct RowPass {
+    static constexpr int kWords = 32 * int(sizeof(T)) / 4;   // words per row: 16 or 32
+    static constexpr int kLpr = kWords / 2;                  // lanes per row: 8 or 16
+    static constexpr int kRpi = 32 / kLpr;                   // rows per instruction: 4 or 2
+    static constexpr int kIters = 32 / kRpi;                 // 8 or 16
+    static constexpr int kElemsPerLane = 8 / int(sizeof(T)); // 4 or 2
+    // Row handled by `lane` in iteration `it`.  For 16-bit types four rows share an instruction; pairing rows
+    // r and r+4 inside each half-warp puts their 16-word runs 16 banks apart (pitch 36 words), so the 8-byte
+    // shared-memory accesses stay conflict free.
+    __device__ __forceinline__ static int row(int it, int lane) {
+        if constexpr (kLpr == 16) return it * 2 + (lane >> 4);
+        else return 8 * (it >> 1) + 2 * (it & 1) + ((lane >> 3) & 1) * 4 + (lane >> 4);
+    }
+};
+
+// rows of the stage -> global: row r goes to base(r) + col0 .. col0+31 (elements of T); base(r) == nullptr skips
+template <typename T, typename RowPtr>
+__device__ __forceinline__ void stage_write_rows(const uint32_t *stage, int lane, int col0, int ncols, RowPtr row_ptr) {
+    using RP = RowPass<T>;
+    const int sub = lane % RP::kLpr;
+    const int col = col0 + sub * RP::kElemsPerLane;
+#pragma unroll
+    for (int it = 0; it < RP::kIters; ++it) {
+        const int r = RP::row(it, lane);
+        const uint2 v = *reinterpret_cast<const uint2 *>(stage + r * kStagePitchWords + 2 * sub);
+        T *dst = row_ptr(r);
+        if (dst != nullptr && col < ncols) *reinterpret_cast<uint2 *>(dst + col) = v;
+    }
+}
+// global -> rows of the stage (zeros where the row is absent or the columns are out of range)
+template <typename T, typename RowPtr>
+__device__ __forceinline__ void stage_read_rows(uint32_t *stage, int lane, int col0, int ncols, RowPtr row_ptr) {
+    using RP = RowPass<T>;
+    const int sub = lane % RP::kLpr;
+    const int col = col0 + sub * RP::kElemsPerLane;
+#pragma unroll
+    for (int it = 0; it < RP::kIters; ++it) {
+        const int r = RP::row(it, lane);
+        const T *src = row_ptr(r);
+        uint2 v = make_uint2(0u, 0u);
+        if (src != nullptr && col < ncols) v = *reinterpret_cast<const uint2 *>(src + col);
+        *reinterpret_cast<uint2 *>(stage + r * kStagePitchWords + 2 * sub) = v;
+    }
+}
+
 template <typename T, int MODE>
-__device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoord &c, uint32_t tbase, int row_in_tile) {
+__device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoord &c, uint32_t tbase, int row_in_tile,
+                                              const EpiSmem &es) {
     const bool have_acc = c.k_iters > 0;
+    const int lane = row_in_tile & 31;
+    const int row0 = row_in_tile - lane;  // first tile row of this warp
+    using RP = RowPass<T>;
 
     if constexpr (MODE == MODE_STORE || MODE == MODE_WGRAD) {
-        T *out;
-        bool row_ok;
+        // per-row destination: grouped row, scattered row (row_map) or a row of dW[e]
+        T *my_out = nullptr;
         if constexpr (MODE == MODE_WGRAD) {
             const int m = c.m_tile * BM + row_in_tile;
-            row_ok = m < p.M;
-            out = reinterpret_cast<T *>(p.out0) + (int64_t(c.e) * p.M + m) * int64_t(p.N);
+            if (m < p.M) my_out = reinterpret_cast<T *>(p.out0) + (int64_t(c.e) * p.M + m) * int64_t(p.N);
         } else {
             int64_t orow = int64_t(c.m_tile) * BM + row_in_tile;
-            row_ok = true;
+            bool row_ok = true;
             if (p.row_map) {  // scatter store: padded row -> caller's row order (each row written once)
                 const int32_t src = p.row_map[orow];
                 row_ok = src >= 0;
-                orow = row_ok ? src : 0;
+                orow = src;
             }
-            out = reinterpret_cast<T *>(p.out0) + orow * int64_t(p.N);
+            if (row_ok) my_out = reinterpret_cast<T *>(p.out0) + orow * int64_t(p.N);
         }
+        // publish the 32 row pointers of this warp as (valid, row index) pairs through rowinfo
+        const int64_t my_off = my_out ? (my_out - reinterpret_cast<T *>(p.out0)) / int64_t(p.N) : -1;
+        es.rowinfo[lane] = int32_t(my_off);  // row index in units of N elements: < 2^31 rows
+        __syncwarp();
+        auto row_ptr = [&](int r) -> T * {
+            const int32_t o = es.rowinfo[r];
+            return o >= 0 ? reinterpret_cast<T *>(p.out0) + int64_t(o) * int64_t(p.N) : nullptr;
+        };
         const int n0 = c.n_tile * BN;
 #pragma unroll 1
         for (int cc = 0; cc < BN; cc += 32) {
@@ -241,26 +373,24 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
 #pragma unroll
                 for (int i = 0; i < 32; ++i) r[i] = 0u;
             }
-            if (row_ok) {
+            float v[32];
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const int n = n0 + cc + g * 8;
-                    if (n < p.N) {
-                        float v[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
-                        store8<T>(out + n, v);
-                    }
-                }
-            }
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            uint32_t w[RP::kWords];
+            pack32<T>(v, w);
+            stage_put_row<RP::kWords>(es.stage, lane, w);
+            __syncwarp();
+            stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, row_ptr);
+            __syncwarp();
         }
     } else if constexpr (MODE == MODE_UP_ACT) {
-        const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
-        const int32_t src = p.row_map[prow];
-        float w = 1.0f;
-        if (p.gate_w) w = (src >= 0) ? DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]) : 0.0f;
-        T *act = reinterpret_cast<T *>(p.out0) + prow * int64_t(p.N);
-        T *h = p.out1 ? reinterpret_cast<T *>(p.out1) + prow * int64_t(2 * p.N) : nullptr;
+        const int64_t prow0 = int64_t(c.m_tile) * BM + row0;
+        const int32_t src = p.row_map[prow0 + lane];
+        float wgt = 1.0f;
+        if (p.gate_w) wgt = (src >= 0) ? DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]) : 0.0f;
+        T *act = reinterpret_cast<T *>(p.out0) + prow0 * int64_t(p.N);
+        T *h = p.out1 ? reinterpret_cast<T *>(p.out1) + prow0 * int64_t(2 * p.N) : nullptr;
+        const int64_t ld_act = p.N, ld_h = 2 * int64_t(p.N);
         const int n0 = c.n_tile * (BN / 2);
 #pragma unroll 1
         for (int cc = 0; cc < BN / 2; cc += 32) {
@@ -268,84 +398,111 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
             ptx::tmem_ld32(tbase + cc, ru);
             ptx::tmem_ld32(tbase + BN / 2 + cc, rg);
             ptx::tmem_ld_wait();
+            float va[32];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const int n = n0 + cc + g * 8;
-                if (n < p.N) {
-                    float vu[8], vg[8], va[8];
+            for (int i = 0; i < 32; ++i) va[i] = wgt * act_fwd(p.act_kind, __uint_as_float(ru[i]), __uint_as_float(rg[i]));
+            uint32_t w[RP::kWords];
+            pack32<T>(va, w);
+            stage_put_row<RP::kWords>(es.stage, lane, w);
+            __syncwarp();
+            stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return act + r * ld_act; });
+            __syncwarp();
+            if (h) {
+                float vf[32];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        vu[i] = __uint_as_float(ru[g * 8 + i]);
-                        vg[i] = __uint_as_float(rg[g * 8 + i]);
-                        va[i] = w * act_fwd(p.act_kind, vu[i], vg[i]);
-                    }
-                    store8<T>(act + n, va);
-                    if (h) {
-                        store8<T>(h + n, vu);
-                        store8<T>(h + p.N + n, vg);
-                    }
-                }
+                for (int i = 0; i < 32; ++i) vf[i] = __uint_as_float(ru[i]);
+                pack32<T>(vf, w);
+                stage_put_row<RP::kWords>(es.stage, lane, w);
+                __syncwarp();
+                stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return h + r * ld_h; });
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) vf[i] = __uint_as_float(rg[i]);
+                pack32<T>(vf, w);
+                stage_put_row<RP::kWords>(es.stage, lane, w);
+                __syncwarp();
+                stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return h + r * ld_h + p.N; });
+                __syncwarp();
             }
         }
     } else if constexpr (MODE == MODE_SCATTER_ADD) {
         const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
         const int32_t src = p.row_map[prow];
-        float *out = p.out32 + int64_t(src >= 0 ? src / p.top_k : 0) * int64_t(p.N);
+        es.rowinfo[lane] = src >= 0 ? src / p.top_k : -1;  // destination token row
+        __syncwarp();
         const int n0 = c.n_tile * BN;
+        const int sub = lane & 7;  // 8 lanes x 16 bytes cover the 32 fp32 columns of one row
 #pragma unroll 1
         for (int cc = 0; cc < BN; cc += 32) {
             uint32_t r[32];
             ptx::tmem_ld32(tbase + cc, r);
             ptx::tmem_ld_wait();
-            if (src >= 0) {
+            stage_put_row<32>(es.stage, lane, r);
+            __syncwarp();
+            const int col = n0 + cc + 4 * sub;
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                    const int n = n0 + cc + g * 4;
-                    if (n < p.N)
-                        ptx::red_add_v4(out + n, __uint_as_float(r[g * 4 + 0]), __uint_as_float(r[g * 4 + 1]),
-                                        __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
-                }
+            for (int it = 0; it < 8; ++it) {
+                const int rr = it * 4 + (lane >> 3);
+                const int32_t tok = es.rowinfo[rr];
+                const float4 v = *reinterpret_cast<const float4 *>(es.stage + rr * kStagePitchWords + 4 * sub);
+                if (tok >= 0 && col < p.N) ptx::red_add_v4(p.out32 + int64_t(tok) * int64_t(p.N) + col, v.x, v.y, v.z, v.w);
             }
+            __syncwarp();
         }
     } else if constexpr (MODE == MODE_ACT_BWD) {
-        const int64_t prow = int64_t(c.m_tile) * BM + row_in_tile;
-        const int32_t src = p.row_map[prow];
-        float w = (src >= 0) ? 1.0f : 0.0f;
-        if (p.gate_w && src >= 0) w = DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]);
-        const T *h = reinterpret_cast<const T *>(p.h_in) + prow * int64_t(2 * p.N);
-        T *dh = reinterpret_cast<T *>(p.out0) + prow * int64_t(2 * p.N);
+        const int64_t prow0 = int64_t(c.m_tile) * BM + row0;
+        const int32_t src = p.row_map[prow0 + lane];
+        float wgt = (src >= 0) ? 1.0f : 0.0f;
+        if (p.gate_w && src >= 0) wgt = DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]);
+        const int64_t ld_h = 2 * int64_t(p.N);
+        const T *h = reinterpret_cast<const T *>(p.h_in) + prow0 * ld_h;
+        T *dh = reinterpret_cast<T *>(p.out0) + prow0 * ld_h;
         const int n0 = c.n_tile * BN;
         float dgate_w = 0.0f;
 #pragma unroll 1
         for (int cc = 0; cc < BN; cc += 32) {
+            if (n0 + cc >= p.N) break;  // whole chunk past the valid columns (uniform across the warp)
+            uint32_t w[RP::kWords];
+            float vu[32], vg[32];
+            stage_read_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> const T * { return h + r * ld_h; });
+            __syncwarp();
+            stage_get_row<RP::kWords>(es.stage, lane, w);
+            unpack32<T>(w, vu);
+            __syncwarp();
+            stage_read_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> const T * { return h + r * ld_h + p.N; });
+            __syncwarp();
+            stage_get_row<RP::kWords>(es.stage, lane, w);
+            unpack32<T>(w, vg);
+            __syncwarp();
             uint32_t r[32];
             ptx::tmem_ld32(tbase + cc, r);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const int n = n0 + cc + g * 8;
-                if (n < p.N) {
-                    float vu[8], vg[8], du[8], dg[8];
-                    load8<T>(h + n, vu);
-                    load8<T>(h + p.N + n, vg);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float acc = __uint_as_float(r[g * 8 + i]);
-                        float a, du_m, dg_m;
-                        act_bwd(p.act_kind, vu[i], vg[i], a, du_m, dg_m);
-                        dgate_w += a * acc;
-                        const float da = w * acc;
-                        du[i] = da * du_m;
-                        dg[i] = da * dg_m;
-                    }
-                    store8<T>(dh + n, du);
-                    store8<T>(dh + p.N + n, dg);
-                }
+            for (int i = 0; i < 32; ++i) {
+                const float acc = __uint_as_float(r[i]);
+                float a, du_m, dg_m;
+                act_bwd(p.act_kind, vu[i], vg[i], a, du_m, dg_m);
+                dgate_w += a * acc;
+                const float da = wgt * acc;
+                vu[i] = da * du_m;
+                vg[i] = da * dg_m;
             }
+            pack32<T>(vu, w);
+            stage_put_row<RP::kWords>(es.stage, lane, w);
+            __syncwarp();
+            stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return dh + r * ld_h; });
+            __syncwarp();
+            pack32<T>(vg, w);
+            stage_put_row<RP::kWords>(es.stage, lane, w);
+            __syncwarp();
+            stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return dh + r * ld_h + p.N; });
+            __syncwarp();
         }
         if (p.dgates && src >= 0) atomicAdd(p.dgates + src, dgate_w);
     }
 }
+
+constexpr size_t kGemmSmemBytes = kGemmSmemBytes_noepi + kEpiSmemBytes;
 
 // ---- the kernel ------------------------------------------------------------------------------------
 template <typename T, int MODE, bool B_MN>
@@ -492,6 +649,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         // =================================== epilogue =======================================
         const int quarter = warp & 3;              // TMEM lanes this warp may read
         const int row_in_tile = quarter * 32 + lane;
+        uint8_t *epi_base = reinterpret_cast<uint8_t *>(ctl) + ((sizeof(SmemCtl) + 15) & ~size_t(15));
+        EpiSmem es;
+        es.stage = reinterpret_cast<uint32_t *>(epi_base + quarter * kStageWarpBytes);
+        es.rowinfo = reinterpret_cast<int32_t *>(epi_base + kEpiWarps * kStageWarpBytes + quarter * 128);
         int it = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++it) {
@@ -500,7 +661,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             if (!wait_barrier(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
             ptx::tc_fence_after();
             const uint32_t tbase = tmem_base + uint32_t(buf) * BN + (uint32_t(quarter * 32) << 16);
-            epilogue_tile<T, MODE>(p, c, tbase, row_in_tile);
+            epilogue_tile<T, MODE>(p, c, tbase, row_in_tile, es);
             // release the accumulator buffer
             ptx::tc_fence_before();
             __syncwarp();
@@ -537,7 +698,7 @@ struct SmemCtlPair {
     int32_t psched[kMaxSchedExperts + 1];  // pair-tile offsets per expert
 };
 
-constexpr size_t kGemmPairSmemBytes = 1024 + size_t(kPairStages) * (kAStageBytes + kBHalfStageBytes) + sizeof(SmemCtlPair);
+constexpr size_t kGemmPairSmemBytes = 1024 + size_t(kPairStages) * (kAStageBytes + kBHalfStageBytes) + sizeof(SmemCtlPair) + kEpiSmemBytes;
 
 template <int MODE, int BK>
 __device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams &p, const SmemCtlPair *ctl, int t, int rank) {
@@ -755,6 +916,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         // ================= epilogue: each CTA drains its own 128 rows =================
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
+        uint8_t *epi_base = reinterpret_cast<uint8_t *>(ctl) + ((sizeof(SmemCtlPair) + 15) & ~size_t(15));
+        EpiSmem es;
+        es.stage = reinterpret_cast<uint32_t *>(epi_base + quarter * kStageWarpBytes);
+        es.rowinfo = reinterpret_cast<int32_t *>(epi_base + kEpiWarps * kStageWarpBytes + quarter * 128);
         const uint32_t leader_empty0 = ptx::mapa_shared(ptx::smem_u32(&ctl->tmem_empty[0]), 0);
         const uint32_t leader_empty1 = ptx::mapa_shared(ptx::smem_u32(&ctl->tmem_empty[1]), 0);
         int it = 0;
@@ -765,7 +930,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             if (!wait_barrier_pair(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
             ptx::tc_fence_after();
             const uint32_t tbase = tmem_base + uint32_t(buf) * BN + (uint32_t(quarter * 32) << 16);
-            if (c.valid) epilogue_tile<T, MODE>(p, c, tbase, row_in_tile);
+            if (c.valid) epilogue_tile<T, MODE>(p, c, tbase, row_in_tile, es);
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(buf ? leader_empty1 : leader_empty0);
