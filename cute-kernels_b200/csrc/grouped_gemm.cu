@@ -330,6 +330,27 @@ __device__ __forceinline__ void stage_read_rows(uint32_t *stage, int lane, int c
     }
 }
 
+// the same transfer split in two, so the global loads of the next chunk fly while the current one is processed
+template <typename T, typename RowPtr>
+__device__ __forceinline__ void rows_prefetch(uint2 *regs, int lane, int col0, int ncols, RowPtr row_ptr) {
+    using RP = RowPass<T>;
+    const int col = col0 + (lane % RP::kLpr) * RP::kElemsPerLane;
+#pragma unroll
+    for (int it = 0; it < RP::kIters; ++it) {
+        const T *src = row_ptr(RP::row(it, lane));
+        regs[it] = make_uint2(0u, 0u);
+        if (src != nullptr && col < ncols) regs[it] = __ldg(reinterpret_cast<const uint2 *>(src + col));
+    }
+}
+template <typename T>
+__device__ __forceinline__ void rows_to_stage(uint32_t *stage, int lane, const uint2 *regs) {
+    using RP = RowPass<T>;
+    const int sub = lane % RP::kLpr;
+#pragma unroll
+    for (int it = 0; it < RP::kIters; ++it)
+        *reinterpret_cast<uint2 *>(stage + RP::row(it, lane) * kStagePitchWords + 2 * sub) = regs[it];
+}
+
 template <typename T, int MODE>
 __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoord &c, uint32_t tbase, int row_in_tile,
                                               const EpiSmem &es) {
@@ -459,21 +480,30 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
         T *dh = reinterpret_cast<T *>(p.out0) + prow0 * ld_h;
         const int n0 = c.n_tile * BN;
         float dgate_w = 0.0f;
+        uint2 pu[RP::kIters], pg[RP::kIters];  // saved up / gate values of the next chunk, in flight
+        auto h_up = [&](int r) -> const T * { return h + r * ld_h; };
+        auto h_gate = [&](int r) -> const T * { return h + r * ld_h + p.N; };
+        rows_prefetch<T>(pu, lane, n0, p.N, h_up);
+        rows_prefetch<T>(pg, lane, n0, p.N, h_gate);
 #pragma unroll 1
         for (int cc = 0; cc < BN; cc += 32) {
             if (n0 + cc >= p.N) break;  // whole chunk past the valid columns (uniform across the warp)
             uint32_t w[RP::kWords];
             float vu[32], vg[32];
-            stage_read_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> const T * { return h + r * ld_h; });
+            rows_to_stage<T>(es.stage, lane, pu);
             __syncwarp();
             stage_get_row<RP::kWords>(es.stage, lane, w);
             unpack32<T>(w, vu);
             __syncwarp();
-            stage_read_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> const T * { return h + r * ld_h + p.N; });
+            rows_to_stage<T>(es.stage, lane, pg);
             __syncwarp();
             stage_get_row<RP::kWords>(es.stage, lane, w);
             unpack32<T>(w, vg);
             __syncwarp();
+            if (cc + 32 < BN && n0 + cc + 32 < p.N) {
+                rows_prefetch<T>(pu, lane, n0 + cc + 32, p.N, h_up);
+                rows_prefetch<T>(pg, lane, n0 + cc + 32, p.N, h_gate);
+            }
             uint32_t r[32];
             ptx::tmem_ld32(tbase + cc, r);
             ptx::tmem_ld_wait();

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids,
             for (int j = 0; j < kLoads; ++j) key[j] = load_key(ids, b + 32 * j, n, size, bad);
 #pragma unroll
             for (int j = 0; j < kLoads; ++j)
-                if (key[j] >= 0) wh[key[j] * 32 + lane] += 1;
+                if (key[j] >= 0) atomicAdd(&wh[key[j] * 32 + lane], 1u);  // private slot: a fire-and-forget shared-memory add
         }
         __syncwarp();
         // lanes -> warp -> block -> one global atomic per value per block (same-sector atomics serialise in L2,
@@ -153,13 +153,15 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
         int32_t *wh = smem_i + wib * E * 32;  // [E][32]
         for (int i = lane; i < E * 32; i += 32) wh[i] = 0;
         __syncwarp();
-        for (int64_t off = begin; off < end; off += kStep) {
+        const IdT *__restrict__ my_ids = ids + begin;
+        const int len = int(end - begin);
+        for (int off = 0; off < len; off += kStep) {
             int key[kLoads];
 #pragma unroll
-            for (int j = 0; j < kLoads; ++j) key[j] = load_key(ids, off + 32 * j + lane, end, E, bad);
+            for (int j = 0; j < kLoads; ++j) key[j] = load_key(my_ids, int64_t(off + 32 * j + lane), int64_t(len), E, bad);
 #pragma unroll
             for (int j = 0; j < kLoads; ++j)
-                if (key[j] >= 0) wh[key[j] * 32 + lane] += 1;
+                if (key[j] >= 0) atomicAdd(&wh[key[j] * 32 + lane], 1);  // private slot, no dependency chain
         }
         __syncwarp();
         for (int e = 0; e < E; ++e) {
