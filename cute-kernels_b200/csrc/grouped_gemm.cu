@@ -59,6 +59,8 @@ struct GemmParams {
     int act_kind;
     int n_fastest; // WGRAD tile order
     int64_t cap;   // rows allocated for the padded layout
+    int gather_fan;   // > 0: A rows are gathered by TMA from the un-permuted token matrix: token = row_map[p] / gather_fan
+    int gather_b_fan; // WGRAD, > 0: the same for the B operand
 };
 
 struct TileCoord {
@@ -593,29 +595,73 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 
     if (warp == 0) {
         // =================================== TMA producer ===================================
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
-                const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
-                for (int kb = 0; kb < c.k_iters; ++kb) {
-                    if (!wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status)) { ok = false; break; }
-                    const uint32_t full = ptx::smem_u32(&ctl->full[stage]);
-                    ptx::mbar_expect_tx(full, kAStageBytes + kBStageBytes);
-                    const uint32_t sa = smem_a + stage * kAStageBytes;
-                    const uint32_t sb = smem_b + stage * kBStageBytes;
-                    if constexpr (MODE == MODE_WGRAD) {
-                        const int krow = c.k_row0 + kb * BK;
+        // Lane 0 waits for free stages, arms the barrier and issues the tiled loads; when an operand is gathered
+        // (TMA gather4 straight from the un-permuted token matrix) every lane fetches four rows of it.
+        const bool gather_a = p.gather_fan > 0;
+        const bool gather_b = (MODE == MODE_WGRAD) && p.gather_b_fan > 0;
+        int stage = 0;
+        uint32_t phase = 0;
+        int ok = 1;
+        for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+            const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
+            int ridx[4] = {0, 0, 0, 0};
+            if (MODE != MODE_WGRAD && gather_a) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int32_t src = p.row_map[int64_t(c.m_tile) * BM + 4 * lane + q];
+                    ridx[q] = src >= 0 ? src / p.gather_fan : 0;  // pad rows fetch token 0; the epilogue weights them by 0
+                }
+            }
+            for (int kb = 0; kb < c.k_iters; ++kb) {
+                const uint32_t full = ptx::smem_u32(&ctl->full[stage]);
+                if (lane == 0) {
+                    ok = wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status) ? 1 : 0;
+                    if (ok) ptx::mbar_expect_tx(full, kAStageBytes + kBStageBytes);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                const uint32_t sa = smem_a + stage * kAStageBytes;
+                const uint32_t sb = smem_b + stage * kBStageBytes;
+                if constexpr (MODE == MODE_WGRAD) {
+                    const int krow = c.k_row0 + kb * BK;
+                    constexpr int kQ = BK / 4;  // gather4 operations per {128 B x BK rows} box
+                    if (gather_a) {
+                        for (int g = lane; g < (BM / TR::kMnBoxElems) * kQ; g += 32) {
+                            const int j = g / kQ, q = g - j * kQ;
+                            int r4[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int32_t src = p.row_map[krow + 4 * q + i];
+                                r4[i] = src >= 0 ? src / p.gather_fan : 0;  // the other operand is zero on pad rows
+                            }
+                            ptx::tma_gather4(sa + j * TR::kMnBoxBytes + q * 512, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
+                        }
+                    } else if (lane == 0) {
 #pragma unroll
                         for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
                             ptx::tma_load_2d(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
+                    }
+                    if (gather_b) {
+                        for (int g = lane; g < (BN / TR::kMnBoxElems) * kQ; g += 32) {
+                            const int j = g / kQ, q = g - j * kQ;
+                            int r4[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int32_t src = p.row_map[krow + 4 * q + i];
+                                r4[i] = src >= 0 ? src / p.gather_b_fan : 0;
+                            }
+                            ptx::tma_gather4(sb + j * TR::kMnBoxBytes + q * 512, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
+                        }
+                    } else if (lane == 0) {
 #pragma unroll
                         for (int j = 0; j < BN / TR::kMnBoxElems; ++j)
                             ptx::tma_load_2d(sb + j * TR::kMnBoxBytes, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, krow);
-                    } else {
-                        const int k0 = kb * BK;
-                        ptx::tma_load_2d(sa, &p.tmA, full, k0, c.m_tile * BM);
+                    }
+                } else {
+                    const int k0 = kb * BK;
+                    if (gather_a) ptx::tma_gather4(sa + lane * 512, &p.tmA, full, k0, ridx[0], ridx[1], ridx[2], ridx[3]);
+                    else if (lane == 0) ptx::tma_load_2d(sa, &p.tmA, full, k0, c.m_tile * BM);
+                    if (lane == 0) {
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < BN / TR::kMnBoxElems; ++j)
@@ -628,13 +674,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                             ptx::tma_load_3d(sb, &p.tmB, full, k0, c.n_tile * BN, c.e);
                         }
                     }
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
+                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
-            if (!ok) {
-                // aborting: give copies already in flight time to land before the CTA exits
-                for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-            }
+        }
+        if (!ok && lane == 0) {
+            // aborting: give copies already in flight time to land before the CTA exits
+            for (int i = 0; i < 2000; ++i) __nanosleep(1000);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -861,30 +907,72 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 
     if (warp == 0) {
         // ================= TMA producer (one per CTA: own A rows, own half of B) =================
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
-                const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
-                for (int kb = 0; kb < c.k_iters; ++kb) {
-                    if (!wait_barrier_pair(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status)) { ok = false; break; }
-                    if (rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), kStageTx);
-                    const uint32_t full = ptx::mapa_shared(ptx::smem_u32(&ctl->full[stage]), 0);  // the leader's barrier
-                    const uint32_t sa = smem_a + stage * kAStageBytes;
-                    const uint32_t sb = smem_b + stage * kBHalfStageBytes;
-                    const int nb0 = c.n_tile * BN + rank * (BN / 2);  // this CTA's half of the N range
-                    if constexpr (MODE == MODE_WGRAD) {
-                        const int krow = c.k_row0 + kb * BK;
+        const bool gather_a = p.gather_fan > 0;
+        const bool gather_b = (MODE == MODE_WGRAD) && p.gather_b_fan > 0;
+        int stage = 0;
+        uint32_t phase = 0;
+        int ok = 1;
+        for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
+            const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
+            int ridx[4] = {0, 0, 0, 0};
+            if (MODE != MODE_WGRAD && gather_a) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int32_t src = p.row_map[int64_t(c.m_tile) * BM + 4 * lane + q];
+                    ridx[q] = src >= 0 ? src / p.gather_fan : 0;
+                }
+            }
+            for (int kb = 0; kb < c.k_iters; ++kb) {
+                if (lane == 0) {
+                    ok = wait_barrier_pair(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status) ? 1 : 0;
+                    if (ok && rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), kStageTx);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                const uint32_t full = ptx::mapa_shared(ptx::smem_u32(&ctl->full[stage]), 0);  // the leader's barrier
+                const uint32_t sa = smem_a + stage * kAStageBytes;
+                const uint32_t sb = smem_b + stage * kBHalfStageBytes;
+                const int nb0 = c.n_tile * BN + rank * (BN / 2);  // this CTA's half of the N range
+                if constexpr (MODE == MODE_WGRAD) {
+                    const int krow = c.k_row0 + kb * BK;
+                    constexpr int kQ = BK / 4;
+                    if (gather_a) {
+                        for (int g = lane; g < (BM / TR::kMnBoxElems) * kQ; g += 32) {
+                            const int j = g / kQ, q = g - j * kQ;
+                            int r4[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int32_t src = p.row_map[krow + 4 * q + i];
+                                r4[i] = src >= 0 ? src / p.gather_fan : 0;
+                            }
+                            ptx::tma_gather4_pair(sa + j * TR::kMnBoxBytes + q * 512, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
+                        }
+                    } else if (lane == 0) {
 #pragma unroll
                         for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
                             ptx::tma_load_2d_pair(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
+                    }
+                    if (gather_b) {
+                        for (int g = lane; g < ((BN / 2) / TR::kMnBoxElems) * kQ; g += 32) {
+                            const int j = g / kQ, q = g - j * kQ;
+                            int r4[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int32_t src = p.row_map[krow + 4 * q + i];
+                                r4[i] = src >= 0 ? src / p.gather_b_fan : 0;
+                            }
+                            ptx::tma_gather4_pair(sb + j * TR::kMnBoxBytes + q * 512, &p.tmB, full, nb0 + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
+                        }
+                    } else if (lane == 0) {
 #pragma unroll
                         for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
                             ptx::tma_load_2d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow);
-                    } else {
-                        const int k0 = kb * BK;
-                        ptx::tma_load_2d_pair(sa, &p.tmA, full, k0, c.m_tile * BM);
+                    }
+                } else {
+                    const int k0 = kb * BK;
+                    if (gather_a) ptx::tma_gather4_pair(sa + lane * 512, &p.tmA, full, k0, ridx[0], ridx[1], ridx[2], ridx[3]);
+                    else if (lane == 0) ptx::tma_load_2d_pair(sa, &p.tmA, full, k0, c.m_tile * BM);
+                    if (lane == 0) {
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
@@ -896,12 +984,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                             ptx::tma_load_3d_pair(sb, &p.tmB, full, k0, nb0, c.e);
                         }
                     }
-                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
                 }
+                if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
             }
-            if (!ok) {
-                for (int i = 0; i < 2000; ++i) __nanosleep(1000);
-            }
+        }
+        if (!ok && lane == 0) {
+            for (int i = 0; i < 2000; ++i) __nanosleep(1000);
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -1092,16 +1180,27 @@ static int map_act_mnmajor(CUtensorMap *tm, const void *a, int64_t cap, int cols
     return encode_map<T>(tm, a, 2, dims, box, true);
 }
 
+// token matrix [rows, K] addressed row by row for TMA gather4: box {BK, 1}
+template <typename T>
+static int map_a_gather(CUtensorMap *tm, const void *a, int64_t rows, int K) {
+    const uint64_t dims[2] = {uint64_t(K), uint64_t(rows)};
+    const uint32_t box[2] = {uint32_t(GemmTraits<T>::BK), 1};
+    return encode_map<T>(tm, a, 2, dims, box);
+}
+
 static bool dims_ok(int64_t cap, int a, int b) { return cap > 0 && cap % BM == 0 && a > 0 && b > 0 && a % 8 == 0 && b % 8 == 0; }
 
 template <typename T>
 static int up_act_fwd_t(const void *xg, const void *wfc, const void *gate_w, const int32_t *row_map,
                         const int32_t *mtile_off, void *act, void *h, int E, int64_t cap, int H, int I, int act_kind,
-                        int32_t *dev_status, cudaStream_t stream) {
+                        int32_t *dev_status, cudaStream_t stream, int64_t gather_rows = 0, int gather_fan = 0) {
     GemmParams p = {};
     p.cap = cap;
     int rc;
-    if ((rc = map_a_kmajor<T>(&p.tmA, xg, cap, H)) != CK_OK) return rc;
+    if (gather_fan > 0) {
+        if ((rc = map_a_gather<T>(&p.tmA, xg, gather_rows, H)) != CK_OK) return rc;
+        p.gather_fan = gather_fan;
+    } else if ((rc = map_a_kmajor<T>(&p.tmA, xg, cap, H)) != CK_OK) return rc;
     if ((rc = map_w_kmajor<T>(&p.tmB, wfc, E, 2 * I, H, BN / 2)) != CK_OK) return rc;
     p.mtile_off = mtile_off; p.row_map = row_map; p.gate_w = gate_w; p.out0 = act; p.out1 = h; p.dev_status = dev_status;
     p.E = E; p.n_tiles = (I + BN / 2 - 1) / (BN / 2); p.N = I; p.K = H; p.act_kind = act_kind; p.top_k = 1;
@@ -1125,11 +1224,14 @@ static int down_combine_fwd_t(const void *act, const void *wproj, const int32_t 
 template <typename T>
 static int dgrad_down_t(const void *dyg, const void *wproj, const void *h, const void *gate_w, const int32_t *row_map,
                         const int32_t *mtile_off, void *dh, float *dgates, int E, int64_t cap, int H, int I, int act_kind,
-                        int32_t *dev_status, cudaStream_t stream) {
+                        int32_t *dev_status, cudaStream_t stream, int64_t gather_rows = 0, int gather_fan = 0) {
     GemmParams p = {};
     p.cap = cap;
     int rc;
-    if ((rc = map_a_kmajor<T>(&p.tmA, dyg, cap, H)) != CK_OK) return rc;
+    if (gather_fan > 0) {
+        if ((rc = map_a_gather<T>(&p.tmA, dyg, gather_rows, H)) != CK_OK) return rc;
+        p.gather_fan = gather_fan;
+    } else if ((rc = map_a_kmajor<T>(&p.tmA, dyg, cap, H)) != CK_OK) return rc;
     if ((rc = map_w_mnmajor<T>(&p.tmB, wproj, E, H, I)) != CK_OK) return rc;
     p.mtile_off = mtile_off; p.row_map = row_map; p.gate_w = gate_w; p.h_in = h; p.out0 = dh; p.dgates = dgates;
     p.dev_status = dev_status;
@@ -1150,14 +1252,28 @@ static int dgrad_up_t(const void *dh, const void *wfc, const int32_t *row_map, c
     return launch_gemm<T, MODE_SCATTER_ADD, true>(p, (cap / BM) * p.n_tiles, stream);
 }
 
+// un-permuted [rows, cols] matrix addressed row by row as an MN-major wgrad operand: box {128 bytes of cols, 1}
+template <typename T>
+static int map_act_mn_gather(CUtensorMap *tm, const void *a, int64_t rows, int cols) {
+    const uint64_t dims[2] = {uint64_t(cols), uint64_t(rows)};
+    const uint32_t box[2] = {uint32_t(GemmTraits<T>::kMnBoxElems), 1};
+    return encode_map<T>(tm, a, 2, dims, box, true);
+}
+
 template <typename T>
 static int wgrad_t(const void *a, const void *b, const int32_t *padded_off, void *dw, int E, int64_t cap, int M, int N,
-                   int32_t *dev_status, cudaStream_t stream) {
+                   int32_t *dev_status, cudaStream_t stream, const int32_t *row_map = nullptr, int64_t a_rows = 0,
+                   int a_fan = 0, int64_t b_rows = 0, int b_fan = 0) {
     GemmParams p = {};
     p.cap = cap;
     int rc;
-    if ((rc = map_act_mnmajor<T>(&p.tmA, a, cap, M)) != CK_OK) return rc;
-    if ((rc = map_act_mnmajor<T>(&p.tmB, b, cap, N)) != CK_OK) return rc;
+    if (a_fan > 0) {
+        if ((rc = map_act_mn_gather<T>(&p.tmA, a, a_rows, M)) != CK_OK) return rc;
+    } else if ((rc = map_act_mnmajor<T>(&p.tmA, a, cap, M)) != CK_OK) return rc;
+    if (b_fan > 0) {
+        if ((rc = map_act_mn_gather<T>(&p.tmB, b, b_rows, N)) != CK_OK) return rc;
+    } else if ((rc = map_act_mnmajor<T>(&p.tmB, b, cap, N)) != CK_OK) return rc;
+    p.gather_fan = a_fan; p.gather_b_fan = b_fan; p.row_map = row_map;
     p.padded_off = padded_off; p.out0 = dw; p.dev_status = dev_status;
     p.E = E; p.m_tiles_w = (M + BM - 1) / BM; p.n_tiles = (N + BN - 1) / BN; p.M = M; p.N = N;
     // keep the smaller operand panel set L2 resident: iterate the shorter output dimension fastest
@@ -1208,6 +1324,15 @@ extern "C" int ck_moe_up_act_fwd(const void *xg, const void *wfc, const void *ga
     CK_DISPATCH_DTYPE(dtype, (up_act_fwd_t<T>(xg, wfc, gate_w, row_map, mtile_off, act, h, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream)));
 }
 
+extern "C" int ck_moe_up_act_fwd_gather(const void *x, int64_t tokens, int top_k, const void *wfc, const void *gate_w,
+                                        const int32_t *row_map, const int32_t *mtile_off, void *act, void *h, int E,
+                                        int64_t cap, int H, int I, int act_kind, int dtype, int32_t *dev_status,
+                                        void *stream) {
+    if (!x || tokens <= 0 || top_k <= 0 || !wfc || !row_map || !mtile_off || !act || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
+    if (act_kind != CK_ACT_SWIGLU && act_kind != CK_ACT_GLU) return CK_ERR_UNSUPPORTED;
+    CK_DISPATCH_DTYPE(dtype, (up_act_fwd_t<T>(x, wfc, gate_w, row_map, mtile_off, act, h, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream, tokens, top_k)));
+}
+
 extern "C" int ck_moe_down_combine_fwd(const void *act, const void *wproj, const int32_t *row_map,
                                        const int32_t *mtile_off, float *out32, int E, int64_t cap, int H, int I,
                                        int top_k, int dtype, int32_t *dev_status, void *stream) {
@@ -1221,6 +1346,23 @@ extern "C" int ck_moe_dgrad_down(const void *dyg, const void *wproj, const void 
     if (!dyg || !wproj || !h || !row_map || !mtile_off || !dh || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
     if (act_kind != CK_ACT_SWIGLU && act_kind != CK_ACT_GLU) return CK_ERR_UNSUPPORTED;
     CK_DISPATCH_DTYPE(dtype, (dgrad_down_t<T>(dyg, wproj, h, gate_w, row_map, mtile_off, dh, dgates, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream)));
+}
+
+extern "C" int ck_moe_dgrad_down_gather(const void *dy, int64_t tokens, int top_k, const void *wproj, const void *h,
+                                        const void *gate_w, const int32_t *row_map, const int32_t *mtile_off, void *dh,
+                                        float *dgates, int E, int64_t cap, int H, int I, int act_kind, int dtype,
+                                        int32_t *dev_status, void *stream) {
+    if (!dy || tokens <= 0 || top_k <= 0 || !wproj || !h || !row_map || !mtile_off || !dh || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
+    if (act_kind != CK_ACT_SWIGLU && act_kind != CK_ACT_GLU) return CK_ERR_UNSUPPORTED;
+    CK_DISPATCH_DTYPE(dtype, (dgrad_down_t<T>(dy, wproj, h, gate_w, row_map, mtile_off, dh, dgates, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream, tokens, top_k)));
+}
+
+extern "C" int ck_moe_wgrad_gather(const void *a, int64_t a_rows, int a_fan, const void *b, int64_t b_rows, int b_fan,
+                                   const int32_t *row_map, const int32_t *padded_off, void *dw, int E, int64_t cap, int M,
+                                   int N, int dtype, int32_t *dev_status, void *stream) {
+    if (!a || !b || !row_map || !padded_off || !dw || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, M, N)) return CK_ERR_SHAPE;
+    if (a_fan < 0 || b_fan < 0 || (a_fan > 0 && a_rows <= 0) || (b_fan > 0 && b_rows <= 0)) return CK_ERR_SHAPE;
+    CK_DISPATCH_DTYPE(dtype, (wgrad_t<T>(a, b, padded_off, dw, E, cap, M, N, dev_status, (cudaStream_t)stream, row_map, a_rows, a_fan, b_rows, b_fan)));
 }
 
 extern "C" int ck_moe_dgrad_up(const void *dh, const void *wfc, const int32_t *row_map, const int32_t *mtile_off,

@@ -41,8 +41,11 @@ PROTOTYPES = {
     "ck_moe_gather_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i64, _i, _vp]),
     "ck_cast_from_f32": (_i, [_vp, _vp, _i64, _i, _vp]),
     "ck_moe_up_act_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_up_act_fwd_gather": (_i, [_vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_moe_down_combine_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_moe_dgrad_down": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_dgrad_down_gather": (_i, [_vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_wgrad_gather": (_i, [_vp, _i64, _i, _vp, _i64, _i, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _vp, _vp]),
     "ck_moe_dgrad_up": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_moe_wgrad": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _vp, _vp]),
     "ck_moe_grouped_linear": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),

@@ -72,6 +72,20 @@ def _up_act_fwd_impl(xg: torch.Tensor, wfc: torch.Tensor, gate_w: torch.Tensor |
     _lib.check(st, "ck_moe_up_act_fwd")
 
 
+def _up_act_fwd_gather_impl(x: torch.Tensor, top_k: int, wfc: torch.Tensor, gate_w: torch.Tensor | None,
+                            row_map: torch.Tensor, mtile_off: torch.Tensor, act: torch.Tensor, h: torch.Tensor | None,
+                            act_kind: int) -> None:
+    _lib.require_cuda(x, wfc, act)
+    status = _lib.status_word(x.device)
+    E, two_i, H = wfc.shape
+    with torch.cuda.device(x.device), _lib.launch("up_act_fwd", 1, 2.0 * act.size(0) * two_i * H):
+        st = _lib.lib.ck_moe_up_act_fwd_gather(x.data_ptr(), x.size(0), top_k, wfc.data_ptr(), _lib.ptr(gate_w),
+                                               row_map.data_ptr(), mtile_off.data_ptr(), act.data_ptr(), _lib.ptr(h), E,
+                                               act.size(0), H, two_i // 2, act_kind, _lib.dtype_code(x.dtype),
+                                               status.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_up_act_fwd_gather")
+
+
 def _down_combine_fwd_impl(act: torch.Tensor, wproj: torch.Tensor, row_map: torch.Tensor, mtile_off: torch.Tensor,
                            out32: torch.Tensor, top_k: int) -> None:
     _lib.require_cuda(act, wproj, out32)
@@ -96,6 +110,35 @@ def _dgrad_down_impl(dyg: torch.Tensor, wproj: torch.Tensor, h: torch.Tensor, ga
                                         dyg.size(0), H, I, act_kind, _lib.dtype_code(dyg.dtype), status.data_ptr(),
                                         _lib.stream_ptr())
     _lib.check(st, "ck_moe_dgrad_down")
+
+
+def _dgrad_down_gather_impl(dy: torch.Tensor, top_k: int, wproj: torch.Tensor, h: torch.Tensor,
+                            gate_w: torch.Tensor | None, row_map: torch.Tensor, mtile_off: torch.Tensor, dh: torch.Tensor,
+                            dgates: torch.Tensor | None, act_kind: int) -> None:
+    _lib.require_cuda(dy, wproj, h, dh, dgates)
+    status = _lib.status_word(dy.device)
+    E, H, I = wproj.shape
+    with torch.cuda.device(dy.device), _lib.launch("dgrad_down", 1, 2.0 * dh.size(0) * H * I):
+        st = _lib.lib.ck_moe_dgrad_down_gather(dy.data_ptr(), dy.size(0), top_k, wproj.data_ptr(), h.data_ptr(),
+                                               _lib.ptr(gate_w), row_map.data_ptr(), mtile_off.data_ptr(), dh.data_ptr(),
+                                               _lib.ptr(dgates), E, dh.size(0), H, I, act_kind,
+                                               _lib.dtype_code(dy.dtype), status.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_dgrad_down_gather")
+
+
+def _wgrad_gather_impl(a: torch.Tensor, a_fan: int, b: torch.Tensor, b_fan: int, row_map: torch.Tensor,
+                       padded_off: torch.Tensor, dw: torch.Tensor) -> None:
+    """dW[e] = A_e^T B_e; an operand with fan > 0 is the un-permuted matrix and is gathered by TMA."""
+    _lib.require_cuda(a, b, dw)
+    status = _lib.status_word(a.device)
+    E, M, N = dw.shape
+    assert a.size(1) == M and b.size(1) == N
+    cap = row_map.numel()
+    with torch.cuda.device(a.device), _lib.launch("wgrad", 1, 2.0 * cap * M * N):
+        st = _lib.lib.ck_moe_wgrad_gather(a.data_ptr(), a.size(0), a_fan, b.data_ptr(), b.size(0), b_fan,
+                                          row_map.data_ptr(), padded_off.data_ptr(), dw.data_ptr(), E, cap, M, N,
+                                          _lib.dtype_code(a.dtype), status.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_wgrad_gather")
 
 
 def _dgrad_up_impl(dh: torch.Tensor, wfc: torch.Tensor, row_map: torch.Tensor, mtile_off: torch.Tensor,
@@ -177,8 +220,11 @@ def _row_dots_impl(a: torch.Tensor, pos: torch.Tensor, b: torch.Tensor, dots: to
 gather_rows = _make_op("moe_gather_rows", _gather_rows_impl, {"dst"})
 cast_from_f32 = _make_op("cast_from_f32", _cast_from_f32_impl, {"dst"})
 up_act_fwd = _make_op("moe_up_act_fwd", _up_act_fwd_impl, {"act", "h"})
+up_act_fwd_gather = _make_op("moe_up_act_fwd_gather", _up_act_fwd_gather_impl, {"act", "h"})
 down_combine_fwd = _make_op("moe_down_combine_fwd", _down_combine_fwd_impl, {"out32"})
 dgrad_down = _make_op("moe_dgrad_down", _dgrad_down_impl, {"dh", "dgates"})
+dgrad_down_gather = _make_op("moe_dgrad_down_gather", _dgrad_down_gather_impl, {"dh", "dgates"})
+wgrad_gather = _make_op("moe_wgrad_gather", _wgrad_gather_impl, {"dw"})
 dgrad_up = _make_op("moe_dgrad_up", _dgrad_up_impl, {"dx32"})
 wgrad = _make_op("moe_wgrad", _wgrad_impl, {"dw"})
 grouped_linear = _make_op("moe_grouped_linear", _grouped_linear_impl, {"y"})
@@ -199,6 +245,14 @@ def _from_f32(src32: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------------
 # fused expert computation
 # ---------------------------------------------------------------------------------------------------
+# Route the permutations through TMA gather4 inside the GEMMs (no grouped copies of x / dy) instead of the
+# streaming gather kernel.  Measured on B200 (Mixtral-shaped layer, bf16): the gathered operand is fetched 512
+# bytes per TMA operation (four 128-byte swizzle rows), and the up projection drops from 1180 to 446 TFLOP/s, wgrad
+# from 1220 to 293; the separate gather costs 0.14 ms per use.  So this stays off unless CK_TMA_GATHER=1.
+import os as _os
+
+TMA_GATHER = _os.environ.get("CK_TMA_GATHER", "0") == "1"
+
 class _FusedExperts(torch.autograd.Function):
     """y[t] = sum_j w[t, j] * W_proj[e_tj] @ act(W_fc[e_tj] @ x[t]) with saved-for-backward tensors in the
     padded grouped layout.  Mirrors _ScatteredExperts (ops.py:143-292) for c_fc + activation + c_proj at once."""
@@ -214,17 +268,24 @@ class _FusedExperts(torch.autograd.Function):
 
         x = x.contiguous()
         gate_w = router_weights.contiguous().view(-1)
-        xg = torch.empty(cap, H, dtype=dt, device=dev)
-        gather_rows(x, xg, row_map, padded_off, top_k)
         act = torch.empty(cap, I, dtype=dt, device=dev)
         h = torch.empty(cap, two_i, dtype=dt, device=dev) if need_grad else None
-        up_act_fwd(xg, w_fc, gate_w, row_map, mtile_off, act, h, act_kind)
+        if TMA_GATHER:
+            # the up projection gathers the routed token rows itself (TMA gather4); the grouped copy of x is
+            # only built in backward, where the weight gradient contracts over it
+            xg = None
+            up_act_fwd_gather(x, top_k, w_fc, gate_w, row_map, mtile_off, act, h, act_kind)
+        else:
+            xg = torch.empty(cap, H, dtype=dt, device=dev)
+            gather_rows(x, xg, row_map, padded_off, top_k)
+            up_act_fwd(xg, w_fc, gate_w, row_map, mtile_off, act, h, act_kind)
         out32 = torch.zeros(T, H, dtype=torch.float32, device=dev)
         down_combine_fwd(act, w_proj, row_map, mtile_off, out32, top_k)
         y = _from_f32(out32, dt)
 
         if need_grad:
-            ctx.save_for_backward(xg, act, h, gate_w, w_fc, w_proj, row_map, mtile_off, padded_off)
+            ctx.save_for_backward(x if xg is None else xg, act, h, gate_w, w_fc, w_proj, row_map, mtile_off, padded_off)
+        ctx.x_is_grouped = xg is not None
         ctx.top_k = top_k
         ctx.act_kind = act_kind
         ctx.tokens = T
@@ -240,23 +301,33 @@ class _FusedExperts(torch.autograd.Function):
         need_x, need_rw, need_wfc, need_wproj = ctx.needs_input_grad[:4]
 
         dy = dy.contiguous().to(dt)
-        dyg = torch.empty(cap, H, dtype=dt, device=dev)
-        gather_rows(dy, dyg, row_map, padded_off, top_k)
         dh = torch.empty(cap, two_i, dtype=dt, device=dev)
         dgates = torch.zeros(T * top_k, dtype=torch.float32, device=dev)
-        dgrad_down(dyg, w_proj, h, gate_w, row_map, mtile_off, dh, dgates, act_kind)
-
         d_wproj = d_wfc = dx = d_rw = None
-        if need_wproj:
-            d_wproj = torch.empty_like(w_proj)
-            wgrad(dyg, act, padded_off, d_wproj)
+        if not ctx.x_is_grouped:
+            # every permutation is done by TMA gather inside the GEMMs: no grouped copies of x or dy exist
+            x = xg
+            dgrad_down_gather(dy, top_k, w_proj, h, gate_w, row_map, mtile_off, dh, dgates, act_kind)
+            if need_wproj:
+                d_wproj = torch.empty_like(w_proj)
+                wgrad_gather(dy, top_k, act, 0, row_map, padded_off, d_wproj)
+            if need_wfc:
+                d_wfc = torch.empty_like(w_fc)
+                wgrad_gather(dh, 0, x, top_k, row_map, padded_off, d_wfc)
+        else:
+            dyg = torch.empty(cap, H, dtype=dt, device=dev)
+            gather_rows(dy, dyg, row_map, padded_off, top_k)
+            dgrad_down(dyg, w_proj, h, gate_w, row_map, mtile_off, dh, dgates, act_kind)
+            if need_wproj:
+                d_wproj = torch.empty_like(w_proj)
+                wgrad(dyg, act, padded_off, d_wproj)
+            if need_wfc:
+                d_wfc = torch.empty_like(w_fc)
+                wgrad(dh, xg, padded_off, d_wfc)
         if need_x:
             dx32 = torch.zeros(T, H, dtype=torch.float32, device=dev)
             dgrad_up(dh, w_fc, row_map, mtile_off, dx32, top_k)
             dx = _from_f32(dx32, dt)
-        if need_wfc:
-            d_wfc = torch.empty_like(w_fc)
-            wgrad(dh, xg, padded_off, d_wfc)
         if need_rw:
             d_rw = dgates.view(T, top_k).to(dt)
         return dx, d_rw, d_wfc, d_wproj, None, None, None, None, None

@@ -152,6 +152,14 @@ CK_API int ck_moe_up_act_fwd(const void *xg, const void *wfc, const void *gate_w
                       const int32_t *mtile_off, void *act, void *h, int E, int64_t cap, int H, int I,
                       int act_kind, int dtype, int32_t *dev_status, void *stream);
 
+/* the same with the gather fused into the kernel: the A operand is fetched row by row from the un-permuted
+ * token matrix x [tokens, H] with TMA gather4 (token of padded row p = row_map[p] / top_k), so the routed
+ * rows are never materialised -- scatter2scatter with x_grouped=False (kernels.py:63-66). */
+CK_API int ck_moe_up_act_fwd_gather(const void *x, int64_t tokens, int top_k, const void *wfc, const void *gate_w,
+                                    const int32_t *row_map, const int32_t *mtile_off, void *act, void *h, int E,
+                                    int64_t cap, int H, int I, int act_kind, int dtype, int32_t *dev_status,
+                                    void *stream);
+
 /* down projection + fused gather-back and top-k combine:
  * out32[row_map[p] / k, :] += act[p, :] @ Wproj[e]^T   (fp32 red.add into a zeroed [T, H] buffer).
  * Wproj: [E, H, I] (c_proj.weight). */
@@ -168,6 +176,13 @@ CK_API int ck_moe_dgrad_down(const void *dyg, const void *wproj, const void *h, 
                       int64_t cap, int H, int I, int act_kind, int dtype, int32_t *dev_status,
                       void *stream);
 
+/* ck_moe_dgrad_down with the grad rows gathered by TMA from the un-permuted dy [tokens, H]
+ * (token of padded row p = row_map[p] / top_k) instead of a pre-gathered dyg. */
+CK_API int ck_moe_dgrad_down_gather(const void *dy, int64_t tokens, int top_k, const void *wproj, const void *h,
+                                    const void *gate_w, const int32_t *row_map, const int32_t *mtile_off, void *dh,
+                                    float *dgates, int E, int64_t cap, int H, int I, int act_kind, int dtype,
+                                    int32_t *dev_status, void *stream);
+
 /* dgrad of the up projection fused with the k-way sum:
  *   dx32[row_map[p] / k, :] += dh[p, :] @ Wfc[e]          (fp32 red.add into a zeroed [T, H])  */
 CK_API int ck_moe_dgrad_up(const void *dh, const void *wfc, const int32_t *row_map, const int32_t *mtile_off,
@@ -179,6 +194,14 @@ CK_API int ck_moe_dgrad_up(const void *dh, const void *wfc, const int32_t *row_m
  * without rows, so the caller needs no memset -- ops.py:252 zero-fills instead). */
 CK_API int ck_moe_wgrad(const void *a, const void *b, const int32_t *padded_off, void *dw, int E, int64_t cap,
                  int M, int N, int dtype, int32_t *dev_status, void *stream);
+
+/* ck_moe_wgrad with either operand gathered by TMA from an un-permuted matrix: with a_fan > 0, A is
+ * [a_rows, M] and row p of the padded layout reads A[row_map[p] / a_fan, :] (likewise B with b_fan / b_rows);
+ * a fan of 0 means that operand is already in the padded layout ([cap, M] / [cap, N]).  The operand that is not
+ * gathered must be zero on pad rows.  Replaces group() + group_bwd_W (ops.py:228-260). */
+CK_API int ck_moe_wgrad_gather(const void *a, int64_t a_rows, int a_fan, const void *b, int64_t b_rows, int b_fan,
+                               const int32_t *row_map, const int32_t *padded_off, void *dw, int E, int64_t cap, int M,
+                               int N, int dtype, int32_t *dev_status, void *stream);
 
 /* plain grouped linear on padded rows (used when the activation is an arbitrary callable and for
  * expert-parallel shards whose rows travel back before the combine):

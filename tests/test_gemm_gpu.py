@@ -163,6 +163,16 @@ def test_fused_forward_pieces(dtype, act_kind, case):
     exp_act = gw[:, None] * up_ * (torch.nn.functional.silu(gate_) if act_kind == 0 else torch.sigmoid(gate_))
     torch.testing.assert_close(act[:total].float().cpu(), exp_act, **TOL[dtype])
 
+    # the TMA-gather flavour of the same kernel reads x directly: identical bits on every valid row
+    from cute_kernels.moe import up_act_fwd_gather
+
+    act_g = torch.full((cap, I), float("nan"), dtype=dtype, device="cuda")
+    h_g = torch.full((cap, 2 * I), float("nan"), dtype=dtype, device="cuda")
+    up_act_fwd_gather(p["x"], k, p["w_fc"], p["gate_w"], r.row_map, r.mtile_off, act_g, h_g, act_kind)
+    vrows = valid.cuda()
+    assert torch.equal(act_g[:total], act[:total])  # pad rows included: they are weighted by zero
+    assert torch.equal(h_g[:total][vrows], h[:total][vrows])
+
     out32 = torch.zeros(T, H, dtype=torch.float32, device="cuda")
     down_combine_fwd(act, p["w_proj"], r.row_map, r.mtile_off, out32, k)
     af = act[:total].float().cpu()
@@ -216,6 +226,34 @@ def test_fused_backward_pieces(dtype, act_kind, case):
     exp_dg[rm[valid]] = (a * g).sum(-1)[valid]
     tol = {k_: v * max(1.0, I**0.5 / 4) for k_, v in TOL[dtype].items()}
     torch.testing.assert_close(dgates.cpu(), exp_dg, **tol)
+
+    # the TMA-gather flavour takes the un-permuted grad rows: build dy so that its gathered rows equal dyg
+    from cute_kernels.moe import dgrad_down_gather, wgrad, wgrad_gather
+
+    if k == 1:
+        dy = torch.zeros(T, H, dtype=dtype, device="cuda")
+        dy[(rm[valid] // k).cuda()] = dyg[:total][valid.cuda()]
+        dh_g = torch.full((r.capacity, 2 * I), float("nan"), dtype=dtype, device="cuda")
+        dg_g = torch.zeros(T * k, dtype=torch.float32, device="cuda")
+        dgrad_down_gather(dy, k, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh_g, dg_g, act_kind)
+        assert torch.equal(dh_g[:total], dh[:total])
+    # wgrad with gathered operands against wgrad on pre-gathered copies
+    from cute_kernels.moe import gather_rows
+
+    dy2 = _padded_rows(ref, H, dtype, 8)[:T].contiguous()  # any [T, H] matrix
+    dyg2 = torch.empty(r.capacity, H, dtype=dtype, device="cuda")
+    gather_rows(dy2, dyg2, r.row_map, r.padded_off, k)
+    actz = _padded_rows(ref, I, dtype, 9)
+    dw_a = torch.empty(E, H, I, dtype=dtype, device="cuda")
+    dw_b = torch.empty(E, H, I, dtype=dtype, device="cuda")
+    wgrad(dyg2, actz, r.padded_off, dw_a)
+    wgrad_gather(dy2, k, actz, 0, r.row_map, r.padded_off, dw_b)
+    assert torch.equal(dw_a, dw_b)
+    dw_c = torch.empty(E, I, H, dtype=dtype, device="cuda")
+    dw_d = torch.empty(E, I, H, dtype=dtype, device="cuda")
+    wgrad(actz, dyg2, r.padded_off, dw_c)
+    wgrad_gather(actz, 0, dy2, k, r.row_map, r.padded_off, dw_d)
+    assert torch.equal(dw_c, dw_d)
 
     dh_in = _padded_rows(ref, 2 * I, dtype, 7)
     dx32 = torch.zeros(T, H, dtype=torch.float32, device="cuda")

@@ -87,6 +87,20 @@ def test_ragged_and_edge_shapes(case):
     _compare(res, ref, torch.bfloat16, case["T"])
 
 
+def test_tma_gather_flavour_matches(monkeypatch):
+    """The whole fused layer with every permutation done by TMA gather4 inside the GEMMs."""
+    import cute_kernels.moe as moe
+
+    inp = orc.gen_moe_inputs(6, T=700, H=128, I=200, E=6, k=4)
+    base = _run_fused(inp, torch.bfloat16)
+    monkeypatch.setattr(moe, "TMA_GATHER", True)
+    got = _run_fused(inp, torch.bfloat16)
+    for key in ("y", "dx", "d_w_fc", "d_w_proj"):
+        torch.testing.assert_close(got[key].float(), base[key].float(), rtol=1e-2, atol=1e-3, msg=lambda m, key=key: f"{key}: {m}")
+    ref = orc.moe_fwd_bwd_ref(inp)
+    _compare(got, ref, torch.bfloat16, 700)
+
+
 def test_glu_activation_fused():
     inp = orc.gen_moe_inputs(2, T=300, H=128, I=256, E=4, k=2)
     glu = lambda t: t[..., : t.size(-1) // 2] * torch.sigmoid(t[..., t.size(-1) // 2 :])  # noqa: E731
