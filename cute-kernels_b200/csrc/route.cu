@@ -61,6 +61,26 @@ __device__ __forceinline__ int load_key(const IdT *__restrict__ ids, int64_t idx
     return -1;
 }
 
+// One warp step: kLoads coalesced 32-id loads.  FULL = the whole step lies inside the range, no bounds checks.
+// `p` already points at (step start + lane); ids outside [0, range) become -1 and set `bad`.
+template <typename IdT, bool FULL>
+__device__ __forceinline__ void load_step(const IdT *__restrict__ p, int remaining, int lane, int range, int (&key)[kLoads], bool &bad) {
+    using U = typename std::make_unsigned<IdT>::type;
+    IdT v[kLoads];
+#pragma unroll
+    for (int j = 0; j < kLoads; ++j) {
+        if (FULL || 32 * j + lane < remaining) v[j] = p[32 * j];
+        else v[j] = IdT(0);
+    }
+#pragma unroll
+    for (int j = 0; j < kLoads; ++j) {
+        const bool in = FULL || 32 * j + lane < remaining;
+        const bool ok = U(v[j]) < U(range);
+        key[j] = (in && ok) ? int(v[j]) : -1;
+        bad |= in && !ok;
+    }
+}
+
 constexpr int kLanePrivateMax = 128;  // largest id range that gets a per-lane histogram (16 KiB per warp)
 
 // ------------------------------------------------------------------------------------------------
@@ -87,14 +107,15 @@ __global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids,
         for (int i = lane; i < size * 32; i += 32) wh[i] = 0;
         for (int i = threadIdx.x; i < size; i += blockDim.x) bh[i] = 0;
         __syncthreads();
+        uint32_t *mine = wh + lane;
         for (int64_t c = warp_id; c < nchunks; c += nwarps) {
-            const int64_t b = c * kStep + lane;
+            const int64_t b = c * kStep;
             int key[kLoads];
-#pragma unroll
-            for (int j = 0; j < kLoads; ++j) key[j] = load_key(ids, b + 32 * j, n, size, bad);
+            if (b + kStep <= n) load_step<IdT, true>(ids + b + lane, kStep, lane, size, key, bad);
+            else load_step<IdT, false>(ids + b + lane, int(n - b), lane, size, key, bad);
 #pragma unroll
             for (int j = 0; j < kLoads; ++j)
-                if (key[j] >= 0) atomicAdd(&wh[key[j] * 32 + lane], 1u);  // private slot: a fire-and-forget shared-memory add
+                if (key[j] >= 0) atomicAdd(mine + key[j] * 32, 1u);  // private slot: a fire-and-forget shared-memory add
         }
         __syncwarp();
         // lanes -> warp -> block -> one global atomic per value per block (same-sector atomics serialise in L2,
@@ -153,15 +174,16 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
         int32_t *wh = smem_i + wib * E * 32;  // [E][32]
         for (int i = lane; i < E * 32; i += 32) wh[i] = 0;
         __syncwarp();
-        const IdT *__restrict__ my_ids = ids + begin;
+        const IdT *__restrict__ my_ids = ids + begin + lane;
         const int len = int(end - begin);
+        int32_t *mine = wh + lane;
         for (int off = 0; off < len; off += kStep) {
             int key[kLoads];
-#pragma unroll
-            for (int j = 0; j < kLoads; ++j) key[j] = load_key(my_ids, int64_t(off + 32 * j + lane), int64_t(len), E, bad);
+            if (off + kStep <= len) load_step<IdT, true>(my_ids + off, kStep, lane, E, key, bad);
+            else load_step<IdT, false>(my_ids + off, len - off, lane, E, key, bad);
 #pragma unroll
             for (int j = 0; j < kLoads; ++j)
-                if (key[j] >= 0) atomicAdd(&wh[key[j] * 32 + lane], 1);  // private slot, no dependency chain
+                if (key[j] >= 0) atomicAdd(mine + key[j] * 32, 1);  // private slot, no dependency chain
         }
         __syncwarp();
         for (int e = 0; e < E; ++e) {
@@ -174,17 +196,17 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
         int32_t *wh = smem_i + wib * E;
         for (int e = lane; e < E; e += 32) wh[e] = 0;
         __syncwarp();
-        for (int64_t off = begin; off < end; off += kStep) {
+        const IdT *__restrict__ my_ids = ids + begin + lane;
+        const int len = int(end - begin);
+        for (int off = 0; off < len; off += kStep) {
             int key[kLoads];
+            if (off + kStep <= len) load_step<IdT, true>(my_ids + off, kStep, lane, E, key, bad);
+            else load_step<IdT, false>(my_ids + off, len - off, lane, E, key, bad);
 #pragma unroll
-            for (int j = 0; j < kLoads; ++j) key[j] = load_key(ids, off + 32 * j + lane, end, E, bad);
-#pragma unroll
-            for (int j = 0; j < kLoads; ++j) {
-                const unsigned m = match_key_bits(key[j], nbits);
-                if (key[j] >= 0 && lane == __ffs(m) - 1) wh[key[j]] += __popc(m);
-                __syncwarp();
-            }
+            for (int j = 0; j < kLoads; ++j)
+                if (key[j] >= 0) atomicAdd(&wh[key[j]], 1);
         }
+        __syncwarp();
         for (int e = lane; e < E; e += 32) whist[int64_t(w) * E + e] = wh[e];
     }
     if (__any_sync(0xffffffffu, bad) && lane == 0 && dev_status) atomicOr(dev_status, CK_DEV_RANGE);
@@ -287,9 +309,12 @@ __global__ void __launch_bounds__(1024)
 // route pass 3: stable scatter.  Each warp walks its slice in order; an id's output position is
 // excl_off[e] + whist[w][e] + (ids == e seen so far in this slice).
 // ------------------------------------------------------------------------------------------------
-template <typename IdT, int NBITS>  // NBITS > 0: ids need exactly NBITS bits (unrolled ballots); 0: run-time bit count
+// Peer mask through shared memory: every lane ORs its bit into a per-expert word; after a warp barrier the
+// word holds exactly the lanes with that expert id.  Three instructions per lane and round where a ballot per id
+// bit costs about thirty; two mask buffers alternate so the clearing store of one round never races the ORs of the next.
+template <typename IdT, bool HAS_SEXP, bool HAS_ROWMAP>
 __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
-    route_scatter_kernel(const IdT *__restrict__ ids, int64_t n, int E, int nbits, int64_t slice, int W,
+    route_scatter_kernel(const IdT *__restrict__ ids, int64_t n, int E, int64_t slice, int W,
                          const int32_t *__restrict__ whist, const int32_t *__restrict__ excl_off,
                          const int32_t *__restrict__ padded_off, int32_t *__restrict__ sorted_idx,
                          int32_t *__restrict__ sorted_expert, int32_t *__restrict__ row_map) {
@@ -297,41 +322,59 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
     const int w = blockIdx.x * kRouteWarpsPerBlock + wib;
-    int32_t *delta = smem_i;                       // [E] padded_off - excl_off (block shared)
-    int32_t *wbase = smem_i + E + wib * E;         // [E] next output position per expert (warp private)
-    for (int e = threadIdx.x; e < E; e += blockDim.x) delta[e] = padded_off ? padded_off[e] - excl_off[e] : 0;
+    int32_t *delta = smem_i;                                   // [E] padded_off - excl_off (block shared)
+    int32_t *wbase = smem_i + E + wib * 3 * E;                 // [E] next output position per expert (warp private)
+    unsigned *wmask = reinterpret_cast<unsigned *>(wbase + E); // [2][E] peer masks
+    if (HAS_ROWMAP)
+        for (int e = threadIdx.x; e < E; e += blockDim.x) delta[e] = padded_off[e] - excl_off[e];
     __syncthreads();
     if (w >= W) return;
-    for (int e = lane; e < E; e += 32) wbase[e] = excl_off[e] + whist[int64_t(w) * E + e];
+    for (int e = lane; e < E; e += 32) {
+        wbase[e] = excl_off[e] + whist[int64_t(w) * E + e];
+        wmask[e] = 0u;
+        wmask[E + e] = 0u;
+    }
     __syncwarp();
 
     const unsigned lt = lanemask_lt();
+    const unsigned bit = 1u << lane;
     const int64_t begin = int64_t(w) * slice;
     const int64_t end = min(begin + slice, n);
-    const IdT *__restrict__ my_ids = ids + begin;
+    const IdT *__restrict__ my_ids = ids + begin + lane;
     const int len = int(end - begin);              // a slice is far below 2^31 ids
     const int32_t src0 = int32_t(begin) + lane;    // n < 2^31 is checked by the host wrapper
     bool bad = false;
+    unsigned *mk = wmask;
+    unsigned *mk_other = wmask + E;
     for (int off = 0; off < len; off += kStep) {
         int key[kLoads];
-#pragma unroll
-        for (int j = 0; j < kLoads; ++j) key[j] = load_key(my_ids, int64_t(off + 32 * j + lane), int64_t(len), E, bad);
+        if (off + kStep <= len) load_step<IdT, true>(my_ids + off, kStep, lane, E, key, bad);
+        else load_step<IdT, false>(my_ids + off, len - off, lane, E, key, bad);
 #pragma unroll
         for (int j = 0; j < kLoads; ++j) {
             const int k = key[j];
-            const unsigned m = NBITS > 0 ? match_key_fixed<NBITS>(k) : match_key_bits(k, nbits);
+            const bool valid = k >= 0;
+            if (valid) atomicOr(mk + k, bit);
+            __syncwarp();
+            unsigned m = 0u;
             int b = 0;
-            if (k >= 0) b = wbase[k];
+            if (valid) {
+                m = mk[k];
+                b = wbase[k];
+            }
             __syncwarp();
-            if (k >= 0 && lane == __ffs(m) - 1) wbase[k] = b + __popc(m);
-            __syncwarp();
-            if (k >= 0) {
+            if (valid) {
+                if ((m & lt) == 0u) {  // lowest lane of the group: advance the expert's cursor, reset the mask
+                    wbase[k] = b + __popc(m);
+                    mk[k] = 0u;
+                }
                 const int pos = b + __popc(m & lt);
                 const int32_t src = src0 + off + 32 * j;
                 sorted_idx[pos] = src;
-                if (sorted_expert) sorted_expert[pos] = k;
-                if (row_map) row_map[pos + delta[k]] = src;
+                if (HAS_SEXP) sorted_expert[pos] = k;
+                if (HAS_ROWMAP) row_map[pos + delta[k]] = src;
             }
+            unsigned *t = mk; mk = mk_other; mk_other = t;
         }
     }
 }
@@ -443,24 +486,24 @@ extern "C" int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint3
     route_scan_kernel<<<E, 1024, 0, stream>>>(whist, W, E, counts, excl_off, end_off, padded_off, mtile_off, ticket);
     CK_LAUNCH_CHECK("route_scan_kernel");
     if (W > 0) {
-        const size_t smem = sizeof(int32_t) * (kRouteWarpsPerBlock + 1) * E;
-#define CK_LAUNCH_SCATTER(IDT, NB)                                                                                        \
-    route_scatter_kernel<IDT, NB><<<blocks, threads, smem, stream>>>((const IDT *)ids, n, E, nbits, slice, W, whist, excl_off, \
-                                                                     padded_off, sorted_idx, sorted_expert, row_map)
-#define CK_SCATTER_BY_BITS(IDT)                         \
-    switch (nbits) {                                    \
-        case 1: CK_LAUNCH_SCATTER(IDT, 1); break;       \
-        case 2: CK_LAUNCH_SCATTER(IDT, 2); break;       \
-        case 3: CK_LAUNCH_SCATTER(IDT, 3); break;       \
-        case 4: CK_LAUNCH_SCATTER(IDT, 4); break;       \
-        case 5: CK_LAUNCH_SCATTER(IDT, 5); break;       \
-        case 6: CK_LAUNCH_SCATTER(IDT, 6); break;       \
-        case 7: CK_LAUNCH_SCATTER(IDT, 7); break;       \
-        case 8: CK_LAUNCH_SCATTER(IDT, 8); break;       \
-        default: CK_LAUNCH_SCATTER(IDT, 0); break;      \
-    }
-        if (ids_is_i64) { CK_SCATTER_BY_BITS(int64_t) } else { CK_SCATTER_BY_BITS(int32_t) }
-#undef CK_SCATTER_BY_BITS
+        const size_t smem = sizeof(int32_t) * (3 * kRouteWarpsPerBlock + 1) * E;
+        const bool sexp = sorted_expert != nullptr, rmap = row_map != nullptr;
+#define CK_LAUNCH_SCATTER(IDT, SE, RM)                                                                                     \
+    do {                                                                                                                   \
+        if (smem > 48 * 1024)                                                                                              \
+            CK_CUDA_TRY(cudaFuncSetAttribute(route_scatter_kernel<IDT, SE, RM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        route_scatter_kernel<IDT, SE, RM><<<blocks, threads, smem, stream>>>((const IDT *)ids, n, E, slice, W, whist, excl_off, \
+                                                                            padded_off, sorted_idx, sorted_expert, row_map); \
+    } while (0)
+#define CK_SCATTER_FLAGS(IDT)                                   \
+    do {                                                        \
+        if (sexp && rmap) CK_LAUNCH_SCATTER(IDT, true, true);   \
+        else if (sexp) CK_LAUNCH_SCATTER(IDT, true, false);     \
+        else if (rmap) CK_LAUNCH_SCATTER(IDT, false, true);     \
+        else CK_LAUNCH_SCATTER(IDT, false, false);              \
+    } while (0)
+        if (ids_is_i64) CK_SCATTER_FLAGS(int64_t); else CK_SCATTER_FLAGS(int32_t);
+#undef CK_SCATTER_FLAGS
 #undef CK_LAUNCH_SCATTER
         CK_LAUNCH_CHECK("route_scatter_kernel");
     }
