@@ -14,7 +14,7 @@
 
 namespace ck {
 
-constexpr int kRouteMaxWarps = 148 * 32;  // upper bound on id slices (fixed so workspace size is device independent)
+constexpr int kRouteMaxSlices = 148 * 4;  // upper bound on id slices, one per thread block (fixed so workspace size is device independent)
 constexpr int kRouteWarpsPerBlock = 8;
 constexpr int kLoads = 16;          // coalesced 32-id loads in flight per warp: 2 KiB (int32) of reads per warp step
 constexpr int kStep = 32 * kLoads;  // ids per warp per unrolled step
@@ -108,14 +108,24 @@ __global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids,
         for (int i = threadIdx.x; i < size; i += blockDim.x) bh[i] = 0;
         __syncthreads();
         uint32_t *mine = wh + lane;
-        for (int64_t c = warp_id; c < nchunks; c += nwarps) {
+        // two steps in flight per warp: the loads of step c + nwarps are issued before step c is counted
+        int cur[kLoads], nxt[kLoads];
+        auto fetch = [&](int64_t c, int (&key)[kLoads]) {
             const int64_t b = c * kStep;
-            int key[kLoads];
             if (b + kStep <= n) load_step<IdT, true>(ids + b + lane, kStep, lane, size, key, bad);
             else load_step<IdT, false>(ids + b + lane, int(n - b), lane, size, key, bad);
+        };
+        if (warp_id < nchunks) fetch(warp_id, cur);
+        for (int64_t c = warp_id; c < nchunks; c += nwarps) {
+            const bool more = c + nwarps < nchunks;
+            if (more) fetch(c + nwarps, nxt);
 #pragma unroll
             for (int j = 0; j < kLoads; ++j)
-                if (key[j] >= 0) atomicAdd(mine + key[j] * 32, 1u);  // private slot: a fire-and-forget shared-memory add
+                if (cur[j] >= 0) atomicAdd(mine + cur[j] * 32, 1u);  // private slot: a fire-and-forget shared-memory add
+            if (more) {
+#pragma unroll
+                for (int j = 0; j < kLoads; ++j) cur[j] = nxt[j];
+            }
         }
         __syncwarp();
         // lanes -> warp -> block -> one global atomic per value per block (same-sector atomics serialise in L2,
@@ -159,56 +169,62 @@ __global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids,
 // ------------------------------------------------------------------------------------------------
 template <typename IdT, bool LANE_PRIVATE>
 __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
-    route_hist_kernel(const IdT *__restrict__ ids, int64_t n, int E, int nbits, int64_t slice, int W,
-                      int32_t *__restrict__ whist, int32_t *dev_status) {
+    route_hist_kernel(const IdT *__restrict__ ids, int64_t n, int E, int64_t slice, int32_t *__restrict__ whist,
+                      int32_t *dev_status) {
+    // one thread block per slice; its warps take the 512-id steps of the slice round-robin
     extern __shared__ int32_t smem_i[];
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
-    const int w = blockIdx.x * kRouteWarpsPerBlock + wib;
-    if (w >= W) return;  // whole warp leaves together (no block-level sync below)
-    const int64_t begin = int64_t(w) * slice;
-    const int64_t end = min(begin + slice, n);
+    const int64_t begin = int64_t(blockIdx.x) * slice;
+    const int len = int(min(begin + slice, n) - begin);
+    const IdT *__restrict__ my_ids = ids + begin + lane;
+    int32_t *bh = smem_i;  // [E] block histogram
+    for (int e = threadIdx.x; e < E; e += blockDim.x) bh[e] = 0;
     bool bad = false;
 
     if constexpr (LANE_PRIVATE) {
-        int32_t *wh = smem_i + wib * E * 32;  // [E][32]
+        int32_t *wh = smem_i + E + wib * E * 32;  // [E][32] per warp, bank == lane
         for (int i = lane; i < E * 32; i += 32) wh[i] = 0;
-        __syncwarp();
-        const IdT *__restrict__ my_ids = ids + begin + lane;
-        const int len = int(end - begin);
+        __syncthreads();
         int32_t *mine = wh + lane;
-        for (int off = 0; off < len; off += kStep) {
-            int key[kLoads];
+        constexpr int kStride = kRouteWarpsPerBlock * kStep;
+        int cur[kLoads], nxt[kLoads];
+        auto fetch = [&](int off, int (&key)[kLoads]) {
             if (off + kStep <= len) load_step<IdT, true>(my_ids + off, kStep, lane, E, key, bad);
             else load_step<IdT, false>(my_ids + off, len - off, lane, E, key, bad);
+        };
+        if (wib * kStep < len) fetch(wib * kStep, cur);
+        for (int off = wib * kStep; off < len; off += kStride) {  // next step's loads fly while this one is counted
+            const bool more = off + kStride < len;
+            if (more) fetch(off + kStride, nxt);
 #pragma unroll
             for (int j = 0; j < kLoads; ++j)
-                if (key[j] >= 0) atomicAdd(mine + key[j] * 32, 1);  // private slot, no dependency chain
+                if (cur[j] >= 0) atomicAdd(mine + cur[j] * 32, 1);  // private slot, no dependency chain
+            if (more) {
+#pragma unroll
+                for (int j = 0; j < kLoads; ++j) cur[j] = nxt[j];
+            }
         }
         __syncwarp();
         for (int e = 0; e < E; ++e) {
             int c = wh[e * 32 + lane];
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
-            if (lane == 0) whist[int64_t(w) * E + e] = c;
+            if (lane == 0 && c) atomicAdd(&bh[e], c);
         }
     } else {
-        int32_t *wh = smem_i + wib * E;
-        for (int e = lane; e < E; e += 32) wh[e] = 0;
-        __syncwarp();
-        const IdT *__restrict__ my_ids = ids + begin + lane;
-        const int len = int(end - begin);
-        for (int off = 0; off < len; off += kStep) {
+        __syncthreads();
+        for (int off = wib * kStep; off < len; off += kRouteWarpsPerBlock * kStep) {
             int key[kLoads];
             if (off + kStep <= len) load_step<IdT, true>(my_ids + off, kStep, lane, E, key, bad);
             else load_step<IdT, false>(my_ids + off, len - off, lane, E, key, bad);
 #pragma unroll
             for (int j = 0; j < kLoads; ++j)
-                if (key[j] >= 0) atomicAdd(&wh[key[j]], 1);
+                if (key[j] >= 0) atomicAdd(&bh[key[j]], 1);
         }
-        __syncwarp();
-        for (int e = lane; e < E; e += 32) whist[int64_t(w) * E + e] = wh[e];
     }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) whist[int64_t(blockIdx.x) * E + e] = bh[e];
     if (__any_sync(0xffffffffu, bad) && lane == 0 && dev_status) atomicOr(dev_status, CK_DEV_RANGE);
 }
 
@@ -254,8 +270,8 @@ __global__ void __launch_bounds__(1024)
     __shared__ int total_s;
     __shared__ int is_last;
     const int e = blockIdx.x;
-    // W <= 148*32 slices: at most kScanItems consecutive slices per thread, all loads issued before one block scan
-    constexpr int kScanItems = (kRouteMaxWarps + 1023) / 1024;
+    // W <= kRouteMaxSlices: kScanItems consecutive slices per thread, all loads issued before one block scan
+    constexpr int kScanItems = (kRouteMaxSlices + 1023) / 1024;
     int v[kScanItems];
     int tsum = 0;
 #pragma unroll
@@ -309,47 +325,63 @@ __global__ void __launch_bounds__(1024)
 // route pass 3: stable scatter.  Each warp walks its slice in order; an id's output position is
 // excl_off[e] + whist[w][e] + (ids == e seen so far in this slice).
 // ------------------------------------------------------------------------------------------------
-// Peer mask through shared memory: every lane ORs its bit into a per-expert word; after a warp barrier the
-// word holds exactly the lanes with that expert id.  Three instructions per lane and round where a ballot per id
-// bit costs about thirty; two mask buffers alternate so the clearing store of one round never races the ORs of the next.
+// route pass 3: stable scatter, one thread block per slice, tiles of 8 x 512 ids.
+//
+// Inside a tile every id gets (expert, rank among the tile's ids of that expert); the tile is counting-sorted
+// into shared memory and written out expert run by expert run, so global stores cover whole 32-byte sectors
+// (an id-at-a-time scatter made every store a partial-sector read-modify-write in L2 and ran at a seventh of
+// this speed).  The rank inside a warp round comes from a peer mask built in shared memory: every lane ORs its
+// bit into a per-expert word, after a warp barrier the word holds exactly the lanes with that expert id.  Two
+// mask buffers alternate so the clearing store of one round never races the ORs of the next.
+constexpr int kTile = kRouteWarpsPerBlock * kStep;  // 4096 ids
+
 template <typename IdT, bool HAS_SEXP, bool HAS_ROWMAP>
 __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
-    route_scatter_kernel(const IdT *__restrict__ ids, int64_t n, int E, int64_t slice, int W,
+    route_scatter_kernel(const IdT *__restrict__ ids, int64_t n, int E, int64_t slice,
                          const int32_t *__restrict__ whist, const int32_t *__restrict__ excl_off,
                          const int32_t *__restrict__ padded_off, int32_t *__restrict__ sorted_idx,
                          int32_t *__restrict__ sorted_expert, int32_t *__restrict__ row_map) {
     extern __shared__ int32_t smem_i[];
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
-    const int w = blockIdx.x * kRouteWarpsPerBlock + wib;
-    int32_t *delta = smem_i;                                   // [E] padded_off - excl_off (block shared)
-    int32_t *wbase = smem_i + E + wib * 3 * E;                 // [E] next output position per expert (warp private)
-    unsigned *wmask = reinterpret_cast<unsigned *>(wbase + E); // [2][E] peer masks
-    if (HAS_ROWMAP)
-        for (int e = threadIdx.x; e < E; e += blockDim.x) delta[e] = padded_off[e] - excl_off[e];
-    __syncthreads();
-    if (w >= W) return;
-    for (int e = lane; e < E; e += 32) {
-        wbase[e] = excl_off[e] + whist[int64_t(w) * E + e];
-        wmask[e] = 0u;
-        wmask[E + e] = 0u;
+    // shared-memory carve-up (ints)
+    int32_t *gbase = smem_i;                         // [E] next global position per expert
+    int32_t *delta = gbase + E;                      // [E] padded_off - excl_off
+    int32_t *tstart = delta + E;                     // [E + 1] start of each expert's run inside the staged tile
+    int32_t *wcnt = tstart + E + 1;                  // [warps][E] per-warp counts, then per-warp prefixes
+    unsigned *wmask = reinterpret_cast<unsigned *>(wcnt + kRouteWarpsPerBlock * E);  // [warps][2][E]
+    int32_t *stage_idx = reinterpret_cast<int32_t *>(wmask + 2 * kRouteWarpsPerBlock * E);  // [kTile]
+    uint16_t *stage_e = reinterpret_cast<uint16_t *>(stage_idx + kTile);                    // [kTile]
+
+    const int64_t begin = int64_t(blockIdx.x) * slice;
+    const int len = int(min(begin + slice, n) - begin);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int ex = excl_off[e];
+        gbase[e] = ex + whist[int64_t(blockIdx.x) * E + e];
+        delta[e] = HAS_ROWMAP ? padded_off[e] - ex : 0;
     }
-    __syncwarp();
+    for (int i = threadIdx.x; i < kRouteWarpsPerBlock * E; i += blockDim.x) wcnt[i] = 0;
+    for (int i = threadIdx.x; i < 2 * kRouteWarpsPerBlock * E; i += blockDim.x) wmask[i] = 0u;
+    __syncthreads();
 
     const unsigned lt = lanemask_lt();
     const unsigned bit = 1u << lane;
-    const int64_t begin = int64_t(w) * slice;
-    const int64_t end = min(begin + slice, n);
-    const IdT *__restrict__ my_ids = ids + begin + lane;
-    const int len = int(end - begin);              // a slice is far below 2^31 ids
-    const int32_t src0 = int32_t(begin) + lane;    // n < 2^31 is checked by the host wrapper
+    int32_t *mycnt = wcnt + wib * E;
+    unsigned *mk = wmask + wib * 2 * E;
+    unsigned *mk_other = mk + E;
     bool bad = false;
-    unsigned *mk = wmask;
-    unsigned *mk_other = wmask + E;
-    for (int off = 0; off < len; off += kStep) {
+
+    for (int tile = 0; tile < len; tile += kTile) {
+        const int off = tile + wib * kStep;  // this warp's 512 ids of the tile
         int key[kLoads];
-        if (off + kStep <= len) load_step<IdT, true>(my_ids + off, kStep, lane, E, key, bad);
-        else load_step<IdT, false>(my_ids + off, len - off, lane, E, key, bad);
+        if (off + kStep <= len) load_step<IdT, true>(ids + begin + off + lane, kStep, lane, E, key, bad);
+        else if (off < len) load_step<IdT, false>(ids + begin + off + lane, len - off, lane, E, key, bad);
+        else {
+#pragma unroll
+            for (int j = 0; j < kLoads; ++j) key[j] = -1;
+        }
+        // rank of every id among the ids of its expert inside this warp's 512
+        int loc[kLoads];
 #pragma unroll
         for (int j = 0; j < kLoads; ++j) {
             const int k = key[j];
@@ -360,22 +392,74 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
             int b = 0;
             if (valid) {
                 m = mk[k];
-                b = wbase[k];
+                b = mycnt[k];
             }
             __syncwarp();
-            if (valid) {
-                if ((m & lt) == 0u) {  // lowest lane of the group: advance the expert's cursor, reset the mask
-                    wbase[k] = b + __popc(m);
-                    mk[k] = 0u;
-                }
-                const int pos = b + __popc(m & lt);
-                const int32_t src = src0 + off + 32 * j;
-                sorted_idx[pos] = src;
-                if (HAS_SEXP) sorted_expert[pos] = k;
-                if (HAS_ROWMAP) row_map[pos + delta[k]] = src;
+            if (valid && (m & lt) == 0u) {  // lowest lane of the group advances the count and resets the mask
+                mycnt[k] = b + __popc(m);
+                mk[k] = 0u;
             }
+            loc[j] = b + __popc(m & lt);
             unsigned *t = mk; mk = mk_other; mk_other = t;
         }
+        __syncthreads();
+        // per expert: counts of the 8 warps -> exclusive prefixes; tile totals -> run starts
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            int run = 0;
+#pragma unroll
+            for (int w = 0; w < kRouteWarpsPerBlock; ++w) {
+                const int c = wcnt[w * E + e];
+                wcnt[w * E + e] = run;
+                run += c;
+            }
+            tstart[e + 1] = run;  // totals for now
+        }
+        __syncthreads();
+        if (wib == 0) {  // exclusive scan of the totals over the experts (E <= 1024: 32 per lane at most)
+            int carry = 0;
+            for (int base = 0; base < E; base += 32) {
+                const int e = base + lane;
+                const int v = e < E ? tstart[e + 1] : 0;
+                int incl = v;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, d);
+                    if (lane >= d) incl += t;
+                }
+                if (e < E) tstart[e + 1] = carry + incl;
+                carry += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) tstart[0] = 0;
+        }
+        __syncthreads();
+        // counting sort of the tile into shared memory
+#pragma unroll
+        for (int j = 0; j < kLoads; ++j) {
+            const int k = key[j];
+            if (k >= 0) {
+                const int p = tstart[k] + mycnt[k] + loc[j];
+                stage_idx[p] = int32_t(begin) + off + 32 * j + lane;  // n < 2^31 is checked by the host wrapper
+                stage_e[p] = uint16_t(k);
+            }
+        }
+        __syncthreads();
+        // write the tile out: consecutive threads -> consecutive positions of one expert's run
+        const int staged = tstart[E];
+        for (int p = threadIdx.x; p < staged; p += blockDim.x) {
+            const int k = stage_e[p];
+            const int32_t src = stage_idx[p];
+            const int pos = gbase[k] + (p - tstart[k]);
+            sorted_idx[pos] = src;
+            if (HAS_SEXP) sorted_expert[pos] = k;
+            if (HAS_ROWMAP) row_map[pos + delta[k]] = src;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < E; e += blockDim.x) {
+            gbase[e] += tstart[e + 1] - tstart[e];
+#pragma unroll
+            for (int w = 0; w < kRouteWarpsPerBlock; ++w) wcnt[w * E + e] = 0;
+        }
+        __syncthreads();
     }
 }
 
@@ -385,8 +469,8 @@ static void route_plan(int64_t n, int64_t *slice, int *W) {
         *W = 0;
         return;
     }
-    int64_t s = ceil_div64(n, kRouteMaxWarps);
-    s = ceil_div64(s, kStep) * kStep;
+    int64_t s = ceil_div64(n, kRouteMaxSlices);
+    s = ceil_div64(s, kTile) * kTile;  // whole tiles: every warp of a block takes one 512-id step per tile
     *slice = s;
     *W = int(ceil_div64(n, s));
 }
@@ -464,16 +548,15 @@ extern "C" int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint3
     if (row_map) CK_CUDA_TRY(cudaMemsetAsync(row_map, 0xFF, sizeof(int32_t) * ck_route_padded_capacity(n, E), stream));
 
     const int threads = kRouteWarpsPerBlock * 32;
-    const int blocks = (W + kRouteWarpsPerBlock - 1) / kRouteWarpsPerBlock;
-    const int nbits = E > 1 ? 32 - __builtin_clz(unsigned(E - 1)) : 0;
+    const int blocks = W;  // one thread block per slice
     if (W > 0) {
         const bool lane_private = E <= kLanePrivateMax;
-        const size_t smem = sizeof(int32_t) * kRouteWarpsPerBlock * E * (lane_private ? 32 : 1);
+        const size_t smem = sizeof(int32_t) * (size_t(E) + (lane_private ? size_t(kRouteWarpsPerBlock) * E * 32 : 0));
 #define CK_LAUNCH_HIST(IDT, LP)                                                                                          \
     do {                                                                                                                 \
         if (smem > 48 * 1024)                                                                                            \
             CK_CUDA_TRY(cudaFuncSetAttribute(route_hist_kernel<IDT, LP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        route_hist_kernel<IDT, LP><<<blocks, threads, smem, stream>>>((const IDT *)ids, n, E, nbits, slice, W, whist, dev_status); \
+        route_hist_kernel<IDT, LP><<<blocks, threads, smem, stream>>>((const IDT *)ids, n, E, slice, whist, dev_status); \
     } while (0)
         if (ids_is_i64) {
             if (lane_private) CK_LAUNCH_HIST(int64_t, true); else CK_LAUNCH_HIST(int64_t, false);
@@ -486,13 +569,13 @@ extern "C" int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint3
     route_scan_kernel<<<E, 1024, 0, stream>>>(whist, W, E, counts, excl_off, end_off, padded_off, mtile_off, ticket);
     CK_LAUNCH_CHECK("route_scan_kernel");
     if (W > 0) {
-        const size_t smem = sizeof(int32_t) * (3 * kRouteWarpsPerBlock + 1) * E;
+        const size_t smem = sizeof(int32_t) * (size_t(27) * E + 1 + kTile + kTile / 2);  // gbase, delta, tstart, wcnt[8], wmask[16], staged ids + experts
         const bool sexp = sorted_expert != nullptr, rmap = row_map != nullptr;
 #define CK_LAUNCH_SCATTER(IDT, SE, RM)                                                                                     \
     do {                                                                                                                   \
         if (smem > 48 * 1024)                                                                                              \
             CK_CUDA_TRY(cudaFuncSetAttribute(route_scatter_kernel<IDT, SE, RM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        route_scatter_kernel<IDT, SE, RM><<<blocks, threads, smem, stream>>>((const IDT *)ids, n, E, slice, W, whist, excl_off, \
+        route_scatter_kernel<IDT, SE, RM><<<blocks, threads, smem, stream>>>((const IDT *)ids, n, E, slice, whist, excl_off, \
                                                                             padded_off, sorted_idx, sorted_expert, row_map); \
     } while (0)
 #define CK_SCATTER_FLAGS(IDT)                                   \

@@ -50,8 +50,8 @@ def route_workspace_bytes(n: int, num_experts: int) -> int:
     """Python mirror of ck_route_workspace_bytes (kept out of ctypes so torch.compile can trace callers)."""
     if n <= 0:
         return 256 + num_experts * 4
-    slice_len = -(-n // (148 * 32))
-    slice_len = -(-slice_len // 512) * 512
+    slice_len = -(-n // (148 * 4))          # at most 592 slices, one per thread block
+    slice_len = -(-slice_len // 4096) * 4096  # whole 4096-id tiles
     return 256 + -(-n // slice_len) * num_experts * 4
 
 

@@ -103,7 +103,7 @@ CK_API int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint32_t 
  * must not meet the device-wide synchronisation of cudaMalloc / cudaFree.  The scratch is a fixed
  * CK_ROUTE_STATIC_SCRATCH_BYTES array inside the library, held by every GPU that loads it until exit.
  * Same outputs, bit for bit, as ck_route.  Limits: ck_route_workspace_bytes(n, E) must not exceed
- * CK_ROUTE_STATIC_SCRATCH_BYTES (any n at E <= 32; n <= 1,212,416 ids at E = 64; n <= 606,208 at E = 128), otherwise
+ * CK_ROUTE_STATIC_SCRATCH_BYTES (any n at E <= 256; n <= 1,212,416 ids at E = 512; n <= 606,208 at E = 1024), otherwise
  * CK_ERR_RANGE and nothing is launched.  The first call on a device looks up the array's device address
  * (make it outside stream capture).  Calls share the array: do not let two of them overlap on one GPU. */
 #define CK_ROUTE_STATIC_SCRATCH_BYTES (256 + 148 * 32 * 32 * 4)

@@ -135,7 +135,7 @@ def test_route_workspace_bytes_mirror_matches_the_library():
     from cute_kernels import _lib
     from cute_kernels.routing import route_workspace_bytes
 
-    for n in (0, 1, 255, 256, 257, 4096, 32768, 262144, 1 << 20, (1 << 24) + 5):
+    for n in (0, 1, 255, 256, 257, 4096, 4097, 32768, 262144, 1 << 20, (1 << 24) + 5, (1 << 27) + 1):
         for E in (1, 8, 64, 72, 1024):
             assert route_workspace_bytes(n, E) == _lib.lib.ck_route_workspace_bytes(n, E), (n, E)
 

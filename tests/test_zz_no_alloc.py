@@ -70,7 +70,7 @@ def test_route_static_rejects_sizes_beyond_its_scratch():
 
     limit = _lib.lib.ck_route_static_max_bytes()
     assert limit == 256 + 148 * 32 * 32 * 4
-    n, E = 1 << 22, 128
+    n, E = 1 << 22, 1024
     assert _lib.lib.ck_route_workspace_bytes(n, E) > limit
     ids = torch.zeros(n, dtype=torch.int32, device="cuda")
     st, b = _call(True, ids, E)
