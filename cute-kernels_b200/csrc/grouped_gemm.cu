@@ -103,11 +103,15 @@ struct SmemCtl {
 constexpr size_t kGemmSmemBytes_noepi = 1024 /*alignment slack*/ + size_t(kStages) * (kAStageBytes + kBStageBytes) + sizeof(SmemCtl);
 
 // bounded wait: false when the CTA is aborting or the time limit ran out
+// BACKOFF: sleep between polls (epilogue warps: 32 polling lanes would otherwise compete for issue slots with the
+// producer / MMA lanes that share their scheduler)
+template <bool BACKOFF = false>
 __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, SmemCtl *ctl, int32_t *dev_status) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = ptx::globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
+        if (BACKOFF) __nanosleep(100);
         if (ptx::mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0) {
             if (ctl->abort_flag) return false;
@@ -191,13 +195,27 @@ __device__ __forceinline__ void load8(const T *ptr, float *v) {
     }
 }
 
+// sigmoid in the epilogues: 16-bit tensors take sigmoid(x) = 0.5 + 0.5 tanh(0.5 x) with the single-instruction
+// tanh.approx (relative error 2^-11, a few percent of a bf16 ulp); fp32 tensors keep the exp / divide form.
+template <typename T>
+__device__ __forceinline__ float sigmoid_epi(float x) {
+    if constexpr (sizeof(T) == 4) {
+        return sigmoid_fast(x);
+    } else {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+        return fmaf(t, 0.5f, 0.5f);
+    }
+}
+template <typename T>
 __device__ __forceinline__ float act_fwd(int kind, float u, float g) {
-    const float s = sigmoid_fast(g);
+    const float s = sigmoid_epi<T>(g);
     return kind == CK_ACT_SWIGLU ? u * g * s : u * s;
 }
 // returns a = act(u, g); d(out)/du and d(out)/dg multipliers
+template <typename T>
 __device__ __forceinline__ void act_bwd(int kind, float u, float g, float &a, float &du_m, float &dg_m) {
-    const float s = sigmoid_fast(g);
+    const float s = sigmoid_epi<T>(g);
     if (kind == CK_ACT_SWIGLU) {
         const float silu = g * s;
         a = u * silu;
@@ -423,7 +441,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
             ptx::tmem_ld_wait();
             float va[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) va[i] = wgt * act_fwd(p.act_kind, __uint_as_float(ru[i]), __uint_as_float(rg[i]));
+            for (int i = 0; i < 32; ++i) va[i] = wgt * act_fwd<T>(p.act_kind, __uint_as_float(ru[i]), __uint_as_float(rg[i]));
             uint32_t w[RP::kWords];
             pack32<T>(va, w);
             stage_put_row<RP::kWords>(es.stage, lane, w);
@@ -513,7 +531,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
             for (int i = 0; i < 32; ++i) {
                 const float acc = __uint_as_float(r[i]);
                 float a, du_m, dg_m;
-                act_bwd(p.act_kind, vu[i], vg[i], a, du_m, dg_m);
+                act_bwd<T>(p.act_kind, vu[i], vg[i], a, du_m, dg_m);
                 dgate_w += a * acc;
                 const float da = wgt * acc;
                 vu[i] = da * du_m;
@@ -599,69 +617,113 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         // (TMA gather4 straight from the un-permuted token matrix) every lane fetches four rows of it.
         const bool gather_a = p.gather_fan > 0;
         const bool gather_b = (MODE == MODE_WGRAD) && p.gather_b_fan > 0;
-        int stage = 0;
-        uint32_t phase = 0;
-        int ok = 1;
-        for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
-            const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
-            int ridx[4] = {0, 0, 0, 0};
-            if (MODE != MODE_WGRAD && gather_a) {
+        if (gather_a || gather_b) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int ok = 1;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
+                int ridx[4] = {0, 0, 0, 0};
+                if (MODE != MODE_WGRAD && gather_a) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int32_t src = p.row_map[int64_t(c.m_tile) * BM + 4 * lane + q];
-                    ridx[q] = src >= 0 ? src / p.gather_fan : 0;  // pad rows fetch token 0; the epilogue weights them by 0
+                    for (int q = 0; q < 4; ++q) {
+                        const int32_t src = p.row_map[int64_t(c.m_tile) * BM + 4 * lane + q];
+                        ridx[q] = src >= 0 ? src / p.gather_fan : 0;  // pad rows fetch token 0; the epilogue weights them by 0
+                    }
+                }
+                for (int kb = 0; kb < c.k_iters; ++kb) {
+                    const uint32_t full = ptx::smem_u32(&ctl->full[stage]);
+                    if (lane == 0) {
+                        ok = wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status) ? 1 : 0;
+                        if (ok) ptx::mbar_expect_tx(full, kAStageBytes + kBStageBytes);
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    const uint32_t sa = smem_a + stage * kAStageBytes;
+                    const uint32_t sb = smem_b + stage * kBStageBytes;
+                    if constexpr (MODE == MODE_WGRAD) {
+                        const int krow = c.k_row0 + kb * BK;
+                        constexpr int kQ = BK / 4;  // gather4 operations per {128 B x BK rows} box
+                        if (gather_a) {
+                            for (int g = lane; g < (BM / TR::kMnBoxElems) * kQ; g += 32) {
+                                const int j = g / kQ, q = g - j * kQ;
+                                int r4[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int32_t src = p.row_map[krow + 4 * q + i];
+                                    r4[i] = src >= 0 ? src / p.gather_fan : 0;  // the other operand is zero on pad rows
+                                }
+                                ptx::tma_gather4(sa + j * TR::kMnBoxBytes + q * 512, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
+                            }
+                        } else if (lane == 0) {
+#pragma unroll
+                            for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
+                                ptx::tma_load_2d(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
+                        }
+                        if (gather_b) {
+                            for (int g = lane; g < (BN / TR::kMnBoxElems) * kQ; g += 32) {
+                                const int j = g / kQ, q = g - j * kQ;
+                                int r4[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int32_t src = p.row_map[krow + 4 * q + i];
+                                    r4[i] = src >= 0 ? src / p.gather_b_fan : 0;
+                                }
+                                ptx::tma_gather4(sb + j * TR::kMnBoxBytes + q * 512, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
+                            }
+                        } else if (lane == 0) {
+#pragma unroll
+                            for (int j = 0; j < BN / TR::kMnBoxElems; ++j)
+                                ptx::tma_load_2d(sb + j * TR::kMnBoxBytes, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, krow);
+                        }
+                    } else {
+                        const int k0 = kb * BK;
+                        if (gather_a) ptx::tma_gather4(sa + lane * 512, &p.tmA, full, k0, ridx[0], ridx[1], ridx[2], ridx[3]);
+                        else if (lane == 0) ptx::tma_load_2d(sa, &p.tmA, full, k0, c.m_tile * BM);
+                        if (lane == 0) {
+                            if constexpr (B_MN) {
+#pragma unroll
+                                for (int j = 0; j < BN / TR::kMnBoxElems; ++j)
+                                    ptx::tma_load_3d(sb + j * TR::kMnBoxBytes, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, k0, c.e);
+                            } else if constexpr (MODE == MODE_UP_ACT) {
+                                // 128 rows of W_up followed by the matching 128 rows of W_gate
+                                ptx::tma_load_3d(sb, &p.tmB, full, k0, c.n_tile * (BN / 2), c.e);
+                                ptx::tma_load_3d(sb + kBStageBytes / 2, &p.tmB, full, k0, p.N + c.n_tile * (BN / 2), c.e);
+                            } else {
+                                ptx::tma_load_3d(sb, &p.tmB, full, k0, c.n_tile * BN, c.e);
+                            }
+                        }
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
-            for (int kb = 0; kb < c.k_iters; ++kb) {
-                const uint32_t full = ptx::smem_u32(&ctl->full[stage]);
-                if (lane == 0) {
-                    ok = wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status) ? 1 : 0;
-                    if (ok) ptx::mbar_expect_tx(full, kAStageBytes + kBStageBytes);
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-                const uint32_t sa = smem_a + stage * kAStageBytes;
-                const uint32_t sb = smem_b + stage * kBStageBytes;
-                if constexpr (MODE == MODE_WGRAD) {
-                    const int krow = c.k_row0 + kb * BK;
-                    constexpr int kQ = BK / 4;  // gather4 operations per {128 B x BK rows} box
-                    if (gather_a) {
-                        for (int g = lane; g < (BM / TR::kMnBoxElems) * kQ; g += 32) {
-                            const int j = g / kQ, q = g - j * kQ;
-                            int r4[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int32_t src = p.row_map[krow + 4 * q + i];
-                                r4[i] = src >= 0 ? src / p.gather_fan : 0;  // the other operand is zero on pad rows
-                            }
-                            ptx::tma_gather4(sa + j * TR::kMnBoxBytes + q * 512, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
-                        }
-                    } else if (lane == 0) {
+            if (!ok && lane == 0) {
+                // aborting: give copies already in flight time to land before the CTA exits
+                for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            }
+        } else if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
+                for (int kb = 0; kb < c.k_iters; ++kb) {
+                    if (!wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status)) { ok = false; break; }
+                    const uint32_t full = ptx::smem_u32(&ctl->full[stage]);
+                    ptx::mbar_expect_tx(full, kAStageBytes + kBStageBytes);
+                    const uint32_t sa = smem_a + stage * kAStageBytes;
+                    const uint32_t sb = smem_b + stage * kBStageBytes;
+                    if constexpr (MODE == MODE_WGRAD) {
+                        const int krow = c.k_row0 + kb * BK;
 #pragma unroll
                         for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
                             ptx::tma_load_2d(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
-                    }
-                    if (gather_b) {
-                        for (int g = lane; g < (BN / TR::kMnBoxElems) * kQ; g += 32) {
-                            const int j = g / kQ, q = g - j * kQ;
-                            int r4[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int32_t src = p.row_map[krow + 4 * q + i];
-                                r4[i] = src >= 0 ? src / p.gather_b_fan : 0;
-                            }
-                            ptx::tma_gather4(sb + j * TR::kMnBoxBytes + q * 512, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
-                        }
-                    } else if (lane == 0) {
 #pragma unroll
                         for (int j = 0; j < BN / TR::kMnBoxElems; ++j)
                             ptx::tma_load_2d(sb + j * TR::kMnBoxBytes, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, krow);
-                    }
-                } else {
-                    const int k0 = kb * BK;
-                    if (gather_a) ptx::tma_gather4(sa + lane * 512, &p.tmA, full, k0, ridx[0], ridx[1], ridx[2], ridx[3]);
-                    else if (lane == 0) ptx::tma_load_2d(sa, &p.tmA, full, k0, c.m_tile * BM);
-                    if (lane == 0) {
+                    } else {
+                        const int k0 = kb * BK;
+                        ptx::tma_load_2d(sa, &p.tmA, full, k0, c.m_tile * BM);
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < BN / TR::kMnBoxElems; ++j)
@@ -674,13 +736,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                             ptx::tma_load_3d(sb, &p.tmB, full, k0, c.n_tile * BN, c.e);
                         }
                     }
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
-                if (++stage == kStages) { stage = 0; phase ^= 1u; }
             }
-        }
-        if (!ok && lane == 0) {
-            // aborting: give copies already in flight time to land before the CTA exits
-            for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            if (!ok) {
+                // aborting: give copies already in flight time to land before the CTA exits
+                for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            }
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -734,7 +796,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++it) {
             const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
             const int buf = it & 1;
-            if (!wait_barrier(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
+            if (!wait_barrier<true>(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
             ptx::tc_fence_after();
             const uint32_t tbase = tmem_base + uint32_t(buf) * BN + (uint32_t(quarter * 32) << 16);
             epilogue_tile<T, MODE>(p, c, tbase, row_in_tile, es);
@@ -818,11 +880,15 @@ __device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams &p, const
     return c;
 }
 
+// BACKOFF: sleep between polls (epilogue warps: 32 polling lanes would otherwise compete for issue slots with the
+// producer / MMA lanes that share their scheduler)
+template <bool BACKOFF = false>
 __device__ __forceinline__ bool wait_barrier_pair(uint32_t bar, uint32_t parity, SmemCtlPair *ctl, int32_t *dev_status) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = ptx::globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
+        if (BACKOFF) __nanosleep(100);
         if (ptx::mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0) {
             if (ctl->abort_flag) return false;
@@ -909,70 +975,113 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         // ================= TMA producer (one per CTA: own A rows, own half of B) =================
         const bool gather_a = p.gather_fan > 0;
         const bool gather_b = (MODE == MODE_WGRAD) && p.gather_b_fan > 0;
-        int stage = 0;
-        uint32_t phase = 0;
-        int ok = 1;
-        for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
-            const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
-            int ridx[4] = {0, 0, 0, 0};
-            if (MODE != MODE_WGRAD && gather_a) {
+        if (gather_a || gather_b) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int ok = 1;
+            for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
+                const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
+                int ridx[4] = {0, 0, 0, 0};
+                if (MODE != MODE_WGRAD && gather_a) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int32_t src = p.row_map[int64_t(c.m_tile) * BM + 4 * lane + q];
-                    ridx[q] = src >= 0 ? src / p.gather_fan : 0;
+                    for (int q = 0; q < 4; ++q) {
+                        const int32_t src = p.row_map[int64_t(c.m_tile) * BM + 4 * lane + q];
+                        ridx[q] = src >= 0 ? src / p.gather_fan : 0;
+                    }
+                }
+                for (int kb = 0; kb < c.k_iters; ++kb) {
+                    if (lane == 0) {
+                        ok = wait_barrier_pair(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status) ? 1 : 0;
+                        if (ok && rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), kStageTx);
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    const uint32_t full = ptx::mapa_shared(ptx::smem_u32(&ctl->full[stage]), 0);  // the leader's barrier
+                    const uint32_t sa = smem_a + stage * kAStageBytes;
+                    const uint32_t sb = smem_b + stage * kBHalfStageBytes;
+                    const int nb0 = c.n_tile * BN + rank * (BN / 2);  // this CTA's half of the N range
+                    if constexpr (MODE == MODE_WGRAD) {
+                        const int krow = c.k_row0 + kb * BK;
+                        constexpr int kQ = BK / 4;
+                        if (gather_a) {
+                            for (int g = lane; g < (BM / TR::kMnBoxElems) * kQ; g += 32) {
+                                const int j = g / kQ, q = g - j * kQ;
+                                int r4[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int32_t src = p.row_map[krow + 4 * q + i];
+                                    r4[i] = src >= 0 ? src / p.gather_fan : 0;
+                                }
+                                ptx::tma_gather4_pair(sa + j * TR::kMnBoxBytes + q * 512, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
+                            }
+                        } else if (lane == 0) {
+#pragma unroll
+                            for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
+                                ptx::tma_load_2d_pair(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
+                        }
+                        if (gather_b) {
+                            for (int g = lane; g < ((BN / 2) / TR::kMnBoxElems) * kQ; g += 32) {
+                                const int j = g / kQ, q = g - j * kQ;
+                                int r4[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int32_t src = p.row_map[krow + 4 * q + i];
+                                    r4[i] = src >= 0 ? src / p.gather_b_fan : 0;
+                                }
+                                ptx::tma_gather4_pair(sb + j * TR::kMnBoxBytes + q * 512, &p.tmB, full, nb0 + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
+                            }
+                        } else if (lane == 0) {
+#pragma unroll
+                            for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
+                                ptx::tma_load_2d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow);
+                        }
+                    } else {
+                        const int k0 = kb * BK;
+                        if (gather_a) ptx::tma_gather4_pair(sa + lane * 512, &p.tmA, full, k0, ridx[0], ridx[1], ridx[2], ridx[3]);
+                        else if (lane == 0) ptx::tma_load_2d_pair(sa, &p.tmA, full, k0, c.m_tile * BM);
+                        if (lane == 0) {
+                            if constexpr (B_MN) {
+#pragma unroll
+                                for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
+                                    ptx::tma_load_3d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, k0, c.e);
+                            } else if constexpr (MODE == MODE_UP_ACT) {
+                                // leader: 128 rows of W_up, peer: the matching 128 rows of W_gate
+                                ptx::tma_load_3d_pair(sb, &p.tmB, full, k0, rank * p.N + c.n_tile * (BN / 2), c.e);
+                            } else {
+                                ptx::tma_load_3d_pair(sb, &p.tmB, full, k0, nb0, c.e);
+                            }
+                        }
+                    }
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
                 }
             }
-            for (int kb = 0; kb < c.k_iters; ++kb) {
-                if (lane == 0) {
-                    ok = wait_barrier_pair(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status) ? 1 : 0;
-                    if (ok && rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), kStageTx);
-                }
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-                const uint32_t full = ptx::mapa_shared(ptx::smem_u32(&ctl->full[stage]), 0);  // the leader's barrier
-                const uint32_t sa = smem_a + stage * kAStageBytes;
-                const uint32_t sb = smem_b + stage * kBHalfStageBytes;
-                const int nb0 = c.n_tile * BN + rank * (BN / 2);  // this CTA's half of the N range
-                if constexpr (MODE == MODE_WGRAD) {
-                    const int krow = c.k_row0 + kb * BK;
-                    constexpr int kQ = BK / 4;
-                    if (gather_a) {
-                        for (int g = lane; g < (BM / TR::kMnBoxElems) * kQ; g += 32) {
-                            const int j = g / kQ, q = g - j * kQ;
-                            int r4[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int32_t src = p.row_map[krow + 4 * q + i];
-                                r4[i] = src >= 0 ? src / p.gather_fan : 0;
-                            }
-                            ptx::tma_gather4_pair(sa + j * TR::kMnBoxBytes + q * 512, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
-                        }
-                    } else if (lane == 0) {
+            if (!ok && lane == 0) {
+                for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            }
+        } else if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
+                const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
+                for (int kb = 0; kb < c.k_iters; ++kb) {
+                    if (!wait_barrier_pair(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status)) { ok = false; break; }
+                    if (rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), kStageTx);
+                    const uint32_t full = ptx::mapa_shared(ptx::smem_u32(&ctl->full[stage]), 0);  // the leader's barrier
+                    const uint32_t sa = smem_a + stage * kAStageBytes;
+                    const uint32_t sb = smem_b + stage * kBHalfStageBytes;
+                    const int nb0 = c.n_tile * BN + rank * (BN / 2);  // this CTA's half of the N range
+                    if constexpr (MODE == MODE_WGRAD) {
+                        const int krow = c.k_row0 + kb * BK;
 #pragma unroll
                         for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
                             ptx::tma_load_2d_pair(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
-                    }
-                    if (gather_b) {
-                        for (int g = lane; g < ((BN / 2) / TR::kMnBoxElems) * kQ; g += 32) {
-                            const int j = g / kQ, q = g - j * kQ;
-                            int r4[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int32_t src = p.row_map[krow + 4 * q + i];
-                                r4[i] = src >= 0 ? src / p.gather_b_fan : 0;
-                            }
-                            ptx::tma_gather4_pair(sb + j * TR::kMnBoxBytes + q * 512, &p.tmB, full, nb0 + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
-                        }
-                    } else if (lane == 0) {
 #pragma unroll
                         for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
                             ptx::tma_load_2d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow);
-                    }
-                } else {
-                    const int k0 = kb * BK;
-                    if (gather_a) ptx::tma_gather4_pair(sa + lane * 512, &p.tmA, full, k0, ridx[0], ridx[1], ridx[2], ridx[3]);
-                    else if (lane == 0) ptx::tma_load_2d_pair(sa, &p.tmA, full, k0, c.m_tile * BM);
-                    if (lane == 0) {
+                    } else {
+                        const int k0 = kb * BK;
+                        ptx::tma_load_2d_pair(sa, &p.tmA, full, k0, c.m_tile * BM);
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
@@ -984,12 +1093,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                             ptx::tma_load_3d_pair(sb, &p.tmB, full, k0, nb0, c.e);
                         }
                     }
+                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
                 }
-                if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
             }
-        }
-        if (!ok && lane == 0) {
-            for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            if (!ok) {
+                for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            }
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -1045,7 +1154,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         for (int t = pair_id; t < ntiles && ok; t += num_pairs, ++it) {
             const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
             const int buf = it & 1;
-            if (!wait_barrier_pair(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
+            if (!wait_barrier_pair<true>(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
             ptx::tc_fence_after();
             const uint32_t tbase = tmem_base + uint32_t(buf) * BN + (uint32_t(quarter * 32) << 16);
             if (c.valid) epilogue_tile<T, MODE>(p, c, tbase, row_in_tile, es);

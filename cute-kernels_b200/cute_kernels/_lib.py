@@ -14,7 +14,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libck_b200.so")
+LIB_PATH = os.environ.get("CK_LIB_PATH") or os.path.join(_HERE, "libck_b200.so")
 
 CK_F32, CK_F16, CK_BF16 = 0, 1, 2
 CK_ACT_SWIGLU, CK_ACT_GLU = 0, 1
