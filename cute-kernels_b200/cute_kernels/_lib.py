@@ -54,6 +54,8 @@ PROTOTYPES = {
     "ck_moe_gather_rows_scaled": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i, _vp]),
     "ck_moe_combine_rows": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i, _vp]),
     "ck_moe_row_dots": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i, _vp]),
+    "ck_router_topk_softmax": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
+    "ck_router_topk_softmax_bwd": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
 }
 
 

@@ -25,6 +25,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import _lib
+from . import router as _router
 from .routing import Routing, route
 
 
@@ -508,9 +509,13 @@ class MoE_Cute(nn.Module):
         hidden_states = self._compute_experts(hidden_states, router_weights, selected_experts)
         return hidden_states.view(original_shape), router_logits
 
-    # the router stays in torch: it is the step before the hot path
+    # the gate projection is a library GEMM; top-k + softmax + int32 ids run as one kernel when the router fits
+    # it (up to 256 experts), else as the reference's three torch ops
     def _compute_routing_weights(self, hidden_states: torch.Tensor):
         router_logits = self.gate(hidden_states)
+        if router_logits.is_cuda and _router.supported(self.num_experts, self.top_k):
+            router_weights, selected_experts = _router.router_topk_softmax(router_logits, self.top_k)
+            return router_logits, router_weights, selected_experts
         router_weights, selected_experts = self._get_topk(router_logits)
         router_weights = F.softmax(router_weights.float(), dim=-1).type_as(hidden_states)
         return router_logits, router_weights, selected_experts

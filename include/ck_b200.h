@@ -238,6 +238,19 @@ CK_API int ck_moe_combine_rows(const void *src, const int32_t *pos, const void *
 CK_API int ck_moe_row_dots(const void *a, const int32_t *pos, const void *b, void *dots, int64_t n, int k,
                            int64_t cols, int dtype, void *stream);
 
+/* ---- router tail --------------------------------------------------------------------------------
+ * ck_router_topk_softmax: for each token, the k largest of its E gate logits (descending; ties to the lower
+ *   expert index), weights = softmax over those k logits computed in fp32 and rounded to `dtype`, ids as int32
+ *   [tokens, k] -- MoE_Torch._compute_routing_weights after the gate projection
+ *   (kernels/scattermoe/torch_implementation.py:122-135 with _get_topk :195-201), one launch instead of
+ *   topk + softmax + type_as, and ids already in the form ck_route reads.  E <= 256, k <= 32 else CK_ERR_RANGE.
+ * ck_router_topk_softmax_bwd: d_logits [tokens, E] = scatter of the softmax backward
+ *   w_j * (dw_j - sum_i w_i dw_i) at ids, zeros elsewhere (what autograd derives for the same three torch ops). */
+CK_API int ck_router_topk_softmax(const void *logits, void *weights, int32_t *ids, int64_t tokens, int E, int k,
+                                  int dtype, void *stream);
+CK_API int ck_router_topk_softmax_bwd(const void *weights, const void *d_weights, const int32_t *ids,
+                                      void *d_logits, int64_t tokens, int E, int k, int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

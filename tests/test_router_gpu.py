@@ -1,0 +1,101 @@
+"""Router tail kernel (top-k + softmax + int32 ids) against the oracle's three-op restatement."""
+
+import pytest
+import torch
+
+import ck_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(1, 8, 1), (5, 8, 2), (300, 8, 2), (257, 64, 8), (1000, 60, 6), (64, 256, 32), (129, 33, 33 - 1), (7, 3, 3)]
+
+
+def _logits(T, E, dtype, seed, ties=False):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, E, generator=g)
+    if ties:
+        x = (x * 2).round() / 2  # many equal logits per row
+    return x.to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("T,E,k", SHAPES)
+def test_router_forward_matches_oracle(dtype, T, E, k):
+    from cute_kernels import router_topk_softmax
+
+    logits = _logits(T, E, dtype, 17 * T + E + k)
+    w, ids = router_topk_softmax(logits.cuda(), k)
+    assert ids.dtype == torch.int32 and w.dtype == dtype and ids.shape == (T, k)
+    w_ref, ids_ref = orc.routing_weights_ref(logits, k, dtype)
+    # the selected logits (values, in order) are bit-identical; ids may differ only between equal logits
+    picked = torch.gather(logits, 1, ids.cpu().long())
+    assert torch.equal(picked, torch.gather(logits, 1, ids_ref))
+    if dtype == torch.float32:
+        assert torch.equal(ids.cpu().long(), ids_ref)
+    # no expert twice in a row
+    assert (torch.sort(ids.cpu(), dim=1).values.diff(dim=1) > 0).all() or k == 1
+    tol = dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(w.cpu().float(), w_ref.float(), **tol)
+
+
+@pytest.mark.parametrize("T,E,k", [(200, 8, 2), (100, 64, 8)])
+def test_router_ties_take_lower_index(T, E, k):
+    from cute_kernels import router_topk_softmax
+
+    logits = _logits(T, E, torch.float32, 5, ties=True)
+    _, ids = router_topk_softmax(logits.cuda(), k)
+    # stable descending sort = descending by value, ties by lower index
+    exp = torch.sort(logits, dim=1, descending=True, stable=True).indices[:, :k]
+    assert torch.equal(ids.cpu().long(), exp)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("T,E,k", [(5, 8, 2), (300, 64, 8), (77, 60, 6), (33, 8, 1)])
+def test_router_backward_matches_autograd(dtype, T, E, k):
+    from cute_kernels import router_topk_softmax
+
+    logits = _logits(T, E, dtype, 3 * T + E)
+    g = torch.Generator().manual_seed(T)
+    dw = torch.randn(T, k, generator=g).to(dtype)
+
+    x = logits.cuda().requires_grad_(True)
+    w, ids = router_topk_softmax(x, k)
+    w.backward(dw.cuda())
+
+    xr = logits.float().requires_grad_(True)
+    vals = torch.gather(xr, 1, ids.cpu().long())          # pinned to the kernel's selection
+    wr = torch.softmax(vals, dim=-1)
+    wr.backward(dw.float())
+    tol = dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.cpu().float(), xr.grad, **tol)
+    # exact zeros off the selection
+    mask = torch.ones(T, E, dtype=torch.bool)
+    mask.scatter_(1, ids.cpu().long(), False)
+    assert (x.grad.cpu()[mask] == 0).all()
+
+
+def test_router_rejects_and_empty():
+    from cute_kernels import router_topk_softmax
+
+    w, ids = router_topk_softmax(torch.empty(0, 8, device="cuda"), 2)
+    assert w.shape == (0, 2) and ids.shape == (0, 2)
+    with pytest.raises(RuntimeError):
+        router_topk_softmax(torch.randn(4, 512, device="cuda"), 2)       # more experts than the kernel holds
+    with pytest.raises(ValueError):
+        router_topk_softmax(torch.randn(4, 8, device="cuda"), 9)
+    with pytest.raises(Exception):
+        router_topk_softmax(torch.randn(4, 8), 2)                          # CPU tensors fail loudly
+
+
+def test_moe_module_uses_int32_router():
+    from cute_kernels import MoE_Cute
+    from cute_kernels.swiglu import swiglu_packed_cute
+
+    torch.manual_seed(0)
+    m = MoE_Cute(num_experts=8, num_experts_per_tok=2, hidden_size=128, intermediate_size=128,
+                 activation_function=swiglu_packed_cute, is_glu=True, add_bias=False, std=0.02).cuda().bfloat16()
+    x = torch.randn(64, 128, device="cuda", dtype=torch.bfloat16)
+    logits, weights, sel = m._compute_routing_weights(x)
+    assert sel.dtype == torch.int32 and weights.dtype == torch.bfloat16
+    y, _ = m(x)
+    assert torch.isfinite(y.float()).all()
