@@ -224,7 +224,25 @@ def gpu_arm(args, w: dict) -> dict | None:
         assert E % world == 0, "experts must divide evenly across ranks"
         epr = E // world
         inp = make_device_inputs(w, device, seed=1000 + rank, experts=slice(rank * epr, (rank + 1) * epr))
-        ep = ExpertParallelMoE(E, k, dist.group.WORLD)
+        ep, transport = None, "nccl_all_to_all"
+        if args.ep_transport in ("auto", "peer"):
+            # rows move by NVLink loads / stores issued from the permutation kernels and the GEMM epilogues
+            ok = torch.ones(1, device=device)
+            try:
+                from cute_kernels.peer_parallel import PeerExpertParallelMoE
+
+                ep = PeerExpertParallelMoE(E, k, T, H, torch.bfloat16, dist.group.WORLD)
+                transport = "peer_memory"
+            except Exception as exc:  # symmetric memory not available on this box
+                if args.ep_transport == "peer":
+                    raise
+                print(f"[bench] rank {rank}: peer-memory transport unavailable ({exc}); using NCCL all-to-all", file=sys.stderr)
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 0:
+                ep, transport = None, "nccl_all_to_all"
+        if ep is None:
+            ep = ExpertParallelMoE(E, k, dist.group.WORLD)
 
         def step(x, rw, sel, grad_out):
             x = x.detach().requires_grad_()
@@ -382,7 +400,8 @@ def gpu_arm(args, w: dict) -> dict | None:
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": w["name"], "tokens_per_gpu": T, "hidden": H, "intermediate": I, "experts": E, "top_k": k,
-                   "parallelism": f"ep{world}" if world > 1 else "single", "l2_policy": "inputs_exceed_l2",
+                   "parallelism": f"ep{world}" if world > 1 else "single",
+                   **({"ep_transport": transport} if world > 1 else {}), "l2_policy": "inputs_exceed_l2",
                    "step": "route+gather+up_swiglu+down_combine+backward(dgrad,wgrad,swiglu_bwd,router_grad)"},
         "clocks": clocks,
         "e2e": {"value": world * T / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
@@ -490,6 +509,9 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c2", "c3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-transport", default="auto", choices=["auto", "peer", "nccl"],
+                    help="N > 1: rows cross GPUs by peer-memory loads/stores from the kernels (default when symmetric "
+                         "memory is available) or by NCCL all-to-all")
     args = ap.parse_args()
     if args.workload in ("c2", "c3"):
         if args.warmup < 3:

@@ -61,7 +61,14 @@ struct GemmParams {
     int64_t cap;   // rows allocated for the padded layout
     int gather_fan;   // > 0: A rows are gathered by TMA from the un-permuted token matrix: token = row_map[p] / gather_fan
     int gather_b_fan; // WGRAD, > 0: the same for the B operand
+    // STORE with peer destinations: row row_map[p] of the result belongs to global slot g = dst_flat[row_map[p]] and is
+    // stored at peer_out[g / peer_rows] + (g % peer_rows) * N (another GPU's memory over NVLink, or this GPU's own buffer)
+    const int32_t *dst_flat;
+    int64_t peer_rows;
+    int n_peers;
+    void *peer_out[CK_MAX_PEERS];
 };
+constexpr int kPeerRowBits = 26;  // rowinfo = rank << 26 | row: up to 32 ranks of 2^26 rows
 
 struct TileCoord {
     int e;       // expert
@@ -396,12 +403,26 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
             if (row_ok) my_out = reinterpret_cast<T *>(p.out0) + orow * int64_t(p.N);
         }
         // publish the 32 row pointers of this warp as (valid, row index) pairs through rowinfo
-        const int64_t my_off = my_out ? (my_out - reinterpret_cast<T *>(p.out0)) / int64_t(p.N) : -1;
+        int64_t my_off = my_out ? (my_out - reinterpret_cast<T *>(p.out0)) / int64_t(p.N) : -1;
+        const bool to_peers = MODE == MODE_STORE && p.dst_flat != nullptr;
+        if (to_peers && my_off >= 0) {
+            const int64_t g = p.dst_flat[my_off];
+            const int64_t rk = g / p.peer_rows;
+            if (g >= 0 && rk < p.n_peers) {
+                my_off = (rk << kPeerRowBits) | (g - rk * p.peer_rows);
+            } else {
+                my_off = -1;
+                if (p.dev_status) atomicOr(p.dev_status, CK_DEV_RANGE);
+            }
+        }
         es.rowinfo[lane] = int32_t(my_off);  // row index in units of N elements: < 2^31 rows
         __syncwarp();
         auto row_ptr = [&](int r) -> T * {
             const int32_t o = es.rowinfo[r];
-            return o >= 0 ? reinterpret_cast<T *>(p.out0) + int64_t(o) * int64_t(p.N) : nullptr;
+            if (o < 0) return nullptr;
+            if (to_peers)
+                return reinterpret_cast<T *>(p.peer_out[o >> kPeerRowBits]) + int64_t(o & ((1 << kPeerRowBits) - 1)) * int64_t(p.N);
+            return reinterpret_cast<T *>(p.out0) + int64_t(o) * int64_t(p.N);
         };
         const int n0 = c.n_tile * BN;
 #pragma unroll 1
@@ -805,6 +826,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->tmem_empty[buf]));
         }
+        if (MODE == MODE_STORE && p.dst_flat) __threadfence_system();  // stores to other GPUs land before the kernel ends
     }
 
     // ---- teardown ------------------------------------------------------------------------------------
@@ -1162,6 +1184,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(buf ? leader_empty1 : leader_empty0);
         }
+        if (MODE == MODE_STORE && p.dst_flat) __threadfence_system();  // stores to other GPUs land before the kernel ends
     }
 
     // teardown: nobody leaves while the partner may still read its shared memory or signal its barriers
@@ -1392,12 +1415,19 @@ static int wgrad_t(const void *a, const void *b, const int32_t *padded_off, void
 
 template <typename T>
 static int grouped_linear_t(const void *x, const void *w, const int32_t *mtile_off, const int32_t *row_map, void *y, int E,
-                            int64_t cap, int N, int K, int trans_w, int32_t *dev_status, cudaStream_t stream) {
+                            int64_t cap, int N, int K, int trans_w, int32_t *dev_status, cudaStream_t stream,
+                            const int32_t *dst_flat = nullptr, void *const *peer_out = nullptr, int n_peers = 0,
+                            int64_t peer_rows = 0) {
     GemmParams p = {};
     p.cap = cap;
     int rc;
     if ((rc = map_a_kmajor<T>(&p.tmA, x, cap, K)) != CK_OK) return rc;
     p.mtile_off = mtile_off; p.row_map = row_map; p.out0 = y; p.dev_status = dev_status;
+    if (dst_flat) {
+        p.dst_flat = dst_flat; p.n_peers = n_peers; p.peer_rows = peer_rows;
+        for (int i = 0; i < n_peers; ++i) p.peer_out[i] = peer_out[i];
+        p.out0 = peer_out[0];  // only the base the row indices are taken against; nothing is stored through it
+    }
     p.E = E; p.n_tiles = (N + BN - 1) / BN; p.N = N; p.K = K; p.top_k = 1;
     if (trans_w) {
         if ((rc = map_w_mnmajor<T>(&p.tmB, w, E, K, N)) != CK_OK) return rc;
@@ -1498,4 +1528,18 @@ extern "C" int ck_moe_grouped_linear_scatter(const void *x, const void *w, const
                                              int32_t *dev_status, void *stream) {
     if (!x || !w || !mtile_off || !row_map || !y || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, N, K)) return CK_ERR_SHAPE;
     CK_DISPATCH_DTYPE(dtype, (grouped_linear_t<T>(x, w, mtile_off, row_map, y, E, cap, N, K, trans_w, dev_status, (cudaStream_t)stream)));
+}
+
+extern "C" int ck_moe_grouped_linear_scatter_peer(const void *x, const void *w, const int32_t *mtile_off,
+                                                  const int32_t *row_map, const int32_t *dst_flat, void *const *peer_out,
+                                                  int n_peers, int64_t rows_per_peer, int E, int64_t cap, int N, int K,
+                                                  int trans_w, int dtype, int32_t *dev_status, void *stream) {
+    if (!x || !w || !mtile_off || !row_map || !dst_flat || !peer_out || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, N, K))
+        return CK_ERR_SHAPE;
+    if (n_peers <= 0 || n_peers > CK_MAX_PEERS || rows_per_peer <= 0) return CK_ERR_SHAPE;
+    if (rows_per_peer > (int64_t(1) << kPeerRowBits) || rows_per_peer * n_peers > INT32_MAX) return CK_ERR_RANGE;
+    for (int i = 0; i < n_peers; ++i)
+        if (!peer_out[i] || (reinterpret_cast<uintptr_t>(peer_out[i]) & 15)) return CK_ERR_SHAPE;
+    CK_DISPATCH_DTYPE(dtype, (grouped_linear_t<T>(x, w, mtile_off, row_map, nullptr, E, cap, N, K, trans_w, dev_status,
+                                                  (cudaStream_t)stream, dst_flat, peer_out, n_peers, rows_per_peer)));
 }

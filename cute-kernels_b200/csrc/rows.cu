@@ -66,10 +66,10 @@ __global__ void __launch_bounds__(kRowThreads)
         for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
         for (int j = 0; j < k; ++j) {
             const int64_t f = t * k + j;
-            const int32_t r = pos[f];
+            const int64_t r = pos ? int64_t(pos[f]) : f;  // pos == NULL: the k rows of token t are rows t*k .. t*k+k-1
             if (r < 0) continue;
             float x[VEC];
-            ld16f(src + int64_t(r) * (vpr * VEC) + c, x);
+            ld16f(src + r * (vpr * VEC) + c, x);
             const float wj = w ? DT<T>::up(w[f]) : 1.0f;
 #pragma unroll
             for (int i = 0; i < VEC; ++i) acc[i] = fmaf(wj, x[i], acc[i]);
@@ -171,7 +171,7 @@ extern "C" int ck_moe_combine_rows(const void *src, const int32_t *pos, const vo
                                    int64_t cols, int dtype, void *stream) {
     if (tokens < 0 || k <= 0 || cols <= 0) return CK_ERR_SHAPE;
     if (tokens == 0) return CK_OK;
-    if (!src || !pos || !out) return CK_ERR_SHAPE;
+    if (!src || !out) return CK_ERR_SHAPE;
     CK_ROWS_DISPATCH(dtype, (combine_t<T>(src, pos, w, out, tokens, k, cols, (cudaStream_t)stream)));
 }
 

@@ -202,10 +202,10 @@ def _gather_rows_scaled_impl(src: torch.Tensor, dst: torch.Tensor, idx: torch.Te
     _lib.check(st, "ck_moe_gather_rows_scaled")
 
 
-def _combine_rows_impl(src: torch.Tensor, pos: torch.Tensor, w: torch.Tensor | None, out: torch.Tensor, k: int) -> None:
-    _lib.require_cuda(src, pos, out)
+def _combine_rows_impl(src: torch.Tensor, pos: torch.Tensor | None, w: torch.Tensor | None, out: torch.Tensor, k: int) -> None:
+    _lib.require_cuda(src, out)
     with torch.cuda.device(src.device), _lib.launch("combine_rows"):
-        st = _lib.lib.ck_moe_combine_rows(src.data_ptr(), pos.data_ptr(), _lib.ptr(w), out.data_ptr(), out.size(0), k,
+        st = _lib.lib.ck_moe_combine_rows(src.data_ptr(), _lib.ptr(pos), _lib.ptr(w), out.data_ptr(), out.size(0), k,
                                           src.size(1), _lib.dtype_code(src.dtype), _lib.stream_ptr())
     _lib.check(st, "ck_moe_combine_rows")
 

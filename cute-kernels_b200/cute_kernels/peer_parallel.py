@@ -1,0 +1,298 @@
+"""Expert parallelism over peer memory (NVLink loads / stores from inside the kernels, no all-to-all).
+
+The all-to-all transport in :mod:`expert_parallel` packs the routed rows, sends them, re-gathers them into the
+padded grouped layout, and does the same three passes on the way back.  Here every rank keeps its token rows,
+router weights and a return buffer in memory that the other ranks of the node have mapped (symmetric memory),
+and the permutation kernels address that memory directly:
+
+  forward   publish x, router weights, expert ids            (local copies into the shared buffers)
+            all-gather the ids (256 KiB per rank; doubles as the "published" barrier)
+            route the gathered ids; this rank's experts own one contiguous run of the sorted order
+            gather the rows of that run from their owners      (ck_moe_gather_rows_peer: NVLink loads)
+            up projection + activation (router weight folded in, fetched with ck_peer_gather_scalars)
+            down projection, every result row stored into its owner's return buffer from the GEMM epilogue
+                                                               (ck_moe_grouped_linear_scatter_peer: NVLink stores)
+            barrier; k-way sum of the local return buffer      (ck_moe_combine_rows)
+  backward  the same shape: publish dy, barrier, gather dy rows from their owners, dgrad(down) + activation
+            backward, weight grads (local), router-weight grads scattered to their owners, dgrad(up) rows stored
+            into the owners' return buffers, barrier, k-way sum.
+
+Rows cross NVLink once per direction, overlapped tile by tile with the GEMM that produces them; no send / receive
+staging buffers exist.  Ordering between ranks comes only from stream-ordered NCCL collectives issued between the
+phases; no kernel waits on another GPU.  A global flat slot names a routed row: ``g = rank * S + token * k + j``
+with ``S = max_tokens * k`` slots per rank.
+
+The reference is single-GPU; the contract is its layer on the concatenated batch (expert weights sharded as in
+:func:`expert_parallel.shard_expert_state_dict`).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .moe import combine_rows, dgrad_down, up_act_fwd, wgrad
+from .routing import Routing, route
+
+
+def _ptr_array(ptrs: list[int]):
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+def _gather_rows_peer(ptrs, S: int, dst, r: Routing, src_flat, fan_out: int) -> None:
+    status = _lib.status_word(dst.device)
+    with torch.cuda.device(dst.device), _lib.launch("gather_rows_peer"):
+        st = _lib.lib.ck_moe_gather_rows_peer(_ptr_array(ptrs), len(ptrs), S, dst.data_ptr(), r.row_map.data_ptr(),
+                                              r.padded_off.data_ptr(), src_flat.data_ptr(), r.padded_off.numel() - 1,
+                                              dst.size(0), fan_out, dst.size(1), _lib.dtype_code(dst.dtype),
+                                              status.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_gather_rows_peer")
+
+
+def _linear_scatter_peer(x, w, r: Routing, dst_flat, ptrs, S: int, trans_w: bool) -> None:
+    status = _lib.status_word(x.device)
+    E = w.size(0)
+    N, K = (w.size(2), w.size(1)) if trans_w else (w.size(1), w.size(2))
+    assert x.size(1) == K
+    with torch.cuda.device(x.device), _lib.launch("grouped_linear_scatter_peer", 1, 2.0 * x.size(0) * N * K):
+        st = _lib.lib.ck_moe_grouped_linear_scatter_peer(x.data_ptr(), w.data_ptr(), r.mtile_off.data_ptr(),
+                                                         r.row_map.data_ptr(), dst_flat.data_ptr(), _ptr_array(ptrs),
+                                                         len(ptrs), S, E, x.size(0), N, K, int(trans_w),
+                                                         _lib.dtype_code(x.dtype), status.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_grouped_linear_scatter_peer")
+
+
+def _gather_scalars_peer(ptrs, S: int, flat, n: int, dst) -> None:
+    status = _lib.status_word(dst.device)
+    with torch.cuda.device(dst.device), _lib.launch("peer_gather_scalars"):
+        st = _lib.lib.ck_peer_gather_scalars(_ptr_array(ptrs), len(ptrs), S, flat.data_ptr(), n, dst.data_ptr(),
+                                             dst.element_size(), status.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_peer_gather_scalars")
+
+
+def _scatter_scalars_peer(vals, flat, n: int, ptrs, S: int) -> None:
+    status = _lib.status_word(vals.device)
+    with torch.cuda.device(vals.device), _lib.launch("peer_scatter_scalars"):
+        st = _lib.lib.ck_peer_scatter_scalars(vals.data_ptr(), flat.data_ptr(), n, _ptr_array(ptrs), len(ptrs), S,
+                                              vals.element_size(), status.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_peer_scatter_scalars")
+
+
+@dataclass
+class PeerBuffers:
+    """One rank's shared buffers and every rank's address of them (``*_ptrs[r]`` = rank r's buffer as mapped here).
+
+    tokens [max_tokens, H]  x in forward, dy in backward          rows [S, H]  returned expert outputs / input grads
+    weights [S]             router weights, dtype of x            dgates [S]   router-weight grads, fp32
+    ids [S] int32           published expert ids (``num_experts`` = "no row" on the unused tail)
+    """
+
+    rank: int
+    world: int
+    max_tokens: int
+    top_k: int
+    tokens: torch.Tensor
+    rows: torch.Tensor
+    weights: torch.Tensor
+    dgates: torch.Tensor
+    ids: torch.Tensor
+    tokens_ptrs: list[int]
+    rows_ptrs: list[int]
+    weights_ptrs: list[int]
+    dgates_ptrs: list[int]
+
+    @property
+    def slots(self) -> int:
+        return self.max_tokens * self.top_k
+
+
+@dataclass
+class _Plan:
+    src_flat: torch.Tensor   # int32 [n_local]: global flat slot of every row this rank's experts own, sorted by expert
+    routing: Routing         # padded layout of those rows over the local experts (row_map -> index into src_flat)
+    n_local: int
+
+
+class PeerExpertEngine:
+    """The per-rank phases; the caller puts a collective between them (see :class:`PeerExpertParallelMoE`)."""
+
+    def __init__(self, buffers: PeerBuffers, num_experts: int, act_kind: int = _lib.CK_ACT_SWIGLU) -> None:
+        if num_experts % buffers.world != 0:
+            raise ValueError("num_experts must be divisible by the number of ranks")
+        self.b = buffers
+        self.num_experts = num_experts
+        self.local_experts = num_experts // buffers.world
+        self.act_kind = act_kind
+
+    # ---- forward -------------------------------------------------------------------------------------
+    def publish(self, x: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor) -> None:
+        b = self.b
+        T = x.size(0)
+        if T > b.max_tokens:
+            raise RuntimeError(f"{T} tokens exceed the shared buffers' {b.max_tokens}")
+        _lib.require_cuda(x, router_weights, selected_experts)
+        b.tokens[:T].copy_(x)
+        b.weights[: T * b.top_k].copy_(router_weights.reshape(-1))
+        b.ids[: T * b.top_k].copy_(selected_experts.reshape(-1))
+        b.ids[T * b.top_k:].fill_(self.num_experts)
+
+    def plan(self, ids_all: torch.Tensor) -> _Plan:
+        """ids_all int32 [world * S]: every rank's published ids, rank-major."""
+        b, E, epr = self.b, self.num_experts, self.local_experts
+        g = route(ids_all, E + 1, with_tile_metadata=False, with_sorted_expert=True)
+        e0 = b.rank * epr
+        lo, hi = torch.stack([g.excl_offsets[e0], g.end_offsets[e0 + epr - 1]]).tolist()  # the one host sync
+        if hi == lo:  # no row chose this rank's experts: one placeholder entry keeps the pointers valid, n_local = 0
+            return _Plan(torch.zeros(1, dtype=torch.int32, device=ids_all.device), route(g.sorted_expert[:0], epr), 0)
+        src_flat = g.sorted_idx[lo:hi]
+        local_ids = g.sorted_expert[lo:hi] - e0
+        return _Plan(src_flat, route(local_ids, epr), hi - lo)
+
+    def fwd_compute(self, plan: _Plan, w_fc: torch.Tensor, w_proj: torch.Tensor, need_grad: bool):
+        b, r = self.b, plan.routing
+        dev, dt = b.tokens.device, b.tokens.dtype
+        H = b.tokens.size(1)
+        two_i = w_fc.size(1)
+        cap = r.row_map.numel()
+        gate = torch.empty(max(plan.n_local, 1), dtype=dt, device=dev)
+        _gather_scalars_peer(b.weights_ptrs, b.slots, plan.src_flat, plan.n_local, gate)
+        xg = torch.empty(cap, H, dtype=dt, device=dev)
+        _gather_rows_peer(b.tokens_ptrs, b.slots, xg, r, plan.src_flat, b.top_k)
+        act = torch.empty(cap, two_i // 2, dtype=dt, device=dev)
+        h = torch.empty(cap, two_i, dtype=dt, device=dev) if need_grad else None
+        up_act_fwd(xg, w_fc, gate, r.row_map, r.mtile_off, act, h, self.act_kind)
+        _linear_scatter_peer(act, w_proj, r, plan.src_flat, b.rows_ptrs, b.slots, False)
+        return xg, act, h, gate
+
+    def fwd_finish(self, T: int) -> torch.Tensor:
+        b = self.b
+        y = torch.empty(T, b.tokens.size(1), dtype=b.tokens.dtype, device=b.tokens.device)
+        if T:
+            combine_rows(b.rows, None, None, y, b.top_k)
+        return y
+
+    # ---- backward ------------------------------------------------------------------------------------
+    def bwd_publish(self, dy: torch.Tensor) -> None:
+        self.b.tokens[: dy.size(0)].copy_(dy)
+
+    def bwd_compute(self, plan: _Plan, saved, w_fc, w_proj, need_wfc: bool, need_wproj: bool, need_x: bool):
+        b, r = self.b, plan.routing
+        xg, act, h, gate = saved
+        dev, dt = xg.device, xg.dtype
+        H = xg.size(1)
+        cap = r.row_map.numel()
+        dyg = torch.empty(cap, H, dtype=dt, device=dev)
+        _gather_rows_peer(b.tokens_ptrs, b.slots, dyg, r, plan.src_flat, b.top_k)
+        dh = torch.empty(cap, w_fc.size(1), dtype=dt, device=dev)
+        dgates = torch.zeros(max(plan.n_local, 1), dtype=torch.float32, device=dev)
+        dgrad_down(dyg, w_proj, h, gate, r.row_map, r.mtile_off, dh, dgates, self.act_kind)
+        d_wproj = d_wfc = None
+        if need_wproj:
+            d_wproj = torch.empty_like(w_proj)
+            wgrad(dyg, act, r.padded_off, d_wproj)
+        _scatter_scalars_peer(dgates, plan.src_flat, plan.n_local, b.dgates_ptrs, b.slots)
+        if need_x:
+            _linear_scatter_peer(dh, w_fc, r, plan.src_flat, b.rows_ptrs, b.slots, True)
+        if need_wfc:
+            d_wfc = torch.empty_like(w_fc)
+            wgrad(dh, xg, r.padded_off, d_wfc)
+        return d_wfc, d_wproj
+
+    def bwd_finish(self, T: int, need_x: bool):
+        b = self.b
+        dx = None
+        if need_x:
+            dx = torch.empty(T, b.tokens.size(1), dtype=b.tokens.dtype, device=b.tokens.device)
+            if T:
+                combine_rows(b.rows, None, None, dx, b.top_k)
+        d_rw = b.dgates[: T * b.top_k].view(T, b.top_k).to(b.tokens.dtype, copy=True)
+        return dx, d_rw
+
+
+class _NcclExchange:
+    """Stream-ordered ordering points between the phases: an all-gather of the ids and a one-element all-reduce."""
+
+    def __init__(self, group, device: torch.device) -> None:
+        self.group = group
+        self.flag = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def all_gather_ids(self, ids_local: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(dist.get_world_size(self.group) * ids_local.numel(), dtype=ids_local.dtype, device=ids_local.device)
+        dist.all_gather_into_tensor(out, ids_local, group=self.group)
+        return out
+
+    def barrier(self) -> None:
+        dist.all_reduce(self.flag, group=self.group)
+
+
+class _PeerExperts(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, router_weights, w_fc, w_proj, selected_experts, engine: PeerExpertEngine, exchange):
+        need_grad = any(ctx.needs_input_grad[:4])
+        engine.publish(x, router_weights, selected_experts)
+        plan = engine.plan(exchange.all_gather_ids(engine.b.ids))
+        saved = engine.fwd_compute(plan, w_fc, w_proj, need_grad)
+        exchange.barrier()
+        y = engine.fwd_finish(x.size(0))
+        ctx.engine, ctx.exchange, ctx.plan, ctx.tokens = engine, exchange, plan, x.size(0)
+        ctx.save_for_backward(w_fc, w_proj, *saved)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        w_fc, w_proj, *saved = ctx.saved_tensors
+        engine, exchange, plan, T = ctx.engine, ctx.exchange, ctx.plan, ctx.tokens
+        need_x, need_rw, need_wfc, need_wproj = ctx.needs_input_grad[:4]
+        engine.bwd_publish(dy.contiguous().to(saved[0].dtype))
+        exchange.barrier()
+        d_wfc, d_wproj = engine.bwd_compute(plan, saved, w_fc, w_proj, need_wfc, need_wproj, need_x)
+        exchange.barrier()
+        dx, d_rw = engine.bwd_finish(T, need_x)
+        return dx, (d_rw if need_rw else None), d_wfc, d_wproj, None, None, None
+
+
+def allocate_symmetric_buffers(max_tokens: int, hidden_size: int, top_k: int, dtype: torch.dtype, group=None,
+                               device: torch.device | None = None) -> PeerBuffers:
+    """Allocates the shared buffers in symmetric memory and exchanges their addresses (collective over ``group``)."""
+    import torch.distributed._symmetric_memory as symm_mem
+
+    group = group if group is not None else dist.group.WORLD
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    S = max_tokens * top_k
+
+    def shared(shape, dt):
+        t = symm_mem.empty(shape, dtype=dt, device=device)
+        hdl = symm_mem.rendezvous(t, group)
+        return t, [int(p) for p in hdl.buffer_ptrs]
+
+    tokens, tokens_ptrs = shared((max_tokens, hidden_size), dtype)
+    rows, rows_ptrs = shared((S, hidden_size), dtype)
+    weights, weights_ptrs = shared((S,), dtype)
+    dgates, dgates_ptrs = shared((S,), torch.float32)
+    ids = torch.empty(S, dtype=torch.int32, device=device)
+    return PeerBuffers(dist.get_rank(group), dist.get_world_size(group), max_tokens, top_k, tokens, rows, weights,
+                       dgates, ids, tokens_ptrs, rows_ptrs, weights_ptrs, dgates_ptrs)
+
+
+class PeerExpertParallelMoE:
+    """Callable with the signature of :class:`expert_parallel.ExpertParallelMoE`:
+    ``y = ep(x, router_weights, selected_experts, w_fc_local, w_proj_local)`` with GLOBAL expert ids.
+
+    The shared buffers are sized for ``max_tokens`` rows of ``hidden_size`` per rank and are reused by every call
+    (forward and backward of one call must finish before the next call's forward starts, which stream order gives)."""
+
+    def __init__(self, num_experts: int, top_k: int, max_tokens: int, hidden_size: int, dtype: torch.dtype, group=None,
+                 act_kind: int = _lib.CK_ACT_SWIGLU, buffers: PeerBuffers | None = None, exchange=None) -> None:
+        self.group = group if group is not None else dist.group.WORLD
+        self.buffers = buffers or allocate_symmetric_buffers(max_tokens, hidden_size, top_k, dtype, self.group)
+        self.engine = PeerExpertEngine(self.buffers, num_experts, act_kind)
+        self.exchange = exchange or _NcclExchange(self.group, self.buffers.tokens.device)
+        self.top_k = top_k
+
+    def __call__(self, x, router_weights, selected_experts, w_fc_local, w_proj_local):
+        return _PeerExperts.apply(x.contiguous(), router_weights, w_fc_local.contiguous(), w_proj_local.contiguous(),
+                                  selected_experts.to(torch.int32), self.engine, self.exchange)

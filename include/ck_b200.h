@@ -227,7 +227,7 @@ CK_API int ck_moe_grouped_linear_scatter(const void *x, const void *w, const int
 /* ---- row permutations around the expert-parallel exchange ---------------------------------------
  * ck_moe_gather_rows_scaled: dst[j, :] = c * src[idx[j] / fan_out, :], c = coeff ? coeff[idx[j]] : 1, zeros
  *   where idx[j] < 0 -- `group` with its optional coefficient (ops.py:108-140, kernels.py:225-280).
- * ck_moe_combine_rows: out[t, :] = sum_{j<k} (w ? w[t*k+j] : 1) * src[pos[t*k+j], :] -- the bmm(gates, out)
+ * ck_moe_combine_rows: out[t, :] = sum_{j<k} (w ? w[t*k+j] : 1) * src[pos ? pos[t*k+j] : t*k+j, :] -- the bmm(gates, out)
  *   combine (ops.py:170-174) and the sum(-2) of the input grad (ops.py:276), deterministic, fp32 accumulate.
  * ck_moe_row_dots: dots[f] = <a[pos[f], :], b[f / k, :]> -- d_gates = bmm(output_expanded, grad_out) (ops.py:214).
  * cols must be a multiple of 16 bytes of elements; pointers 16-byte aligned. */
@@ -250,6 +250,37 @@ CK_API int ck_router_topk_softmax(const void *logits, void *weights, int32_t *id
                                   int dtype, void *stream);
 CK_API int ck_router_topk_softmax_bwd(const void *weights, const void *d_weights, const int32_t *ids,
                                       void *d_logits, int64_t tokens, int E, int k, int dtype, void *stream);
+
+/* ---- expert parallelism over peer memory ------------------------------------------------------------
+ * No reference counterpart (the reference is single-GPU); per rank these are its `group` (ops.py:108-140) and
+ * `scatter2scatter` with y_grouped=False (ops.py:31-78) with the other side of the permutation living on another
+ * GPU.  Every rank exposes buffers of `rows_per_peer` slots; a routed row is named by its global flat slot
+ * g = rank * rows_per_peer + f, f = token * k + j on the owning rank.  `peer_*` are HOST arrays of `n_peers`
+ * device pointers (rank r's buffer as mapped into this process; entry [own rank] is the local buffer), all
+ * 16-byte aligned, n_peers <= CK_MAX_PEERS, n_peers * rows_per_peer < 2^31.  The kernels never wait on another
+ * GPU; the host orders the phases with stream-ordered collectives.
+ * ck_moe_gather_rows_peer: dst[p, :] = peer_src[g / S][(g % S) / fan_out, :], g = src_flat[row_map[p]], zeros
+ *   where row_map[p] < 0, for p < padded_off[E].
+ * ck_moe_grouped_linear_scatter_peer: ck_moe_grouped_linear_scatter whose row row_map[p] is stored at
+ *   peer_out[g / S] + (g % S) * N, g = dst_flat[row_map[p]]  (rows_per_peer <= 2^26).
+ * ck_peer_gather_scalars / ck_peer_scatter_scalars: dst[j] = peer_src[g / S][g % S] and peer_dst[g / S][g % S] =
+ *   vals[j], g = flat[j], for 2- or 4-byte scalars (router weights and their gradients).
+ * A slot outside [0, n_peers * S) is skipped and sets CK_DEV_RANGE in *dev_status. */
+#define CK_MAX_PEERS 16
+CK_API int ck_moe_gather_rows_peer(const void *const *peer_src, int n_peers, int64_t rows_per_peer, void *dst,
+                                   const int32_t *row_map, const int32_t *padded_off, const int32_t *src_flat, int E,
+                                   int64_t cap, int fan_out, int64_t cols, int dtype, int32_t *dev_status,
+                                   void *stream);
+CK_API int ck_moe_grouped_linear_scatter_peer(const void *x, const void *w, const int32_t *mtile_off,
+                                              const int32_t *row_map, const int32_t *dst_flat, void *const *peer_out,
+                                              int n_peers, int64_t rows_per_peer, int E, int64_t cap, int N, int K,
+                                              int trans_w, int dtype, int32_t *dev_status, void *stream);
+CK_API int ck_peer_gather_scalars(const void *const *peer_src, int n_peers, int64_t rows_per_peer,
+                                  const int32_t *flat, int64_t n, void *dst, int elem_bytes, int32_t *dev_status,
+                                  void *stream);
+CK_API int ck_peer_scatter_scalars(const void *vals, const int32_t *flat, int64_t n, void *const *peer_dst,
+                                   int n_peers, int64_t rows_per_peer, int elem_bytes, int32_t *dev_status,
+                                   void *stream);
 
 #ifdef __cplusplus
 }

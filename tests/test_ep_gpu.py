@@ -1,4 +1,5 @@
-"""Expert parallelism on real GPUs (NCCL all-to-all + the fused grouped-GEMM path) against the CPU oracle.
+"""Expert parallelism on real GPUs against the CPU oracle, over both transports: NCCL all-to-all around the fused
+grouped-GEMM path, and peer-memory loads / stores issued by the kernels themselves (symmetric memory).
 Needs at least 2 GPUs; skipped otherwise."""
 
 import os
@@ -37,7 +38,12 @@ def _worker(rank, world, port, cfg, out_dir):
         rw = full["router_weights"][sl].to(dt).cuda().requires_grad_()
         w_fc = full["w_fc"][rank * epr : (rank + 1) * epr].to(dt).cuda().requires_grad_()
         w_proj = full["w_proj"][rank * epr : (rank + 1) * epr].to(dt).cuda().requires_grad_()
-        ep = ExpertParallelMoE(E, k, None)
+        if cfg.get("transport") == "peer":
+            from cute_kernels.peer_parallel import PeerExpertParallelMoE
+
+            ep = PeerExpertParallelMoE(E, k, T + 7, cfg["H"], dt, None)   # buffers larger than the batch
+        else:
+            ep = ExpertParallelMoE(E, k, None)
         y = ep(x, rw, full["selected_experts"][sl].cuda(), w_fc, w_proj)
         y.backward(full["grad_out"][sl].to(dt).cuda())
         torch.cuda.synchronize()
@@ -50,7 +56,9 @@ def _worker(rank, world, port, cfg, out_dir):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("cfg", [dict(E=8, k=2, T=300, H=128, I=256, expert_bias=False, seed=0),
-                                 dict(E=16, k=4, T=257, H=64, I=72, expert_bias=True, seed=1)])
+                                 dict(E=16, k=4, T=257, H=64, I=72, expert_bias=True, seed=1),
+                                 dict(E=8, k=2, T=300, H=128, I=256, expert_bias=False, seed=0, transport="peer"),
+                                 dict(E=2, k=1, T=513, H=256, I=128, expert_bias=True, seed=2, transport="peer")])
 def test_expert_parallel_two_gpus(tmp_path, cfg):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), cfg, str(tmp_path)), nprocs=world, join=True)

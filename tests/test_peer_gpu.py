@@ -1,0 +1,111 @@
+"""Expert parallelism over peer memory, emulated on one GPU: every virtual rank owns its buffers, the pointer tables
+name all of them, and the phases run in lock step (the place of the collectives) -- the kernels, the slot arithmetic
+and the autograd bookkeeping are the ones the multi-GPU run uses.  Checked against the CPU oracle on the
+concatenated batch."""
+
+import pytest
+import torch
+
+import ck_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _virtual_world(world, max_tokens, H, k, dt):
+    from cute_kernels.peer_parallel import PeerBuffers
+
+    S = max_tokens * k
+    dev = torch.device("cuda")
+    raw = [dict(tokens=torch.full((max_tokens, H), float("nan"), dtype=dt, device=dev),
+                rows=torch.full((S, H), float("nan"), dtype=dt, device=dev),
+                weights=torch.full((S,), float("nan"), dtype=dt, device=dev),
+                dgates=torch.full((S,), float("nan"), dtype=torch.float32, device=dev),
+                ids=torch.empty(S, dtype=torch.int32, device=dev)) for _ in range(world)]
+    ptrs = {name: [r[name].data_ptr() for r in raw] for name in ("tokens", "rows", "weights", "dgates")}
+    return [PeerBuffers(rank, world, max_tokens, k, raw[rank]["tokens"], raw[rank]["rows"], raw[rank]["weights"],
+                        raw[rank]["dgates"], raw[rank]["ids"], ptrs["tokens"], ptrs["rows"], ptrs["weights"],
+                        ptrs["dgates"]) for rank in range(world)]
+
+
+CASES = [
+    dict(world=2, E=8, k=2, T=[300, 300], H=128, I=256, seed=0),
+    dict(world=4, E=8, k=2, T=[130, 97, 5, 256], H=64, I=72, seed=1),     # ragged ranks, discard bin in use
+    dict(world=4, E=4, k=1, T=[64, 64, 64, 64], H=128, I=128, seed=2),    # one expert per rank, top-1
+    dict(world=2, E=16, k=4, T=[257, 0], H=64, I=136, seed=3),            # a rank without tokens
+    dict(world=8, E=8, k=2, T=[40] * 8, H=256, I=128, seed=4),
+]
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("cfg", CASES)
+def test_peer_engine_lockstep(cfg, dt):
+    import cute_kernels as ck
+    from cute_kernels.peer_parallel import PeerExpertEngine
+
+    world, E, k, H, I = cfg["world"], cfg["E"], cfg["k"], cfg["H"], cfg["I"]
+    Ts = cfg["T"]
+    full = orc.gen_moe_inputs(cfg["seed"], sum(Ts), H, I, E, k, False)
+    ref = orc.moe_fwd_bwd_ref(full)
+    epr = E // world
+    starts = [sum(Ts[:r]) for r in range(world)]
+    sl = [slice(starts[r], starts[r] + Ts[r]) for r in range(world)]
+    bufs = _virtual_world(world, max(max(Ts), 1), H, k, dt)
+    eng = [PeerExpertEngine(b, E) for b in bufs]
+    w_fc = [full["w_fc"][r * epr:(r + 1) * epr].to(dt).cuda().contiguous() for r in range(world)]
+    w_proj = [full["w_proj"][r * epr:(r + 1) * epr].to(dt).cuda().contiguous() for r in range(world)]
+
+    # ---- forward, phase by phase ----
+    for r in range(world):
+        eng[r].publish(full["x"][sl[r]].to(dt).cuda(), full["router_weights"][sl[r]].to(dt).cuda(),
+                       full["selected_experts"][sl[r]].to(torch.int32).cuda())
+    ids_all = torch.cat([b.ids for b in bufs])
+    plans = [eng[r].plan(ids_all) for r in range(world)]
+    assert sum(p.n_local for p in plans) == sum(Ts) * k
+    saved = [eng[r].fwd_compute(plans[r], w_fc[r], w_proj[r], True) for r in range(world)]
+    ys = [eng[r].fwd_finish(Ts[r]) for r in range(world)]
+    # ---- backward ----
+    for r in range(world):
+        eng[r].bwd_publish(full["grad_out"][sl[r]].to(dt).cuda())
+    grads = [eng[r].bwd_compute(plans[r], saved[r], w_fc[r], w_proj[r], True, True, True) for r in range(world)]
+    backs = [eng[r].bwd_finish(Ts[r], True) for r in range(world)]
+    torch.cuda.synchronize()
+    ck.check_device_status()
+
+    tol = dict(rtol=2e-2, atol=2e-2) if dt == torch.bfloat16 else dict(rtol=6e-3, atol=6e-3)  # fp32 runs as TF32
+    n = sum(Ts)
+    wtol = dict(rtol=tol["rtol"], atol=tol["atol"] * max(1.0, (n / 64) ** 0.5))
+    for r in range(world):
+        el = slice(r * epr, (r + 1) * epr)
+        torch.testing.assert_close(ys[r].float().cpu(), ref["y"][sl[r]], **tol)
+        dx, d_rw = backs[r]
+        torch.testing.assert_close(dx.float().cpu(), ref["dx"][sl[r]], **tol)
+        torch.testing.assert_close(d_rw.float().cpu(), ref["d_router_weights"][sl[r]],
+                                   rtol=tol["rtol"], atol=tol["atol"] * max(1.0, (I / 256) ** 0.5))
+        torch.testing.assert_close(grads[r][0].float().cpu(), ref["d_w_fc"][el], **wtol)
+        torch.testing.assert_close(grads[r][1].float().cpu(), ref["d_w_proj"][el], **wtol)
+
+
+def test_peer_kernels_reject_bad_tables():
+    from cute_kernels import _lib
+    import ctypes
+
+    x = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    i32 = torch.zeros(130, dtype=torch.int32, device="cuda")
+    arr = (ctypes.c_void_p * 1)(x.data_ptr() + 2)  # misaligned buffer
+    st = _lib.lib.ck_moe_gather_rows_peer(arr, 1, 128, x.data_ptr(), i32.data_ptr(), i32.data_ptr(), i32.data_ptr(), 1, 128, 1,
+                                          64, _lib.dtype_code(torch.bfloat16), None, None)
+    assert st == -1
+    arr = (ctypes.c_void_p * 1)(x.data_ptr())
+    st = _lib.lib.ck_peer_gather_scalars(arr, 17, 128, i32.data_ptr(), 1, x.data_ptr(), 2, None, None)   # too many peers
+    assert st == -1
+    st = _lib.lib.ck_peer_gather_scalars(arr, 1, 1 << 31, i32.data_ptr(), 1, x.data_ptr(), 2, None, None)  # slots overflow int32
+    assert st == -2
+
+
+def test_combine_rows_identity_positions():
+    from cute_kernels.moe import combine_rows
+
+    src = torch.randn(24, 64, device="cuda").bfloat16()
+    out = torch.empty(8, 64, device="cuda", dtype=torch.bfloat16)
+    combine_rows(src, None, None, out, 3)
+    torch.testing.assert_close(out.float(), src.float().view(8, 3, 64).sum(1), rtol=1e-2, atol=1e-2)
