@@ -44,7 +44,7 @@ WORKLOADS = {
 METRIC = "moe_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 GEMM_KERNELS = ("up_act_fwd", "down_combine_fwd", "dgrad_down", "dgrad_up", "wgrad", "grouped_linear",
-                "grouped_linear_scatter")
+                "grouped_linear_scatter", "grouped_linear_scatter_peer")
 
 
 def measured_peaks() -> dict:
@@ -315,15 +315,17 @@ def gpu_arm(args, w: dict) -> dict | None:
     dx_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
 
     # Every step's inputs come from pinned host memory and its results go back to it, all inside the timed region.
-    # The copies run on a second stream: inputs of step i+1 and results of step i-1 move while step i computes.
-    copy_stream = torch.cuda.Stream(device=device)
+    # The copies run on two more streams, one per direction (PCIe is full duplex): inputs of step i+1 and results of
+    # step i-1 move while step i computes.
+    h2d_stream = torch.cuda.Stream(device=device)
+    d2h_stream = torch.cuda.Stream(device=device)
     main_stream = torch.cuda.current_stream()
 
     def stage_in():
-        with torch.cuda.stream(copy_stream):
+        with torch.cuda.stream(h2d_stream):
             dev = {n: v.to(device, non_blocking=True) for n, v in host.items()}
             ev = torch.cuda.Event()
-            ev.record(copy_stream)
+            ev.record(h2d_stream)
         return dev, ev
 
     def e2e_loop(n_steps: int) -> None:
@@ -338,14 +340,14 @@ def gpu_arm(args, w: dict) -> dict | None:
             y, dx = step(dev["x"], dev["router_weights"], dev["selected_experts"], dev["grad_out"])
             done = torch.cuda.Event()
             done.record(main_stream)
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(done)
+            with torch.cuda.stream(d2h_stream):
+                d2h_stream.wait_event(done)
                 y_host.copy_(y, non_blocking=True)
                 dx_host.copy_(dx, non_blocking=True)
-                y.record_stream(copy_stream)
-                dx.record_stream(copy_stream)
+                y.record_stream(d2h_stream)
+                dx.record_stream(d2h_stream)
             zero_wgrads()
-        main_stream.wait_stream(copy_stream)  # the last results have reached the host before the clock stops
+        main_stream.wait_stream(d2h_stream)  # the last results have reached the host before the clock stops
 
     e2e_loop(max(1, min(args.warmup, 2)))
     barrier()

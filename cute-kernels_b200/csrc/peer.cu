@@ -18,9 +18,12 @@ struct PeerTable {
 };
 
 constexpr int kPeerThreads = 256;
-constexpr int kPeerUnroll = 4;
+constexpr int kPeerUnroll = 8;
 
-// dst[p, :] = peer[g / S][(g % S) / fan_out, :] with g = src_flat[row_map[p]]; zeros where row_map[p] < 0
+// dst[p, :] = peer[g / S][(g % S) / fan_out, :] with g = src_flat[row_map[p]]; zeros where row_map[p] < 0.
+// Every block owns one contiguous run of padded rows, so at any moment the grid reads from all parts of the
+// sorted order at once.  The sorted order is source-rank major inside an expert: a grid-stride sweep would have
+// every GPU of the node pulling from the same source rank at the same time and queue on that rank's links.
 template <typename T>
 __global__ void __launch_bounds__(kPeerThreads)
     gather_rows_peer_kernel(const PeerTable peers, int n_peers, int64_t S, T *__restrict__ dst,
@@ -30,16 +33,18 @@ __global__ void __launch_bounds__(kPeerThreads)
     constexpr int VEC = Vec16<T>::N;
     int64_t rows = padded_off[E];
     if (rows > cap) rows = cap;
-    const int64_t nvec = rows * vpr;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    const int64_t rows_per_block = ceil_div64(rows, gridDim.x);
+    const int64_t row0 = int64_t(blockIdx.x) * rows_per_block;
+    const int64_t row1 = min(row0 + rows_per_block, rows);
+    const int64_t v_begin = row0 * vpr, v_end = row1 * vpr;
     bool bad = false;
-    for (int64_t v0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * kPeerUnroll) {
+    for (int64_t v0 = v_begin + threadIdx.x; v0 < v_end; v0 += int64_t(kPeerThreads) * kPeerUnroll) {
         int4 x[kPeerUnroll];
 #pragma unroll
         for (int j = 0; j < kPeerUnroll; ++j) {
-            const int64_t v = v0 + j * stride;
+            const int64_t v = v0 + j * kPeerThreads;
             x[j] = make_int4(0, 0, 0, 0);
-            if (v < nvec) {
+            if (v < v_end) {
                 const int64_t p = v / vpr, c = (v - p * vpr) * VEC;
                 const int32_t s = row_map[p];
                 if (s >= 0) {
@@ -56,8 +61,8 @@ __global__ void __launch_bounds__(kPeerThreads)
         }
 #pragma unroll
         for (int j = 0; j < kPeerUnroll; ++j) {
-            const int64_t v = v0 + j * stride;
-            if (v < nvec) *reinterpret_cast<int4 *>(dst + v * VEC) = x[j];
+            const int64_t v = v0 + j * kPeerThreads;
+            if (v < v_end) *reinterpret_cast<int4 *>(dst + v * VEC) = x[j];
         }
     }
     if (bad && dev_status) atomicOr(dev_status, CK_DEV_RANGE);
