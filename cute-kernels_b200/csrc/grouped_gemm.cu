@@ -61,7 +61,8 @@ struct GemmParams {
     int64_t cap;   // rows allocated for the padded layout
     int gather_fan;   // > 0: A rows are gathered by TMA from the un-permuted token matrix: token = row_map[p] / gather_fan
     int gather_b_fan; // WGRAD, > 0: the same for the B operand
-    // STORE with peer destinations: row row_map[p] of the result belongs to global slot g = dst_flat[row_map[p]] and is
+    // STORE with peer destinations (n_peers > 0): row row_map[p] of the result belongs to global slot
+    // g = dst_flat ? dst_flat[row_map[p]] : row_map[p] and is
     // stored at peer_out[g / peer_rows] + (g % peer_rows) * N (another GPU's memory over NVLink, or this GPU's own buffer)
     const int32_t *dst_flat;
     int64_t peer_rows;
@@ -404,9 +405,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
         }
         // publish the 32 row pointers of this warp as (valid, row index) pairs through rowinfo
         int64_t my_off = my_out ? (my_out - reinterpret_cast<T *>(p.out0)) / int64_t(p.N) : -1;
-        const bool to_peers = MODE == MODE_STORE && p.dst_flat != nullptr;
+        const bool to_peers = MODE == MODE_STORE && p.n_peers > 0;
         if (to_peers && my_off >= 0) {
-            const int64_t g = p.dst_flat[my_off];
+            const int64_t g = p.dst_flat ? int64_t(p.dst_flat[my_off]) : my_off;  // no table: row_map already holds the slot
             const int64_t rk = g / p.peer_rows;
             if (g >= 0 && rk < p.n_peers) {
                 my_off = (rk << kPeerRowBits) | (g - rk * p.peer_rows);
@@ -826,7 +827,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->tmem_empty[buf]));
         }
-        if (MODE == MODE_STORE && p.dst_flat) __threadfence_system();  // stores to other GPUs land before the kernel ends
+        if (MODE == MODE_STORE && p.n_peers > 0) __threadfence_system();  // stores to other GPUs land before the kernel ends
     }
 
     // ---- teardown ------------------------------------------------------------------------------------
@@ -1184,7 +1185,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(buf ? leader_empty1 : leader_empty0);
         }
-        if (MODE == MODE_STORE && p.dst_flat) __threadfence_system();  // stores to other GPUs land before the kernel ends
+        if (MODE == MODE_STORE && p.n_peers > 0) __threadfence_system();  // stores to other GPUs land before the kernel ends
     }
 
     // teardown: nobody leaves while the partner may still read its shared memory or signal its barriers
@@ -1423,7 +1424,7 @@ static int grouped_linear_t(const void *x, const void *w, const int32_t *mtile_o
     int rc;
     if ((rc = map_a_kmajor<T>(&p.tmA, x, cap, K)) != CK_OK) return rc;
     p.mtile_off = mtile_off; p.row_map = row_map; p.out0 = y; p.dev_status = dev_status;
-    if (dst_flat) {
+    if (n_peers > 0) {
         p.dst_flat = dst_flat; p.n_peers = n_peers; p.peer_rows = peer_rows;
         for (int i = 0; i < n_peers; ++i) p.peer_out[i] = peer_out[i];
         p.out0 = peer_out[0];  // only the base the row indices are taken against; nothing is stored through it
@@ -1534,7 +1535,7 @@ extern "C" int ck_moe_grouped_linear_scatter_peer(const void *x, const void *w, 
                                                   const int32_t *row_map, const int32_t *dst_flat, void *const *peer_out,
                                                   int n_peers, int64_t rows_per_peer, int E, int64_t cap, int N, int K,
                                                   int trans_w, int dtype, int32_t *dev_status, void *stream) {
-    if (!x || !w || !mtile_off || !row_map || !dst_flat || !peer_out || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, N, K))
+    if (!x || !w || !mtile_off || !row_map || !peer_out || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, N, K))
         return CK_ERR_SHAPE;
     if (n_peers <= 0 || n_peers > CK_MAX_PEERS || rows_per_peer <= 0) return CK_ERR_SHAPE;
     if (rows_per_peer > (int64_t(1) << kPeerRowBits) || rows_per_peer * n_peers > INT32_MAX) return CK_ERR_RANGE;

@@ -20,7 +20,8 @@ struct PeerTable {
 constexpr int kPeerThreads = 256;
 constexpr int kPeerUnroll = 8;
 
-// dst[p, :] = peer[g / S][(g % S) / fan_out, :] with g = src_flat[row_map[p]]; zeros where row_map[p] < 0.
+// dst[p, :] = peer[g / S][(g % S) / fan_out, :] with g = src_flat ? src_flat[row_map[p]] : row_map[p]; zeros where
+// row_map[p] < 0.
 // Every block owns one contiguous run of padded rows, so at any moment the grid reads from all parts of the
 // sorted order at once.  The sorted order is source-rank major inside an expert: a grid-stride sweep would have
 // every GPU of the node pulling from the same source rank at the same time and queue on that rank's links.
@@ -48,7 +49,7 @@ __global__ void __launch_bounds__(kPeerThreads)
                 const int64_t p = v / vpr, c = (v - p * vpr) * VEC;
                 const int32_t s = row_map[p];
                 if (s >= 0) {
-                    const int64_t g = src_flat[s];
+                    const int64_t g = src_flat ? int64_t(src_flat[s]) : int64_t(s);
                     const int64_t r = g / S;
                     if (g >= 0 && r < n_peers) {
                         const T *src = reinterpret_cast<const T *>(peers.p[r]) + ((g - r * S) / fan_out) * (vpr * VEC) + c;
@@ -82,16 +83,18 @@ __global__ void __launch_bounds__(kPeerThreads)
     }
 }
 
-// peer[g / S][g % S] = vals[j], g = flat[j]: every slot has exactly one writer across all ranks
+// peer[g / S][g % S] = by_slot ? vals[g] : vals[j], g = flat[j]; entries with g < 0 (pad rows) are skipped.
+// Every slot has exactly one writer across all ranks.
 template <typename U>
 __global__ void __launch_bounds__(kPeerThreads)
-    peer_scatter_scalars_kernel(const U *__restrict__ vals, const int32_t *__restrict__ flat, int64_t n,
+    peer_scatter_scalars_kernel(const U *__restrict__ vals, const int32_t *__restrict__ flat, int64_t n, int by_slot,
                                 const PeerTable peers, int n_peers, int64_t S, int32_t *dev_status) {
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     for (int64_t j = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; j < n; j += stride) {
         const int64_t g = flat[j];
+        if (g < 0) continue;
         const int64_t r = g / S;
-        if (g >= 0 && r < n_peers) reinterpret_cast<U *>(peers.p[r])[g - r * S] = vals[j];
+        if (r < n_peers) reinterpret_cast<U *>(peers.p[r])[g - r * S] = vals[by_slot ? g : j];
         else if (dev_status) atomicOr(dev_status, CK_DEV_RANGE);
     }
     __threadfence_system();  // the stores must have landed on the peer before this rank's next collective
@@ -135,7 +138,7 @@ extern "C" int ck_moe_gather_rows_peer(const void *const *peer_src, int n_peers,
                                        int64_t cap, int fan_out, int64_t cols, int dtype, int32_t *dev_status,
                                        void *stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
-    if (!dst || !row_map || !padded_off || !src_flat || E <= 0 || cap < 0 || fan_out <= 0 || cols <= 0 || rows_per_peer <= 0)
+    if (!dst || !row_map || !padded_off || E <= 0 || cap < 0 || fan_out <= 0 || cols <= 0 || rows_per_peer <= 0)
         return CK_ERR_SHAPE;
     if (rows_per_peer * n_peers > INT32_MAX) return CK_ERR_RANGE;
     PeerTable t;
@@ -169,8 +172,9 @@ extern "C" int ck_peer_gather_scalars(const void *const *peer_src, int n_peers, 
     return CK_OK;
 }
 
-extern "C" int ck_peer_scatter_scalars(const void *vals, const int32_t *flat, int64_t n, void *const *peer_dst, int n_peers,
-                                       int64_t rows_per_peer, int elem_bytes, int32_t *dev_status, void *stream_) {
+extern "C" int ck_peer_scatter_scalars(const void *vals, const int32_t *flat, int64_t n, int by_slot, void *const *peer_dst,
+                                       int n_peers, int64_t rows_per_peer, int elem_bytes, int32_t *dev_status,
+                                       void *stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (n < 0 || rows_per_peer <= 0 || (elem_bytes != 2 && elem_bytes != 4)) return CK_ERR_SHAPE;
     if (rows_per_peer * n_peers > INT32_MAX) return CK_ERR_RANGE;
@@ -180,9 +184,9 @@ extern "C" int ck_peer_scatter_scalars(const void *vals, const int32_t *flat, in
     if (n == 0) return CK_OK;
     if (!flat || !vals) return CK_ERR_SHAPE;
     if (elem_bytes == 2)
-        peer_scatter_scalars_kernel<uint16_t><<<peer_grid(n), kPeerThreads, 0, stream>>>((const uint16_t *)vals, flat, n, t, n_peers, rows_per_peer, dev_status);
+        peer_scatter_scalars_kernel<uint16_t><<<peer_grid(n), kPeerThreads, 0, stream>>>((const uint16_t *)vals, flat, n, by_slot, t, n_peers, rows_per_peer, dev_status);
     else
-        peer_scatter_scalars_kernel<uint32_t><<<peer_grid(n), kPeerThreads, 0, stream>>>((const uint32_t *)vals, flat, n, t, n_peers, rows_per_peer, dev_status);
+        peer_scatter_scalars_kernel<uint32_t><<<peer_grid(n), kPeerThreads, 0, stream>>>((const uint32_t *)vals, flat, n, by_slot, t, n_peers, rows_per_peer, dev_status);
     CK_LAUNCH_CHECK("peer_scatter_scalars_kernel");
     return CK_OK;
 }

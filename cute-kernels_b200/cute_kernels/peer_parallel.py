@@ -6,10 +6,10 @@ router weights and a return buffer in memory that the other ranks of the node ha
 and the permutation kernels address that memory directly:
 
   forward   publish x, router weights, expert ids            (local copies into the shared buffers)
-            all-gather the ids (256 KiB per rank; doubles as the "published" barrier)
-            route the gathered ids; this rank's experts own one contiguous run of the sorted order
+            all-gather the ids and weights (a few hundred KiB; doubles as the "published" barrier)
+            route all slots over this rank's experts plus a 'not mine' bin: row_map then names global slots
             gather the rows of that run from their owners      (ck_moe_gather_rows_peer: NVLink loads)
-            up projection + activation (router weight folded in, fetched with ck_peer_gather_scalars)
+            up projection + activation (router weight folded in; the weights travel with the ids)
             down projection, every result row stored into its owner's return buffer from the GEMM epilogue
                                                                (ck_moe_grouped_linear_scatter_peer: NVLink stores)
             barrier; k-way sum of the local return buffer      (ck_moe_combine_rows)
@@ -43,42 +43,34 @@ def _ptr_array(ptrs: list[int]):
     return (ctypes.c_void_p * len(ptrs))(*ptrs)
 
 
-def _gather_rows_peer(ptrs, S: int, dst, r: Routing, src_flat, fan_out: int) -> None:
+def _gather_rows_peer(ptrs, S: int, dst, r: Routing, experts: int, fan_out: int) -> None:
     status = _lib.status_word(dst.device)
     with torch.cuda.device(dst.device), _lib.launch("gather_rows_peer"):
         st = _lib.lib.ck_moe_gather_rows_peer(_ptr_array(ptrs), len(ptrs), S, dst.data_ptr(), r.row_map.data_ptr(),
-                                              r.padded_off.data_ptr(), src_flat.data_ptr(), r.padded_off.numel() - 1,
+                                              r.padded_off.data_ptr(), None, experts,
                                               dst.size(0), fan_out, dst.size(1), _lib.dtype_code(dst.dtype),
                                               status.data_ptr(), _lib.stream_ptr())
     _lib.check(st, "ck_moe_gather_rows_peer")
 
 
-def _linear_scatter_peer(x, w, r: Routing, dst_flat, ptrs, S: int, trans_w: bool) -> None:
+def _linear_scatter_peer(x, w, r: Routing, ptrs, S: int, trans_w: bool) -> None:
     status = _lib.status_word(x.device)
     E = w.size(0)
     N, K = (w.size(2), w.size(1)) if trans_w else (w.size(1), w.size(2))
     assert x.size(1) == K
     with torch.cuda.device(x.device), _lib.launch("grouped_linear_scatter_peer", 1, 2.0 * x.size(0) * N * K):
         st = _lib.lib.ck_moe_grouped_linear_scatter_peer(x.data_ptr(), w.data_ptr(), r.mtile_off.data_ptr(),
-                                                         r.row_map.data_ptr(), dst_flat.data_ptr(), _ptr_array(ptrs),
+                                                         r.row_map.data_ptr(), None, _ptr_array(ptrs),
                                                          len(ptrs), S, E, x.size(0), N, K, int(trans_w),
                                                          _lib.dtype_code(x.dtype), status.data_ptr(), _lib.stream_ptr())
     _lib.check(st, "ck_moe_grouped_linear_scatter_peer")
 
 
-def _gather_scalars_peer(ptrs, S: int, flat, n: int, dst) -> None:
-    status = _lib.status_word(dst.device)
-    with torch.cuda.device(dst.device), _lib.launch("peer_gather_scalars"):
-        st = _lib.lib.ck_peer_gather_scalars(_ptr_array(ptrs), len(ptrs), S, flat.data_ptr(), n, dst.data_ptr(),
-                                             dst.element_size(), status.data_ptr(), _lib.stream_ptr())
-    _lib.check(st, "ck_peer_gather_scalars")
-
-
-def _scatter_scalars_peer(vals, flat, n: int, ptrs, S: int) -> None:
-    status = _lib.status_word(vals.device)
-    with torch.cuda.device(vals.device), _lib.launch("peer_scatter_scalars"):
-        st = _lib.lib.ck_peer_scatter_scalars(vals.data_ptr(), flat.data_ptr(), n, _ptr_array(ptrs), len(ptrs), S,
-                                              vals.element_size(), status.data_ptr(), _lib.stream_ptr())
+def _scatter_scalars_peer(vals_by_slot, flat, n: int, ptrs, S: int) -> None:
+    status = _lib.status_word(vals_by_slot.device)
+    with torch.cuda.device(vals_by_slot.device), _lib.launch("peer_scatter_scalars"):
+        st = _lib.lib.ck_peer_scatter_scalars(vals_by_slot.data_ptr(), flat.data_ptr(), n, 1, _ptr_array(ptrs), len(ptrs), S,
+                                              vals_by_slot.element_size(), status.data_ptr(), _lib.stream_ptr())
     _lib.check(st, "ck_peer_scatter_scalars")
 
 
@@ -87,7 +79,7 @@ class PeerBuffers:
     """One rank's shared buffers and every rank's address of them (``*_ptrs[r]`` = rank r's buffer as mapped here).
 
     tokens [max_tokens, H]  x in forward, dy in backward          rows [S, H]  returned expert outputs / input grads
-    weights [S]             router weights, dtype of x            dgates [S]   router-weight grads, fp32
+    weights [S]             router weights, dtype of x (local)    dgates [S]   router-weight grads, fp32
     ids [S] int32           published expert ids (``num_experts`` = "no row" on the unused tail)
     """
 
@@ -102,7 +94,6 @@ class PeerBuffers:
     ids: torch.Tensor
     tokens_ptrs: list[int]
     rows_ptrs: list[int]
-    weights_ptrs: list[int]
     dgates_ptrs: list[int]
 
     @property
@@ -112,9 +103,9 @@ class PeerBuffers:
 
 @dataclass
 class _Plan:
-    src_flat: torch.Tensor   # int32 [n_local]: global flat slot of every row this rank's experts own, sorted by expert
-    routing: Routing         # padded layout of those rows over the local experts (row_map -> index into src_flat)
-    n_local: int
+    routing: Routing   # all ranks' slots routed over [this rank's experts..., "not mine"]; row_map[p] = global flat slot
+    rows: int          # padded rows of the local experts (a multiple of 128, may be 0)
+    cap: int           # rows to allocate: max(rows, 128)
 
 
 class PeerExpertEngine:
@@ -141,32 +132,30 @@ class PeerExpertEngine:
         b.ids[T * b.top_k:].fill_(self.num_experts)
 
     def plan(self, ids_all: torch.Tensor) -> _Plan:
-        """ids_all int32 [world * S]: every rank's published ids, rank-major."""
-        b, E, epr = self.b, self.num_experts, self.local_experts
-        g = route(ids_all, E + 1, with_tile_metadata=False, with_sorted_expert=True)
-        e0 = b.rank * epr
-        lo, hi = torch.stack([g.excl_offsets[e0], g.end_offsets[e0 + epr - 1]]).tolist()  # the one host sync
-        if hi == lo:  # no row chose this rank's experts: one placeholder entry keeps the pointers valid, n_local = 0
-            return _Plan(torch.zeros(1, dtype=torch.int32, device=ids_all.device), route(g.sorted_expert[:0], epr), 0)
-        src_flat = g.sorted_idx[lo:hi]
-        local_ids = g.sorted_expert[lo:hi] - e0
-        return _Plan(src_flat, route(local_ids, epr), hi - lo)
+        """ids_all int32 [world * S]: every rank's published ids, rank-major.  One routing pass over all slots with
+        the ids of other ranks' experts folded into a last "not mine" bin: the local experts' segments of the padded
+        layout then list global flat slots, in (source rank, token) order inside every expert."""
+        epr = self.local_experts
+        loc = ids_all - self.b.rank * epr
+        loc = torch.where((loc >= 0) & (loc < epr), loc, epr)
+        r = route(loc, epr + 1)
+        rows = int(r.padded_off[epr].item())  # the one host sync: rows to allocate
+        return _Plan(r, rows, max(rows, _lib.CK_TILE_M))
 
-    def fwd_compute(self, plan: _Plan, w_fc: torch.Tensor, w_proj: torch.Tensor, need_grad: bool):
+    def fwd_compute(self, plan: _Plan, weights_all: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor,
+                    need_grad: bool):
+        """weights_all [world * S]: every rank's published router weights (indexed by global flat slot)."""
         b, r = self.b, plan.routing
         dev, dt = b.tokens.device, b.tokens.dtype
         H = b.tokens.size(1)
         two_i = w_fc.size(1)
-        cap = r.row_map.numel()
-        gate = torch.empty(max(plan.n_local, 1), dtype=dt, device=dev)
-        _gather_scalars_peer(b.weights_ptrs, b.slots, plan.src_flat, plan.n_local, gate)
-        xg = torch.empty(cap, H, dtype=dt, device=dev)
-        _gather_rows_peer(b.tokens_ptrs, b.slots, xg, r, plan.src_flat, b.top_k)
-        act = torch.empty(cap, two_i // 2, dtype=dt, device=dev)
-        h = torch.empty(cap, two_i, dtype=dt, device=dev) if need_grad else None
-        up_act_fwd(xg, w_fc, gate, r.row_map, r.mtile_off, act, h, self.act_kind)
-        _linear_scatter_peer(act, w_proj, r, plan.src_flat, b.rows_ptrs, b.slots, False)
-        return xg, act, h, gate
+        xg = torch.empty(plan.cap, H, dtype=dt, device=dev)
+        _gather_rows_peer(b.tokens_ptrs, b.slots, xg, r, self.local_experts, b.top_k)
+        act = torch.empty(plan.cap, two_i // 2, dtype=dt, device=dev)
+        h = torch.empty(plan.cap, two_i, dtype=dt, device=dev) if need_grad else None
+        up_act_fwd(xg, w_fc, weights_all, r.row_map, r.mtile_off, act, h, self.act_kind)
+        _linear_scatter_peer(act, w_proj, r, b.rows_ptrs, b.slots, False)
+        return xg, act, h
 
     def fwd_finish(self, T: int) -> torch.Tensor:
         b = self.b
@@ -179,24 +168,22 @@ class PeerExpertEngine:
     def bwd_publish(self, dy: torch.Tensor) -> None:
         self.b.tokens[: dy.size(0)].copy_(dy)
 
-    def bwd_compute(self, plan: _Plan, saved, w_fc, w_proj, need_wfc: bool, need_wproj: bool, need_x: bool):
+    def bwd_compute(self, plan: _Plan, saved, weights_all, w_fc, w_proj, need_wfc: bool, need_wproj: bool, need_x: bool):
         b, r = self.b, plan.routing
-        xg, act, h, gate = saved
+        xg, act, h = saved
         dev, dt = xg.device, xg.dtype
-        H = xg.size(1)
-        cap = r.row_map.numel()
-        dyg = torch.empty(cap, H, dtype=dt, device=dev)
-        _gather_rows_peer(b.tokens_ptrs, b.slots, dyg, r, plan.src_flat, b.top_k)
-        dh = torch.empty(cap, w_fc.size(1), dtype=dt, device=dev)
-        dgates = torch.zeros(max(plan.n_local, 1), dtype=torch.float32, device=dev)
-        dgrad_down(dyg, w_proj, h, gate, r.row_map, r.mtile_off, dh, dgates, self.act_kind)
+        dyg = torch.empty(plan.cap, xg.size(1), dtype=dt, device=dev)
+        _gather_rows_peer(b.tokens_ptrs, b.slots, dyg, r, self.local_experts, b.top_k)
+        dh = torch.empty(plan.cap, w_fc.size(1), dtype=dt, device=dev)
+        dgates = torch.zeros(b.world * b.slots, dtype=torch.float32, device=dev)  # by global flat slot
+        dgrad_down(dyg, w_proj, h, weights_all, r.row_map, r.mtile_off, dh, dgates, self.act_kind)
         d_wproj = d_wfc = None
         if need_wproj:
             d_wproj = torch.empty_like(w_proj)
             wgrad(dyg, act, r.padded_off, d_wproj)
-        _scatter_scalars_peer(dgates, plan.src_flat, plan.n_local, b.dgates_ptrs, b.slots)
+        _scatter_scalars_peer(dgates, r.row_map, plan.rows, b.dgates_ptrs, b.slots)  # local experts' rows only
         if need_x:
-            _linear_scatter_peer(dh, w_fc, r, plan.src_flat, b.rows_ptrs, b.slots, True)
+            _linear_scatter_peer(dh, w_fc, r, b.rows_ptrs, b.slots, True)
         if need_wfc:
             d_wfc = torch.empty_like(w_fc)
             wgrad(dh, xg, r.padded_off, d_wfc)
@@ -220,9 +207,9 @@ class _NcclExchange:
         self.group = group
         self.flag = torch.zeros(1, dtype=torch.float32, device=device)
 
-    def all_gather_ids(self, ids_local: torch.Tensor) -> torch.Tensor:
-        out = torch.empty(dist.get_world_size(self.group) * ids_local.numel(), dtype=ids_local.dtype, device=ids_local.device)
-        dist.all_gather_into_tensor(out, ids_local, group=self.group)
+    def all_gather(self, local: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(dist.get_world_size(self.group) * local.numel(), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local, group=self.group)
         return out
 
     def barrier(self) -> None:
@@ -234,22 +221,24 @@ class _PeerExperts(torch.autograd.Function):
     def forward(ctx, x, router_weights, w_fc, w_proj, selected_experts, engine: PeerExpertEngine, exchange):
         need_grad = any(ctx.needs_input_grad[:4])
         engine.publish(x, router_weights, selected_experts)
-        plan = engine.plan(exchange.all_gather_ids(engine.b.ids))
-        saved = engine.fwd_compute(plan, w_fc, w_proj, need_grad)
+        ids_all = exchange.all_gather(engine.b.ids)            # also the "everything is published" ordering point
+        weights_all = exchange.all_gather(engine.b.weights)
+        plan = engine.plan(ids_all)
+        saved = engine.fwd_compute(plan, weights_all, w_fc, w_proj, need_grad)
         exchange.barrier()
         y = engine.fwd_finish(x.size(0))
         ctx.engine, ctx.exchange, ctx.plan, ctx.tokens = engine, exchange, plan, x.size(0)
-        ctx.save_for_backward(w_fc, w_proj, *saved)
+        ctx.save_for_backward(w_fc, w_proj, weights_all, *saved)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        w_fc, w_proj, *saved = ctx.saved_tensors
+        w_fc, w_proj, weights_all, *saved = ctx.saved_tensors
         engine, exchange, plan, T = ctx.engine, ctx.exchange, ctx.plan, ctx.tokens
         need_x, need_rw, need_wfc, need_wproj = ctx.needs_input_grad[:4]
         engine.bwd_publish(dy.contiguous().to(saved[0].dtype))
         exchange.barrier()
-        d_wfc, d_wproj = engine.bwd_compute(plan, saved, w_fc, w_proj, need_wfc, need_wproj, need_x)
+        d_wfc, d_wproj = engine.bwd_compute(plan, saved, weights_all, w_fc, w_proj, need_wfc, need_wproj, need_x)
         exchange.barrier()
         dx, d_rw = engine.bwd_finish(T, need_x)
         return dx, (d_rw if need_rw else None), d_wfc, d_wproj, None, None, None
@@ -271,11 +260,11 @@ def allocate_symmetric_buffers(max_tokens: int, hidden_size: int, top_k: int, dt
 
     tokens, tokens_ptrs = shared((max_tokens, hidden_size), dtype)
     rows, rows_ptrs = shared((S, hidden_size), dtype)
-    weights, weights_ptrs = shared((S,), dtype)
+    weights = torch.empty(S, dtype=dtype, device=device)
     dgates, dgates_ptrs = shared((S,), torch.float32)
     ids = torch.empty(S, dtype=torch.int32, device=device)
     return PeerBuffers(dist.get_rank(group), dist.get_world_size(group), max_tokens, top_k, tokens, rows, weights,
-                       dgates, ids, tokens_ptrs, rows_ptrs, weights_ptrs, dgates_ptrs)
+                       dgates, ids, tokens_ptrs, rows_ptrs, dgates_ptrs)
 
 
 class PeerExpertParallelMoE:

@@ -259,12 +259,15 @@ CK_API int ck_router_topk_softmax_bwd(const void *weights, const void *d_weights
  * device pointers (rank r's buffer as mapped into this process; entry [own rank] is the local buffer), all
  * 16-byte aligned, n_peers <= CK_MAX_PEERS, n_peers * rows_per_peer < 2^31.  The kernels never wait on another
  * GPU; the host orders the phases with stream-ordered collectives.
- * ck_moe_gather_rows_peer: dst[p, :] = peer_src[g / S][(g % S) / fan_out, :], g = src_flat[row_map[p]], zeros
- *   where row_map[p] < 0, for p < padded_off[E].
+ * ck_moe_gather_rows_peer: dst[p, :] = peer_src[g / S][(g % S) / fan_out, :], g = src_flat[row_map[p]] (row_map[p]
+ *   itself when src_flat is NULL: the ids of all ranks were routed as one array), zeros where row_map[p] < 0,
+ *   for p < padded_off[E].
  * ck_moe_grouped_linear_scatter_peer: ck_moe_grouped_linear_scatter whose row row_map[p] is stored at
- *   peer_out[g / S] + (g % S) * N, g = dst_flat[row_map[p]]  (rows_per_peer <= 2^26).
- * ck_peer_gather_scalars / ck_peer_scatter_scalars: dst[j] = peer_src[g / S][g % S] and peer_dst[g / S][g % S] =
- *   vals[j], g = flat[j], for 2- or 4-byte scalars (router weights and their gradients).
+ *   peer_out[g / S] + (g % S) * N, g = dst_flat[row_map[p]] or row_map[p] when dst_flat is NULL
+ *   (rows_per_peer <= 2^26).
+ * ck_peer_gather_scalars: dst[j] = peer_src[g / S][g % S], g = flat[j].
+ * ck_peer_scatter_scalars: peer_dst[g / S][g % S] = by_slot ? vals[g] : vals[j], g = flat[j], entries with g < 0
+ *   skipped.  Both for 2- or 4-byte scalars (router weights and their gradients).
  * A slot outside [0, n_peers * S) is skipped and sets CK_DEV_RANGE in *dev_status. */
 #define CK_MAX_PEERS 16
 CK_API int ck_moe_gather_rows_peer(const void *const *peer_src, int n_peers, int64_t rows_per_peer, void *dst,
@@ -278,9 +281,9 @@ CK_API int ck_moe_grouped_linear_scatter_peer(const void *x, const void *w, cons
 CK_API int ck_peer_gather_scalars(const void *const *peer_src, int n_peers, int64_t rows_per_peer,
                                   const int32_t *flat, int64_t n, void *dst, int elem_bytes, int32_t *dev_status,
                                   void *stream);
-CK_API int ck_peer_scatter_scalars(const void *vals, const int32_t *flat, int64_t n, void *const *peer_dst,
-                                   int n_peers, int64_t rows_per_peer, int elem_bytes, int32_t *dev_status,
-                                   void *stream);
+CK_API int ck_peer_scatter_scalars(const void *vals, const int32_t *flat, int64_t n, int by_slot,
+                                   void *const *peer_dst, int n_peers, int64_t rows_per_peer, int elem_bytes,
+                                   int32_t *dev_status, void *stream);
 
 #ifdef __cplusplus
 }

@@ -21,10 +21,10 @@ def _virtual_world(world, max_tokens, H, k, dt):
                 weights=torch.full((S,), float("nan"), dtype=dt, device=dev),
                 dgates=torch.full((S,), float("nan"), dtype=torch.float32, device=dev),
                 ids=torch.empty(S, dtype=torch.int32, device=dev)) for _ in range(world)]
-    ptrs = {name: [r[name].data_ptr() for r in raw] for name in ("tokens", "rows", "weights", "dgates")}
+    ptrs = {name: [r[name].data_ptr() for r in raw] for name in ("tokens", "rows", "dgates")}
     return [PeerBuffers(rank, world, max_tokens, k, raw[rank]["tokens"], raw[rank]["rows"], raw[rank]["weights"],
-                        raw[rank]["dgates"], raw[rank]["ids"], ptrs["tokens"], ptrs["rows"], ptrs["weights"],
-                        ptrs["dgates"]) for rank in range(world)]
+                        raw[rank]["dgates"], raw[rank]["ids"], ptrs["tokens"], ptrs["rows"], ptrs["dgates"])
+            for rank in range(world)]
 
 
 CASES = [
@@ -59,14 +59,16 @@ def test_peer_engine_lockstep(cfg, dt):
         eng[r].publish(full["x"][sl[r]].to(dt).cuda(), full["router_weights"][sl[r]].to(dt).cuda(),
                        full["selected_experts"][sl[r]].to(torch.int32).cuda())
     ids_all = torch.cat([b.ids for b in bufs])
+    weights_all = torch.cat([b.weights for b in bufs])
     plans = [eng[r].plan(ids_all) for r in range(world)]
-    assert sum(p.n_local for p in plans) == sum(Ts) * k
-    saved = [eng[r].fwd_compute(plans[r], w_fc[r], w_proj[r], True) for r in range(world)]
+    owned = sum(int(p.routing.counts[:epr].long().sum()) for p in plans)
+    assert owned == sum(Ts) * k                       # every routed row has exactly one owner
+    saved = [eng[r].fwd_compute(plans[r], weights_all, w_fc[r], w_proj[r], True) for r in range(world)]
     ys = [eng[r].fwd_finish(Ts[r]) for r in range(world)]
     # ---- backward ----
     for r in range(world):
         eng[r].bwd_publish(full["grad_out"][sl[r]].to(dt).cuda())
-    grads = [eng[r].bwd_compute(plans[r], saved[r], w_fc[r], w_proj[r], True, True, True) for r in range(world)]
+    grads = [eng[r].bwd_compute(plans[r], saved[r], weights_all, w_fc[r], w_proj[r], True, True, True) for r in range(world)]
     backs = [eng[r].bwd_finish(Ts[r], True) for r in range(world)]
     torch.cuda.synchronize()
     ck.check_device_status()
@@ -100,6 +102,26 @@ def test_peer_kernels_reject_bad_tables():
     assert st == -1
     st = _lib.lib.ck_peer_gather_scalars(arr, 1, 1 << 31, i32.data_ptr(), 1, x.data_ptr(), 2, None, None)  # slots overflow int32
     assert st == -2
+
+
+def test_peer_scalar_kernels():
+    from cute_kernels import _lib
+    import ctypes
+
+    S, world = 50, 3
+    bufs = [torch.arange(S, device="cuda", dtype=torch.float32) + 100 * r for r in range(world)]
+    arr = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    flat = torch.tensor([0, 49, 50, 149, 77], dtype=torch.int32, device="cuda")
+    out = torch.empty(5, dtype=torch.float32, device="cuda")
+    assert _lib.lib.ck_peer_gather_scalars(arr, world, S, flat.data_ptr(), 5, out.data_ptr(), 4, None, None) == 0
+    assert out.tolist() == [0.0, 49.0, 100.0, 249.0, 127.0]
+    vals = torch.arange(world * S, device="cuda", dtype=torch.float32) * -1.0
+    flat2 = torch.tensor([3, -1, 60, 149], dtype=torch.int32, device="cuda")
+    assert _lib.lib.ck_peer_scatter_scalars(vals.data_ptr(), flat2.data_ptr(), 4, 1, arr, world, S, 4, None, None) == 0
+    assert bufs[0][3].item() == -3.0 and bufs[1][10].item() == -60.0 and bufs[2][49].item() == -149.0
+    assert _lib.lib.ck_peer_scatter_scalars(vals.data_ptr(), flat2.data_ptr(), 4, 0, arr, world, S, 4, None, None) == 0
+    assert bufs[0][3].item() == 0.0 and bufs[1][10].item() == -2.0 and bufs[2][49].item() == -3.0
+    assert bufs[0][4].item() == 4.0   # untouched neighbours
 
 
 def test_combine_rows_identity_positions():
