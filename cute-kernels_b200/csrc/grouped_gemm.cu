@@ -135,7 +135,7 @@ __device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, Smem
 template <int MODE>
 __device__ __forceinline__ int total_tiles(const GemmParams &p, const SmemCtl *ctl) {
     if constexpr (MODE == MODE_WGRAD) return p.E * p.m_tiles_w * p.n_tiles;
-    return ctl->sched[p.E] * p.n_tiles;
+    return (ctl->sched[p.E] - ctl->sched[0]) * p.n_tiles;  // mtile_off may start above 0: a window of the padded rows
 }
 
 template <int MODE, int BK>
@@ -158,6 +158,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, const Smem
     } else {
         // experts in order; inside an expert n-major with the m-tiles fastest, so that concurrently
         // running CTAs share one weight panel and the expert's activation rows stay L2 resident
+        t += ctl->sched[0] * p.n_tiles;
         int lo = 0, hi = p.E;  // find e with sched[e]*n_tiles <= t < sched[e+1]*n_tiles
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;

@@ -30,12 +30,14 @@ __global__ void __launch_bounds__(kPeerThreads)
     gather_rows_peer_kernel(const PeerTable peers, int n_peers, int64_t S, T *__restrict__ dst,
                             const int32_t *__restrict__ row_map, const int32_t *__restrict__ padded_off,
                             const int32_t *__restrict__ src_flat, int E, int64_t cap, int fan_out, int64_t vpr,
-                            int32_t *dev_status) {
+                            int64_t row_begin, int64_t row_end, int32_t *dev_status) {
     constexpr int VEC = Vec16<T>::N;
     int64_t rows = padded_off[E];
     if (rows > cap) rows = cap;
-    const int64_t rows_per_block = ceil_div64(rows, gridDim.x);
-    const int64_t row0 = int64_t(blockIdx.x) * rows_per_block;
+    if (rows > row_end) rows = row_end;
+    if (rows <= row_begin) return;
+    const int64_t rows_per_block = ceil_div64(rows - row_begin, gridDim.x);
+    const int64_t row0 = row_begin + int64_t(blockIdx.x) * rows_per_block;
     const int64_t row1 = min(row0 + rows_per_block, rows);
     const int64_t v_begin = row0 * vpr, v_end = row1 * vpr;
     bool bad = false;
@@ -119,12 +121,13 @@ static inline unsigned peer_grid(int64_t items) {
 template <typename T>
 static int gather_rows_peer_t(const PeerTable &t, int n_peers, int64_t S, void *dst, const int32_t *row_map,
                               const int32_t *padded_off, const int32_t *src_flat, int E, int64_t cap, int fan_out,
-                              int64_t cols, int32_t *dev_status, cudaStream_t stream) {
+                              int64_t cols, int64_t row_begin, int64_t row_end, int32_t *dev_status, cudaStream_t stream) {
     constexpr int VEC = Vec16<T>::N;
     if (cols % VEC != 0 || (reinterpret_cast<uintptr_t>(dst) & 15)) return CK_ERR_SHAPE;
     const int64_t vpr = cols / VEC;
-    gather_rows_peer_kernel<T><<<peer_grid(ceil_div64(cap * vpr, kPeerUnroll)), kPeerThreads, 0, stream>>>(
-        t, n_peers, S, (T *)dst, row_map, padded_off, src_flat, E, cap, fan_out, vpr, dev_status);
+    const int64_t span = (row_end < cap ? row_end : cap) - row_begin;
+    gather_rows_peer_kernel<T><<<peer_grid(ceil_div64(span * vpr, kPeerUnroll)), kPeerThreads, 0, stream>>>(
+        t, n_peers, S, (T *)dst, row_map, padded_off, src_flat, E, cap, fan_out, vpr, row_begin, row_end, dev_status);
     CK_LAUNCH_CHECK("gather_rows_peer_kernel");
     return CK_OK;
 }
@@ -135,8 +138,8 @@ using namespace ck;
 
 extern "C" int ck_moe_gather_rows_peer(const void *const *peer_src, int n_peers, int64_t rows_per_peer, void *dst,
                                        const int32_t *row_map, const int32_t *padded_off, const int32_t *src_flat, int E,
-                                       int64_t cap, int fan_out, int64_t cols, int dtype, int32_t *dev_status,
-                                       void *stream_) {
+                                       int64_t cap, int fan_out, int64_t cols, int64_t row_begin, int64_t row_end,
+                                       int dtype, int32_t *dev_status, void *stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (!dst || !row_map || !padded_off || E <= 0 || cap < 0 || fan_out <= 0 || cols <= 0 || rows_per_peer <= 0)
         return CK_ERR_SHAPE;
@@ -144,11 +147,12 @@ extern "C" int ck_moe_gather_rows_peer(const void *const *peer_src, int n_peers,
     PeerTable t;
     const int rc = fill_table(t, peer_src, n_peers);
     if (rc != CK_OK) return rc;
-    if (cap == 0) return CK_OK;
+    if (row_begin < 0 || row_end < row_begin) return CK_ERR_SHAPE;
+    if (cap == 0 || row_begin >= cap || row_end == row_begin) return CK_OK;
     switch (dtype) {
-        case CK_F32: return gather_rows_peer_t<float>(t, n_peers, rows_per_peer, dst, row_map, padded_off, src_flat, E, cap, fan_out, cols, dev_status, stream);
-        case CK_F16: return gather_rows_peer_t<__half>(t, n_peers, rows_per_peer, dst, row_map, padded_off, src_flat, E, cap, fan_out, cols, dev_status, stream);
-        case CK_BF16: return gather_rows_peer_t<__nv_bfloat16>(t, n_peers, rows_per_peer, dst, row_map, padded_off, src_flat, E, cap, fan_out, cols, dev_status, stream);
+        case CK_F32: return gather_rows_peer_t<float>(t, n_peers, rows_per_peer, dst, row_map, padded_off, src_flat, E, cap, fan_out, cols, row_begin, row_end, dev_status, stream);
+        case CK_F16: return gather_rows_peer_t<__half>(t, n_peers, rows_per_peer, dst, row_map, padded_off, src_flat, E, cap, fan_out, cols, row_begin, row_end, dev_status, stream);
+        case CK_BF16: return gather_rows_peer_t<__nv_bfloat16>(t, n_peers, rows_per_peer, dst, row_map, padded_off, src_flat, E, cap, fan_out, cols, row_begin, row_end, dev_status, stream);
         default: return CK_ERR_UNSUPPORTED;
     }
 }

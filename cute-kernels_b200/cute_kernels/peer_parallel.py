@@ -8,7 +8,9 @@ and the permutation kernels address that memory directly:
   forward   publish x, router weights, expert ids            (local copies into the shared buffers)
             all-gather the ids and weights (a few hundred KiB; doubles as the "published" barrier)
             route all slots over this rank's experts plus a 'not mine' bin: row_map then names global slots
-            gather the rows of that run from their owners      (ck_moe_gather_rows_peer: NVLink loads)
+            gather those rows from their owners                (ck_moe_gather_rows_peer: NVLink loads; in two
+                                                               windows, the second pulled on a side stream while
+                                                               the GEMM already runs on the first)
             up projection + activation (router weight folded in; the weights travel with the ids)
             down projection, every result row stored into its owner's return buffer from the GEMM epilogue
                                                                (ck_moe_grouped_linear_scatter_peer: NVLink stores)
@@ -43,13 +45,13 @@ def _ptr_array(ptrs: list[int]):
     return (ctypes.c_void_p * len(ptrs))(*ptrs)
 
 
-def _gather_rows_peer(ptrs, S: int, dst, r: Routing, experts: int, fan_out: int) -> None:
+def _gather_rows_peer(ptrs, S: int, dst, r: Routing, experts: int, fan_out: int, row_begin: int, row_end: int) -> None:
     status = _lib.status_word(dst.device)
     with torch.cuda.device(dst.device), _lib.launch("gather_rows_peer"):
         st = _lib.lib.ck_moe_gather_rows_peer(_ptr_array(ptrs), len(ptrs), S, dst.data_ptr(), r.row_map.data_ptr(),
                                               r.padded_off.data_ptr(), None, experts,
-                                              dst.size(0), fan_out, dst.size(1), _lib.dtype_code(dst.dtype),
-                                              status.data_ptr(), _lib.stream_ptr())
+                                              dst.size(0), fan_out, dst.size(1), row_begin, row_end,
+                                              _lib.dtype_code(dst.dtype), status.data_ptr(), _lib.stream_ptr())
     _lib.check(st, "ck_moe_gather_rows_peer")
 
 
@@ -106,6 +108,9 @@ class _Plan:
     routing: Routing   # all ranks' slots routed over [this rank's experts..., "not mine"]; row_map[p] = global flat slot
     rows: int          # padded rows of the local experts (a multiple of 128, may be 0)
     cap: int           # rows to allocate: max(rows, 128)
+    split: int         # m-tiles in the first window of the pull (0: one window)
+    mtile_first: torch.Tensor | None   # mtile_off clamped to the first window / to the rest
+    mtile_rest: torch.Tensor | None
 
 
 class PeerExpertEngine:
@@ -118,6 +123,7 @@ class PeerExpertEngine:
         self.num_experts = num_experts
         self.local_experts = num_experts // buffers.world
         self.act_kind = act_kind
+        self._side: torch.cuda.Stream | None = None
 
     # ---- forward -------------------------------------------------------------------------------------
     def publish(self, x: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor) -> None:
@@ -140,7 +146,44 @@ class PeerExpertEngine:
         loc = torch.where((loc >= 0) & (loc < epr), loc, epr)
         r = route(loc, epr + 1)
         rows = int(r.padded_off[epr].item())  # the one host sync: rows to allocate
-        return _Plan(r, rows, max(rows, _lib.CK_TILE_M))
+        # Two windows of the padded rows: the pull of the second runs on a side stream under the GEMM on the first.
+        tiles = rows // _lib.CK_TILE_M
+        split = 0
+        if tiles >= self.MIN_TILES_TO_SPLIT:
+            split = min(tiles - 2, max(2, (tiles // 4 + 1) & ~1))  # a quarter of the rows, whole CTA pairs
+        first = r.mtile_off.clamp(max=split) if split else None
+        rest = r.mtile_off.clamp(min=split) if split else None
+        return _Plan(r, rows, max(rows, _lib.CK_TILE_M), split, first, rest)
+
+    MIN_TILES_TO_SPLIT = 16
+
+    def _side_stream(self) -> torch.cuda.Stream:
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.b.tokens.device)
+        return self._side
+
+    def _pull_then(self, plan: _Plan, dst: torch.Tensor, gemm) -> None:
+        """Pulls the padded rows of ``dst`` from their owners and runs ``gemm(mtile_off)`` on them.  With two windows:
+        pull A; then pull B on the side stream while gemm(A) runs; gemm(B) once B has landed."""
+        b, r = self.b, plan.routing
+        if not plan.split:
+            _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, 0, plan.cap)
+            gemm(r.mtile_off)
+            return
+        main, side = torch.cuda.current_stream(), self._side_stream()
+        edge = plan.split * _lib.CK_TILE_M
+        _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, 0, edge)
+        first_done = torch.cuda.Event()
+        first_done.record(main)
+        side.wait_event(first_done)
+        with torch.cuda.stream(side):
+            _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, edge, plan.cap)
+            rest_done = torch.cuda.Event()
+            rest_done.record(side)
+        dst.record_stream(side)
+        gemm(plan.mtile_first)
+        main.wait_event(rest_done)
+        gemm(plan.mtile_rest)
 
     def fwd_compute(self, plan: _Plan, weights_all: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor,
                     need_grad: bool):
@@ -150,10 +193,9 @@ class PeerExpertEngine:
         H = b.tokens.size(1)
         two_i = w_fc.size(1)
         xg = torch.empty(plan.cap, H, dtype=dt, device=dev)
-        _gather_rows_peer(b.tokens_ptrs, b.slots, xg, r, self.local_experts, b.top_k)
         act = torch.empty(plan.cap, two_i // 2, dtype=dt, device=dev)
         h = torch.empty(plan.cap, two_i, dtype=dt, device=dev) if need_grad else None
-        up_act_fwd(xg, w_fc, weights_all, r.row_map, r.mtile_off, act, h, self.act_kind)
+        self._pull_then(plan, xg, lambda mt: up_act_fwd(xg, w_fc, weights_all, r.row_map, mt, act, h, self.act_kind))
         _linear_scatter_peer(act, w_proj, r, b.rows_ptrs, b.slots, False)
         return xg, act, h
 
@@ -173,10 +215,10 @@ class PeerExpertEngine:
         xg, act, h = saved
         dev, dt = xg.device, xg.dtype
         dyg = torch.empty(plan.cap, xg.size(1), dtype=dt, device=dev)
-        _gather_rows_peer(b.tokens_ptrs, b.slots, dyg, r, self.local_experts, b.top_k)
         dh = torch.empty(plan.cap, w_fc.size(1), dtype=dt, device=dev)
         dgates = torch.zeros(b.world * b.slots, dtype=torch.float32, device=dev)  # by global flat slot
-        dgrad_down(dyg, w_proj, h, weights_all, r.row_map, r.mtile_off, dh, dgates, self.act_kind)
+        self._pull_then(plan, dyg,
+                        lambda mt: dgrad_down(dyg, w_proj, h, weights_all, r.row_map, mt, dh, dgates, self.act_kind))
         d_wproj = d_wfc = None
         if need_wproj:
             d_wproj = torch.empty_like(w_proj)

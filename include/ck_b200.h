@@ -143,6 +143,9 @@ CK_API int ck_cast_from_f32(const float *src, void *dst, int64_t n, int dtype, v
  * kernels.py:12-222).  Notation: Rp = padded_off[E] rows (capacity `cap` allocated), H hidden,
  * I intermediate, T tokens, k top-k.  All matrices row-major, 16-byte aligned, leading dimensions
  * equal to the logical widths.  H % 8 == 0 and I % 8 == 0.
+ * Every entry that takes mtile_off processes the m-tiles [mtile_off[e], mtile_off[e+1]) of expert e; mtile_off[0]
+ * may be above 0 and the array may be a clamped copy (min(max(mtile_off, lo), hi)): the call then covers only the
+ * padded rows [128 lo, 128 hi), which lets a caller run one window while another is still being filled.
  * `tmap_cache` is reserved (pass NULL). */
 
 /* up projection + fused activation:  h[p, :] = xg[p, :] @ Wfc[e]^T  ([up | gate], 2I wide),
@@ -261,7 +264,8 @@ CK_API int ck_router_topk_softmax_bwd(const void *weights, const void *d_weights
  * GPU; the host orders the phases with stream-ordered collectives.
  * ck_moe_gather_rows_peer: dst[p, :] = peer_src[g / S][(g % S) / fan_out, :], g = src_flat[row_map[p]] (row_map[p]
  *   itself when src_flat is NULL: the ids of all ranks were routed as one array), zeros where row_map[p] < 0,
- *   for p < padded_off[E].
+ *   for p in [row_begin, min(row_end, padded_off[E])): a window of the padded rows, so that a caller can pull one
+ *   part while a GEMM already runs on another.
  * ck_moe_grouped_linear_scatter_peer: ck_moe_grouped_linear_scatter whose row row_map[p] is stored at
  *   peer_out[g / S] + (g % S) * N, g = dst_flat[row_map[p]] or row_map[p] when dst_flat is NULL
  *   (rows_per_peer <= 2^26).
@@ -272,8 +276,8 @@ CK_API int ck_router_topk_softmax_bwd(const void *weights, const void *d_weights
 #define CK_MAX_PEERS 16
 CK_API int ck_moe_gather_rows_peer(const void *const *peer_src, int n_peers, int64_t rows_per_peer, void *dst,
                                    const int32_t *row_map, const int32_t *padded_off, const int32_t *src_flat, int E,
-                                   int64_t cap, int fan_out, int64_t cols, int dtype, int32_t *dev_status,
-                                   void *stream);
+                                   int64_t cap, int fan_out, int64_t cols, int64_t row_begin, int64_t row_end,
+                                   int dtype, int32_t *dev_status, void *stream);
 CK_API int ck_moe_grouped_linear_scatter_peer(const void *x, const void *w, const int32_t *mtile_off,
                                               const int32_t *row_map, const int32_t *dst_flat, void *const *peer_out,
                                               int n_peers, int64_t rows_per_peer, int E, int64_t cap, int N, int K,

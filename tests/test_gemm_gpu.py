@@ -88,6 +88,32 @@ def test_grouped_linear(dtype, trans_w, case):
     assert torch.isnan(y[total:].float()).all()  # rows past the padded total are never written
 
 
+@pytest.mark.parametrize("split", [1, 2, 3, 5])
+@pytest.mark.parametrize("case", [([300, 17, 128, 0, 256], 136, 264), ([700, 900], 512, 1024), ([0, 0, 5], 64, 256)])
+def test_grouped_linear_row_windows(case, split):
+    """Two calls with clamped copies of mtile_off (m-tiles [0, split) and [split, end)) write exactly what one call writes."""
+    from cute_kernels.moe import grouped_linear
+
+    counts, K, N = case
+    E = len(counts)
+    ids, r, ref = _routing(counts, 1)
+    x = _padded_rows(ref, K, torch.bfloat16, 1)
+    g = torch.Generator().manual_seed(2)
+    w = torch.randn(E, N, K, generator=g).mul(0.1).bfloat16().cuda()
+    full = torch.full((x.size(0), N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    grouped_linear(x, w, r.mtile_off, full, False)
+    y = torch.full_like(full, float("nan"))
+    total = int(ref["padded_off"][-1])
+    split = min(split, total // 128)                         # the window edge stays inside the padded rows
+    grouped_linear(x, w, r.mtile_off.clamp(max=split), y, False)
+    lo = split * 128
+    assert torch.equal(y[:lo].view(torch.int16), full[:lo].view(torch.int16))
+    assert torch.isnan(y[lo:].float()).all()                 # the second window is untouched so far
+    grouped_linear(x, w, r.mtile_off.clamp(min=split), y, False)
+    assert torch.equal(y[:total].view(torch.int16), full[:total].view(torch.int16))
+    assert torch.isnan(y[total:].float()).all()
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("case", [([130, 0, 5], 64, 256), ([300, 17, 128, 0, 256], 136, 264), ([700, 900], 512, 384)])
 def test_wgrad(dtype, case):

@@ -33,6 +33,8 @@ CASES = [
     dict(world=4, E=4, k=1, T=[64, 64, 64, 64], H=128, I=128, seed=2),    # one expert per rank, top-1
     dict(world=2, E=16, k=4, T=[257, 0], H=64, I=136, seed=3),            # a rank without tokens
     dict(world=8, E=8, k=2, T=[40] * 8, H=256, I=128, seed=4),
+    dict(world=2, E=8, k=2, T=[300, 300], H=128, I=256, seed=5, min_tiles_to_split=4),   # two-window pull, small
+    dict(world=2, E=4, k=2, T=[1500, 1400], H=64, I=64, seed=6),                          # two-window pull, default rule
 ]
 
 
@@ -51,6 +53,8 @@ def test_peer_engine_lockstep(cfg, dt):
     sl = [slice(starts[r], starts[r] + Ts[r]) for r in range(world)]
     bufs = _virtual_world(world, max(max(Ts), 1), H, k, dt)
     eng = [PeerExpertEngine(b, E) for b in bufs]
+    for e in eng:
+        e.MIN_TILES_TO_SPLIT = cfg.get("min_tiles_to_split", e.MIN_TILES_TO_SPLIT)
     w_fc = [full["w_fc"][r * epr:(r + 1) * epr].to(dt).cuda().contiguous() for r in range(world)]
     w_proj = [full["w_proj"][r * epr:(r + 1) * epr].to(dt).cuda().contiguous() for r in range(world)]
 
@@ -63,6 +67,8 @@ def test_peer_engine_lockstep(cfg, dt):
     plans = [eng[r].plan(ids_all) for r in range(world)]
     owned = sum(int(p.routing.counts[:epr].long().sum()) for p in plans)
     assert owned == sum(Ts) * k                       # every routed row has exactly one owner
+    if cfg["seed"] >= 5:
+        assert all(p.split > 0 for p in plans)        # these cases exercise the overlapped two-window pull
     saved = [eng[r].fwd_compute(plans[r], weights_all, w_fc[r], w_proj[r], True) for r in range(world)]
     ys = [eng[r].fwd_finish(Ts[r]) for r in range(world)]
     # ---- backward ----
@@ -95,7 +101,7 @@ def test_peer_kernels_reject_bad_tables():
     i32 = torch.zeros(130, dtype=torch.int32, device="cuda")
     arr = (ctypes.c_void_p * 1)(x.data_ptr() + 2)  # misaligned buffer
     st = _lib.lib.ck_moe_gather_rows_peer(arr, 1, 128, x.data_ptr(), i32.data_ptr(), i32.data_ptr(), i32.data_ptr(), 1, 128, 1,
-                                          64, _lib.dtype_code(torch.bfloat16), None, None)
+                                          64, 0, 128, _lib.dtype_code(torch.bfloat16), None, None)
     assert st == -1
     arr = (ctypes.c_void_p * 1)(x.data_ptr())
     st = _lib.lib.ck_peer_gather_scalars(arr, 17, 128, i32.data_ptr(), 1, x.data_ptr(), 2, None, None)   # too many peers
