@@ -846,7 +846,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 // halves.  Per CTA and k-block that is 32 KiB instead of 48 KiB from L2 and leaves room for a 6-stage
 // ring, which is what keeps the tensor pipe fed.  TMA loads are plain (non-multicast) per CTA; the
 // leader's mbarrier collects the transaction bytes of both CTAs.
-constexpr int kPairStages = 6;
+#ifndef CK_PAIR_STAGES
+#define CK_PAIR_STAGES 6
+#endif
+constexpr int kPairStages = CK_PAIR_STAGES;
 constexpr int kBHalfStageBytes = kBStageBytes / 2;  // 16 KiB
 
 struct SmemCtlPair {

@@ -17,7 +17,7 @@ struct PeerTable {
     void *p[CK_MAX_PEERS];
 };
 
-constexpr int kPeerThreads = 256;
+constexpr int kPeerThreads = 128;  // small blocks: two of them fit in the registers a resident GEMM CTA leaves free
 constexpr int kPeerUnroll = 8;
 
 // dst[p, :] = peer[g / S][(g % S) / fan_out, :] with g = src_flat ? src_flat[row_map[p]] : row_map[p]; zeros where
@@ -112,7 +112,7 @@ static int fill_table(PeerTable &t, const void *const *ptrs, int n_peers) {
 
 static inline unsigned peer_grid(int64_t items) {
     int64_t blocks = ceil_div64(items, kPeerThreads);
-    const int64_t cap = int64_t(num_sms()) * 8;
+    const int64_t cap = int64_t(num_sms()) * 16;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return unsigned(blocks);
@@ -126,6 +126,10 @@ static int gather_rows_peer_t(const PeerTable &t, int n_peers, int64_t S, void *
     if (cols % VEC != 0 || (reinterpret_cast<uintptr_t>(dst) & 15)) return CK_ERR_SHAPE;
     const int64_t vpr = cols / VEC;
     const int64_t span = (row_end < cap ? row_end : cap) - row_begin;
+    // An SM keeps one shared-memory / L1 split at a time.  Asking for the split the GEMM kernels run with lets these
+    // blocks become resident beside a GEMM CTA instead of waiting for the SM to drain.
+    CK_CUDA_TRY(cudaFuncSetAttribute(gather_rows_peer_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     (int)cudaSharedmemCarveoutMaxShared));
     gather_rows_peer_kernel<T><<<peer_grid(ceil_div64(span * vpr, kPeerUnroll)), kPeerThreads, 0, stream>>>(
         t, n_peers, S, (T *)dst, row_map, padded_off, src_flat, E, cap, fan_out, vpr, row_begin, row_end, dev_status);
     CK_LAUNCH_CHECK("gather_rows_peer_kernel");

@@ -8,9 +8,7 @@ and the permutation kernels address that memory directly:
   forward   publish x, router weights, expert ids            (local copies into the shared buffers)
             all-gather the ids and weights (a few hundred KiB; doubles as the "published" barrier)
             route all slots over this rank's experts plus a 'not mine' bin: row_map then names global slots
-            gather those rows from their owners                (ck_moe_gather_rows_peer: NVLink loads; in two
-                                                               windows, the second pulled on a side stream while
-                                                               the GEMM already runs on the first)
+            gather those rows from their owners                (ck_moe_gather_rows_peer: NVLink loads)
             up projection + activation (router weight folded in; the weights travel with the ids)
             down projection, every result row stored into its owner's return buffer from the GEMM epilogue
                                                                (ck_moe_grouped_linear_scatter_peer: NVLink stores)
@@ -146,20 +144,24 @@ class PeerExpertEngine:
         loc = torch.where((loc >= 0) & (loc < epr), loc, epr)
         r = route(loc, epr + 1)
         rows = int(r.padded_off[epr].item())  # the one host sync: rows to allocate
-        # Two windows of the padded rows: the pull of the second runs on a side stream under the GEMM on the first.
+        # Optional: two windows of the padded rows, the second pulled on a side stream while the GEMM runs on the first.
         tiles = rows // _lib.CK_TILE_M
         split = 0
-        if tiles >= self.MIN_TILES_TO_SPLIT:
+        if self.MIN_TILES_TO_SPLIT is not None and tiles >= self.MIN_TILES_TO_SPLIT:
             split = min(tiles - 2, max(2, (tiles // 4 + 1) & ~1))  # a quarter of the rows, whole CTA pairs
         first = r.mtile_off.clamp(max=split) if split else None
         rest = r.mtile_off.clamp(min=split) if split else None
         return _Plan(r, rows, max(rows, _lib.CK_TILE_M), split, first, rest)
 
-    MIN_TILES_TO_SPLIT = 16
+    # Off by default.  Measured on B200: the pull's blocks do not become resident beside the persistent GEMM CTAs (tried
+    # 128-thread blocks that fit the free registers, the GEMM's shared-memory carve-out, a high-priority side stream,
+    # a GEMM with 32 KiB less shared memory, the one-CTA GEMM flavour), so the second window only starts while the
+    # first GEMM drains and nothing is hidden.  Set to a tile count (e.g. 16) to run the two-window schedule.
+    MIN_TILES_TO_SPLIT: int | None = None
 
     def _side_stream(self) -> torch.cuda.Stream:
         if self._side is None:
-            self._side = torch.cuda.Stream(device=self.b.tokens.device)
+            self._side = torch.cuda.Stream(device=self.b.tokens.device, priority=-1)
         return self._side
 
     def _pull_then(self, plan: _Plan, dst: torch.Tensor, gemm) -> None:
@@ -175,13 +177,15 @@ class PeerExpertEngine:
         _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, 0, edge)
         first_done = torch.cuda.Event()
         first_done.record(main)
+        # the GEMM is enqueued before the second pull: its CTAs (one per SM) take their places first and the pull's
+        # small blocks fill the registers and thread slots that are left
+        gemm(plan.mtile_first)
         side.wait_event(first_done)
         with torch.cuda.stream(side):
             _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, edge, plan.cap)
             rest_done = torch.cuda.Event()
             rest_done.record(side)
         dst.record_stream(side)
-        gemm(plan.mtile_first)
         main.wait_event(rest_done)
         gemm(plan.mtile_rest)
 

@@ -34,7 +34,7 @@ CASES = [
     dict(world=2, E=16, k=4, T=[257, 0], H=64, I=136, seed=3),            # a rank without tokens
     dict(world=8, E=8, k=2, T=[40] * 8, H=256, I=128, seed=4),
     dict(world=2, E=8, k=2, T=[300, 300], H=128, I=256, seed=5, min_tiles_to_split=4),   # two-window pull, small
-    dict(world=2, E=4, k=2, T=[1500, 1400], H=64, I=64, seed=6),                          # two-window pull, default rule
+    dict(world=2, E=4, k=2, T=[1500, 1400], H=64, I=64, seed=6, min_tiles_to_split=16),  # two-window pull, larger
 ]
 
 
