@@ -386,7 +386,8 @@ def gpu_arm(args, w: dict) -> dict | None:
     dom = max((n for n in kernels if n in algo), key=lambda n: kernels[n]["ms_total"])
     peak = float(peaks.get("bf16_tflops_sustained") or peaks["bf16_tflops"])
     roofline = dict(
-        bound="tensor", kernel=f"grouped_gemm_kernel<bf16> ({dom})", achieved=kernels[dom]["tflops"], peak=peak,
+        bound="tensor",
+        kernel=f"{'grouped_gemm_pair_kernel' if os.environ.get('CK_GEMM_CTA_PAIR', '1') != '0' else 'grouped_gemm_kernel'}<bf16> ({dom})", achieved=kernels[dom]["tflops"], peak=peak,
         unit="TFLOP/s", frac=kernels[dom]["tflops"] / peak, traffic=None, peak_source=f"bf16_tflops_sustained of {peaks['source']}",
         all_gemms=dict(ms_per_step=gemm_ms, tflops=gemm_flops / (gemm_ms * 1e-3) / 1e12,
                        frac_of_measured_sustained=gemm_flops / (gemm_ms * 1e-3) / 1e12 / peak,
