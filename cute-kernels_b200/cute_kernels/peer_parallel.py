@@ -153,10 +153,12 @@ class PeerExpertEngine:
         rest = r.mtile_off.clamp(min=split) if split else None
         return _Plan(r, rows, max(rows, _lib.CK_TILE_M), split, first, rest)
 
-    # Off by default.  Measured on B200: the pull's blocks do not become resident beside the persistent GEMM CTAs (tried
-    # 128-thread blocks that fit the free registers, the GEMM's shared-memory carve-out, a high-priority side stream,
-    # a GEMM with 32 KiB less shared memory, the one-CTA GEMM flavour), so the second window only starts while the
-    # first GEMM drains and nothing is hidden.  Set to a tile count (e.g. 16) to run the two-window schedule.
+    # Off by default.  Measured on B200: the pull and the persistent GEMM never become resident on an SM together, in
+    # either launch order (tried 128-thread blocks, at most two per SM, the GEMM's shared-memory carve-out, a high-priority
+    # side stream, a GEMM with 32 KiB less shared memory, the one-CTA GEMM flavour): the second window only runs while the
+    # first GEMM drains, and nothing is hidden.  The GEMM's epilogue warps hold 218-255 registers per thread, which
+    # leaves at most one 64-register warp's worth free in the scheduler partitions that host two of them.  Set to a tile
+    # count (e.g. 16) to run the two-window schedule anyway.
     MIN_TILES_TO_SPLIT: int | None = None
 
     def _side_stream(self) -> torch.cuda.Stream:
