@@ -43,6 +43,12 @@ WORKLOADS = {
 }
 METRIC = "moe_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
+# DRAM bytes (read + write) per launch of each GEMM family on the full c4 workload, from the one-pass ncu capture summarised
+# in profiles/grouped_gemm_c4_dram_traffic.md (dram__bytes_read.sum + dram__bytes_write.sum; wgrad = mean of its two launches)
+MEASURED_DRAM_TRAFFIC = {
+    "c4_mixtral_moe_fwd_bwd": {"up_act_fwd": 8677e6, "down_combine_fwd": 10038e6, "dgrad_down": 7964e6, "wgrad": 5722e6,
+                               "dgrad_up": 22008e6},
+}
 GEMM_KERNELS = ("up_act_fwd", "down_combine_fwd", "dgrad_down", "dgrad_up", "wgrad", "grouped_linear",
                 "grouped_linear_scatter", "grouped_linear_scatter_peer")
 
@@ -388,7 +394,10 @@ def gpu_arm(args, w: dict) -> dict | None:
     roofline = dict(
         bound="tensor",
         kernel=f"{'grouped_gemm_pair_kernel' if os.environ.get('CK_GEMM_CTA_PAIR', '1') != '0' else 'grouped_gemm_kernel'}<bf16> ({dom})", achieved=kernels[dom]["tflops"], peak=peak,
-        unit="TFLOP/s", frac=kernels[dom]["tflops"] / peak, traffic=None, peak_source=f"bf16_tflops_sustained of {peaks['source']}",
+        unit="TFLOP/s", frac=kernels[dom]["tflops"] / peak,
+        traffic=(MEASURED_DRAM_TRAFFIC.get(w["name"], {}).get(dom) if world == 1 else None),
+        traffic_unit="bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture)",
+        peak_source=f"bf16_tflops_sustained of {peaks['source']}",
         all_gemms=dict(ms_per_step=gemm_ms, tflops=gemm_flops / (gemm_ms * 1e-3) / 1e12,
                        frac_of_measured_sustained=gemm_flops / (gemm_ms * 1e-3) / 1e12 / peak,
                        frac_of_measured_burst=gemm_flops / (gemm_ms * 1e-3) / 1e12 / float(peaks["bf16_tflops"]),
