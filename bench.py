@@ -43,8 +43,8 @@ WORKLOADS = {
 }
 METRIC = "moe_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
-# DRAM bytes (read + write) per launch of each GEMM family on the full c4 workload, from the one-pass ncu capture summarised
-# in profiles/grouped_gemm_c4_dram_traffic.md (dram__bytes_read.sum + dram__bytes_write.sum; wgrad = mean of its two launches)
+# DRAM bytes (read + write) per launch of each GEMM family on the full c4 workload, from a one-pass ncu capture of this
+# command (dram__bytes_read.sum + dram__bytes_write.sum; wgrad = mean of its two launches); the summary is under profiles/
 MEASURED_DRAM_TRAFFIC = {
     "c4_mixtral_moe_fwd_bwd": {"up_act_fwd": 8677e6, "down_combine_fwd": 10038e6, "dgrad_down": 7964e6, "wgrad": 5722e6,
                                "dgrad_up": 22008e6},
