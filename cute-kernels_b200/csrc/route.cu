@@ -130,11 +130,12 @@ __global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids,
         __syncwarp();
         // lanes -> warp -> block -> one global atomic per value per block (same-sector atomics serialise in L2,
         // so the number of global atomics, not the histogram itself, would otherwise set the run time)
-        for (int v = 0; v < size; ++v) {
-            uint32_t c = wh[v * 32 + lane];
+        // lane l sums the 32 private slots of values l, l + 32, ...; the rotated slot order keeps the 32 lanes on 32 banks
+        for (int v = lane; v < size; v += 32) {
+            uint32_t c = 0;
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
-            if (lane == 0 && c) atomicAdd(&bh[v], c);
+            for (int j = 0; j < 32; ++j) c += wh[v * 32 + ((lane + j) & 31)];
+            if (c) atomicAdd(&bh[v], c);
         }
         __syncthreads();
         for (int i = threadIdx.x; i < size; i += blockDim.x) {
@@ -206,11 +207,12 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
             }
         }
         __syncwarp();
-        for (int e = 0; e < E; ++e) {
-            int c = wh[e * 32 + lane];
+        // lane l sums the 32 private slots of experts l, l + 32, ...; the rotated slot order keeps the 32 lanes on 32 banks
+        for (int e = lane; e < E; e += 32) {
+            int c = 0;
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
-            if (lane == 0 && c) atomicAdd(&bh[e], c);
+            for (int j = 0; j < 32; ++j) c += wh[e * 32 + ((lane + j) & 31)];
+            if (c) atomicAdd(&bh[e], c);
         }
     } else {
         __syncthreads();
