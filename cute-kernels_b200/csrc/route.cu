@@ -81,6 +81,18 @@ __device__ __forceinline__ void load_step(const IdT *__restrict__ p, int remaini
     }
 }
 
+// Whole step inside the range, ids mapped to [0, range]: `range` itself stands for "out of range" and indexes a spare
+// histogram row, so the counting loop needs neither a predicate nor a flag per id.
+template <typename IdT>
+__device__ __forceinline__ void load_step_clamped(const IdT *__restrict__ p, int range, int (&key)[kLoads]) {
+    using U = typename std::make_unsigned<IdT>::type;
+    IdT v[kLoads];
+#pragma unroll
+    for (int j = 0; j < kLoads; ++j) v[j] = p[32 * j];
+#pragma unroll
+    for (int j = 0; j < kLoads; ++j) key[j] = int(min(U(v[j]), U(range)));
+}
+
 constexpr int kLanePrivateMax = 128;  // largest id range that gets a per-lane histogram (16 KiB per warp)
 
 // ------------------------------------------------------------------------------------------------
@@ -102,9 +114,9 @@ __global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids,
 
     if constexpr (LANE_PRIVATE) {
         const int wpb = blockDim.x >> 5;
-        uint32_t *wh = hist + wib * size * 32;      // [size][32] per warp
-        uint32_t *bh = hist + wpb * size * 32;      // [size] block totals
-        for (int i = lane; i < size * 32; i += 32) wh[i] = 0;
+        uint32_t *wh = hist + wib * (size + 1) * 32;  // [size + 1][32] per warp; the last row collects out-of-range ids
+        uint32_t *bh = hist + wpb * (size + 1) * 32;  // [size] block totals
+        for (int i = lane; i < (size + 1) * 32; i += 32) wh[i] = 0;
         for (int i = threadIdx.x; i < size; i += blockDim.x) bh[i] = 0;
         __syncthreads();
         uint32_t *mine = wh + lane;
@@ -112,16 +124,20 @@ __global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids,
         int cur[kLoads], nxt[kLoads];
         auto fetch = [&](int64_t c, int (&key)[kLoads]) {
             const int64_t b = c * kStep;
-            if (b + kStep <= n) load_step<IdT, true>(ids + b + lane, kStep, lane, size, key, bad);
-            else load_step<IdT, false>(ids + b + lane, int(n - b), lane, size, key, bad);
+            if (b + kStep <= n) {
+                load_step_clamped<IdT>(ids + b + lane, size, key);
+            } else {  // the ragged last step: positions past the end go to the spare row too
+                load_step<IdT, false>(ids + b + lane, int(n - b), lane, size, key, bad);
+#pragma unroll
+                for (int j = 0; j < kLoads; ++j) key[j] = key[j] < 0 ? size : key[j];
+            }
         };
         if (warp_id < nchunks) fetch(warp_id, cur);
         for (int64_t c = warp_id; c < nchunks; c += nwarps) {
             const bool more = c + nwarps < nchunks;
             if (more) fetch(c + nwarps, nxt);
 #pragma unroll
-            for (int j = 0; j < kLoads; ++j)
-                if (cur[j] >= 0) atomicAdd(mine + cur[j] * 32, 1u);  // private slot: a fire-and-forget shared-memory add
+            for (int j = 0; j < kLoads; ++j) atomicAdd(mine + cur[j] * 32, 1u);  // private slot: a fire-and-forget shared-memory add
             if (more) {
 #pragma unroll
                 for (int j = 0; j < kLoads; ++j) cur[j] = nxt[j];
@@ -184,29 +200,38 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
     bool bad = false;
 
     if constexpr (LANE_PRIVATE) {
-        int32_t *wh = smem_i + E + wib * E * 32;  // [E][32] per warp, bank == lane
-        for (int i = lane; i < E * 32; i += 32) wh[i] = 0;
+        int32_t *wh = smem_i + E + wib * (E + 1) * 32;  // [E + 1][32] per warp, bank == lane; row E collects what is not counted
+        for (int i = lane; i < (E + 1) * 32; i += 32) wh[i] = 0;
         __syncthreads();
         int32_t *mine = wh + lane;
         constexpr int kStride = kRouteWarpsPerBlock * kStep;
         int cur[kLoads], nxt[kLoads];
+        int spare_ok = 0;  // entries this lane sent to row E that are not range errors (positions past the slice end)
         auto fetch = [&](int off, int (&key)[kLoads]) {
-            if (off + kStep <= len) load_step<IdT, true>(my_ids + off, kStep, lane, E, key, bad);
-            else load_step<IdT, false>(my_ids + off, len - off, lane, E, key, bad);
+            if (off + kStep <= len) {
+                load_step_clamped<IdT>(my_ids + off, E, key);  // range errors land in row E and are found there afterwards
+            } else {
+                load_step<IdT, false>(my_ids + off, len - off, lane, E, key, bad);  // flags its own range errors
+#pragma unroll
+                for (int j = 0; j < kLoads; ++j) {
+                    spare_ok += key[j] < 0;
+                    key[j] = key[j] < 0 ? E : key[j];
+                }
+            }
         };
         if (wib * kStep < len) fetch(wib * kStep, cur);
         for (int off = wib * kStep; off < len; off += kStride) {  // next step's loads fly while this one is counted
             const bool more = off + kStride < len;
             if (more) fetch(off + kStride, nxt);
 #pragma unroll
-            for (int j = 0; j < kLoads; ++j)
-                if (cur[j] >= 0) atomicAdd(mine + cur[j] * 32, 1);  // private slot, no dependency chain
+            for (int j = 0; j < kLoads; ++j) atomicAdd(mine + cur[j] * 32, 1);  // private slot, no dependency chain
             if (more) {
 #pragma unroll
                 for (int j = 0; j < kLoads; ++j) cur[j] = nxt[j];
             }
         }
         __syncwarp();
+        bad |= mine[E * 32] != spare_ok;
         // lane l sums the 32 private slots of experts l, l + 32, ...; the rotated slot order keeps the 32 lanes on 32 banks
         for (int e = lane; e < E; e += 32) {
             int c = 0;
@@ -492,9 +517,9 @@ extern "C" int ck_continuous_count(const void *ids, int ids_is_i64, int64_t n, i
     const bool lane_private = size <= kLanePrivateMax;
     const int nbits = size > 1 ? 32 - __builtin_clz(unsigned(size - 1)) : 0;
     int wpb = 16;  // warps per block; one block per SM keeps the count of global atomics at num_sms * size
-    if (lane_private) wpb = std::max(1, std::min(16, int((200 * 1024) / (size_t(size) * 128))));
+    if (lane_private) wpb = std::max(1, std::min(16, int((200 * 1024) / (size_t(size + 1) * 128))));
     const int threads = wpb * 32;
-    const size_t smem = lane_private ? sizeof(uint32_t) * size * (32 * wpb + 1) : sizeof(uint32_t) * size;
+    const size_t smem = lane_private ? sizeof(uint32_t) * (size_t(size + 1) * 32 * wpb + size) : sizeof(uint32_t) * size;
     const int64_t nchunks = ceil_div64(n, kStep);
     int64_t grid = ceil_div64(nchunks, wpb);
     const int64_t cap = int64_t(num_sms()) * (lane_private ? 1 : 2);
@@ -553,7 +578,7 @@ extern "C" int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint3
     const int blocks = W;  // one thread block per slice
     if (W > 0) {
         const bool lane_private = E <= kLanePrivateMax;
-        const size_t smem = sizeof(int32_t) * (size_t(E) + (lane_private ? size_t(kRouteWarpsPerBlock) * E * 32 : 0));
+        const size_t smem = sizeof(int32_t) * (size_t(E) + (lane_private ? size_t(kRouteWarpsPerBlock) * (E + 1) * 32 : 0));
 #define CK_LAUNCH_HIST(IDT, LP)                                                                                          \
     do {                                                                                                                 \
         if (smem > 48 * 1024)                                                                                            \
