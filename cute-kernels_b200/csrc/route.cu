@@ -16,6 +16,8 @@ namespace ck {
 
 constexpr int kRouteMaxSlices = 148 * 4;  // upper bound on id slices, one per thread block (fixed so workspace size is device independent)
 constexpr int kRouteWarpsPerBlock = 8;
+constexpr int kHistWarpsPerBlock = 4;  // histogram pass: 33 KiB of private histograms per block at 64 experts, so that all 592
+                                       // slices are resident at once (8 warps: 3 blocks per SM, a second wave a third full)
 constexpr int kLoads = 16;          // coalesced 32-id loads in flight per warp: 2 KiB (int32) of reads per warp step
 constexpr int kStep = 32 * kLoads;  // ids per warp per unrolled step
 
@@ -185,7 +187,7 @@ __global__ void __launch_bounds__(512) count_kernel(const IdT *__restrict__ ids,
 // route pass 1: per-warp histogram of a contiguous slice of ids -> whist[w][E]
 // ------------------------------------------------------------------------------------------------
 template <typename IdT, bool LANE_PRIVATE>
-__global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kHistWarpsPerBlock * 32)
     route_hist_kernel(const IdT *__restrict__ ids, int64_t n, int E, int64_t slice, int32_t *__restrict__ whist,
                       int32_t *dev_status) {
     // one thread block per slice; its warps take the 512-id steps of the slice round-robin
@@ -204,7 +206,7 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
         for (int i = lane; i < (E + 1) * 32; i += 32) wh[i] = 0;
         __syncthreads();
         int32_t *mine = wh + lane;
-        constexpr int kStride = kRouteWarpsPerBlock * kStep;
+        constexpr int kStride = kHistWarpsPerBlock * kStep;
         int cur[kLoads], nxt[kLoads];
         int spare_ok = 0;  // entries this lane sent to row E that are not range errors (positions past the slice end)
         auto fetch = [&](int off, int (&key)[kLoads]) {
@@ -241,7 +243,7 @@ __global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
         }
     } else {
         __syncthreads();
-        for (int off = wib * kStep; off < len; off += kRouteWarpsPerBlock * kStep) {
+        for (int off = wib * kStep; off < len; off += kHistWarpsPerBlock * kStep) {
             int key[kLoads];
             if (off + kStep <= len) load_step<IdT, true>(my_ids + off, kStep, lane, E, key, bad);
             else load_step<IdT, false>(my_ids + off, len - off, lane, E, key, bad);
@@ -363,7 +365,7 @@ __global__ void __launch_bounds__(1024)
 constexpr int kTile = kRouteWarpsPerBlock * kStep;  // 4096 ids
 
 template <typename IdT, bool HAS_SEXP, bool HAS_ROWMAP>
-__global__ void __launch_bounds__(kRouteWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kRouteWarpsPerBlock * 32, 4)  // 4 blocks per SM: all 592 slices resident at once
     route_scatter_kernel(const IdT *__restrict__ ids, int64_t n, int E, int64_t slice,
                          const int32_t *__restrict__ whist, const int32_t *__restrict__ excl_off,
                          const int32_t *__restrict__ padded_off, int32_t *__restrict__ sorted_idx,
@@ -578,12 +580,12 @@ extern "C" int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint3
     const int blocks = W;  // one thread block per slice
     if (W > 0) {
         const bool lane_private = E <= kLanePrivateMax;
-        const size_t smem = sizeof(int32_t) * (size_t(E) + (lane_private ? size_t(kRouteWarpsPerBlock) * (E + 1) * 32 : 0));
+        const size_t smem = sizeof(int32_t) * (size_t(E) + (lane_private ? size_t(kHistWarpsPerBlock) * (E + 1) * 32 : 0));
 #define CK_LAUNCH_HIST(IDT, LP)                                                                                          \
     do {                                                                                                                 \
         if (smem > 48 * 1024)                                                                                            \
             CK_CUDA_TRY(cudaFuncSetAttribute(route_hist_kernel<IDT, LP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        route_hist_kernel<IDT, LP><<<blocks, threads, smem, stream>>>((const IDT *)ids, n, E, slice, whist, dev_status); \
+        route_hist_kernel<IDT, LP><<<blocks, kHistWarpsPerBlock * 32, smem, stream>>>((const IDT *)ids, n, E, slice, whist, dev_status); \
     } while (0)
         if (ids_is_i64) {
             if (lane_private) CK_LAUNCH_HIST(int64_t, true); else CK_LAUNCH_HIST(int64_t, false);
