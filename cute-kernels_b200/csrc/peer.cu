@@ -17,7 +17,7 @@ struct PeerTable {
     void *p[CK_MAX_PEERS];
 };
 
-constexpr int kPeerThreads = 128;  // small blocks: two of them fit in the registers a resident GEMM CTA leaves free
+constexpr int kPeerThreads = 128;
 constexpr int kPeerUnroll = 8;
 
 // dst[p, :] = peer[g / S][(g % S) / fan_out, :] with g = src_flat ? src_flat[row_map[p]] : row_map[p]; zeros where
@@ -39,33 +39,34 @@ __global__ void __launch_bounds__(kPeerThreads)
     const int64_t rows_per_block = ceil_div64(rows - row_begin, gridDim.x);
     const int64_t row0 = row_begin + int64_t(blockIdx.x) * rows_per_block;
     const int64_t row1 = min(row0 + rows_per_block, rows);
-    const int64_t v_begin = row0 * vpr, v_end = row1 * vpr;
+    const int lane = threadIdx.x & 31;
     bool bad = false;
-    for (int64_t v0 = v_begin + threadIdx.x; v0 < v_end; v0 += int64_t(kPeerThreads) * kPeerUnroll) {
-        int4 x[kPeerUnroll];
-#pragma unroll
-        for (int j = 0; j < kPeerUnroll; ++j) {
-            const int64_t v = v0 + j * kPeerThreads;
-            x[j] = make_int4(0, 0, 0, 0);
-            if (v < v_end) {
-                const int64_t p = v / vpr, c = (v - p * vpr) * VEC;
-                const int32_t s = row_map[p];
-                if (s >= 0) {
-                    const int64_t g = src_flat ? int64_t(src_flat[s]) : int64_t(s);
-                    const int64_t r = g / S;
-                    if (g >= 0 && r < n_peers) {
-                        const T *src = reinterpret_cast<const T *>(peers.p[r]) + ((g - r * S) / fan_out) * (vpr * VEC) + c;
-                        x[j] = *reinterpret_cast<const int4 *>(src);  // plain load: the source may be another GPU's memory
-                    } else {
-                        bad = true;
-                    }
-                }
-            }
+    // one warp per row of the block's run: the slot is decoded once per row, the lanes stream the row
+    for (int64_t p = row0 + (threadIdx.x >> 5); p < row1; p += kPeerThreads / 32) {
+        const int32_t s = row_map[p];
+        const int4 *sr = nullptr;
+        if (s >= 0) {
+            const int64_t g = src_flat ? int64_t(src_flat[s]) : int64_t(s);
+            const int64_t r = g / S;
+            if (g >= 0 && r < n_peers)
+                sr = reinterpret_cast<const int4 *>(reinterpret_cast<const T *>(peers.p[r]) + ((g - r * S) / fan_out) * (vpr * VEC));
+            else
+                bad = true;
         }
+        int4 *d = reinterpret_cast<int4 *>(dst + p * (vpr * VEC));
+        for (int64_t c0 = lane; c0 < vpr; c0 += 32 * kPeerUnroll) {
+            int4 x[kPeerUnroll];
 #pragma unroll
-        for (int j = 0; j < kPeerUnroll; ++j) {
-            const int64_t v = v0 + j * kPeerThreads;
-            if (v < v_end) *reinterpret_cast<int4 *>(dst + v * VEC) = x[j];
+            for (int j = 0; j < kPeerUnroll; ++j) {
+                const int64_t c = c0 + 32 * j;
+                x[j] = make_int4(0, 0, 0, 0);
+                if (sr && c < vpr) x[j] = sr[c];  // plain load: the source may be another GPU's memory
+            }
+#pragma unroll
+            for (int j = 0; j < kPeerUnroll; ++j) {
+                const int64_t c = c0 + 32 * j;
+                if (c < vpr) d[c] = x[j];
+            }
         }
     }
     if (bad && dev_status) atomicOr(dev_status, CK_DEV_RANGE);
@@ -126,10 +127,6 @@ static int gather_rows_peer_t(const PeerTable &t, int n_peers, int64_t S, void *
     if (cols % VEC != 0 || (reinterpret_cast<uintptr_t>(dst) & 15)) return CK_ERR_SHAPE;
     const int64_t vpr = cols / VEC;
     const int64_t span = (row_end < cap ? row_end : cap) - row_begin;
-    // An SM keeps one shared-memory / L1 split at a time.  Asking for the split the GEMM kernels run with lets these
-    // blocks become resident beside a GEMM CTA instead of waiting for the SM to drain.
-    CK_CUDA_TRY(cudaFuncSetAttribute(gather_rows_peer_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                     (int)cudaSharedmemCarveoutMaxShared));
     gather_rows_peer_kernel<T><<<peer_grid(ceil_div64(span * vpr, kPeerUnroll)), kPeerThreads, 0, stream>>>(
         t, n_peers, S, (T *)dst, row_map, padded_off, src_flat, E, cap, fan_out, vpr, row_begin, row_end, dev_status);
     CK_LAUNCH_CHECK("gather_rows_peer_kernel");

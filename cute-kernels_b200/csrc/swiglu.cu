@@ -218,7 +218,9 @@ __global__ void __launch_bounds__(kEwThreads)
     }
 }
 
-// dst[p, :] = src[row_map[p] / fan_out, :], zeros where row_map[p] < 0; p < padded_off[E]
+// dst[p, :] = src[row_map[p] / fan_out, :], zeros where row_map[p] < 0; p < padded_off[E].
+// One warp per padded row: the row index is read once (a broadcast load) and the lanes stream the row in 16-byte
+// vectors, four in flight each; no division per vector.
 template <typename T>
 __global__ void __launch_bounds__(kEwThreads)
     gather_rows_kernel(const T *__restrict__ src, T *__restrict__ dst, const int32_t *__restrict__ row_map,
@@ -226,27 +228,26 @@ __global__ void __launch_bounds__(kEwThreads)
     constexpr int VEC = Vec16<T>::N;
     int64_t rows = padded_off[E];
     if (rows > cap) rows = cap;
-    const int64_t nvec = rows * vpr;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t v0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; v0 < nvec; v0 += stride * kEwUnroll) {
-        Vec16<T> x[kEwUnroll];
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    for (int64_t p = warp; p < rows; p += nwarps) {
+        const int32_t s = row_map[p];
+        int4 *d = reinterpret_cast<int4 *>(dst + p * (vpr * VEC));
+        const int4 *sr = reinterpret_cast<const int4 *>(src + int64_t(s < 0 ? 0 : s / fan_out) * (vpr * VEC));
+        for (int64_t c0 = lane; c0 < vpr; c0 += 32 * kEwUnroll) {
+            int4 x[kEwUnroll];
 #pragma unroll
-        for (int j = 0; j < kEwUnroll; ++j) {
-            const int64_t v = v0 + j * stride;
-            if (v < nvec) {
-                const int64_t p = v / vpr, c = (v - p * vpr) * VEC;
-                const int32_t s = row_map[p];
-                if (s >= 0) {
-                    x[j] = ldg16(src + int64_t(s / fan_out) * (vpr * VEC) + c);
-                } else {
-                    *reinterpret_cast<int4 *>(&x[j]) = make_int4(0, 0, 0, 0);
-                }
+            for (int j = 0; j < kEwUnroll; ++j) {
+                const int64_t c = c0 + 32 * j;
+                x[j] = make_int4(0, 0, 0, 0);
+                if (s >= 0 && c < vpr) x[j] = __ldg(sr + c);
             }
-        }
 #pragma unroll
-        for (int j = 0; j < kEwUnroll; ++j) {
-            const int64_t v = v0 + j * stride;
-            if (v < nvec) stg16(dst + v * VEC, x[j]);
+            for (int j = 0; j < kEwUnroll; ++j) {
+                const int64_t c = c0 + 32 * j;
+                if (c < vpr) d[c] = x[j];
+            }
         }
     }
 }
@@ -399,8 +400,8 @@ static int gather_rows_t(const void *src, void *dst, const int32_t *row_map, con
     constexpr int VEC = Vec16<T>::N;
     if (cols % VEC != 0 || !aligned16(src) || !aligned16(dst)) return CK_ERR_SHAPE;
     const int64_t vpr = cols / VEC;
-    gather_rows_kernel<T><<<ew_grid(cap * vpr, kEwUnroll), kEwThreads, 0, stream>>>((const T *)src, (T *)dst, row_map,
-                                                                               padded_off, E, cap, fan_out, vpr);
+    gather_rows_kernel<T><<<ew_grid(cap * 32, 1), kEwThreads, 0, stream>>>((const T *)src, (T *)dst, row_map, padded_off, E,
+                                                                           cap, fan_out, vpr);
     CK_LAUNCH_CHECK("gather_rows_kernel");
     return CK_OK;
 }
