@@ -143,7 +143,11 @@ class PeerExpertEngine:
         loc = ids_all - self.b.rank * epr
         loc = torch.where((loc >= 0) & (loc < epr), loc, epr)
         r = route(loc, epr + 1)
-        rows = int(r.padded_off[epr].item())  # the one host sync: rows to allocate
+        # ids outside [0, num_experts] would be "not mine" on every rank and their rows would never be computed
+        n_bad = ((ids_all < 0) | (ids_all > self.num_experts)).sum(dtype=torch.int32)
+        rows, bad = torch.stack([r.padded_off[epr], n_bad]).tolist()  # the one host sync: rows to allocate
+        if bad:
+            raise RuntimeError(f"{bad} expert ids outside [0, {self.num_experts}) reached the expert-parallel layer")
         # Optional: two windows of the padded rows, the second pulled on a side stream while the GEMM runs on the first.
         tiles = rows // _lib.CK_TILE_M
         split = 0

@@ -93,6 +93,19 @@ def test_peer_engine_lockstep(cfg, dt):
         torch.testing.assert_close(grads[r][1].float().cpu(), ref["d_w_proj"][el], **wtol)
 
 
+def test_peer_plan_rejects_out_of_range_ids():
+    from cute_kernels.peer_parallel import PeerExpertEngine
+
+    bufs = _virtual_world(2, 16, 64, 2, torch.bfloat16)
+    eng = PeerExpertEngine(bufs[0], 8)
+    ids = torch.randint(0, 8, (2 * 32,), dtype=torch.int32, device="cuda")
+    ids[5] = 9
+    with pytest.raises(RuntimeError, match="outside"):
+        eng.plan(ids)
+    ids[5] = 8          # the padding value of unused slots is fine
+    assert eng.plan(ids).rows % 128 == 0
+
+
 def test_peer_kernels_reject_bad_tables():
     from cute_kernels import _lib
     import ctypes
