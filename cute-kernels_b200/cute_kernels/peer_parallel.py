@@ -183,8 +183,7 @@ class PeerExpertEngine:
         _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, 0, edge)
         first_done = torch.cuda.Event()
         first_done.record(main)
-        # the GEMM is enqueued before the second pull: its CTAs (one per SM) take their places first and the pull's
-        # small blocks fill the registers and thread slots that are left
+        # the GEMM on the first window is enqueued before the second pull, which waits only for the first pull
         gemm(plan.mtile_first)
         side.wait_event(first_done)
         with torch.cuda.stream(side):
