@@ -340,7 +340,7 @@ __device__ __forceinline__ void stage_write_rows(const uint32_t *stage, int lane
         const int r = RP::row(it, lane);
         const uint2 v = *reinterpret_cast<const uint2 *>(stage + r * kStagePitchWords + 2 * sub);
         T *dst = row_ptr(r);
-        if (dst != nullptr && col < ncols) *reinterpret_cast<uint2 *>(dst + col) = v;
+        if (dst != nullptr && col < ncols) __stcs(reinterpret_cast<uint2 *>(dst + col), v);  // written once: evict-first, keeps the operand panels in L2
     }
 }
 // global -> rows of the stage (zeros where the row is absent or the columns are out of range)
