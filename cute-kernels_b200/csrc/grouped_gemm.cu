@@ -61,6 +61,8 @@ struct GemmParams {
     int64_t cap;   // rows allocated for the padded layout
     int gather_fan;   // > 0: A rows are gathered by TMA from the un-permuted token matrix: token = row_map[p] / gather_fan
     int gather_b_fan; // WGRAD, > 0: the same for the B operand
+    int l2_hint_a;    // ptx::L2_EVICT_* for the tiled loads of A / B (CTA-pair kernels)
+    int l2_hint_b;
     // STORE with peer destinations (n_peers > 0): row row_map[p] of the result belongs to global slot
     // g = dst_flat ? dst_flat[row_map[p]] : row_map[p] and is
     // stored at peer_out[g / peer_rows] + (g % peer_rows) * N (another GPU's memory over NVLink, or this GPU's own buffer)
@@ -1089,6 +1091,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            const uint64_t pol_a = ptx::l2_policy(p.l2_hint_a), pol_b = ptx::l2_policy(p.l2_hint_b);
             for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
                 const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
                 for (int kb = 0; kb < c.k_iters; ++kb) {
@@ -1102,22 +1105,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         const int krow = c.k_row0 + kb * BK;
 #pragma unroll
                         for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
-                            ptx::tma_load_2d_pair(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
+                            ptx::tma_load_2d_pair_hint(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow, pol_a);
 #pragma unroll
                         for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
-                            ptx::tma_load_2d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow);
+                            ptx::tma_load_2d_pair_hint(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow, pol_b);
                     } else {
                         const int k0 = kb * BK;
-                        ptx::tma_load_2d_pair(sa, &p.tmA, full, k0, c.m_tile * BM);
+                        ptx::tma_load_2d_pair_hint(sa, &p.tmA, full, k0, c.m_tile * BM, pol_a);
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
-                                ptx::tma_load_3d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, k0, c.e);
+                                ptx::tma_load_3d_pair_hint(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, k0, c.e, pol_b);
                         } else if constexpr (MODE == MODE_UP_ACT) {
                             // leader: 128 rows of W_up, peer: the matching 128 rows of W_gate
-                            ptx::tma_load_3d_pair(sb, &p.tmB, full, k0, rank * p.N + c.n_tile * (BN / 2), c.e);
+                            ptx::tma_load_3d_pair_hint(sb, &p.tmB, full, k0, rank * p.N + c.n_tile * (BN / 2), c.e, pol_b);
                         } else {
-                            ptx::tma_load_3d_pair(sb, &p.tmB, full, k0, nb0, c.e);
+                            ptx::tma_load_3d_pair_hint(sb, &p.tmB, full, k0, nb0, c.e, pol_b);
                         }
                     }
                     if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
@@ -1268,6 +1271,16 @@ static bool use_cta_pair() {
 
 template <typename T, int MODE, bool B_MN>
 static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t stream) {
+    // L2 policy of the operand loads.  Inside an expert the tiles run with one dimension fastest: the panels along it
+    // are shared by the tiles in flight and then never needed again (evict-first); the panels of the other operand are
+    // what every following wave comes back to (evict-last while one expert's share of them, rows x K, is of L2 size).
+    if (MODE == MODE_WGRAD) {
+        p.l2_hint_a = p.n_fastest ? ptx::L2_EVICT_NORMAL : ptx::L2_EVICT_LAST;
+        p.l2_hint_b = p.n_fastest ? ptx::L2_EVICT_LAST : ptx::L2_EVICT_NORMAL;
+    } else {
+        p.l2_hint_a = (p.K <= 8192) ? ptx::L2_EVICT_LAST : ptx::L2_EVICT_NORMAL;
+        p.l2_hint_b = ptx::L2_EVICT_NORMAL;
+    }
     if (use_cta_pair()) {
         auto kern2 = grouped_gemm_pair_kernel<T, MODE, B_MN>;
         CK_CUDA_TRY(cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmPairSmemBytes));
