@@ -46,8 +46,8 @@ UNIT = "tokens/s"
 # DRAM bytes (read + write) per launch of each GEMM family on the full c4 workload, from a one-pass ncu capture of this
 # command (dram__bytes_read.sum + dram__bytes_write.sum; wgrad = mean of its two launches); the summary is under profiles/
 MEASURED_DRAM_TRAFFIC = {
-    "c4_mixtral_moe_fwd_bwd": {"up_act_fwd": 8677e6, "down_combine_fwd": 10038e6, "dgrad_down": 7964e6, "wgrad": 5722e6,
-                               "dgrad_up": 22008e6},
+    "c4_mixtral_moe_fwd_bwd": {"up_act_fwd": 5910e6, "down_combine_fwd": 6276e6, "dgrad_down": 6500e6, "wgrad": 3686e6,
+                               "dgrad_up": 13209e6},
 }
 GEMM_KERNELS = ("up_act_fwd", "down_combine_fwd", "dgrad_down", "dgrad_up", "wgrad", "grouped_linear",
                 "grouped_linear_scatter", "grouped_linear_scatter_peer")
