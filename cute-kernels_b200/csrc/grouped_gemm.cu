@@ -370,7 +370,7 @@ __device__ __forceinline__ void rows_prefetch(uint2 *regs, int lane, int col0, i
     for (int it = 0; it < RP::kIters; ++it) {
         const T *src = row_ptr(RP::row(it, lane));
         regs[it] = make_uint2(0u, 0u);
-        if (src != nullptr && col < ncols) regs[it] = __ldg(reinterpret_cast<const uint2 *>(src + col));
+        if (src != nullptr && col < ncols) regs[it] = __ldcs(reinterpret_cast<const uint2 *>(src + col));  // read once: evict-first
     }
 }
 template <typename T>
