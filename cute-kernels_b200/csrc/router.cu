@@ -31,13 +31,15 @@ __global__ void __launch_bounds__(kRouterThreads)
         float my_val = 0.0f;  // lane j keeps the j-th winner
         int my_idx = 0;
         float vmax = 0.0f;
+        unsigned taken = 0u;  // bit i: this lane's i-th logit is already among the winners
         for (int j = 0; j < k; ++j) {
             float best = -INFINITY;
             int best_e = 0x7fffffff;
 #pragma unroll
             for (int i = 0; i < kPerLane; ++i) {
                 const int e = lane + 32 * i;
-                if (e < E && (v[i] > best || (v[i] == best && e < best_e))) {
+                // the first candidate not yet taken is accepted whatever its value: masked (-inf) logits still give k distinct experts
+                if (e < E && !((taken >> i) & 1u) && (best_e == 0x7fffffff || v[i] > best)) {
                     best = v[i];
                     best_e = e;
                 }
@@ -56,11 +58,7 @@ __global__ void __launch_bounds__(kRouterThreads)
                 my_val = best;
                 my_idx = best_e;
             }
-            if ((best_e & 31) == lane) {  // the owner retires the winner
-#pragma unroll
-                for (int i = 0; i < kPerLane; ++i)
-                    if (i == (best_e >> 5)) v[i] = -INFINITY;
-            }
+            if (best_e != 0x7fffffff && (best_e & 31) == lane) taken |= 1u << (best_e >> 5);  // the owner retires the winner
         }
         // softmax over the k selected logits in fp32 (k <= 32: one per lane)
         const float ex = lane < k ? expf(my_val - vmax) : 0.0f;

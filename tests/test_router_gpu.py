@@ -74,6 +74,19 @@ def test_router_backward_matches_autograd(dtype, T, E, k):
     assert (x.grad.cpu()[mask] == 0).all()
 
 
+def test_router_masked_logits_give_distinct_experts():
+    from cute_kernels import router_topk_softmax
+
+    logits = torch.full((6, 16), float("-inf"))
+    logits[:, 5] = 1.0                      # one live expert, k = 3: the other two picks are masked experts 0 and 1
+    logits[3, 9] = 2.0
+    w, ids = router_topk_softmax(logits.cuda(), 3)
+    ids = ids.cpu()
+    assert ids[0].tolist() == [5, 0, 1] and ids[3].tolist() == [9, 5, 0]
+    assert (torch.sort(ids, dim=1).values.diff(dim=1) > 0).all()
+    torch.testing.assert_close(w.cpu()[0], torch.tensor([1.0, 0.0, 0.0]))
+
+
 def test_router_rejects_and_empty():
     from cute_kernels import router_topk_softmax
 
