@@ -381,6 +381,7 @@ def gpu_arm(args, w: dict) -> dict | None:
         "up_act_fwd": 2.0 * R * (2 * I) * H, "down_combine_fwd": 2.0 * R * H * I, "dgrad_down": 2.0 * R * H * I,
         "dgrad_up": 2.0 * R * (2 * I) * H, "wgrad": 2.0 * R * H * I * 1.5,  # two launches per step: (H x I) and (2I x H)
         "grouped_linear_scatter": 2.0 * R * H * I * 1.5,  # expert-parallel shards: down (H x I) and dgrad-up (2I x H)
+        "grouped_linear_scatter_peer": 2.0 * R * H * I * 1.5,  # the same two GEMMs storing into the owners' buffers
     }
     kernels = {}
     for name, ts in per_kernel.items():
