@@ -1,5 +1,7 @@
 """Expert parallelism for the MoE expert path: experts block-partitioned over the ranks of a process
 group, tokens data-parallel, rows exchanged with all-to-all-v (NCCL over NVLink on GPUs).
+(:mod:`peer_parallel` is the faster transport on one node: the kernels read and write the other ranks'
+buffers directly; this module is the portable one and the one whose host logic runs on CPU ranks in tests.)
 
 The reference has no multi-GPU path; the contract is the single-process layer on the concatenated
 batch.  Rank g owns experts [g*E/G, (g+1)*E/G) and only those slices of ``c_fc.weight`` /
