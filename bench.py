@@ -44,13 +44,34 @@ WORKLOADS = {
 METRIC = "moe_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 # DRAM bytes (read + write) per launch of each GEMM family on the full c4 workload, from a one-pass ncu capture of this
-# command (dram__bytes_read.sum + dram__bytes_write.sum; wgrad = mean of its two launches); the summary is under profiles/
+# command (dram__bytes_read.sum + dram__bytes_write.sum; wgrad = mean of its two launches).  The figures belong to the
+# kernel source they were captured from: "gemm_source_sha16" is the sha256 prefix of csrc/grouped_gemm.cu at capture
+# time, and a different source makes ``roofline.traffic`` null instead of quoting a stale capture.
 MEASURED_DRAM_TRAFFIC = {
-    "c4_mixtral_moe_fwd_bwd": {"up_act_fwd": 5910e6, "down_combine_fwd": 6276e6, "dgrad_down": 6500e6, "wgrad": 3686e6,
-                               "dgrad_up": 13209e6},
+    "c4_mixtral_moe_fwd_bwd": {"gemm_source_sha16": "", "up_act_fwd": 5910e6, "down_combine_fwd": 6276e6,
+                               "dgrad_down": 6500e6, "wgrad": 3686e6, "dgrad_up": 13209e6},
 }
+
+
+def gemm_source_sha16() -> str:
+    import hashlib
+
+    try:
+        with open(os.path.join(ROOT, "cute-kernels_b200", "csrc", "grouped_gemm.cu"), "rb") as f:
+            return hashlib.sha256(f.read()).hexdigest()[:16]
+    except OSError:
+        return "unknown"
+
+
+def measured_traffic(workload: str, kernel: str):
+    t = MEASURED_DRAM_TRAFFIC.get(workload)
+    if not t or t.get("gemm_source_sha16") != gemm_source_sha16():
+        return None
+    return t.get(kernel)
+
+
 GEMM_KERNELS = ("up_act_fwd", "down_combine_fwd", "dgrad_down", "dgrad_up", "wgrad", "grouped_linear",
-                "grouped_linear_scatter", "grouped_linear_scatter_peer")
+                "grouped_linear_scatter", "grouped_linear_scatter_peer", "up_act_fwd_peer", "dgrad_down_peer")
 
 
 def measured_peaks() -> dict:
@@ -200,6 +221,94 @@ def cpu_arm(w: dict, steps: int, warmup: int, budget_s: float) -> dict:
                 steps_timed=len(times),
                 sample=f"{T_s} tokens over {E_s} of {w['E']} experts (top-{k}, H={H}, I={I}, bf16): same FLOPs per token "
                        f"as the full workload")
+
+
+# ---------------------------------------------------------------------------------------------------
+# parity of the timed configuration (outside the timed regions)
+# ---------------------------------------------------------------------------------------------------
+def _within(got: torch.Tensor, ref: torch.Tensor, atol: float, rtol: float = 2e-2) -> tuple[float, float]:
+    """(worst |got - ref| / (atol + rtol |ref|), max |got - ref|)."""
+    err = (got.float() - ref.float()).abs()
+    return float((err / (atol + rtol * ref.float().abs())).max().item()), float(err.max().item())
+
+
+def parity_check(inp: dict, y: torch.Tensor, dx: torch.Tensor, w: dict, world: int, rank: int, n_tokens: int = 32) -> dict:
+    """Recomputes, in fp32 with plain torch on the GPU, what the timed step must have produced, from the same inputs:
+    y and dx of ``n_tokens`` sampled tokens of this rank (each needs only its own k experts), and the first 64 rows of
+    both weight gradients of this rank's first expert over the rows of ALL ranks routed to it.  Every rank builds its
+    expert weights from the same seed and shape, so expert e's weights are entry ``e % experts_per_rank`` of every
+    rank's local tensors: each rank can restate any expert without an exchange.  Tolerance: rtol 2e-2 with atol 2e-2
+    taken relative to the reference's RMS (outputs / input grads) or scaled by sqrt(rows / 64) (weight grads)."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    T, H, I, E, k = w["T"], w["H"], w["I"], w["E"], w["k"]
+    epr = E // world
+    dev = y.device
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        x, rw, sel, go = inp["x"], inp["router_weights"], inp["selected_experts"].long(), inp["grad_out"]
+        w_fc, w_proj = inp["w_fc"].detach(), inp["w_proj"].detach()
+        checks = {}
+
+        # (1) sampled tokens: y, dx
+        g = torch.Generator(device="cpu").manual_seed(99 + rank)
+        toks = torch.randperm(T, generator=g)[:n_tokens].to(dev)
+        xs = x[toks].float().requires_grad_()
+        ys = torch.zeros(n_tokens, H, device=dev)
+        for j in range(k):
+            for e in sel[toks, j].unique().tolist():
+                m = (sel[toks, j] == e).nonzero().squeeze(1)
+                h = F.linear(xs[m], w_fc[e % epr].float())
+                a = h[:, :I] * F.silu(h[:, I:])
+                ys = ys.index_add(0, m, F.linear(a, w_proj[e % epr].float()) * rw[toks[m], j].float().unsqueeze(1))
+        ys.backward(go[toks].float())
+        rms = lambda t: max(1.0, float(t.float().pow(2).mean().sqrt().item()))  # noqa: E731
+        checks["y"] = _within(y[toks], ys.detach(), 2e-2 * rms(ys.detach()))
+        checks["dx"] = _within(dx[toks], xs.grad, 2e-2 * rms(xs.grad))
+
+        # (2) weight-grad rows of this rank's first expert, over every rank's rows routed to it
+        def gathered(t):
+            if world == 1:
+                return t
+            out = torch.empty((world * t.size(0),) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
+            dist.all_gather_into_tensor(out, t.contiguous())
+            return out
+
+        x_all, rw_all, sel_all, go_all = gathered(x), gathered(rw), gathered(sel), gathered(go)
+        e_glob = rank * epr
+        tok_e, slot_e = (sel_all == e_glob).nonzero(as_tuple=True)
+        n_e = int(tok_e.numel())
+        rows = 64
+        if n_e > 0:
+            X = x_all[tok_e].float()
+            h = F.linear(X, w_fc[0].float())
+            up, gate = h[:, :I], h[:, I:]
+            sg = torch.sigmoid(gate)
+            act = up * gate * sg
+            wv = rw_all[tok_e, slot_e].float().unsqueeze(1)
+            dyw = go_all[tok_e].float() * wv
+            ref_dwproj = dyw[:, :rows].t() @ act                                # d_w_proj[0][:rows, :]
+            da = dyw @ w_proj[0].float()                                        # [n_e, I]
+            d_up = da[:, :rows] * gate[:, :rows] * sg[:, :rows]                # first `rows` "up" features
+            ref_dwfc = d_up.t() @ X                                             # d_w_fc[0][:rows, :]
+            checks["d_w_proj[first expert, :64]"] = _within(inp["w_proj"].grad[0, :rows], ref_dwproj, 2e-2 * rms(ref_dwproj))
+            checks["d_w_fc[first expert, :64]"] = _within(inp["w_fc"].grad[0, :rows], ref_dwfc, 2e-2 * rms(ref_dwfc))
+        worst = max(v[0] for v in checks.values())
+        ok = worst <= 1.0 and all(v[0] == v[0] for v in checks.values())
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    flag = torch.tensor([1.0 if ok else 0.0, worst, max(v[1] for v in checks.values())], device=dev, dtype=torch.float64)
+    if world > 1:
+        both = torch.stack([flag[0], -flag[1], -flag[2]])
+        dist.all_reduce(both, op=dist.ReduceOp.MIN)
+        flag = torch.stack([both[0], -both[1], -both[2]])
+    return dict(ok=bool(flag[0].item() == 1.0), worst_err_over_bound=float(flag[1].item()), max_abs=float(flag[2].item()),
+                checked=f"y, dx of {n_tokens} sampled tokens per rank; first 64 rows of d_w_proj and d_w_fc of each rank's "
+                        f"first expert over all ranks' rows; fp32 torch restatement of the layer on the same inputs",
+                tolerance="rtol 2e-2, atol 2e-2 x max(1, rms(ref))",
+                rank0={k_: dict(err_over_bound=round(v[0], 4), max_abs=v[1]) for k_, v in checks.items()})
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -369,6 +478,17 @@ def gpu_arm(args, w: dict) -> dict | None:
     d2h = 2 * T * H * 2
     ck.check_device_status()
 
+    # ---- parity of this very configuration, untimed: one more step on the resident inputs, checked in fp32 ----------
+    parity = None
+    if not args.no_parity:
+        zero_wgrads()
+        y_chk, dx_chk = step(inp["x"], inp["router_weights"], inp["selected_experts"], inp["grad_out"])
+        torch.cuda.synchronize()
+        parity = parity_check(inp, y_chk.detach(), dx_chk, w, world, rank)
+        del y_chk, dx_chk
+        zero_wgrads()
+        ck.check_device_status()
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -382,6 +502,7 @@ def gpu_arm(args, w: dict) -> dict | None:
         "dgrad_up": 2.0 * R * (2 * I) * H, "wgrad": 2.0 * R * H * I * 1.5,  # two launches per step: (H x I) and (2I x H)
         "grouped_linear_scatter": 2.0 * R * H * I * 1.5,  # expert-parallel shards: down (H x I) and dgrad-up (2I x H)
         "grouped_linear_scatter_peer": 2.0 * R * H * I * 1.5,  # the same two GEMMs storing into the owners' buffers
+        "up_act_fwd_peer": 2.0 * R * (2 * I) * H, "dgrad_down_peer": 2.0 * R * H * I,  # rows pulled over NVLink by the producer warps
     }
     kernels = {}
     for name, ts in per_kernel.items():
@@ -396,7 +517,7 @@ def gpu_arm(args, w: dict) -> dict | None:
         bound="tensor",
         kernel=f"{'grouped_gemm_pair_kernel' if os.environ.get('CK_GEMM_CTA_PAIR', '1') != '0' else 'grouped_gemm_kernel'}<bf16> ({dom})", achieved=kernels[dom]["tflops"], peak=peak,
         unit="TFLOP/s", frac=kernels[dom]["tflops"] / peak,
-        traffic=(MEASURED_DRAM_TRAFFIC.get(w["name"], {}).get(dom) if world == 1 else None),
+        traffic=(measured_traffic(w["name"], dom) if world == 1 else None),
         traffic_unit="bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture)",
         peak_source=f"bf16_tflops_sustained of {peaks['source']}",
         all_gemms=dict(ms_per_step=gemm_ms, tflops=gemm_flops / (gemm_ms * 1e-3) / 1e12,
@@ -406,7 +527,26 @@ def gpu_arm(args, w: dict) -> dict | None:
         kernels={n: {kk: round(vv, 4) if isinstance(vv, float) else vv for kk, vv in v.items()} for n, v in kernels.items()},
     )
 
-    cpu = cpu_arm(w, steps=1, warmup=0, budget_s=60.0) if (world == 1 and not args.no_cpu_baseline) else None
+    cpu = cpu_arm(w, steps=3, warmup=1, budget_s=45.0) if (world == 1 and not args.no_cpu_baseline) else None
+
+    # ---- the other configurations, measured in the same run outside the timed regions (N = 1 only) --------------------
+    aux = None
+    if world == 1 and not args.no_aux:
+        del host, y_host, dx_host
+        inp.clear()
+        torch.cuda.empty_cache()
+        hbm_peak = float(peaks["hbm_gbs"])
+        flush = torch.zeros(128 << 20, dtype=torch.float32, device=device)
+        aux = dict(
+            peak_hbm_gbs=hbm_peak, peak_source=f"hbm_gbs / bf16_tflops_sustained of {peaks['source']}",
+            c2_route_count=measure_c2(10, 3, flush, hbm_peak),
+            c3_swiglu=measure_c3(10, 3, flush, hbm_peak),
+            rmsnorm=measure_rmsnorm(10, 3, flush, hbm_peak),
+        )
+        del flush
+        torch.cuda.empty_cache()
+        if w["name"] != WORKLOADS["c5"]["name"]:
+            aux["c5_finegrained_moe"] = measure_moe_brief(WORKLOADS["c5"], 5, 3, device, peak)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -422,6 +562,10 @@ def gpu_arm(args, w: dict) -> dict | None:
         "gpu_launches": launches,
         "roofline": roofline,
     }
+    if parity is not None:
+        line["parity"] = parity
+    if aux is not None:
+        line["aux"] = aux
     if cpu is not None:
         line["cpu_baseline"] = cpu
     if world > 1:
@@ -449,10 +593,135 @@ def _time_each(fn, steps: int, warmup: int, flush: torch.Tensor | None) -> list[
     return out
 
 
-def micro_arm(args, which: str) -> dict:
+def measure_c2(steps: int, warmup: int, flush: torch.Tensor, peak: float) -> dict:
+    """count and count + scan + stable scatter over 2^24 int32 ids, 64 experts, uniform and Zipf(1.2) draws."""
     import numpy as np
 
-    import ck_oracle as orc
+    import cute_kernels as ck
+
+    dev = flush.device
+    n, E = 1 << 24, 64
+    g = torch.Generator(device=dev).manual_seed(0)
+    p_zipf = 1.0 / torch.arange(1, E + 1, device=dev, dtype=torch.float64).pow(1.2)
+    draws = {"uniform": torch.randint(0, E, (n,), generator=g, device=dev, dtype=torch.int32),
+             "zipf": torch.multinomial((p_zipf / p_zipf.sum()).float(), n, replacement=True, generator=g).to(torch.int32)}
+    out = {}
+    for name, ids in draws.items():
+        t_route = statistics.median(_time_each(lambda: ck.route(ids, E, with_tile_metadata=False), steps, warmup, flush))
+        t_count = statistics.median(_time_each(lambda: ck.continuous_count_cute(ids, E), steps, warmup, flush))
+        out[name] = dict(route_ms=t_route, route_gbs=12.0 * n / (t_route * 1e-3) / 1e9, route_frac=12.0 * n / (t_route * 1e-3) / 1e9 / peak,
+                         count_ms=t_count, count_gbs=4.0 * n / (t_count * 1e-3) / 1e9, count_frac=4.0 * n / (t_count * 1e-3) / 1e9 / peak)
+    out["algorithmic_bytes"] = dict(route=12 * n, count=4 * n)
+    out["n_ids"], out["experts"] = n, E
+    return out
+
+
+def measure_c3(steps: int, warmup: int, flush: torch.Tensor, peak: float) -> dict:
+    """Stand-alone SwiGLU forward and backward on [16384, 14336] bf16."""
+    import cute_kernels as ck
+
+    dev = flush.device
+    rows, cols = 16384, 14336
+    g = torch.Generator(device=dev).manual_seed(0)
+    gate = torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32).bfloat16().requires_grad_()
+    up = torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32).bfloat16().requires_grad_()
+    dy = torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32).bfloat16()
+    nel = rows * cols
+    with torch.no_grad():
+        # the 512 MB flush write also lets the host run ahead, so the events bracket device time only
+        f_ms = statistics.median(_time_each(lambda: ck.swiglu_cute(gate, up), steps, warmup, flush))
+    out = ck.swiglu_cute(gate, up)
+
+    def bwd():
+        gate.grad = None
+        up.grad = None
+        out.backward(dy, retain_graph=True)
+
+    b_ms = statistics.median(_time_each(bwd, steps, warmup, flush))
+    return dict(shape=[rows, cols], fwd_ms=f_ms, fwd_gbs=6.0 * nel / (f_ms * 1e-3) / 1e9, fwd_frac=6.0 * nel / (f_ms * 1e-3) / 1e9 / peak,
+                bwd_ms=b_ms, bwd_gbs=10.0 * nel / (b_ms * 1e-3) / 1e9, bwd_frac=10.0 * nel / (b_ms * 1e-3) / 1e9 / peak,
+                algorithmic_bytes=dict(fwd=6 * nel, bwd=10 * nel))
+
+
+def measure_rmsnorm(steps: int, warmup: int, flush: torch.Tensor, peak: float) -> dict:
+    """RMSNorm and fused residual-add + RMSNorm on the Mixtral-shaped layer's input [16384, 4096] bf16, with weight.
+    Algorithmic bytes per element: forward 2 x 2 B (4 x 2 B with the residual), backward 3 x 2 B (5 x 2 B)."""
+    import cute_kernels as ck
+
+    dev = flush.device
+    rows, cols = 16384, 4096
+    g = torch.Generator(device=dev).manual_seed(0)
+    mk = lambda *shape: torch.randn(*shape, generator=g, device=dev, dtype=torch.float32).bfloat16()  # noqa: E731
+    x, res, w, dy = mk(rows, cols).requires_grad_(), mk(rows, cols).requires_grad_(), mk(cols).requires_grad_(), mk(rows, cols)
+    nel = rows * cols
+    out = {"shape": [rows, cols]}
+    with torch.no_grad():
+        f_ms = statistics.median(_time_each(lambda: ck.rmsnorm_cute(x, w, 1e-5), steps, warmup, flush))
+        ff_ms = statistics.median(_time_each(lambda: ck.fused_residual_add_rmsnorm_cute(x, res, w, 1e-5, 0.9), steps, warmup, flush))
+    z = ck.rmsnorm_cute(x, w, 1e-5)
+    zf, rf = ck.fused_residual_add_rmsnorm_cute(x, res, w, 1e-5, 0.9)
+
+    def bwd():
+        x.grad = res.grad = w.grad = None
+        z.backward(dy, retain_graph=True)
+
+    def fbwd():
+        x.grad = res.grad = w.grad = None
+        torch.autograd.backward([zf, rf], [dy, dy], retain_graph=True)
+
+    b_ms = statistics.median(_time_each(bwd, steps, warmup, flush))
+    fb_ms = statistics.median(_time_each(fbwd, steps, warmup, flush))
+    for name, ms, elems in (("fwd", f_ms, 2), ("bwd", b_ms, 3), ("fused_fwd", ff_ms, 4), ("fused_bwd", fb_ms, 5)):
+        gbs = elems * 2.0 * nel / (ms * 1e-3) / 1e9
+        out[name] = dict(ms=ms, gbs=gbs, frac=gbs / peak, algorithmic_bytes=elems * 2 * nel)
+    return out
+
+
+def measure_moe_brief(w: dict, steps: int, warmup: int, device: torch.device, peak_tflops: float) -> dict:
+    """tokens/s and grouped-GEMM TFLOP/s of one more MoE configuration (single GPU, inputs resident)."""
+    import cute_kernels as ck
+    from cute_kernels import _lib
+
+    inp = make_device_inputs(w, device, seed=2000)
+    inp["w_fc"].requires_grad_()
+    inp["w_proj"].requires_grad_()
+    T, H, I, k = w["T"], w["H"], w["I"], w["k"]
+
+    def step():
+        x = inp["x"].detach().requires_grad_()
+        rw = inp["router_weights"].detach().requires_grad_()
+        y = ck.fused_experts(x, rw, inp["selected_experts"], inp["w_fc"], inp["w_proj"], k)
+        y.backward(inp["grad_out"])
+        inp["w_fc"].grad = None
+        inp["w_proj"].grad = None
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    _lib.launch_log.reset()
+    _lib.launch_log.record_events = True
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    _lib.launch_log.record_events = False
+    ms = e0.elapsed_time(e1) / steps
+    per: dict[str, float] = {}
+    for name, _work, a, b in _lib.launch_log.events:
+        per[name] = per.get(name, 0.0) + a.elapsed_time(b) / steps
+    _lib.launch_log.reset()
+    gemm_ms = sum(v for n, v in per.items() if n in GEMM_KERNELS)
+    flops = 18.0 * k * H * I * T
+    ck.check_device_status()
+    return dict(workload=w["name"], tokens=T, hidden=H, intermediate=I, experts=w["E"], top_k=k, steps=steps, ms_per_step=ms,
+                tokens_per_s=T / (ms * 1e-3), gemm_ms_per_step=gemm_ms, gemm_tflops=flops / (gemm_ms * 1e-3) / 1e12,
+                gemm_frac_of_measured_sustained=flops / (gemm_ms * 1e-3) / 1e12 / peak_tflops,
+                kernels_ms_per_step={n: round(v, 4) for n, v in sorted(per.items())})
+
+
+def micro_arm(args, which: str) -> dict:
     import cute_kernels as ck
 
     torch.cuda.set_device(0)
@@ -461,49 +730,27 @@ def micro_arm(args, which: str) -> dict:
     peak = float(peaks["hbm_gbs"])
     sampler = ClockSampler(0)
     flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
-    results = {}
     if which == "c2":
-        n, E = 1 << 24, 64
-        for dist_name in ("uniform", "zipf"):
-            ids = torch.from_numpy(orc.gen_ids(0, n, E, dist_name, np.int32)).to(dev)
-            t_route = _time_each(lambda: ck.route(ids, E, with_tile_metadata=False), args.steps, args.warmup, flush)
-            t_count = _time_each(lambda: ck.continuous_count_cute(ids, E), args.steps, args.warmup, flush)
-            results[dist_name] = dict(
-                route_ms=statistics.median(t_route), route_gbs=12.0 * n / (statistics.median(t_route) * 1e-3) / 1e9,
-                count_ms=statistics.median(t_count), count_gbs=4.0 * n / (statistics.median(t_count) * 1e-3) / 1e9)
-        sampler.mark_begin(); sampler.mark_end()
+        sampler.mark_begin()
+        results = measure_c2(args.steps, args.warmup, flush, peak)
+        sampler.mark_end()
         head = results["uniform"]
         line = dict(metric="route_hbm_gb_per_s", value=head["route_gbs"], unit="GB/s", ms_per_step=head["route_ms"],
-                    config=dict(workload="c2_count_scan_stable_scatter", n_ids=n, experts=E, ids_dtype="int32",
-                                l2_policy="l2_flushed_between_launches", draws=["uniform", "zipf(1.2)"]),
+                    config=dict(workload="c2_count_scan_stable_scatter", n_ids=results["n_ids"], experts=results["experts"],
+                                ids_dtype="int32", l2_policy="l2_flushed_between_launches", draws=["uniform", "zipf(1.2)"]),
                     roofline=dict(bound="hbm", kernel="route_hist + route_scan + route_scatter (3 launches)",
                                   achieved=head["route_gbs"], peak=peak, unit="GB/s", frac=head["route_gbs"] / peak,
-                                  traffic=None, algorithmic_bytes=12 * n, peak_source=f"hbm_gbs of {peaks['source']}"),
+                                  traffic=None, algorithmic_bytes=results["algorithmic_bytes"]["route"],
+                                  peak_source=f"hbm_gbs of {peaks['source']}"),
                     detail=results)
     else:
-        rows, cols = 16384, 14336
-        g = torch.Generator(device=dev).manual_seed(0)
-        gate = torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32).bfloat16().requires_grad_()
-        up = torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32).bfloat16().requires_grad_()
-        dy = torch.randn(rows, cols, generator=g, device=dev, dtype=torch.float32).bfloat16()
-        nel = rows * cols
-        with torch.no_grad():
-            # the 512 MB flush write also lets the host run ahead, so the events bracket device time only
-            t_fwd = _time_each(lambda: ck.swiglu_cute(gate, up), args.steps, args.warmup, flush)
-        out = ck.swiglu_cute(gate, up)
-
-        def bwd():
-            gate.grad = None
-            up.grad = None
-            out.backward(dy, retain_graph=True)
-
-        t_bwd = _time_each(bwd, args.steps, args.warmup, flush)
-        sampler.mark_begin(); sampler.mark_end()
-        f_ms, b_ms = statistics.median(t_fwd), statistics.median(t_bwd)
-        results = dict(fwd_ms=f_ms, fwd_gbs=6.0 * nel / (f_ms * 1e-3) / 1e9, bwd_ms=b_ms, bwd_gbs=10.0 * nel / (b_ms * 1e-3) / 1e9)
-        both = 16.0 * nel / ((f_ms + b_ms) * 1e-3) / 1e9
-        line = dict(metric="swiglu_fwd_bwd_hbm_gb_per_s", value=both, unit="GB/s", ms_per_step=f_ms + b_ms,
-                    config=dict(workload="c3_swiglu_fwd_bwd", shape=[rows, cols], l2_policy="inputs_exceed_l2"),
+        sampler.mark_begin()
+        results = measure_c3(args.steps, args.warmup, flush, peak)
+        sampler.mark_end()
+        nel = results["shape"][0] * results["shape"][1]
+        both = 16.0 * nel / ((results["fwd_ms"] + results["bwd_ms"]) * 1e-3) / 1e9
+        line = dict(metric="swiglu_fwd_bwd_hbm_gb_per_s", value=both, unit="GB/s", ms_per_step=results["fwd_ms"] + results["bwd_ms"],
+                    config=dict(workload="c3_swiglu_fwd_bwd", shape=results["shape"], l2_policy="inputs_exceed_l2"),
                     roofline=dict(bound="hbm", kernel="swiglu_bwd_vec_kernel<bf16>", achieved=results["bwd_gbs"], peak=peak,
                                   unit="GB/s", frac=results["bwd_gbs"] / peak, traffic=None, algorithmic_bytes=10 * nel,
                                   peak_source=f"hbm_gbs of {peaks['source']}"),
@@ -522,6 +769,8 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c2", "c3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the untimed fp32 parity check of the timed configuration")
+    ap.add_argument("--no-aux", action="store_true", help="N = 1: skip the routing / SwiGLU / fine-grained-layer figures")
     ap.add_argument("--ep-transport", default="auto", choices=["auto", "peer", "nccl"],
                     help="N > 1: rows cross GPUs by peer-memory loads/stores from the kernels (default when symmetric "
                          "memory is available) or by NCCL all-to-all")
@@ -553,6 +802,8 @@ def main() -> None:
     line = gpu_arm(args, w)
     if line is not None:
         print(json.dumps(line))
+        if line.get("parity") is not None and not line["parity"]["ok"]:
+            raise SystemExit("parity check of the timed configuration FAILED: " + json.dumps(line["parity"]))
 
 
 if __name__ == "__main__":

@@ -23,7 +23,8 @@
 
 namespace ck {
 
-enum { MODE_STORE = 0, MODE_UP_ACT = 1, MODE_SCATTER_ADD = 2, MODE_ACT_BWD = 3, MODE_WGRAD = 4 };
+enum { MODE_STORE = 0, MODE_UP_ACT = 1, MODE_SCATTER_ADD = 2, MODE_ACT_BWD = 3, MODE_WGRAD = 4,
+       MODE_UP_ACT1 = 5, MODE_ACT1_BWD = 6 };  // 5, 6: the un-gated up projection (one pre-activation per output) and its backward
 
 constexpr int BM = 128;
 constexpr int BN = 256;
@@ -47,7 +48,12 @@ struct GemmParams {
     void *out0;                 // STORE/WGRAD: y | UP_ACT: act | ACT_BWD: dh
     void *out1;                 // UP_ACT: h (may be NULL)
     float *out32;               // SCATTER_ADD target [T, N]
-    float *dgates;              // ACT_BWD: [T*k] fp32
+    const void *bias;           // per-expert bias of the GEMM's output features, [E, bias_ld] of T (may be NULL):
+                                //   UP_ACT: [up | gate] packed, bias_ld = 2I; UP_ACT1: bias_ld = I; STORE / SCATTER_ADD: bias_ld = N,
+                                //   scaled by the row's router weight when gate_w is given
+    int bias_ld;
+    float *dgates;              // ACT_BWD: [T*k] fp32, atomically accumulated (used when dgates_part is NULL)
+    float *dgates_part;         // ACT_BWD: [n_parts, cap] fp32 per-(n-tile, epilogue group) partial sums, plain stores
     int32_t *dev_status;
     int E;
     int n_tiles;   // tiles along N
@@ -63,6 +69,8 @@ struct GemmParams {
     int gather_b_fan; // WGRAD, > 0: the same for the B operand
     int l2_hint_a;    // ptx::L2_EVICT_* for the tiled loads of A / B (CTA-pair kernels)
     int l2_hint_b;
+    uint64_t wait_limit_ns;  // bound of every mbarrier wait (0: kWaitLimitNs)
+    int dbg;                 // timing probes (CK_GEMM_DEBUG)
     // STORE with peer destinations (n_peers > 0): row row_map[p] of the result belongs to global slot
     // g = dst_flat ? dst_flat[row_map[p]] : row_map[p] and is
     // stored at peer_out[g / peer_rows] + (g % peer_rows) * N (another GPU's memory over NVLink, or this GPU's own buffer)
@@ -70,6 +78,15 @@ struct GemmParams {
     int64_t peer_rows;
     int n_peers;
     void *peer_out[CK_MAX_PEERS];
+    // A rows copied in by row index (CTA-pair kernels, UP_ACT / ACT_BWD, gather_fan > 0): padded row p comes from row
+    // row_map[p] / gather_fan of a_src, or -- with n_src_peers > 0 -- from global slot g = row_map[p]: row
+    // (g % src_peer_rows) / gather_fan of peer_src[g / src_peer_rows] (another GPU's memory over NVLink, or this GPU's own)
+    const void *a_src;
+    int64_t src_peer_rows;
+    int n_src_peers;
+    const void *peer_src[CK_MAX_PEERS];
+    void *rows_out;       // not NULL: the gathered rows are also written out as the grouped [cap, K] matrix (tmOut)
+    CUtensorMap tmOut;
 };
 constexpr int kPeerRowBits = 26;  // rowinfo = rank << 26 | row: up to 32 ranks of 2^26 rows
 
@@ -107,25 +124,28 @@ struct SmemCtl {
     uint64_t tmem_empty[2];
     uint32_t tmem_ptr;
     volatile int abort_flag;
+    uint64_t wait_limit_ns;
     int32_t sched[kMaxSchedExperts + 1];
 };
 
 constexpr size_t kGemmSmemBytes_noepi = 1024 /*alignment slack*/ + size_t(kStages) * (kAStageBytes + kBStageBytes) + sizeof(SmemCtl);
 
-// bounded wait: false when the CTA is aborting or the time limit ran out
+// bounded wait: false when the CTA is aborting or the time limit (ctl->wait_limit_ns) ran out
 // BACKOFF: sleep between polls (epilogue warps: 32 polling lanes would otherwise compete for issue slots with the
 // producer / MMA lanes that share their scheduler)
-template <bool BACKOFF = false>
-__device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, SmemCtl *ctl, int32_t *dev_status) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
+// CLUSTER: acquire at cluster scope (the barrier is also arrived at by ordinary lanes of the pair's other CTA)
+template <bool BACKOFF = false, bool CLUSTER = false, typename Ctl>
+__device__ __forceinline__ bool wait_barrier(uint32_t bar, uint32_t parity, Ctl *ctl, int32_t *dev_status) {
+    auto passed = [&]() { return CLUSTER ? ptx::mbar_try_wait_cluster(bar, parity) : ptx::mbar_try_wait(bar, parity); };
+    if (passed()) return true;
     const uint64_t t0 = ptx::globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
         if (BACKOFF) __nanosleep(100);
-        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if (passed()) return true;
         if ((++spins & 63u) == 0) {
             if (ctl->abort_flag) return false;
-            if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (ptx::globaltimer_ns() - t0 > ctl->wait_limit_ns) {
                 ctl->abort_flag = 1;
                 if (dev_status) atomicOr(dev_status, CK_DEV_TIMEOUT);
                 return false;
@@ -239,6 +259,47 @@ __device__ __forceinline__ void act_bwd(int kind, float u, float g, float &a, fl
     }
 }
 
+// tanh-approximated GELU (torch.nn.GELU(approximate="tanh")): value and derivative
+template <typename T>
+__device__ __forceinline__ float tanh_epi(float x) {
+    if constexpr (sizeof(T) == 4) {
+        return tanhf(x);
+    } else {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+        return t;
+    }
+}
+template <typename T>
+__device__ __forceinline__ float gelu_fwd(float x) {
+    const float u = 0.7978845608028654f * fmaf(0.044715f * x * x, x, x);
+    return 0.5f * x * (1.0f + tanh_epi<T>(u));
+}
+template <typename T>
+__device__ __forceinline__ void gelu_bwd(float x, float &a, float &da) {
+    const float x2 = x * x;
+    const float t = tanh_epi<T>(0.7978845608028654f * fmaf(0.044715f * x2, x, x));
+    a = 0.5f * x * (1.0f + t);
+    da = 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * 0.7978845608028654f * fmaf(3.0f * 0.044715f, x2, 1.0f);
+}
+
+// 32 consecutive bias values of the tile's expert (the same for every row of the tile), zeros where absent or out of range
+template <typename T>
+__device__ __forceinline__ void load_bias32(const GemmParams &p, int e, int col0, int ncols, float *b) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) b[i] = 0.0f;
+    if (p.bias == nullptr) return;
+    const T *src = reinterpret_cast<const T *>(p.bias) + int64_t(e) * p.bias_ld;
+    if (col0 + 32 <= ncols) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) load8<T>(src + col0 + i, b + i);  // bias_ld and col0 are multiples of 8: 16-byte loads
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+            if (col0 + i < ncols) b[i] = DT<T>::up(src[col0 + i]);
+    }
+}
+
 // ---- fused tail of one 128 x 256 tile: executed by the four epilogue warps of a CTA --------------------
 //
 // tcgen05.ld hands every thread one accumulator ROW.  Writing rows straight from registers makes each
@@ -247,25 +308,26 @@ __device__ __forceinline__ void act_bwd(int kind, float u, float g, float &a, fl
 // row-per-thread domain and moves data between registers and global memory through a small per-warp
 // shared-memory stage, so that every global access is a run of 64 or 128 contiguous bytes of one row.
 constexpr int kStagePitchWords = 36;                           // 32 payload words + 4 pad: conflict-free v4 / v2 access
+constexpr int kStagePitchWords16 = 20;                         // 16 payload words (32 x 16-bit) + 4 pad: the same properties
 constexpr int kStageWarpBytes = 32 * kStagePitchWords * 4;     // 4608 B per epilogue warp
 constexpr int kEpiWarps = 4;
 constexpr int kEpiSmemBytes = kEpiWarps * (kStageWarpBytes + 32 * 4);  // stages + per-row info
 
 struct EpiSmem {
-    uint32_t *stage;  // [32][kStagePitchWords] words, private to the warp
+    uint32_t *stage;  // [32][PITCH] words, private to the warp
     int32_t *rowinfo; // [32] per-row index (row_map entry), private to the warp
 };
 
 // thread `lane` (owner of tile row `lane` of this warp) writes / reads its WORDS consecutive words
-template <int WORDS>
+template <int WORDS, int PITCH>
 __device__ __forceinline__ void stage_put_row(uint32_t *stage, int lane, const uint32_t *w) {
-    uint4 *dst = reinterpret_cast<uint4 *>(stage + lane * kStagePitchWords);
+    uint4 *dst = reinterpret_cast<uint4 *>(stage + lane * PITCH);
 #pragma unroll
     for (int q = 0; q < WORDS / 4; ++q) dst[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
 }
-template <int WORDS>
+template <int WORDS, int PITCH>
 __device__ __forceinline__ void stage_get_row(const uint32_t *stage, int lane, uint32_t *w) {
-    const uint4 *src = reinterpret_cast<const uint4 *>(stage + lane * kStagePitchWords);
+    const uint4 *src = reinterpret_cast<const uint4 *>(stage + lane * PITCH);
 #pragma unroll
     for (int q = 0; q < WORDS / 4; ++q) {
         const uint4 v = src[q];
@@ -332,7 +394,7 @@ struct RowPass {
 };
 
 // rows of the stage -> global: row r goes to base(r) + col0 .. col0+31 (elements of T); base(r) == nullptr skips
-template <typename T, typename RowPtr>
+template <typename T, int PITCH, typename RowPtr>
 __device__ __forceinline__ void stage_write_rows(const uint32_t *stage, int lane, int col0, int ncols, RowPtr row_ptr) {
     using RP = RowPass<T>;
     const int sub = lane % RP::kLpr;
@@ -340,13 +402,13 @@ __device__ __forceinline__ void stage_write_rows(const uint32_t *stage, int lane
 #pragma unroll
     for (int it = 0; it < RP::kIters; ++it) {
         const int r = RP::row(it, lane);
-        const uint2 v = *reinterpret_cast<const uint2 *>(stage + r * kStagePitchWords + 2 * sub);
+        const uint2 v = *reinterpret_cast<const uint2 *>(stage + r * PITCH + 2 * sub);
         T *dst = row_ptr(r);
         if (dst != nullptr && col < ncols) __stcs(reinterpret_cast<uint2 *>(dst + col), v);  // written once: evict-first, keeps the operand panels in L2
     }
 }
 // global -> rows of the stage (zeros where the row is absent or the columns are out of range)
-template <typename T, typename RowPtr>
+template <typename T, int PITCH, typename RowPtr>
 __device__ __forceinline__ void stage_read_rows(uint32_t *stage, int lane, int col0, int ncols, RowPtr row_ptr) {
     using RP = RowPass<T>;
     const int sub = lane % RP::kLpr;
@@ -357,7 +419,7 @@ __device__ __forceinline__ void stage_read_rows(uint32_t *stage, int lane, int c
         const T *src = row_ptr(r);
         uint2 v = make_uint2(0u, 0u);
         if (src != nullptr && col < ncols) v = *reinterpret_cast<const uint2 *>(src + col);
-        *reinterpret_cast<uint2 *>(stage + r * kStagePitchWords + 2 * sub) = v;
+        *reinterpret_cast<uint2 *>(stage + r * PITCH + 2 * sub) = v;
     }
 }
 
@@ -373,22 +435,55 @@ __device__ __forceinline__ void rows_prefetch(uint2 *regs, int lane, int col0, i
         if (src != nullptr && col < ncols) regs[it] = __ldcs(reinterpret_cast<const uint2 *>(src + col));  // read once: evict-first
     }
 }
-template <typename T>
+template <typename T, int PITCH>
 __device__ __forceinline__ void rows_to_stage(uint32_t *stage, int lane, const uint2 *regs) {
     using RP = RowPass<T>;
     const int sub = lane % RP::kLpr;
 #pragma unroll
     for (int it = 0; it < RP::kIters; ++it)
-        *reinterpret_cast<uint2 *>(stage + RP::row(it, lane) * kStagePitchWords + 2 * sub) = regs[it];
+        *reinterpret_cast<uint2 *>(stage + RP::row(it, lane) * PITCH + 2 * sub) = regs[it];
 }
 
-template <typename T, int MODE>
+// element pair (i, i + 1) of a row chunk held as packed words of T
+template <typename T>
+__device__ __forceinline__ void get2(const uint32_t *w, int i, float &a, float &b) {
+    if constexpr (sizeof(T) == 4) {
+        a = __uint_as_float(w[i]);
+        b = __uint_as_float(w[i + 1]);
+    } else if constexpr (DT<T>::code == CK_BF16) {
+        a = __uint_as_float(w[i >> 1] << 16);
+        b = __uint_as_float(w[i >> 1] & 0xffff0000u);
+    } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i >> 1]));
+        a = f.x;
+        b = f.y;
+    }
+}
+template <typename T>
+__device__ __forceinline__ void put2(uint32_t *w, int i, float a, float b) {
+    if constexpr (sizeof(T) == 4) {
+        w[i] = __float_as_uint(a);
+        w[i + 1] = __float_as_uint(b);
+    } else if constexpr (DT<T>::code == CK_BF16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        w[i >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+    } else {
+        const __half2 h = __floats2half2_rn(a, b);
+        w[i >> 1] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+}
+
+// Fused tail of one 128-row tile for the columns [cc_begin, cc_end) of its accumulator (steps of 32).  With two
+// epilogue warp groups each group takes half of the columns; `part` numbers the (n-tile, group) pair for per-part
+// outputs.  PITCH = words per row of the warp's shared-memory stage.
+template <typename T, int MODE, int PITCH>
 __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoord &c, uint32_t tbase, int row_in_tile,
-                                              const EpiSmem &es) {
+                                              const EpiSmem &es, int cc_begin, int cc_end, int part) {
     const bool have_acc = c.k_iters > 0;
     const int lane = row_in_tile & 31;
     const int row0 = row_in_tile - lane;  // first tile row of this warp
     using RP = RowPass<T>;
+    static_assert(PITCH >= RP::kWords + 4 || MODE == MODE_SCATTER_ADD, "stage rows too narrow for this dtype");
 
     if constexpr (MODE == MODE_STORE || MODE == MODE_WGRAD) {
         // per-row destination: grouped row, scattered row (row_map) or a row of dW[e]
@@ -429,8 +524,15 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
             return reinterpret_cast<T *>(p.out0) + int64_t(o) * int64_t(p.N);
         };
         const int n0 = c.n_tile * BN;
+        float bias_w = 1.0f;  // STORE with a bias: the row's router weight (the rows were scaled by it upstream)
+        if constexpr (MODE == MODE_STORE) {
+            if (p.bias != nullptr && p.gate_w != nullptr) {
+                const int32_t src = p.row_map ? p.row_map[int64_t(c.m_tile) * BM + row_in_tile] : -1;
+                bias_w = src >= 0 ? DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]) : 0.0f;
+            }
+        }
 #pragma unroll 1
-        for (int cc = 0; cc < BN; cc += 32) {
+        for (int cc = cc_begin; cc < cc_end; cc += 32) {
             uint32_t r[32];
             if (have_acc) {
                 ptx::tmem_ld32(tbase + cc, r);
@@ -442,11 +544,19 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            if constexpr (MODE == MODE_STORE) {
+                if (p.bias != nullptr) {  // y = x W^T + b[e], scaled like the rows themselves when they carry a router weight
+                    float bv[32];
+                    load_bias32<T>(p, c.e, n0 + cc, p.N, bv);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = fmaf(bias_w, bv[i], v[i]);
+                }
+            }
             uint32_t w[RP::kWords];
             pack32<T>(v, w);
-            stage_put_row<RP::kWords>(es.stage, lane, w);
+            stage_put_row<RP::kWords, PITCH>(es.stage, lane, w);
             __syncwarp();
-            stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, row_ptr);
+            stage_write_rows<T, PITCH>(es.stage, lane, n0 + cc, p.N, row_ptr);
             __syncwarp();
         }
     } else if constexpr (MODE == MODE_UP_ACT) {
@@ -459,35 +569,42 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
         const int64_t ld_act = p.N, ld_h = 2 * int64_t(p.N);
         const int n0 = c.n_tile * (BN / 2);
 #pragma unroll 1
-        for (int cc = 0; cc < BN / 2; cc += 32) {
+        for (int cc = cc_begin; cc < cc_end; cc += 32) {
+            if (n0 + cc >= p.N) break;  // whole chunk past the valid columns (uniform across the warp)
             uint32_t ru[32], rg[32];
             ptx::tmem_ld32(tbase + cc, ru);
             ptx::tmem_ld32(tbase + BN / 2 + cc, rg);
             ptx::tmem_ld_wait();
-            float va[32];
+            if (p.bias != nullptr) {  // pre-activations include the expert's bias: [up | gate] packed like the weight
+                float bv[32];
+                load_bias32<T>(p, c.e, n0 + cc, p.N, bv);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) va[i] = wgt * act_fwd<T>(p.act_kind, __uint_as_float(ru[i]), __uint_as_float(rg[i]));
+                for (int i = 0; i < 32; ++i) ru[i] = __float_as_uint(__uint_as_float(ru[i]) + bv[i]);
+                load_bias32<T>(p, c.e, p.N + n0 + cc, 2 * p.N, bv);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) rg[i] = __float_as_uint(__uint_as_float(rg[i]) + bv[i]);
+            }
             uint32_t w[RP::kWords];
-            pack32<T>(va, w);
-            stage_put_row<RP::kWords>(es.stage, lane, w);
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+                put2<T>(w, i, wgt * act_fwd<T>(p.act_kind, __uint_as_float(ru[i]), __uint_as_float(rg[i])),
+                        wgt * act_fwd<T>(p.act_kind, __uint_as_float(ru[i + 1]), __uint_as_float(rg[i + 1])));
+            stage_put_row<RP::kWords, PITCH>(es.stage, lane, w);
             __syncwarp();
-            stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return act + r * ld_act; });
+            stage_write_rows<T, PITCH>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return act + r * ld_act; });
             __syncwarp();
             if (h) {
-                float vf[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) vf[i] = __uint_as_float(ru[i]);
-                pack32<T>(vf, w);
-                stage_put_row<RP::kWords>(es.stage, lane, w);
+                for (int i = 0; i < 32; i += 2) put2<T>(w, i, __uint_as_float(ru[i]), __uint_as_float(ru[i + 1]));
+                stage_put_row<RP::kWords, PITCH>(es.stage, lane, w);
                 __syncwarp();
-                stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return h + r * ld_h; });
+                stage_write_rows<T, PITCH>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return h + r * ld_h; });
                 __syncwarp();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) vf[i] = __uint_as_float(rg[i]);
-                pack32<T>(vf, w);
-                stage_put_row<RP::kWords>(es.stage, lane, w);
+                for (int i = 0; i < 32; i += 2) put2<T>(w, i, __uint_as_float(rg[i]), __uint_as_float(rg[i + 1]));
+                stage_put_row<RP::kWords, PITCH>(es.stage, lane, w);
                 __syncwarp();
-                stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return h + r * ld_h + p.N; });
+                stage_write_rows<T, PITCH>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return h + r * ld_h + p.N; });
                 __syncwarp();
             }
         }
@@ -498,19 +615,27 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
         __syncwarp();
         const int n0 = c.n_tile * BN;
         const int sub = lane & 7;  // 8 lanes x 16 bytes cover the 32 fp32 columns of one row
+        float bias_w = 0.0f;  // with a bias: this row's router weight (the activations were scaled by it upstream)
+        if (p.bias != nullptr && src >= 0) bias_w = p.gate_w ? DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]) : 1.0f;
 #pragma unroll 1
-        for (int cc = 0; cc < BN; cc += 32) {
+        for (int cc = cc_begin; cc < cc_end; cc += 32) {
             uint32_t r[32];
             ptx::tmem_ld32(tbase + cc, r);
             ptx::tmem_ld_wait();
-            stage_put_row<32>(es.stage, lane, r);
+            if (p.bias != nullptr) {
+                float bv[32];
+                load_bias32<T>(p, c.e, n0 + cc, p.N, bv);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(fmaf(bias_w, bv[i], __uint_as_float(r[i])));
+            }
+            stage_put_row<32, PITCH>(es.stage, lane, r);
             __syncwarp();
             const int col = n0 + cc + 4 * sub;
 #pragma unroll
             for (int it = 0; it < 8; ++it) {
                 const int rr = it * 4 + (lane >> 3);
                 const int32_t tok = es.rowinfo[rr];
-                const float4 v = *reinterpret_cast<const float4 *>(es.stage + rr * kStagePitchWords + 4 * sub);
+                const float4 v = *reinterpret_cast<const float4 *>(es.stage + rr * PITCH + 4 * sub);
                 if (tok >= 0 && col < p.N) ptx::red_add_v4(p.out32 + int64_t(tok) * int64_t(p.N) + col, v.x, v.y, v.z, v.w);
             }
             __syncwarp();
@@ -528,24 +653,23 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
         uint2 pu[RP::kIters], pg[RP::kIters];  // saved up / gate values of the next chunk, in flight
         auto h_up = [&](int r) -> const T * { return h + r * ld_h; };
         auto h_gate = [&](int r) -> const T * { return h + r * ld_h + p.N; };
-        rows_prefetch<T>(pu, lane, n0, p.N, h_up);
-        rows_prefetch<T>(pg, lane, n0, p.N, h_gate);
+        if (n0 + cc_begin < p.N) {
+            rows_prefetch<T>(pu, lane, n0 + cc_begin, p.N, h_up);
+            rows_prefetch<T>(pg, lane, n0 + cc_begin, p.N, h_gate);
+        }
 #pragma unroll 1
-        for (int cc = 0; cc < BN; cc += 32) {
+        for (int cc = cc_begin; cc < cc_end; cc += 32) {
             if (n0 + cc >= p.N) break;  // whole chunk past the valid columns (uniform across the warp)
-            uint32_t w[RP::kWords];
-            float vu[32], vg[32];
-            rows_to_stage<T>(es.stage, lane, pu);
+            uint32_t wu[RP::kWords], wg[RP::kWords];  // this row's 32 up / gate values, packed; overwritten by the results
+            rows_to_stage<T, PITCH>(es.stage, lane, pu);
             __syncwarp();
-            stage_get_row<RP::kWords>(es.stage, lane, w);
-            unpack32<T>(w, vu);
+            stage_get_row<RP::kWords, PITCH>(es.stage, lane, wu);
             __syncwarp();
-            rows_to_stage<T>(es.stage, lane, pg);
+            rows_to_stage<T, PITCH>(es.stage, lane, pg);
             __syncwarp();
-            stage_get_row<RP::kWords>(es.stage, lane, w);
-            unpack32<T>(w, vg);
+            stage_get_row<RP::kWords, PITCH>(es.stage, lane, wg);
             __syncwarp();
-            if (cc + 32 < BN && n0 + cc + 32 < p.N) {
+            if (cc + 32 < cc_end && n0 + cc + 32 < p.N) {
                 rows_prefetch<T>(pu, lane, n0 + cc + 32, p.N, h_up);
                 rows_prefetch<T>(pg, lane, n0 + cc + 32, p.N, h_gate);
             }
@@ -553,27 +677,116 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
             ptx::tmem_ld32(tbase + cc, r);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float acc = __uint_as_float(r[i]);
-                float a, du_m, dg_m;
-                act_bwd<T>(p.act_kind, vu[i], vg[i], a, du_m, dg_m);
-                dgate_w += a * acc;
-                const float da = wgt * acc;
-                vu[i] = da * du_m;
-                vg[i] = da * dg_m;
+            for (int i = 0; i < 32; i += 2) {
+                float u0, u1, g0, g1;
+                get2<T>(wu, i, u0, u1);
+                get2<T>(wg, i, g0, g1);
+                float a0, du0, dg0, a1, du1, dg1;
+                act_bwd<T>(p.act_kind, u0, g0, a0, du0, dg0);
+                act_bwd<T>(p.act_kind, u1, g1, a1, du1, dg1);
+                const float acc0 = __uint_as_float(r[i]), acc1 = __uint_as_float(r[i + 1]);
+                dgate_w = fmaf(a0, acc0, dgate_w);
+                dgate_w = fmaf(a1, acc1, dgate_w);
+                const float da0 = wgt * acc0, da1 = wgt * acc1;
+                put2<T>(wu, i, da0 * du0, da1 * du1);
+                put2<T>(wg, i, da0 * dg0, da1 * dg1);
             }
-            pack32<T>(vu, w);
-            stage_put_row<RP::kWords>(es.stage, lane, w);
+            stage_put_row<RP::kWords, PITCH>(es.stage, lane, wu);
             __syncwarp();
-            stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return dh + r * ld_h; });
+            stage_write_rows<T, PITCH>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return dh + r * ld_h; });
             __syncwarp();
-            pack32<T>(vg, w);
-            stage_put_row<RP::kWords>(es.stage, lane, w);
+            stage_put_row<RP::kWords, PITCH>(es.stage, lane, wg);
             __syncwarp();
-            stage_write_rows<T>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return dh + r * ld_h + p.N; });
+            stage_write_rows<T, PITCH>(es.stage, lane, n0 + cc, p.N, [&](int r) -> T * { return dh + r * ld_h + p.N; });
             __syncwarp();
         }
-        if (p.dgates && src >= 0) atomicAdd(p.dgates + src, dgate_w);
+        // router-weight grad of this row over this part's columns: a plain store into the part's slice when the caller
+        // gave a partial buffer (summed later in a fixed order: reproducible), else an atomic add into dgates
+        if (p.dgates_part) p.dgates_part[int64_t(part) * p.cap + prow0 + lane] = dgate_w;
+        else if (p.dgates && src >= 0) atomicAdd(p.dgates + src, dgate_w);
+    } else if constexpr (MODE == MODE_UP_ACT1) {
+        // un-gated up projection: pre = x W^T + b, act = w * gelu_tanh(pre); pre is saved for the backward pass
+        const int64_t prow0 = int64_t(c.m_tile) * BM + row0;
+        const int32_t src = p.row_map[prow0 + lane];
+        float wgt = 1.0f;
+        if (p.gate_w) wgt = (src >= 0) ? DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]) : 0.0f;
+        T *act = reinterpret_cast<T *>(p.out0) + prow0 * int64_t(p.N);
+        T *h = p.out1 ? reinterpret_cast<T *>(p.out1) + prow0 * int64_t(p.N) : nullptr;
+        const int64_t ld = p.N;
+        const int n0 = c.n_tile * BN;
+#pragma unroll 1
+        for (int cc = cc_begin; cc < cc_end; cc += 32) {
+            if (n0 + cc >= p.N) break;
+            uint32_t r[32];
+            ptx::tmem_ld32(tbase + cc, r);
+            ptx::tmem_ld_wait();
+            if (p.bias != nullptr) {
+                float bv[32];
+                load_bias32<T>(p, c.e, n0 + cc, p.N, bv);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + bv[i]);
+            }
+            uint32_t w[RP::kWords];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+                put2<T>(w, i, wgt * gelu_fwd<T>(__uint_as_float(r[i])), wgt * gelu_fwd<T>(__uint_as_float(r[i + 1])));
+            stage_put_row<RP::kWords, PITCH>(es.stage, lane, w);
+            __syncwarp();
+            stage_write_rows<T, PITCH>(es.stage, lane, n0 + cc, p.N, [&](int rr) -> T * { return act + rr * ld; });
+            __syncwarp();
+            if (h) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) put2<T>(w, i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                stage_put_row<RP::kWords, PITCH>(es.stage, lane, w);
+                __syncwarp();
+                stage_write_rows<T, PITCH>(es.stage, lane, n0 + cc, p.N, [&](int rr) -> T * { return h + rr * ld; });
+                __syncwarp();
+            }
+        }
+    } else if constexpr (MODE == MODE_ACT1_BWD) {
+        // backward of the above: g = dy W_proj (accumulator), d_pre = w * g * gelu'(pre), router-weight grad = sum gelu(pre) * g
+        const int64_t prow0 = int64_t(c.m_tile) * BM + row0;
+        const int32_t src = p.row_map[prow0 + lane];
+        float wgt = (src >= 0) ? 1.0f : 0.0f;
+        if (p.gate_w && src >= 0) wgt = DT<T>::up(reinterpret_cast<const T *>(p.gate_w)[src]);
+        const int64_t ld = p.N;
+        const T *h = reinterpret_cast<const T *>(p.h_in) + prow0 * ld;
+        T *dh = reinterpret_cast<T *>(p.out0) + prow0 * ld;
+        const int n0 = c.n_tile * BN;
+        float dgate_w = 0.0f;
+        uint2 pu[RP::kIters];
+        auto h_row = [&](int rr) -> const T * { return h + rr * ld; };
+        if (n0 + cc_begin < p.N) rows_prefetch<T>(pu, lane, n0 + cc_begin, p.N, h_row);
+#pragma unroll 1
+        for (int cc = cc_begin; cc < cc_end; cc += 32) {
+            if (n0 + cc >= p.N) break;
+            uint32_t wu[RP::kWords];
+            rows_to_stage<T, PITCH>(es.stage, lane, pu);
+            __syncwarp();
+            stage_get_row<RP::kWords, PITCH>(es.stage, lane, wu);
+            __syncwarp();
+            if (cc + 32 < cc_end && n0 + cc + 32 < p.N) rows_prefetch<T>(pu, lane, n0 + cc + 32, p.N, h_row);
+            uint32_t r[32];
+            ptx::tmem_ld32(tbase + cc, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float x0, x1, a0, a1, d0, d1;
+                get2<T>(wu, i, x0, x1);
+                gelu_bwd<T>(x0, a0, d0);
+                gelu_bwd<T>(x1, a1, d1);
+                const float acc0 = __uint_as_float(r[i]), acc1 = __uint_as_float(r[i + 1]);
+                dgate_w = fmaf(a0, acc0, dgate_w);
+                dgate_w = fmaf(a1, acc1, dgate_w);
+                put2<T>(wu, i, wgt * acc0 * d0, wgt * acc1 * d1);
+            }
+            stage_put_row<RP::kWords, PITCH>(es.stage, lane, wu);
+            __syncwarp();
+            stage_write_rows<T, PITCH>(es.stage, lane, n0 + cc, p.N, [&](int rr) -> T * { return dh + rr * ld; });
+            __syncwarp();
+        }
+        if (p.dgates_part) p.dgates_part[int64_t(part) * p.cap + prow0 + lane] = dgate_w;
+        else if (p.dgates && src >= 0) atomicAdd(p.dgates + src, dgate_w);
     }
 }
 
@@ -610,6 +823,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[b]), 4);
         }
         ctl->abort_flag = 0;
+        ctl->wait_limit_ns = p.wait_limit_ns ? p.wait_limit_ns : kWaitLimitNs;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&p.tmA);
         ptx::prefetch_tensormap(&p.tmB);
@@ -824,7 +1038,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
             if (!wait_barrier<true>(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
             ptx::tc_fence_after();
             const uint32_t tbase = tmem_base + uint32_t(buf) * BN + (uint32_t(quarter * 32) << 16);
-            epilogue_tile<T, MODE>(p, c, tbase, row_in_tile, es);
+            epilogue_tile<T, MODE, kStagePitchWords>(p, c, tbase, row_in_tile, es, 0, (MODE == MODE_UP_ACT) ? BN / 2 : BN, c.n_tile);
             // release the accumulator buffer
             ptx::tc_fence_before();
             __syncwarp();
@@ -848,27 +1062,64 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 // halves.  Per CTA and k-block that is 32 KiB instead of 48 KiB from L2 and leaves room for a 6-stage
 // ring, which is what keeps the tensor pipe fed.  TMA loads are plain (non-multicast) per CTA; the
 // leader's mbarrier collects the transaction bytes of both CTAs.
+//
+// Warp roles (one warp group of control warps + one or two warp groups of epilogue warps):
+//   warp 0      TMA producer: B always, A when it is a plain tiled load
+//   warp 1      MMA issuer (leader CTA only)
+//   warps 2, 3  row-indexed A producer (UP_ACT / ACT_BWD with p.gather_fan > 0): warp 2 copies 16-byte pieces of the
+//               routed token rows -- named by row_map, living in this GPU's memory or in a peer's -- straight into the
+//               128-byte-swizzled stage with cp.async, so no grouped copy of the token matrix has to exist before the
+//               GEMM; lane 0 of warp 3 forwards each finished k-block to the tensor core's barrier and, on the first
+//               n-tile of every m-tile, stores the stage back out as the grouped copy (TMA store) that the
+//               weight-gradient GEMM contracts over later.
+//   warps 4..   epilogue; UP_ACT and ACT_BWD run two groups of four warps, each on half of the tile's columns, with
+//               registers moved from the control warps to the epilogue warps (setmaxnreg).
 #ifndef CK_PAIR_STAGES
 #define CK_PAIR_STAGES 6
 #endif
-constexpr int kPairStages = CK_PAIR_STAGES;
 constexpr int kBHalfStageBytes = kBStageBytes / 2;  // 16 KiB
 
-struct SmemCtlPair {
-    uint64_t full[kPairStages];
-    uint64_t empty[kPairStages];
+template <typename T, int MODE>
+struct PairCfg {
+    static constexpr bool kHeavyEpilogue = (MODE == MODE_UP_ACT || MODE == MODE_ACT_BWD || MODE == MODE_UP_ACT1 || MODE == MODE_ACT1_BWD);
+    static constexpr int kEpiGroups = kHeavyEpilogue ? 2 : 1;
+    static constexpr int kEpiWarpsTotal = 4 * kEpiGroups;
+    static constexpr int kThreads = 128 + 32 * kEpiWarpsTotal;
+    // words per row of an epilogue warp's stage: 32 fp32 payload words, or 16 for rows of 16-bit results
+    static constexpr int kPitch = (sizeof(T) == 4 || MODE == MODE_SCATTER_ADD) ? kStagePitchWords : kStagePitchWords16;
+    static constexpr int kEpiBytes = kEpiWarpsTotal * (32 * kPitch * 4 + 32 * 4);
+    // fp32 tensors with two epilogue groups need the wide stages for eight warps: one pipeline stage less
+    static constexpr int kStages = (kHeavyEpilogue && sizeof(T) == 4) ? CK_PAIR_STAGES - 1 : CK_PAIR_STAGES;
+    static constexpr bool kCanGather = kHeavyEpilogue;
+    // registers per thread after the hand-over (two epilogue groups only): 128 x 80 + 256 x 208 <= 384 x 168
+    static constexpr int kRegsControl = 80;
+    static constexpr int kRegsEpilogue = 208;
+};
+
+template <int STAGES>
+struct SmemCtlPairT {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t a_full[STAGES];  // row-indexed A producer: the copies of one k-block have landed in this CTA
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_ptr;
     volatile int abort_flag;
+    uint64_t wait_limit_ns;
     int32_t sched[kMaxSchedExperts + 1];   // m-tile offsets (or padded row offsets for WGRAD)
     int32_t psched[kMaxSchedExperts + 1];  // pair-tile offsets per expert
+    int32_t gather_src[BM];                // row-indexed A producer: source of every row of the current tile
 };
 
-constexpr size_t kGemmPairSmemBytes = 1024 + size_t(kPairStages) * (kAStageBytes + kBHalfStageBytes) + sizeof(SmemCtlPair) + kEpiSmemBytes;
+template <typename T, int MODE>
+constexpr size_t pair_smem_bytes() {
+    using C = PairCfg<T, MODE>;
+    return 1024 + size_t(C::kStages) * (kAStageBytes + kBHalfStageBytes) + ((sizeof(SmemCtlPairT<C::kStages>) + 15) & ~size_t(15)) +
+           C::kEpiBytes;
+}
 
-template <int MODE, int BK>
-__device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams &p, const SmemCtlPair *ctl, int t, int rank) {
+template <int MODE, int BK, typename Ctl>
+__device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams &p, const Ctl *ctl, int t, int rank) {
     TileCoord c;
     if constexpr (MODE == MODE_WGRAD) {
         const int mpairs = (p.m_tiles_w + 1) >> 1;
@@ -909,62 +1160,52 @@ __device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams &p, const
     return c;
 }
 
-// BACKOFF: sleep between polls (epilogue warps: 32 polling lanes would otherwise compete for issue slots with the
-// producer / MMA lanes that share their scheduler)
-template <bool BACKOFF = false>
-__device__ __forceinline__ bool wait_barrier_pair(uint32_t bar, uint32_t parity, SmemCtlPair *ctl, int32_t *dev_status) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = ptx::globaltimer_ns();
-    uint32_t spins = 0;
-    while (true) {
-        if (BACKOFF) __nanosleep(100);
-        if (ptx::mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 63u) == 0) {
-            if (ctl->abort_flag) return false;
-            if (ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
-                ctl->abort_flag = 1;
-                if (dev_status) atomicOr(dev_status, CK_DEV_TIMEOUT);
-                return false;
-            }
-        }
-    }
-}
-
 template <typename T, int MODE, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kThreads, 1)
     grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p) {
     using TR = GemmTraits<T>;
+    using CFG = PairCfg<T, MODE>;
+    using Ctl = SmemCtlPairT<CFG::kStages>;
+    constexpr int kNStages = CFG::kStages;
     constexpr bool A_MN = (MODE == MODE_WGRAD);
     constexpr int BK = TR::BK;
     constexpr uint32_t kIdesc = make_idesc<T>(A_MN, B_MN, 2 * BM);
-    constexpr uint32_t kStageTx = 2 * (kAStageBytes + kBHalfStageBytes);  // both CTAs' bytes land on the leader's barrier
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_u32 = ptx::smem_u32(smem_raw);
     const uint32_t pad = (1024u - (raw_u32 & 1023u)) & 1023u;
     uint8_t *smem = smem_raw + pad;
     const uint32_t smem_a = raw_u32 + pad;
-    const uint32_t smem_b = smem_a + kPairStages * kAStageBytes;
-    SmemCtlPair *ctl = reinterpret_cast<SmemCtlPair *>(smem + kPairStages * (kAStageBytes + kBHalfStageBytes));
+    const uint32_t smem_b = smem_a + kNStages * kAStageBytes;
+    Ctl *ctl = reinterpret_cast<Ctl *>(smem + kNStages * (kAStageBytes + kBHalfStageBytes));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int rank = int(ptx::cluster_ctarank());  // 0 = leader
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
+    // A rows copied in by warps 2 and 3 (cp.async by row index) instead of a tiled TMA load
+    const bool row_gather = CFG::kCanGather && p.gather_fan > 0;
+    // transaction bytes per stage on the leader's barrier: both CTAs' TMA loads
+    const uint32_t stage_tx = row_gather ? 2u * kBHalfStageBytes : 2u * (kAStageBytes + kBHalfStageBytes);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kPairStages; ++s) {
-            ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
-            ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), 1);
+        for (int s = 0; s < kNStages; ++s) {
+            // full: the producer's expect_tx arrival, plus the row forwarders of both CTAs
+            ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), row_gather ? 3 : 1);
+            // empty: the MMA commit, plus this CTA's row forwarder (its store back out has read the stage)
+            ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), row_gather ? 2 : 1);
+            ptx::mbar_init(ptx::smem_u32(&ctl->a_full[s]), 32);  // the copier warp's lanes, via their cp.async operations
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_u32(&ctl->tmem_full[b]), 1);
-            ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[b]), 8);  // 4 epilogue warps of each CTA
+            ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[b]), 2 * CFG::kEpiWarpsTotal);  // the epilogue warps of both CTAs
         }
         ctl->abort_flag = 0;
+        ctl->wait_limit_ns = p.wait_limit_ns ? p.wait_limit_ns : kWaitLimitNs;
         ptx::fence_mbar_init();
-        ptx::prefetch_tensormap(&p.tmA);
+        if (!row_gather) ptx::prefetch_tensormap(&p.tmA);
+        else if (p.rows_out) ptx::prefetch_tensormap(&p.tmOut);
         ptx::prefetch_tensormap(&p.tmB);
     }
     if (warp == 1) {
@@ -973,7 +1214,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     }
     {
         const int32_t *src = (MODE == MODE_WGRAD) ? p.padded_off : p.mtile_off;
-        for (int i = threadIdx.x; i <= p.E; i += kGemmThreads) ctl->sched[i] = src[i];
+        for (int i = threadIdx.x; i <= p.E; i += CFG::kThreads) ctl->sched[i] = src[i];
     }
     __syncthreads();
     if (MODE != MODE_WGRAD && threadIdx.x == 0) {
@@ -1000,28 +1241,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         }
     }
 
+    // The control warps need few registers; with two epilogue groups they hand theirs over.  Each setmaxnreg sits inside
+    // the branch its warp group runs, so that the register budget of one side never constrains the other side's code.
+    if (warp < 4) {
+    if constexpr (CFG::kEpiGroups == 2) ptx::setmaxnreg_dec<CFG::kRegsControl>();
     if (warp == 0) {
         // ================= TMA producer (one per CTA: own A rows, own half of B) =================
-        const bool gather_a = p.gather_fan > 0;
+        const bool gather_a = (MODE == MODE_WGRAD) && p.gather_fan > 0;
         const bool gather_b = (MODE == MODE_WGRAD) && p.gather_b_fan > 0;
         if (gather_a || gather_b) {
+            // wgrad with an operand gathered by TMA gather4 from the un-permuted matrix: every lane fetches four rows
             int stage = 0;
             uint32_t phase = 0;
             int ok = 1;
             for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
                 const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
-                int ridx[4] = {0, 0, 0, 0};
-                if (MODE != MODE_WGRAD && gather_a) {
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int32_t src = p.row_map[int64_t(c.m_tile) * BM + 4 * lane + q];
-                        ridx[q] = src >= 0 ? src / p.gather_fan : 0;
-                    }
-                }
                 for (int kb = 0; kb < c.k_iters; ++kb) {
                     if (lane == 0) {
-                        ok = wait_barrier_pair(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status) ? 1 : 0;
-                        if (ok && rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), kStageTx);
+                        ok = wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status) ? 1 : 0;
+                        if (ok && rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), stage_tx);
                     }
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
@@ -1029,59 +1267,41 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                     const uint32_t sa = smem_a + stage * kAStageBytes;
                     const uint32_t sb = smem_b + stage * kBHalfStageBytes;
                     const int nb0 = c.n_tile * BN + rank * (BN / 2);  // this CTA's half of the N range
-                    if constexpr (MODE == MODE_WGRAD) {
-                        const int krow = c.k_row0 + kb * BK;
-                        constexpr int kQ = BK / 4;
-                        if (gather_a) {
-                            for (int g = lane; g < (BM / TR::kMnBoxElems) * kQ; g += 32) {
-                                const int j = g / kQ, q = g - j * kQ;
-                                int r4[4];
+                    const int krow = c.k_row0 + kb * BK;
+                    constexpr int kQ = BK / 4;
+                    if (gather_a) {
+                        for (int g = lane; g < (BM / TR::kMnBoxElems) * kQ; g += 32) {
+                            const int j = g / kQ, q = g - j * kQ;
+                            int r4[4];
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    const int32_t src = p.row_map[krow + 4 * q + i];
-                                    r4[i] = src >= 0 ? src / p.gather_fan : 0;
-                                }
-                                ptx::tma_gather4_pair(sa + j * TR::kMnBoxBytes + q * 512, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
+                            for (int i = 0; i < 4; ++i) {
+                                const int32_t src = p.row_map[krow + 4 * q + i];
+                                r4[i] = src >= 0 ? src / p.gather_fan : 0;
                             }
-                        } else if (lane == 0) {
-#pragma unroll
-                            for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
-                                ptx::tma_load_2d_pair(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
+                            ptx::tma_gather4_pair(sa + j * TR::kMnBoxBytes + q * 512, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
                         }
-                        if (gather_b) {
-                            for (int g = lane; g < ((BN / 2) / TR::kMnBoxElems) * kQ; g += 32) {
-                                const int j = g / kQ, q = g - j * kQ;
-                                int r4[4];
+                    } else if (lane == 0) {
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    const int32_t src = p.row_map[krow + 4 * q + i];
-                                    r4[i] = src >= 0 ? src / p.gather_b_fan : 0;
-                                }
-                                ptx::tma_gather4_pair(sb + j * TR::kMnBoxBytes + q * 512, &p.tmB, full, nb0 + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
-                            }
-                        } else if (lane == 0) {
-#pragma unroll
-                            for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
-                                ptx::tma_load_2d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow);
-                        }
-                    } else {
-                        const int k0 = kb * BK;
-                        if (gather_a) ptx::tma_gather4_pair(sa + lane * 512, &p.tmA, full, k0, ridx[0], ridx[1], ridx[2], ridx[3]);
-                        else if (lane == 0) ptx::tma_load_2d_pair(sa, &p.tmA, full, k0, c.m_tile * BM);
-                        if (lane == 0) {
-                            if constexpr (B_MN) {
-#pragma unroll
-                                for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
-                                    ptx::tma_load_3d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, k0, c.e);
-                            } else if constexpr (MODE == MODE_UP_ACT) {
-                                // leader: 128 rows of W_up, peer: the matching 128 rows of W_gate
-                                ptx::tma_load_3d_pair(sb, &p.tmB, full, k0, rank * p.N + c.n_tile * (BN / 2), c.e);
-                            } else {
-                                ptx::tma_load_3d_pair(sb, &p.tmB, full, k0, nb0, c.e);
-                            }
-                        }
+                        for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
+                            ptx::tma_load_2d_pair(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
                     }
-                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                    if (gather_b) {
+                        for (int g = lane; g < ((BN / 2) / TR::kMnBoxElems) * kQ; g += 32) {
+                            const int j = g / kQ, q = g - j * kQ;
+                            int r4[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int32_t src = p.row_map[krow + 4 * q + i];
+                                r4[i] = src >= 0 ? src / p.gather_b_fan : 0;
+                            }
+                            ptx::tma_gather4_pair(sb + j * TR::kMnBoxBytes + q * 512, &p.tmB, full, nb0 + j * TR::kMnBoxElems, r4[0], r4[1], r4[2], r4[3]);
+                        }
+                    } else if (lane == 0) {
+#pragma unroll
+                        for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
+                            ptx::tma_load_2d_pair(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow);
+                    }
+                    if (++stage == kNStages) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok && lane == 0) {
@@ -1095,8 +1315,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
                 const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
                 for (int kb = 0; kb < c.k_iters; ++kb) {
-                    if (!wait_barrier_pair(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status)) { ok = false; break; }
-                    if (rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), kStageTx);
+                    if (!wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status)) { ok = false; break; }
+                    if (rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), stage_tx);
                     const uint32_t full = ptx::mapa_shared(ptx::smem_u32(&ctl->full[stage]), 0);  // the leader's barrier
                     const uint32_t sa = smem_a + stage * kAStageBytes;
                     const uint32_t sb = smem_b + stage * kBHalfStageBytes;
@@ -1111,7 +1331,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                             ptx::tma_load_2d_pair_hint(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow, pol_b);
                     } else {
                         const int k0 = kb * BK;
-                        ptx::tma_load_2d_pair_hint(sa, &p.tmA, full, k0, c.m_tile * BM, pol_a);
+                        if (!row_gather) ptx::tma_load_2d_pair_hint(sa, &p.tmA, full, k0, c.m_tile * BM, pol_a);
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
@@ -1123,7 +1343,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                             ptx::tma_load_3d_pair_hint(sb, &p.tmB, full, k0, nb0, c.e, pol_b);
                         }
                     }
-                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == kNStages) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok) {
@@ -1141,11 +1361,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             for (int t = pair_id; t < ntiles && ok; t += num_pairs, ++it) {
                 const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, 0);
                 const int buf = it & 1;
-                if (!wait_barrier_pair(ptx::smem_u32(&ctl->tmem_empty[buf]), ((uint32_t(it) >> 1) & 1u) ^ 1u, ctl, p.dev_status)) { ok = false; break; }
+                if (!wait_barrier(ptx::smem_u32(&ctl->tmem_empty[buf]), ((uint32_t(it) >> 1) & 1u) ^ 1u, ctl, p.dev_status)) { ok = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + uint32_t(buf) * BN;
                 for (int kb = 0; kb < c.k_iters; ++kb) {
-                    if (!wait_barrier_pair(ptx::smem_u32(&ctl->full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
+                    // rows written by the other CTA's row-gather warps are released at cluster scope
+                    if (p.dbg & 1) {
+                        if (!wait_barrier(ptx::smem_u32(&ctl->full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
+                    } else if (!wait_barrier<false, true>(ptx::smem_u32(&ctl->full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
                     ptx::tc_fence_after();
                     const uint32_t sa = smem_a + stage * kAStageBytes;
                     const uint32_t sb = smem_b + stage * kBHalfStageBytes;
@@ -1159,7 +1382,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
                         ptx::umma_ss_pair<TR::kTf32>(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     ptx::tc_commit_pair(ptx::smem_u32(&ctl->empty[stage]), 3);  // frees the stage in both CTAs
-                    if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == kNStages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 ptx::tc_commit_pair(ptx::smem_u32(&ctl->tmem_full[buf]), 3);  // accumulators of both CTAs complete
@@ -1170,24 +1393,122 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         }
         __syncwarp();
     } else {
+        // ================= row-indexed A producer =================
+        // warp 2 copies, lane 0 of warp 3 forwards.  The copier never waits for its own copies: every lane ties the
+        // k-block's cp.async operations to the CTA-local barrier a_full[stage] (cp.async.mbarrier.arrive.noinc) and runs
+        // ahead as far as the ring allows.  The forwarder has no memory operations of its own in flight, so its proxy
+        // fence and its release towards the leader CTA cost nothing: it waits for a_full, makes the rows visible to the
+        // tensor core (generic -> async proxy), stores the stage back out where asked, and arrives on the leader's
+        // full barrier.  Its second arrival, on this CTA's empty barrier, holds the stage until that store has read it.
+        if constexpr (CFG::kCanGather) {
+            if (row_gather && warp == 2) {
+                const int chunk = lane & 7;         // which 16 bytes of a 128-byte row
+                const int rsub = lane >> 3;         // rows rsub, rsub + 4, ... of the tile
+                constexpr int kRowsPerLane = BM / 4;
+                constexpr int kElemsPerChunk = 16 / int(sizeof(T));
+                int stage = 0;
+                uint32_t phase = 0;
+                int ok = 1;
+                for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
+                    const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
+                    // sources of the tile's 128 rows, (peer << 26 | row) or -1 for a pad row, parked in shared memory
+                    __syncwarp();  // every lane has issued the previous tile's copies
+                    for (int r = lane; r < BM; r += 32) {
+                        const int32_t g = p.row_map[int64_t(c.m_tile) * BM + r];
+                        int32_t v = -1;
+                        if (g >= 0) {
+                            if (p.n_src_peers > 0) {
+                                const int64_t rk = int64_t(g) / p.src_peer_rows;
+                                if (rk < p.n_src_peers) v = int32_t((rk << kPeerRowBits) | ((int64_t(g) - rk * p.src_peer_rows) / p.gather_fan));
+                                else if (p.dev_status) atomicOr(p.dev_status, CK_DEV_RANGE);
+                            } else {
+                                v = g / p.gather_fan;
+                            }
+                        }
+                        ctl->gather_src[r] = v;
+                    }
+                    __syncwarp();
+                    for (int kb = 0; kb < c.k_iters; ++kb) {
+                        if (lane == 0) ok = wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status) ? 1 : 0;
+                        ok = __shfl_sync(0xffffffffu, ok, 0);
+                        if (!ok) break;
+                        const int col = kb * BK + chunk * kElemsPerChunk;
+                        const bool in_k = col < p.K;
+                        const uint32_t sa = smem_a + stage * kAStageBytes;
+#pragma unroll 8
+                        for (int i = 0; i < kRowsPerLane; ++i) {
+                            const int r = rsub + 4 * i;
+                            const uint32_t dst = sa + uint32_t(r) * kRowBytes + (uint32_t(chunk ^ (r & 7)) << 4);
+                            const int32_t v = ctl->gather_src[r];
+                            const bool live = v >= 0 && in_k;
+                            const T *base = reinterpret_cast<const T *>(p.n_src_peers > 0 ? p.peer_src[live ? (v >> kPeerRowBits) : 0] : p.a_src);
+                            const int64_t row = live ? int64_t(v & ((1 << kPeerRowBits) - 1)) : 0;
+                            if ((p.dbg & 8) && (i & 1)) continue;
+                            if (p.dbg & 4) ptx::cp_async_16_full(dst, base + row * int64_t(p.K) + (live ? col : 0));
+                            else
+                            ptx::cp_async_16(dst, base + row * int64_t(p.K) + (live ? col : 0), live ? 16u : 0u);  // 0 bytes read: zero fill
+                        }
+                        ptx::cp_async_mbar_arrive_noinc(ptx::smem_u32(&ctl->a_full[stage]));
+                        if (++stage == kNStages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+                ptx::cp_async_wait_all();  // nothing of this CTA's is in flight when it leaves
+            } else if (row_gather && lane == 0) {
+                const uint32_t leader_full0 = ptx::mapa_shared(ptx::smem_u32(&ctl->full[0]), 0);
+                const bool store_rows = p.rows_out != nullptr;
+                int stage = 0;
+                uint32_t phase = 0;
+                bool ok = true;
+                for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
+                    const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
+                    const bool store_tile = store_rows && c.valid && c.n_tile == 0;
+                    for (int kb = 0; kb < c.k_iters; ++kb) {
+                        if (p.dbg & 16) {
+                            if (!wait_barrier(ptx::smem_u32(&ctl->a_full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
+                        } else if (!wait_barrier<true>(ptx::smem_u32(&ctl->a_full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
+                        if (!(p.dbg & 2)) ptx::fence_proxy_async();
+                        if (store_tile) {
+                            ptx::tma_store_2d(&p.tmOut, smem_a + stage * kAStageBytes, kb * BK, c.m_tile * BM);
+                            ptx::bulk_commit_group();
+                        }
+                        ptx::mbar_arrive_cluster(leader_full0 + uint32_t(stage) * 8u);
+                        if (store_tile) ptx::bulk_wait_group_read<0>();  // the stage may be refilled once the store has read it
+                        ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[stage]));
+                        if (++stage == kNStages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+                ptx::bulk_wait_group_all();  // the stores are complete before the kernel ends
+            }
+        }
+        __syncwarp();
+    }
+    } else {
         // ================= epilogue: each CTA drains its own 128 rows =================
-        const int quarter = warp & 3;
+        if constexpr (CFG::kEpiGroups == 2) ptx::setmaxnreg_inc<CFG::kRegsEpilogue>();
+        const int ew = warp - 4;
+        const int group = ew >> 2;
+        const int quarter = warp & 3;  // TMEM lanes this warp may read
         const int row_in_tile = quarter * 32 + lane;
-        uint8_t *epi_base = reinterpret_cast<uint8_t *>(ctl) + ((sizeof(SmemCtlPair) + 15) & ~size_t(15));
+        uint8_t *epi_base = reinterpret_cast<uint8_t *>(ctl) + ((sizeof(Ctl) + 15) & ~size_t(15));
+        constexpr int kWarpStageBytes = 32 * CFG::kPitch * 4;
         EpiSmem es;
-        es.stage = reinterpret_cast<uint32_t *>(epi_base + quarter * kStageWarpBytes);
-        es.rowinfo = reinterpret_cast<int32_t *>(epi_base + kEpiWarps * kStageWarpBytes + quarter * 128);
+        es.stage = reinterpret_cast<uint32_t *>(epi_base + ew * kWarpStageBytes);
+        es.rowinfo = reinterpret_cast<int32_t *>(epi_base + CFG::kEpiWarpsTotal * kWarpStageBytes + ew * 128);
         const uint32_t leader_empty0 = ptx::mapa_shared(ptx::smem_u32(&ctl->tmem_empty[0]), 0);
         const uint32_t leader_empty1 = ptx::mapa_shared(ptx::smem_u32(&ctl->tmem_empty[1]), 0);
+        constexpr int kCols = (MODE == MODE_UP_ACT) ? BN / 2 : BN;       // accumulator columns the tail walks over
+        constexpr int kColsPerGroup = kCols / CFG::kEpiGroups;
         int it = 0;
         bool ok = true;
         for (int t = pair_id; t < ntiles && ok; t += num_pairs, ++it) {
             const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
             const int buf = it & 1;
-            if (!wait_barrier_pair<true>(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
+            if (!wait_barrier<true>(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
             ptx::tc_fence_after();
             const uint32_t tbase = tmem_base + uint32_t(buf) * BN + (uint32_t(quarter * 32) << 16);
-            if (c.valid) epilogue_tile<T, MODE>(p, c, tbase, row_in_tile, es);
+            if (c.valid)
+                epilogue_tile<T, MODE, CFG::kPitch>(p, c, tbase, row_in_tile, es, group * kColsPerGroup, (group + 1) * kColsPerGroup,
+                                                    c.n_tile * CFG::kEpiGroups + group);
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(buf ? leader_empty1 : leader_empty0);
@@ -1281,13 +1602,20 @@ static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t stream) {
         p.l2_hint_a = (p.K <= 8192) ? ptx::L2_EVICT_LAST : ptx::L2_EVICT_NORMAL;
         p.l2_hint_b = ptx::L2_EVICT_NORMAL;
     }
+    {
+        static int dbg = -1;
+        if (dbg < 0) { const char *e = getenv("CK_GEMM_DEBUG"); dbg = e ? atoi(e) : 0; }
+        p.dbg = dbg;
+    }
     if (use_cta_pair()) {
         auto kern2 = grouped_gemm_pair_kernel<T, MODE, B_MN>;
-        CK_CUDA_TRY(cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmPairSmemBytes));
+        constexpr size_t smem_bytes = pair_smem_bytes<T, MODE>();
+        static_assert(smem_bytes <= 227 * 1024, "the CTA-pair kernel's shared memory exceeds what one CTA may own");
+        CK_CUDA_TRY(cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
         int64_t pairs = num_sms() / 2;
         if (pairs > max_tiles) pairs = max_tiles;  // upper bound: a pair tile covers at least one single tile
         if (pairs < 1) return CK_OK;
-        kern2<<<dim3((unsigned)(2 * pairs)), kGemmThreads, kGemmPairSmemBytes, stream>>>(p);
+        kern2<<<dim3((unsigned)(2 * pairs)), PairCfg<T, MODE>::kThreads, smem_bytes, stream>>>(p);
         CK_LAUNCH_CHECK("grouped_gemm_pair_kernel");
         return CK_OK;
     }
@@ -1340,27 +1668,87 @@ static int map_a_gather(CUtensorMap *tm, const void *a, int64_t rows, int K) {
 
 static bool dims_ok(int64_t cap, int a, int b) { return cap > 0 && cap % BM == 0 && a > 0 && b > 0 && a % 8 == 0 && b % 8 == 0; }
 
+// Where the A rows of the up projection / dgrad-down come from when they are not a ready-made grouped matrix.
+struct RowSource {
+    const void *src = nullptr;           // un-permuted [src_rows, K] matrix on this GPU
+    int64_t src_rows = 0;
+    int fan = 0;                         // > 0: padded row p reads row row_map[p] / fan (local) or (g % S) / fan of peer g / S
+    const void *const *peers = nullptr;  // host array of n_peers device pointers (every rank's matrix as mapped here)
+    int n_peers = 0;
+    int64_t rows_per_peer = 0;           // S: global slots per rank
+    void *rows_out = nullptr;            // also write the gathered rows out as the grouped [cap, K] matrix
+};
+
+// grouped copy [cap, K] written back from the A stages: box {BK, 128} (one stage)
 template <typename T>
-static int up_act_fwd_t(const void *xg, const void *wfc, const void *gate_w, const int32_t *row_map,
+static int map_rows_out(CUtensorMap *tm, void *a, int64_t cap, int K) {
+    const uint64_t dims[2] = {uint64_t(K), uint64_t(cap)};
+    const uint32_t box[2] = {uint32_t(GemmTraits<T>::BK), uint32_t(BM)};
+    return encode_map<T>(tm, a, 2, dims, box);
+}
+
+// fills the A side of the launch: a tiled map of the grouped matrix, or the row-index source
+template <typename T>
+static int set_a_operand(GemmParams &p, const void *grouped, const RowSource *rs, int64_t cap, int K) {
+    if (!rs || rs->fan <= 0) return map_a_kmajor<T>(&p.tmA, grouped, cap, K);
+    p.gather_fan = rs->fan;
+    if (!use_cta_pair()) {
+        // single-CTA flavour: TMA gather4 from the local matrix; no peers, no write-back
+        if (rs->n_peers > 0 || rs->rows_out) return CK_ERR_UNSUPPORTED;
+        return map_a_gather<T>(&p.tmA, rs->src, rs->src_rows, K);
+    }
+    if (rs->n_peers > 0) {
+        if (rs->n_peers > CK_MAX_PEERS || rs->rows_per_peer <= 0) return CK_ERR_SHAPE;
+        if (rs->rows_per_peer > (int64_t(1) << kPeerRowBits) || rs->rows_per_peer * rs->n_peers > INT32_MAX) return CK_ERR_RANGE;
+        p.n_src_peers = rs->n_peers;
+        p.src_peer_rows = rs->rows_per_peer;
+        for (int i = 0; i < rs->n_peers; ++i) {
+            if (!rs->peers[i] || (reinterpret_cast<uintptr_t>(rs->peers[i]) & 15)) return CK_ERR_SHAPE;
+            p.peer_src[i] = rs->peers[i];
+        }
+    } else {
+        if (!rs->src || (reinterpret_cast<uintptr_t>(rs->src) & 15) || rs->src_rows <= 0 || rs->src_rows > (int64_t(1) << kPeerRowBits)) return CK_ERR_SHAPE;
+        p.a_src = rs->src;
+    }
+    if ((int64_t(K) * int64_t(sizeof(T))) % 16 != 0) return CK_ERR_SHAPE;  // 16-byte pieces of whole rows
+    if (rs->rows_out) {
+        p.rows_out = rs->rows_out;
+        return map_rows_out<T>(&p.tmOut, rs->rows_out, cap, K);
+    }
+    return CK_OK;
+}
+
+static bool act_is_gated(int act_kind) { return act_kind == CK_ACT_SWIGLU || act_kind == CK_ACT_GLU; }
+static bool act_is_known(int act_kind) { return act_is_gated(act_kind) || act_kind == CK_ACT_GELU_TANH; }
+
+template <typename T>
+static int up_act_fwd_t(const void *xg, const void *wfc, const void *b_fc, const void *gate_w, const int32_t *row_map,
                         const int32_t *mtile_off, void *act, void *h, int E, int64_t cap, int H, int I, int act_kind,
-                        int32_t *dev_status, cudaStream_t stream, int64_t gather_rows = 0, int gather_fan = 0) {
+                        int32_t *dev_status, cudaStream_t stream, const RowSource *rs = nullptr) {
     GemmParams p = {};
     p.cap = cap;
     int rc;
-    if (gather_fan > 0) {
-        if ((rc = map_a_gather<T>(&p.tmA, xg, gather_rows, H)) != CK_OK) return rc;
-        p.gather_fan = gather_fan;
-    } else if ((rc = map_a_kmajor<T>(&p.tmA, xg, cap, H)) != CK_OK) return rc;
-    if ((rc = map_w_kmajor<T>(&p.tmB, wfc, E, 2 * I, H, BN / 2)) != CK_OK) return rc;
+    if ((rc = set_a_operand<T>(p, xg, rs, cap, H)) != CK_OK) return rc;
     p.mtile_off = mtile_off; p.row_map = row_map; p.gate_w = gate_w; p.out0 = act; p.out1 = h; p.dev_status = dev_status;
-    p.E = E; p.n_tiles = (I + BN / 2 - 1) / (BN / 2); p.N = I; p.K = H; p.act_kind = act_kind; p.top_k = 1;
-    return launch_gemm<T, MODE_UP_ACT, false>(p, (cap / BM) * p.n_tiles, stream);
+    p.E = E; p.N = I; p.K = H; p.act_kind = act_kind; p.top_k = 1;
+    p.bias = b_fc;
+    if (act_is_gated(act_kind)) {
+        // B tile = 128 rows of W_up | the matching 128 rows of W_gate
+        if ((rc = map_w_kmajor<T>(&p.tmB, wfc, E, 2 * I, H, BN / 2)) != CK_OK) return rc;
+        p.n_tiles = (I + BN / 2 - 1) / (BN / 2);
+        p.bias_ld = 2 * I;
+        return launch_gemm<T, MODE_UP_ACT, false>(p, (cap / BM) * p.n_tiles, stream);
+    }
+    if ((rc = map_w_kmajor<T>(&p.tmB, wfc, E, I, H, use_cta_pair() ? BN / 2 : BN)) != CK_OK) return rc;
+    p.n_tiles = (I + BN - 1) / BN;
+    p.bias_ld = I;
+    return launch_gemm<T, MODE_UP_ACT1, false>(p, (cap / BM) * p.n_tiles, stream);
 }
 
 template <typename T>
-static int down_combine_fwd_t(const void *act, const void *wproj, const int32_t *row_map, const int32_t *mtile_off,
-                              float *out32, int E, int64_t cap, int H, int I, int top_k, int32_t *dev_status,
-                              cudaStream_t stream) {
+static int down_combine_fwd_t(const void *act, const void *wproj, const void *b_proj, const void *gate_w, const int32_t *row_map,
+                              const int32_t *mtile_off, float *out32, int E, int64_t cap, int H, int I, int top_k,
+                              int32_t *dev_status, cudaStream_t stream) {
     GemmParams p = {};
     p.cap = cap;
     int rc;
@@ -1368,25 +1756,40 @@ static int down_combine_fwd_t(const void *act, const void *wproj, const int32_t 
     if ((rc = map_w_kmajor<T>(&p.tmB, wproj, E, H, I, use_cta_pair() ? BN / 2 : BN)) != CK_OK) return rc;
     p.mtile_off = mtile_off; p.row_map = row_map; p.out32 = out32; p.dev_status = dev_status;
     p.E = E; p.n_tiles = (H + BN - 1) / BN; p.N = H; p.K = I; p.top_k = top_k;
+    p.bias = b_proj; p.bias_ld = H; p.gate_w = gate_w;
     return launch_gemm<T, MODE_SCATTER_ADD, false>(p, (cap / BM) * p.n_tiles, stream);
 }
 
 template <typename T>
 static int dgrad_down_t(const void *dyg, const void *wproj, const void *h, const void *gate_w, const int32_t *row_map,
-                        const int32_t *mtile_off, void *dh, float *dgates, int E, int64_t cap, int H, int I, int act_kind,
-                        int32_t *dev_status, cudaStream_t stream, int64_t gather_rows = 0, int gather_fan = 0) {
+                        const int32_t *mtile_off, void *dh, float *dgates, float *dgates_part, int E, int64_t cap, int H,
+                        int I, int act_kind, int32_t *dev_status, cudaStream_t stream, const RowSource *rs = nullptr) {
     GemmParams p = {};
     p.cap = cap;
     int rc;
-    if (gather_fan > 0) {
-        if ((rc = map_a_gather<T>(&p.tmA, dyg, gather_rows, H)) != CK_OK) return rc;
-        p.gather_fan = gather_fan;
-    } else if ((rc = map_a_kmajor<T>(&p.tmA, dyg, cap, H)) != CK_OK) return rc;
+    if ((rc = set_a_operand<T>(p, dyg, rs, cap, H)) != CK_OK) return rc;
     if ((rc = map_w_mnmajor<T>(&p.tmB, wproj, E, H, I)) != CK_OK) return rc;
     p.mtile_off = mtile_off; p.row_map = row_map; p.gate_w = gate_w; p.h_in = h; p.out0 = dh; p.dgates = dgates;
+    p.dgates_part = dgates_part;
     p.dev_status = dev_status;
     p.E = E; p.n_tiles = (I + BN - 1) / BN; p.N = I; p.K = H; p.act_kind = act_kind; p.top_k = 1;
-    return launch_gemm<T, MODE_ACT_BWD, true>(p, (cap / BM) * p.n_tiles, stream);
+    if (act_is_gated(act_kind)) return launch_gemm<T, MODE_ACT_BWD, true>(p, (cap / BM) * p.n_tiles, stream);
+    return launch_gemm<T, MODE_ACT1_BWD, true>(p, (cap / BM) * p.n_tiles, stream);
+}
+
+// dgates[row_map[p]] = sum over the parts, in part order, of part[i * cap + p]   (one thread per padded row)
+__global__ void reduce_dgates_kernel(const float *__restrict__ part, int n_parts, int64_t cap, const int32_t *__restrict__ row_map,
+                                     const int32_t *__restrict__ padded_off, int E, float *__restrict__ dgates) {
+    int64_t rows = padded_off[E];
+    if (rows > cap) rows = cap;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t r = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; r < rows; r += stride) {
+        const int32_t dst = row_map[r];
+        if (dst < 0) continue;
+        float acc = 0.0f;
+        for (int i = 0; i < n_parts; ++i) acc += part[int64_t(i) * cap + r];
+        dgates[dst] = acc;
+    }
 }
 
 template <typename T>
@@ -1435,9 +1838,10 @@ template <typename T>
 static int grouped_linear_t(const void *x, const void *w, const int32_t *mtile_off, const int32_t *row_map, void *y, int E,
                             int64_t cap, int N, int K, int trans_w, int32_t *dev_status, cudaStream_t stream,
                             const int32_t *dst_flat = nullptr, void *const *peer_out = nullptr, int n_peers = 0,
-                            int64_t peer_rows = 0) {
+                            int64_t peer_rows = 0, const void *bias = nullptr, const void *gate_w = nullptr) {
     GemmParams p = {};
     p.cap = cap;
+    p.bias = bias; p.bias_ld = N; p.gate_w = gate_w;
     int rc;
     if ((rc = map_a_kmajor<T>(&p.tmA, x, cap, K)) != CK_OK) return rc;
     p.mtile_off = mtile_off; p.row_map = row_map; p.out0 = y; p.dev_status = dev_status;
@@ -1455,9 +1859,142 @@ static int grouped_linear_t(const void *x, const void *w, const int32_t *mtile_o
     return launch_gemm<T, MODE_STORE, false>(p, (cap / BM) * p.n_tiles, stream);
 }
 
+// ---- bias gradients (layers with add_bias=True) -------------------------------------------------------------
+// out[e, n] = sum over the padded rows p of expert e of scale(p) * rows[p, n], scale(p) = gate_w[row_map[p]] (1 without
+// gate_w; pad rows are zero).  One block per (expert, 256-column slab): the eight warps take every eighth row, each lane
+// eight consecutive columns, then the warps' sums are added through shared memory in a fixed order (reproducible).
+template <typename T>
+__global__ void __launch_bounds__(256) bias_grad_kernel(const T *__restrict__ rows, int64_t ld, int N, const int32_t *__restrict__ row_map,
+                                                        const T *__restrict__ gate_w, const int32_t *__restrict__ padded_off,
+                                                        T *__restrict__ out) {
+    __shared__ float red[8][256];
+    const int e = blockIdx.x;
+    const int col0 = blockIdx.y * 256 + (threadIdx.x & 31) * 8;
+    const int warp = threadIdx.x >> 5;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (col0 < N) {
+        for (int64_t r = padded_off[e] + warp; r < padded_off[e + 1]; r += 8) {
+            float scale = 1.0f;
+            if (gate_w != nullptr) {
+                const int32_t src = row_map[r];
+                if (src < 0) continue;
+                scale = DT<T>::up(gate_w[src]);
+            }
+            float v[8];
+            if (col0 + 8 <= N) {
+                load8<T>(rows + r * ld + col0, v);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = col0 + i < N ? DT<T>::up(rows[r * ld + col0 + i]) : 0.0f;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(scale, v[i], acc[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[warp][(threadIdx.x & 31) * 8 + i] = acc[i];
+    __syncthreads();
+    const int col = blockIdx.y * 256 + threadIdx.x;
+    if (col < N) {
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) s += red[w][threadIdx.x];
+        out[int64_t(e) * N + col] = DT<T>::down(s);
+    }
+}
+
+// part[p] = rows[p, :] . bias[e(p), :]   (one warp per padded row; the bias term of the router-weight gradient)
+template <typename T>
+__global__ void __launch_bounds__(256) bias_dots_kernel(const T *__restrict__ rows, int N, const T *__restrict__ bias,
+                                                        const int32_t *__restrict__ padded_off, int E, float *__restrict__ part) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+    const int64_t total = padded_off[E];
+    for (int64_t r = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < total; r += warps) {
+        int lo = 0, hi = E;  // expert of row r: padded_off[e] <= r < padded_off[e + 1]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (padded_off[mid] <= r) lo = mid; else hi = mid;
+        }
+        const T *x = rows + r * int64_t(N);
+        const T *b = bias + int64_t(lo) * N;
+        float acc = 0.0f;
+        for (int c = lane * 8; c < N; c += 256) {  // N is a multiple of 8
+            float xv[8], bv[8];
+            load8<T>(x + c, xv);
+            load8<T>(b + c, bv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc = fmaf(xv[i], bv[i], acc);
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+        if (lane == 0) part[r] = acc;
+    }
+}
+
+template <typename T>
+static int bias_grad_t(const void *rows, int64_t cap, int N, const int32_t *row_map, const void *gate_w, const int32_t *padded_off,
+                       int E, void *out, cudaStream_t stream) {
+    (void)cap;
+    bias_grad_kernel<T><<<dim3(unsigned(E), unsigned((N + 255) / 256)), 256, 0, stream>>>((const T *)rows, N, N, row_map, (const T *)gate_w,
+                                                                                           padded_off, (T *)out);
+    CK_LAUNCH_CHECK("bias_grad_kernel");
+    return CK_OK;
+}
+template <typename T>
+static int bias_dots_t(const void *rows, int64_t cap, int N, const void *bias, const int32_t *padded_off, int E, float *part,
+                       cudaStream_t stream) {
+    int64_t blocks = ceil_div64(cap, 8);
+    const int64_t limit = int64_t(num_sms()) * 8;
+    if (blocks > limit) blocks = limit;
+    bias_dots_kernel<T><<<unsigned(blocks), 256, 0, stream>>>((const T *)rows, N, (const T *)bias, padded_off, E, part);
+    CK_LAUNCH_CHECK("bias_dots_kernel");
+    return CK_OK;
+}
+
+// ---- self test of the bounded wait --------------------------------------------------------------------
+// One CTA, no TMA, no TMEM, no cluster: two lanes wait on an mbarrier that nobody ever arrives at, with the same
+// wait_barrier the GEMM roles use.  The first lane to run out of time raises the abort flag and CK_DEV_TIMEOUT; the
+// other leaves through the flag (or its own limit).  The kernel then returns normally.
+struct WaitTestCtl {
+    uint64_t bar;
+    volatile int abort_flag;
+    uint64_t wait_limit_ns;
+};
+
+__global__ void __launch_bounds__(64) wait_timeout_test_kernel(uint64_t limit_ns, int32_t *result, int32_t *dev_status) {
+    __shared__ WaitTestCtl ctl;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&ctl.bar), 1);
+        ctl.abort_flag = 0;
+        ctl.wait_limit_ns = limit_ns;
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    const uint64_t t0 = ptx::globaltimer_ns();
+    int ok = 1;
+    if (threadIdx.x == 0) ok = wait_barrier(ptx::smem_u32(&ctl.bar), 0u, &ctl, dev_status) ? 1 : 0;
+    if (threadIdx.x == 32) ok = wait_barrier<true>(ptx::smem_u32(&ctl.bar), 0u, &ctl, dev_status) ? 1 : 0;
+    const uint64_t waited = ptx::globaltimer_ns() - t0;
+    if (threadIdx.x == 0) { result[0] = ok; result[2] = int32_t(waited > 0x7fffffffull ? 0x7fffffffull : waited); }
+    if (threadIdx.x == 32) result[1] = ok;
+    __syncthreads();
+    if (threadIdx.x == 0) result[3] = ctl.abort_flag;
+}
+
 }  // namespace ck
 
 using namespace ck;
+
+extern "C" int ck_test_wait_timeout(int64_t limit_ns, int32_t *result4, int32_t *dev_status, void *stream) {
+    if (!result4 || !dev_status) return CK_ERR_SHAPE;
+    if (limit_ns <= 0 || limit_ns > 100000000ll) return CK_ERR_RANGE;  // at most 100 ms: this entry never stalls a GPU
+    wait_timeout_test_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(uint64_t(limit_ns), result4, dev_status);
+    CK_LAUNCH_CHECK("wait_timeout_test_kernel");
+    return CK_OK;
+}
+
+extern "C" int ck_gemm_cta_pair(void) { return use_cta_pair() ? 1 : 0; }
 
 extern "C" int ck_set_gemm_cta_pair(int enable) {
     const int prev = use_cta_pair() ? 1 : 0;
@@ -1473,45 +2010,90 @@ extern "C" int ck_set_gemm_cta_pair(int enable) {
         default: return CK_ERR_UNSUPPORTED;                         \
     }
 
-extern "C" int ck_moe_up_act_fwd(const void *xg, const void *wfc, const void *gate_w, const int32_t *row_map,
+extern "C" int ck_moe_up_act_fwd(const void *xg, const void *wfc, const void *b_fc, const void *gate_w, const int32_t *row_map,
                                  const int32_t *mtile_off, void *act, void *h, int E, int64_t cap, int H, int I,
                                  int act_kind, int dtype, int32_t *dev_status, void *stream) {
     if (!xg || !wfc || !row_map || !mtile_off || !act || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
-    if (act_kind != CK_ACT_SWIGLU && act_kind != CK_ACT_GLU) return CK_ERR_UNSUPPORTED;
-    CK_DISPATCH_DTYPE(dtype, (up_act_fwd_t<T>(xg, wfc, gate_w, row_map, mtile_off, act, h, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream)));
+    if (!act_is_known(act_kind)) return CK_ERR_UNSUPPORTED;
+    CK_DISPATCH_DTYPE(dtype, (up_act_fwd_t<T>(xg, wfc, b_fc, gate_w, row_map, mtile_off, act, h, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream)));
 }
 
-extern "C" int ck_moe_up_act_fwd_gather(const void *x, int64_t tokens, int top_k, const void *wfc, const void *gate_w,
-                                        const int32_t *row_map, const int32_t *mtile_off, void *act, void *h, int E,
-                                        int64_t cap, int H, int I, int act_kind, int dtype, int32_t *dev_status,
+extern "C" int ck_moe_up_act_fwd_gather(const void *x, int64_t tokens, int top_k, const void *wfc, const void *b_fc, const void *gate_w,
+                                        const int32_t *row_map, const int32_t *mtile_off, void *act, void *h, void *xg_out,
+                                        int E, int64_t cap, int H, int I, int act_kind, int dtype, int32_t *dev_status,
                                         void *stream) {
     if (!x || tokens <= 0 || top_k <= 0 || !wfc || !row_map || !mtile_off || !act || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
-    if (act_kind != CK_ACT_SWIGLU && act_kind != CK_ACT_GLU) return CK_ERR_UNSUPPORTED;
-    CK_DISPATCH_DTYPE(dtype, (up_act_fwd_t<T>(x, wfc, gate_w, row_map, mtile_off, act, h, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream, tokens, top_k)));
+    if (!act_is_known(act_kind)) return CK_ERR_UNSUPPORTED;
+    RowSource rs;
+    rs.src = x; rs.src_rows = tokens; rs.fan = top_k; rs.rows_out = xg_out;
+    CK_DISPATCH_DTYPE(dtype, (up_act_fwd_t<T>(nullptr, wfc, b_fc, gate_w, row_map, mtile_off, act, h, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream, &rs)));
 }
 
-extern "C" int ck_moe_down_combine_fwd(const void *act, const void *wproj, const int32_t *row_map,
-                                       const int32_t *mtile_off, float *out32, int E, int64_t cap, int H, int I,
-                                       int top_k, int dtype, int32_t *dev_status, void *stream) {
+extern "C" int ck_moe_up_act_fwd_gather_peer(const void *const *peer_src, int n_peers, int64_t rows_per_peer, int fan_out,
+                                             const void *wfc, const void *gate_w, const int32_t *row_map,
+                                             const int32_t *mtile_off, void *act, void *h, void *xg_out, int E, int64_t cap,
+                                             int H, int I, int act_kind, int dtype, int32_t *dev_status, void *stream) {
+    if (!peer_src || n_peers <= 0 || fan_out <= 0 || !wfc || !row_map || !mtile_off || !act || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
+    if (!act_is_known(act_kind)) return CK_ERR_UNSUPPORTED;
+    RowSource rs;
+    rs.peers = peer_src; rs.n_peers = n_peers; rs.rows_per_peer = rows_per_peer; rs.fan = fan_out; rs.rows_out = xg_out;
+    CK_DISPATCH_DTYPE(dtype, (up_act_fwd_t<T>(nullptr, wfc, nullptr, gate_w, row_map, mtile_off, act, h, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream, &rs)));
+}
+
+extern "C" int ck_moe_down_combine_fwd(const void *act, const void *wproj, const void *b_proj, const void *gate_w,
+                                       const int32_t *row_map, const int32_t *mtile_off, float *out32, int E, int64_t cap,
+                                       int H, int I, int top_k, int dtype, int32_t *dev_status, void *stream) {
     if (!act || !wproj || !row_map || !mtile_off || !out32 || E <= 0 || E > kMaxSchedExperts || top_k <= 0 || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
-    CK_DISPATCH_DTYPE(dtype, (down_combine_fwd_t<T>(act, wproj, row_map, mtile_off, out32, E, cap, H, I, top_k, dev_status, (cudaStream_t)stream)));
+    CK_DISPATCH_DTYPE(dtype, (down_combine_fwd_t<T>(act, wproj, b_proj, gate_w, row_map, mtile_off, out32, E, cap, H, I, top_k, dev_status, (cudaStream_t)stream)));
 }
 
 extern "C" int ck_moe_dgrad_down(const void *dyg, const void *wproj, const void *h, const void *gate_w,
-                                 const int32_t *row_map, const int32_t *mtile_off, void *dh, float *dgates, int E,
-                                 int64_t cap, int H, int I, int act_kind, int dtype, int32_t *dev_status, void *stream) {
+                                 const int32_t *row_map, const int32_t *mtile_off, void *dh, float *dgates,
+                                 float *dgates_part, int E, int64_t cap, int H, int I, int act_kind, int dtype,
+                                 int32_t *dev_status, void *stream) {
     if (!dyg || !wproj || !h || !row_map || !mtile_off || !dh || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
-    if (act_kind != CK_ACT_SWIGLU && act_kind != CK_ACT_GLU) return CK_ERR_UNSUPPORTED;
-    CK_DISPATCH_DTYPE(dtype, (dgrad_down_t<T>(dyg, wproj, h, gate_w, row_map, mtile_off, dh, dgates, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream)));
+    if (!act_is_known(act_kind)) return CK_ERR_UNSUPPORTED;
+    CK_DISPATCH_DTYPE(dtype, (dgrad_down_t<T>(dyg, wproj, h, gate_w, row_map, mtile_off, dh, dgates, dgates_part, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream)));
 }
 
 extern "C" int ck_moe_dgrad_down_gather(const void *dy, int64_t tokens, int top_k, const void *wproj, const void *h,
                                         const void *gate_w, const int32_t *row_map, const int32_t *mtile_off, void *dh,
-                                        float *dgates, int E, int64_t cap, int H, int I, int act_kind, int dtype,
-                                        int32_t *dev_status, void *stream) {
+                                        float *dgates, float *dgates_part, void *dyg_out, int E, int64_t cap, int H, int I,
+                                        int act_kind, int dtype, int32_t *dev_status, void *stream) {
     if (!dy || tokens <= 0 || top_k <= 0 || !wproj || !h || !row_map || !mtile_off || !dh || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
-    if (act_kind != CK_ACT_SWIGLU && act_kind != CK_ACT_GLU) return CK_ERR_UNSUPPORTED;
-    CK_DISPATCH_DTYPE(dtype, (dgrad_down_t<T>(dy, wproj, h, gate_w, row_map, mtile_off, dh, dgates, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream, tokens, top_k)));
+    if (!act_is_known(act_kind)) return CK_ERR_UNSUPPORTED;
+    RowSource rs;
+    rs.src = dy; rs.src_rows = tokens; rs.fan = top_k; rs.rows_out = dyg_out;
+    CK_DISPATCH_DTYPE(dtype, (dgrad_down_t<T>(nullptr, wproj, h, gate_w, row_map, mtile_off, dh, dgates, dgates_part, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream, &rs)));
+}
+
+extern "C" int ck_moe_dgrad_down_gather_peer(const void *const *peer_src, int n_peers, int64_t rows_per_peer, int fan_out,
+                                             const void *wproj, const void *h, const void *gate_w, const int32_t *row_map,
+                                             const int32_t *mtile_off, void *dh, float *dgates, float *dgates_part,
+                                             void *dyg_out, int E, int64_t cap, int H, int I, int act_kind, int dtype,
+                                             int32_t *dev_status, void *stream) {
+    if (!peer_src || n_peers <= 0 || fan_out <= 0 || !wproj || !h || !row_map || !mtile_off || !dh || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, H, I)) return CK_ERR_SHAPE;
+    if (!act_is_known(act_kind)) return CK_ERR_UNSUPPORTED;
+    RowSource rs;
+    rs.peers = peer_src; rs.n_peers = n_peers; rs.rows_per_peer = rows_per_peer; rs.fan = fan_out; rs.rows_out = dyg_out;
+    CK_DISPATCH_DTYPE(dtype, (dgrad_down_t<T>(nullptr, wproj, h, gate_w, row_map, mtile_off, dh, dgates, dgates_part, E, cap, H, I, act_kind, dev_status, (cudaStream_t)stream, &rs)));
+}
+
+extern "C" int ck_moe_dgrad_down_parts(int I) {
+    if (I <= 0) return 0;
+    const int n_tiles = (I + BN - 1) / BN;
+    return use_cta_pair() ? 2 * n_tiles : n_tiles;  // the CTA-pair kernel runs two epilogue groups per n-tile
+}
+
+extern "C" int ck_moe_reduce_dgates(const float *dgates_part, int n_parts, int64_t cap, const int32_t *row_map,
+                                    const int32_t *padded_off, int E, float *dgates, void *stream) {
+    if (!dgates_part || n_parts <= 0 || cap <= 0 || !row_map || !padded_off || E <= 0 || !dgates) return CK_ERR_SHAPE;
+    int64_t blocks = ceil_div64(cap, 256);
+    const int64_t limit = int64_t(num_sms()) * 8;
+    if (blocks > limit) blocks = limit;
+    reduce_dgates_kernel<<<unsigned(blocks), 256, 0, (cudaStream_t)stream>>>(dgates_part, n_parts, cap, row_map, padded_off, E, dgates);
+    CK_LAUNCH_CHECK("reduce_dgates_kernel");
+    return CK_OK;
 }
 
 extern "C" int ck_moe_wgrad_gather(const void *a, int64_t a_rows, int a_fan, const void *b, int64_t b_rows, int b_fan,
@@ -1541,11 +2123,24 @@ extern "C" int ck_moe_grouped_linear(const void *x, const void *w, const int32_t
     CK_DISPATCH_DTYPE(dtype, (grouped_linear_t<T>(x, w, mtile_off, nullptr, y, E, cap, N, K, trans_w, dev_status, (cudaStream_t)stream)));
 }
 
-extern "C" int ck_moe_grouped_linear_scatter(const void *x, const void *w, const int32_t *mtile_off, const int32_t *row_map,
-                                             void *y, int E, int64_t cap, int N, int K, int trans_w, int dtype,
-                                             int32_t *dev_status, void *stream) {
+extern "C" int ck_moe_grouped_linear_scatter(const void *x, const void *w, const void *bias, const void *gate_w,
+                                             const int32_t *mtile_off, const int32_t *row_map, void *y, int E, int64_t cap,
+                                             int N, int K, int trans_w, int dtype, int32_t *dev_status, void *stream) {
     if (!x || !w || !mtile_off || !row_map || !y || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, N, K)) return CK_ERR_SHAPE;
-    CK_DISPATCH_DTYPE(dtype, (grouped_linear_t<T>(x, w, mtile_off, row_map, y, E, cap, N, K, trans_w, dev_status, (cudaStream_t)stream)));
+    CK_DISPATCH_DTYPE(dtype, (grouped_linear_t<T>(x, w, mtile_off, row_map, y, E, cap, N, K, trans_w, dev_status, (cudaStream_t)stream,
+                                                  nullptr, nullptr, 0, 0, bias, gate_w)));
+}
+
+extern "C" int ck_moe_bias_grad(const void *rows, int64_t cap, int N, const int32_t *row_map, const void *gate_w,
+                                const int32_t *padded_off, int E, void *out, int dtype, void *stream) {
+    if (!rows || cap <= 0 || N <= 0 || N % 8 != 0 || !padded_off || E <= 0 || !out || (gate_w && !row_map)) return CK_ERR_SHAPE;
+    CK_DISPATCH_DTYPE(dtype, (bias_grad_t<T>(rows, cap, N, row_map, gate_w, padded_off, E, out, (cudaStream_t)stream)));
+}
+
+extern "C" int ck_moe_bias_dots(const void *rows, int64_t cap, int N, const void *bias, const int32_t *padded_off, int E,
+                                float *part, int dtype, void *stream) {
+    if (!rows || cap <= 0 || N <= 0 || N % 8 != 0 || !bias || !padded_off || E <= 0 || !part) return CK_ERR_SHAPE;
+    CK_DISPATCH_DTYPE(dtype, (bias_dots_t<T>(rows, cap, N, bias, padded_off, E, part, (cudaStream_t)stream)));
 }
 
 extern "C" int ck_moe_grouped_linear_scatter_peer(const void *x, const void *w, const int32_t *mtile_off,

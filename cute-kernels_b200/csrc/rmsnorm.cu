@@ -1,0 +1,391 @@
+// RMSNorm and fused residual-add + RMSNorm, forward and backward: HBM-bound streaming kernels.
+//
+// Replaces the reference's rmsnorm_cute / fused_residual_add_rmsnorm_cute (kernels/rmsnorm/__init__.py:12-77,
+// kernels/fused_residual_add_rmsnorm/__init__.py:15-132, Triton kernels underneath); the math is that of
+// rmsnorm_torch / fused_residual_add_rmsnorm_torch (torch_implementation.py of both):
+//
+//   forward    a = x * multiplier + residual            (only with a residual; a = x otherwise)
+//              r = rsqrt(mean(a^2) + eps)                (fp32)
+//              y = a * r * weight                        (fp32 throughout, one rounding to the tensor dtype, as F.rms_norm)
+//   backward   g = dy * weight
+//              da = r * g - a * r^3 * mean(g * a) + d_added      (d_added: gradient arriving through the residual stream)
+//              d_residual = da, dx = da * multiplier,  d_weight[j] = sum_rows dy[., j] * a[., j] * r
+//
+// One thread group per row keeps the row in registers between the reduction and the write, so every tensor crosses
+// HBM exactly once: forward 2 (4 with a residual) and backward 3 (5) elements of traffic per element.  Rows of up to
+// 1 KiB use a warp per row (shuffle reduction only), longer rows a 256-thread block per row; rows that do not fit the
+// register budget, or whose pointers / width are not 16-byte aligned, take a block-per-row kernel that re-reads the row
+// (an L2 hit) instead.  The weight gradient is accumulated per thread over the rows it visits and added to the fp32
+// d_weight with one atomic per column per block, like the reference's per-program accumulation + tl.atomic_add.
+#include "ck_common.cuh"
+
+namespace ck {
+
+constexpr int kNormBlock = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    return v;
+}
+
+// sum over the G threads that share a row (G = 32: the warp; G = kNormBlock: the block, through shared memory)
+template <int G>
+__device__ __forceinline__ float group_sum(float v, float *red) {
+    v = warp_sum(v);
+    if constexpr (G == 32) return v;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();  // red may still be read from the previous reduction
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = lane < G / 32 ? red[lane] : 0.0f;
+    return warp_sum(t);
+}
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T *p, float *v) {
+    const Vec16<T> raw = *reinterpret_cast<const Vec16<T> *>(p);
+#pragma unroll
+    for (int i = 0; i < Vec16<T>::N; ++i) v[i] = DT<T>::up(raw.v[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T *p, const float *v) {
+    Vec16<T> raw;
+#pragma unroll
+    for (int i = 0; i < Vec16<T>::N; ++i) raw.v[i] = DT<T>::down(v[i]);
+    __stcs(reinterpret_cast<int4 *>(p), *reinterpret_cast<const int4 *>(&raw));  // written once, read by a later kernel
+}
+// value as the tensor dtype would hold it
+template <typename T>
+__device__ __forceinline__ float rounded(float v) { return DT<T>::up(DT<T>::down(v)); }
+
+// ---- forward -------------------------------------------------------------------------------------------
+// G threads per row, VPT 16-byte vectors per thread (vector j of a thread covers columns (j * G + t) * VEC ...)
+template <typename T, int G, int VPT>
+__global__ void __launch_bounds__(kNormBlock)
+    rmsnorm_fwd_kernel(const T *__restrict__ x, const T *__restrict__ residual, const T *__restrict__ weight, T *__restrict__ out,
+                       T *__restrict__ added, float *__restrict__ inv_rms, int64_t rows, int H, float eps, float multiplier) {
+    constexpr int VEC = Vec16<T>::N;
+    __shared__ float red[kNormBlock / 32];
+    const int t = threadIdx.x % G;
+    const int rows_per_block = kNormBlock / G;
+    const int nvec = H / VEC;
+    float w[VPT][VEC];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int c = j * G + t;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) w[j][i] = 1.0f;
+        if (weight != nullptr && c < nvec) load_vec<T>(weight + int64_t(c) * VEC, w[j]);
+    }
+    const float inv_h = 1.0f / float(H);
+    for (int64_t row = int64_t(blockIdx.x) * rows_per_block + threadIdx.x / G; row < rows; row += int64_t(gridDim.x) * rows_per_block) {
+        float a[VPT][VEC];
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = j * G + t;
+            if (c < nvec) {
+                const int64_t off = row * int64_t(H) + int64_t(c) * VEC;
+                load_vec<T>(x + off, a[j]);
+                if (residual != nullptr) {
+                    float r[VEC];
+                    load_vec<T>(residual + off, r);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) a[j][i] = rounded<T>(__fadd_rn(rounded<T>(__fmul_rn(a[j][i], multiplier)), r[i]));
+                    if (added != nullptr) store_vec<T>(added + off, a[j]);
+                }
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) ss = fmaf(a[j][i], a[j][i], ss);
+            }
+        }
+        ss = group_sum<G>(ss, red);
+        const float r = rsqrtf(ss * inv_h + eps);
+        if (inv_rms != nullptr && t == 0) inv_rms[row] = r;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = j * G + t;
+            if (c < nvec) {
+                float y[VEC];
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) y[i] = a[j][i] * r * w[j][i];
+                store_vec<T>(out + row * int64_t(H) + int64_t(c) * VEC, y);
+            }
+        }
+    }
+}
+
+// any width / alignment: one block per row, the row is read twice (the second read hits L2)
+template <typename T>
+__global__ void __launch_bounds__(kNormBlock)
+    rmsnorm_fwd_generic_kernel(const T *__restrict__ x, const T *__restrict__ residual, const T *__restrict__ weight,
+                               T *__restrict__ out, T *__restrict__ added, float *__restrict__ inv_rms, int64_t rows, int64_t H,
+                               float eps, float multiplier) {
+    __shared__ float red[kNormBlock / 32];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T *xr = x + row * H;
+        const T *rr = residual ? residual + row * H : nullptr;
+        T *ar = (added && residual) ? added + row * H : nullptr;
+        float ss = 0.0f;
+        for (int64_t c = threadIdx.x; c < H; c += kNormBlock) {
+            float a = DT<T>::up(xr[c]);
+            if (rr) a = rounded<T>(__fadd_rn(rounded<T>(__fmul_rn(a, multiplier)), DT<T>::up(rr[c])));
+            if (ar) ar[c] = DT<T>::down(a);
+            ss = fmaf(a, a, ss);
+        }
+        ss = group_sum<kNormBlock>(ss, red);
+        const float r = rsqrtf(ss / float(H) + eps);
+        if (inv_rms && threadIdx.x == 0) inv_rms[row] = r;
+        for (int64_t c = threadIdx.x; c < H; c += kNormBlock) {
+            float a = DT<T>::up(xr[c]);
+            if (rr) a = rounded<T>(__fadd_rn(rounded<T>(__fmul_rn(a, multiplier)), DT<T>::up(rr[c])));
+            const float wv = weight ? DT<T>::up(weight[c]) : 1.0f;
+            out[row * H + c] = DT<T>::down(a * r * wv);
+        }
+    }
+}
+
+// ---- backward ------------------------------------------------------------------------------------------
+template <typename T, int G, int VPT>
+__global__ void __launch_bounds__(kNormBlock)
+    rmsnorm_bwd_kernel(const T *__restrict__ a_in, const T *__restrict__ weight, const T *__restrict__ dy, const T *__restrict__ d_added,
+                       const float *__restrict__ inv_rms, T *__restrict__ dx, T *__restrict__ d_residual, float *__restrict__ d_weight,
+                       int64_t rows, int H, float eps, float multiplier) {
+    constexpr int VEC = Vec16<T>::N;
+    __shared__ float red[kNormBlock / 32];
+    const int t = threadIdx.x % G;
+    const int rows_per_block = kNormBlock / G;
+    const int nvec = H / VEC;
+    float w[VPT][VEC], dw[VPT][VEC];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int c = j * G + t;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) { w[j][i] = 1.0f; dw[j][i] = 0.0f; }
+        if (weight != nullptr && c < nvec) load_vec<T>(weight + int64_t(c) * VEC, w[j]);
+    }
+    const float inv_h = 1.0f / float(H);
+    for (int64_t row = int64_t(blockIdx.x) * rows_per_block + threadIdx.x / G; row < rows; row += int64_t(gridDim.x) * rows_per_block) {
+        float a[VPT][VEC], g[VPT][VEC];
+        float ss = 0.0f, dot = 0.0f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = j * G + t;
+            if (c < nvec) {
+                const int64_t off = row * int64_t(H) + int64_t(c) * VEC;
+                load_vec<T>(a_in + off, a[j]);
+                load_vec<T>(dy + off, g[j]);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    ss = fmaf(a[j][i], a[j][i], ss);
+                    dot = fmaf(g[j][i] * w[j][i], a[j][i], dot);
+                }
+            }
+        }
+        float r;
+        if (inv_rms != nullptr) {
+            r = inv_rms[row];
+        } else {
+            ss = group_sum<G>(ss, red);
+            r = rsqrtf(ss * inv_h + eps);
+        }
+        dot = group_sum<G>(dot, red);
+        const float coef = dot * inv_h * r * r * r;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = j * G + t;
+            if (c < nvec) {
+                const int64_t off = row * int64_t(H) + int64_t(c) * VEC;
+                float da[VEC];
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    da[i] = r * g[j][i] * w[j][i] - coef * a[j][i];
+                    dw[j][i] = fmaf(g[j][i], a[j][i] * r, dw[j][i]);
+                }
+                if (d_added != nullptr) {
+                    float e[VEC];
+                    load_vec<T>(d_added + off, e);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) da[i] += e[i];
+                }
+                if (d_residual != nullptr) store_vec<T>(d_residual + off, da);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) da[i] *= multiplier;
+                store_vec<T>(dx + off, da);
+            }
+        }
+    }
+    if (d_weight != nullptr) {
+        if constexpr (G == 32) {
+            // the warps of a block hold different rows over the same columns: add them up in shared memory first
+            __shared__ float acc[VPT * 32 * VEC];
+            for (int i = threadIdx.x; i < VPT * 32 * VEC; i += kNormBlock) acc[i] = 0.0f;
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < VPT; ++j)
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) atomicAdd(&acc[(j * 32 + t) * VEC + i], dw[j][i]);
+            __syncthreads();
+            for (int i = threadIdx.x; i < VPT * 32 * VEC; i += kNormBlock)
+                if (i < H) atomicAdd(d_weight + i, acc[i]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const int c = j * G + t;
+                if (c < nvec) {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) atomicAdd(d_weight + int64_t(c) * VEC + i, dw[j][i]);
+                }
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNormBlock)
+    rmsnorm_bwd_generic_kernel(const T *__restrict__ a_in, const T *__restrict__ weight, const T *__restrict__ dy,
+                               const T *__restrict__ d_added, const float *__restrict__ inv_rms, T *__restrict__ dx,
+                               T *__restrict__ d_residual, float *__restrict__ d_weight, int64_t rows, int64_t H, float eps,
+                               float multiplier) {
+    __shared__ float red[kNormBlock / 32];
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const T *ar = a_in + row * H;
+        const T *gr = dy + row * H;
+        float ss = 0.0f, dot = 0.0f;
+        for (int64_t c = threadIdx.x; c < H; c += kNormBlock) {
+            const float a = DT<T>::up(ar[c]);
+            const float wv = weight ? DT<T>::up(weight[c]) : 1.0f;
+            ss = fmaf(a, a, ss);
+            dot = fmaf(DT<T>::up(gr[c]) * wv, a, dot);
+        }
+        float r;
+        if (inv_rms) {
+            r = inv_rms[row];
+        } else {
+            ss = group_sum<kNormBlock>(ss, red);
+            r = rsqrtf(ss / float(H) + eps);
+        }
+        dot = group_sum<kNormBlock>(dot, red);
+        const float coef = dot / float(H) * r * r * r;
+        for (int64_t c = threadIdx.x; c < H; c += kNormBlock) {
+            const float a = DT<T>::up(ar[c]);
+            const float g = DT<T>::up(gr[c]);
+            const float wv = weight ? DT<T>::up(weight[c]) : 1.0f;
+            float da = r * g * wv - coef * a;
+            if (d_added) da += DT<T>::up(d_added[row * H + c]);
+            if (d_residual) d_residual[row * H + c] = DT<T>::down(da);
+            dx[row * H + c] = DT<T>::down(da * multiplier);
+            if (d_weight) atomicAdd(d_weight + c, g * (a * r));
+        }
+    }
+}
+
+// ---- launch --------------------------------------------------------------------------------------------
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static unsigned norm_grid(int64_t row_groups, int blocks_per_sm) {
+    int64_t g = row_groups;
+    const int64_t cap = int64_t(num_sms()) * blocks_per_sm;
+    if (g > cap) g = cap;
+    if (g < 1) g = 1;
+    return unsigned(g);
+}
+
+template <typename T, int G, int VPT>
+static void launch_fwd(const void *x, const void *res, const void *w, void *out, void *added, float *inv, int64_t rows, int H,
+                       float eps, float mult, cudaStream_t s) {
+    const int rpb = kNormBlock / G;
+    rmsnorm_fwd_kernel<T, G, VPT><<<norm_grid(ceil_div64(rows, rpb), 8), kNormBlock, 0, s>>>(
+        (const T *)x, (const T *)res, (const T *)w, (T *)out, (T *)added, inv, rows, H, eps, mult);
+}
+template <typename T, int G, int VPT>
+static void launch_bwd(const void *a, const void *w, const void *dy, const void *dadd, const float *inv, void *dx, void *dres,
+                       float *dw, int64_t rows, int H, float eps, float mult, cudaStream_t s) {
+    const int rpb = kNormBlock / G;
+    // fewer blocks when a weight gradient is accumulated: every block ends with one atomic per column
+    rmsnorm_bwd_kernel<T, G, VPT><<<norm_grid(ceil_div64(rows, rpb), dw ? 4 : 8), kNormBlock, 0, s>>>(
+        (const T *)a, (const T *)w, (const T *)dy, (const T *)dadd, inv, (T *)dx, (T *)dres, dw, rows, H, eps, mult);
+}
+
+// picks (G, VPT) for a row of nvec 16-byte vectors; false: use the generic kernels
+#define CK_NORM_DISPATCH(T, nvec, CALL_W, CALL_B)                      \
+    if ((nvec) <= 32) { CALL_W(T, 32, 1); }                            \
+    else if ((nvec) <= 64) { CALL_W(T, 32, 2); }                       \
+    else if ((nvec) <= 128) { CALL_W(T, 32, 4); }                      \
+    else if ((nvec) <= 256) { CALL_B(T, kNormBlock, 1); }              \
+    else if ((nvec) <= 512) { CALL_B(T, kNormBlock, 2); }              \
+    else if ((nvec) <= 1024) { CALL_B(T, kNormBlock, 4); }             \
+    else { CALL_B(T, kNormBlock, 8); }
+
+template <typename T>
+static int rmsnorm_fwd_t(const void *x, const void *res, const void *w, void *out, void *added, float *inv, int64_t rows, int64_t H,
+                         float eps, float mult, cudaStream_t s) {
+    constexpr int VEC = Vec16<T>::N;
+    const bool vec_ok = H % VEC == 0 && H / VEC <= 2048 && aligned16(x) && aligned16(out) && (!res || aligned16(res)) &&
+                        (!w || aligned16(w)) && (!added || aligned16(added));
+    if (vec_ok) {
+        const int nvec = int(H / VEC);
+#define FWD_CALL(TT, GG, VV) launch_fwd<TT, GG, VV>(x, res, w, out, added, inv, rows, int(H), eps, mult, s)
+        CK_NORM_DISPATCH(T, nvec, FWD_CALL, FWD_CALL)
+#undef FWD_CALL
+    } else {
+        rmsnorm_fwd_generic_kernel<T><<<norm_grid(rows, 8), kNormBlock, 0, s>>>((const T *)x, (const T *)res, (const T *)w, (T *)out,
+                                                                                 (T *)added, inv, rows, H, eps, mult);
+    }
+    CK_LAUNCH_CHECK("rmsnorm_fwd_kernel");
+    return CK_OK;
+}
+
+template <typename T>
+static int rmsnorm_bwd_t(const void *a, const void *w, const void *dy, const void *dadd, const float *inv, void *dx, void *dres,
+                         float *dw, int64_t rows, int64_t H, float eps, float mult, cudaStream_t s) {
+    constexpr int VEC = Vec16<T>::N;
+    const bool vec_ok = H % VEC == 0 && H / VEC <= 1024 && aligned16(a) && aligned16(dy) && aligned16(dx) && (!w || aligned16(w)) &&
+                        (!dadd || aligned16(dadd)) && (!dres || aligned16(dres));
+    if (vec_ok) {
+        const int nvec = int(H / VEC);
+#define BWD_CALL(TT, GG, VV) launch_bwd<TT, GG, VV>(a, w, dy, dadd, inv, dx, dres, dw, rows, int(H), eps, mult, s)
+        CK_NORM_DISPATCH(T, nvec, BWD_CALL, BWD_CALL)
+#undef BWD_CALL
+    } else {
+        rmsnorm_bwd_generic_kernel<T><<<norm_grid(rows, dw ? 4 : 8), kNormBlock, 0, s>>>(
+            (const T *)a, (const T *)w, (const T *)dy, (const T *)dadd, inv, (T *)dx, (T *)dres, dw, rows, H, eps, mult);
+    }
+    CK_LAUNCH_CHECK("rmsnorm_bwd_kernel");
+    return CK_OK;
+}
+
+}  // namespace ck
+
+using namespace ck;
+
+extern "C" int ck_rmsnorm_fwd(const void *x, const void *residual, const void *weight, void *out, void *added_out,
+                              float *inv_rms_out, int64_t rows, int64_t H, float eps, float multiplier, int dtype,
+                              void *stream) {
+    if (rows < 0 || H <= 0 || H > INT32_MAX) return CK_ERR_SHAPE;
+    if (rows == 0) return CK_OK;
+    if (!x || !out) return CK_ERR_SHAPE;
+    if (added_out && !residual) return CK_ERR_SHAPE;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (dtype) {
+        case CK_F32: return rmsnorm_fwd_t<float>(x, residual, weight, out, added_out, inv_rms_out, rows, H, eps, multiplier, s);
+        case CK_F16: return rmsnorm_fwd_t<__half>(x, residual, weight, out, added_out, inv_rms_out, rows, H, eps, multiplier, s);
+        case CK_BF16: return rmsnorm_fwd_t<__nv_bfloat16>(x, residual, weight, out, added_out, inv_rms_out, rows, H, eps, multiplier, s);
+        default: return CK_ERR_UNSUPPORTED;
+    }
+}
+
+extern "C" int ck_rmsnorm_bwd(const void *a, const void *weight, const void *dy, const void *d_added, const float *inv_rms,
+                              void *dx, void *d_residual, float *d_weight, int64_t rows, int64_t H, float eps, float multiplier,
+                              int dtype, void *stream) {
+    if (rows < 0 || H <= 0 || H > INT32_MAX) return CK_ERR_SHAPE;
+    if (rows == 0) return CK_OK;
+    if (!a || !dy || !dx) return CK_ERR_SHAPE;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (dtype) {
+        case CK_F32: return rmsnorm_bwd_t<float>(a, weight, dy, d_added, inv_rms, dx, d_residual, d_weight, rows, H, eps, multiplier, s);
+        case CK_F16: return rmsnorm_bwd_t<__half>(a, weight, dy, d_added, inv_rms, dx, d_residual, d_weight, rows, H, eps, multiplier, s);
+        case CK_BF16: return rmsnorm_bwd_t<__nv_bfloat16>(a, weight, dy, d_added, inv_rms, dx, d_residual, d_weight, rows, H, eps, multiplier, s);
+        default: return CK_ERR_UNSUPPORTED;
+    }
+}

@@ -13,6 +13,18 @@ constexpr int kRouterMaxExperts = 256;
 constexpr int kRouterMaxK = 32;
 constexpr int kRouterThreads = 256;
 
+// Total order on the logits: the key of a float grows with its value, every NaN maps to the largest key (torch.topk
+// treats NaN as the greatest value) and -0.0 equals +0.0.  With (key, expert) compared lexicographically every lane of a
+// butterfly reduction arrives at the same winner, whatever the row holds.
+__device__ __forceinline__ uint32_t order_key(float v) {
+    if (v != v) return 0xffffffffu;
+    const uint32_t b = __float_as_uint(v + 0.0f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kRouterThreads)
     router_topk_softmax_kernel(const T *__restrict__ logits, T *__restrict__ weights, int32_t *__restrict__ ids,
@@ -21,46 +33,52 @@ __global__ void __launch_bounds__(kRouterThreads)
     const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
     constexpr int kPerLane = kRouterMaxExperts / 32;
+    constexpr int kNone = 0x7fffffff;
     for (int64_t t = warp; t < tokens; t += nwarps) {
-        float v[kPerLane];
+        uint32_t key[kPerLane];
 #pragma unroll
         for (int i = 0; i < kPerLane; ++i) {
             const int e = lane + 32 * i;
-            v[i] = e < E ? DT<T>::up(logits[t * E + e]) : -INFINITY;
+            key[i] = e < E ? order_key(DT<T>::up(logits[t * E + e])) : 0u;  // real keys are >= 0x007fffff (-inf)
         }
         float my_val = 0.0f;  // lane j keeps the j-th winner
         int my_idx = 0;
         float vmax = 0.0f;
         unsigned taken = 0u;  // bit i: this lane's i-th logit is already among the winners
         for (int j = 0; j < k; ++j) {
-            float best = -INFINITY;
-            int best_e = 0x7fffffff;
+            uint32_t best = 0u;
+            int best_e = kNone;
 #pragma unroll
             for (int i = 0; i < kPerLane; ++i) {
                 const int e = lane + 32 * i;
-                // the first candidate not yet taken is accepted whatever its value: masked (-inf) logits still give k distinct experts
-                if (e < E && !((taken >> i) & 1u) && (best_e == 0x7fffffff || v[i] > best)) {
-                    best = v[i];
+                // any candidate not yet taken beats "none": masked (-inf) and NaN logits still give k distinct experts
+                if (e < E && !((taken >> i) & 1u) && key[i] > best) {
+                    best = key[i];
                     best_e = e;
                 }
             }
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, d);
+                const uint32_t ob = __shfl_xor_sync(0xffffffffu, best, d);
                 const int oe = __shfl_xor_sync(0xffffffffu, best_e, d);
                 if (ob > best || (ob == best && oe < best_e)) {
                     best = ob;
                     best_e = oe;
                 }
             }
-            if (j == 0) vmax = best;
+            // one winner for the whole warp, whatever the lanes computed
+            best = __shfl_sync(0xffffffffu, best, 0);
+            best_e = __shfl_sync(0xffffffffu, best_e, 0);
+            const float best_v = key_value(best);
+            if (j == 0) vmax = best_v;
             if (lane == j) {
-                my_val = best;
-                my_idx = best_e;
+                my_val = best_v;
+                my_idx = best_e != kNone ? best_e : 0;  // k <= E, so a candidate always exists; never emit an id outside [0, E)
             }
-            if (best_e != 0x7fffffff && (best_e & 31) == lane) taken |= 1u << (best_e >> 5);  // the owner retires the winner
+            if (best_e != kNone && (best_e & 31) == lane) taken |= 1u << (best_e >> 5);  // the owner retires the winner
         }
-        // softmax over the k selected logits in fp32 (k <= 32: one per lane)
+        // softmax over the k selected logits in fp32 (k <= 32: one per lane); -inf - -inf and NaN rows give NaN weights
+        // as torch.softmax does
         const float ex = lane < k ? expf(my_val - vmax) : 0.0f;
         float sum = ex;
 #pragma unroll
@@ -76,7 +94,8 @@ __global__ void __launch_bounds__(kRouterThreads)
 template <typename T>
 __global__ void __launch_bounds__(kRouterThreads)
     router_topk_softmax_bwd_kernel(const T *__restrict__ weights, const T *__restrict__ d_weights,
-                                   const int32_t *__restrict__ ids, T *__restrict__ d_logits, int64_t tokens, int E, int k) {
+                                   const int32_t *__restrict__ ids, T *__restrict__ d_logits, int64_t tokens, int E, int k,
+                                   int32_t *__restrict__ dev_status) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
@@ -88,7 +107,11 @@ __global__ void __launch_bounds__(kRouterThreads)
         for (int d = 16; d > 0; d >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);
         for (int e = lane; e < E; e += 32) d_logits[t * E + e] = DT<T>::down(0.0f);
         __syncwarp();
-        if (lane < k) d_logits[t * E + ids[t * k + lane]] = DT<T>::down(w * (dw - dot));
+        if (lane < k) {
+            const int32_t e = ids[t * k + lane];
+            if (e >= 0 && e < E) d_logits[t * E + e] = DT<T>::down(w * (dw - dot));
+            else if (dev_status) atomicOr(dev_status, CK_DEV_RANGE);  // an id outside [0, E) is skipped, never written through
+        }
     }
 }
 
@@ -122,16 +145,16 @@ extern "C" int ck_router_topk_softmax(const void *logits, void *weights, int32_t
 }
 
 extern "C" int ck_router_topk_softmax_bwd(const void *weights, const void *d_weights, const int32_t *ids, void *d_logits,
-                                          int64_t tokens, int E, int k, int dtype, void *stream_) {
+                                          int64_t tokens, int E, int k, int dtype, int32_t *dev_status, void *stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (tokens < 0 || E <= 0 || k <= 0 || k > E) return CK_ERR_SHAPE;
     if (k > kRouterMaxK) return CK_ERR_RANGE;
     if (tokens == 0) return CK_OK;
     if (!weights || !d_weights || !ids || !d_logits) return CK_ERR_SHAPE;
     switch (dtype) {
-        case CK_F32: router_topk_softmax_bwd_kernel<float><<<router_grid(tokens), kRouterThreads, 0, stream>>>((const float *)weights, (const float *)d_weights, ids, (float *)d_logits, tokens, E, k); break;
-        case CK_F16: router_topk_softmax_bwd_kernel<__half><<<router_grid(tokens), kRouterThreads, 0, stream>>>((const __half *)weights, (const __half *)d_weights, ids, (__half *)d_logits, tokens, E, k); break;
-        case CK_BF16: router_topk_softmax_bwd_kernel<__nv_bfloat16><<<router_grid(tokens), kRouterThreads, 0, stream>>>((const __nv_bfloat16 *)weights, (const __nv_bfloat16 *)d_weights, ids, (__nv_bfloat16 *)d_logits, tokens, E, k); break;
+        case CK_F32: router_topk_softmax_bwd_kernel<float><<<router_grid(tokens), kRouterThreads, 0, stream>>>((const float *)weights, (const float *)d_weights, ids, (float *)d_logits, tokens, E, k, dev_status); break;
+        case CK_F16: router_topk_softmax_bwd_kernel<__half><<<router_grid(tokens), kRouterThreads, 0, stream>>>((const __half *)weights, (const __half *)d_weights, ids, (__half *)d_logits, tokens, E, k, dev_status); break;
+        case CK_BF16: router_topk_softmax_bwd_kernel<__nv_bfloat16><<<router_grid(tokens), kRouterThreads, 0, stream>>>((const __nv_bfloat16 *)weights, (const __nv_bfloat16 *)d_weights, ids, (__nv_bfloat16 *)d_logits, tokens, E, k, dev_status); break;
         default: return CK_ERR_UNSUPPORTED;
     }
     CK_LAUNCH_CHECK("router_topk_softmax_bwd_kernel");

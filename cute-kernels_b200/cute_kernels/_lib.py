@@ -17,7 +17,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("CK_LIB_PATH") or os.path.join(_HERE, "libck_b200.so")
 
 CK_F32, CK_F16, CK_BF16 = 0, 1, 2
-CK_ACT_SWIGLU, CK_ACT_GLU = 0, 1
+CK_ACT_SWIGLU, CK_ACT_GLU, CK_ACT_GELU_TANH = 0, 1, 2
 CK_DEV_RANGE, CK_DEV_TIMEOUT, CK_DEV_META = 1, 2, 4
 CK_TILE_M = 128
 CK_COUNT_MAX_SIZE = 16384
@@ -40,26 +40,36 @@ PROTOTYPES = {
     "ck_swiglu_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i, _vp]),
     "ck_moe_gather_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i64, _i, _vp]),
     "ck_cast_from_f32": (_i, [_vp, _vp, _i64, _i, _vp]),
-    "ck_moe_up_act_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
-    "ck_moe_up_act_fwd_gather": (_i, [_vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
-    "ck_moe_down_combine_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
-    "ck_moe_dgrad_down": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
-    "ck_moe_dgrad_down_gather": (_i, [_vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_up_act_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_up_act_fwd_gather": (_i, [_vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_up_act_fwd_gather_peer": (_i, [_vp, _i, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_down_combine_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_dgrad_down": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_dgrad_down_parts": (_i, [_i]),
+    "ck_moe_reduce_dgates": (_i, [_vp, _i, _i64, _vp, _vp, _i, _vp, _vp]),
+    "ck_moe_dgrad_down_gather": (_i, [_vp, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_dgrad_down_gather_peer": (_i, [_vp, _i, _i64, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_moe_wgrad_gather": (_i, [_vp, _i64, _i, _vp, _i64, _i, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _vp, _vp]),
     "ck_moe_dgrad_up": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_moe_wgrad": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _vp, _vp]),
     "ck_moe_grouped_linear": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_set_gemm_cta_pair": (_i, [_i]),
-    "ck_moe_grouped_linear_scatter": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_gemm_cta_pair": (_i, []),
+    "ck_moe_grouped_linear_scatter": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
+    "ck_moe_bias_grad": (_i, [_vp, _i64, _i, _vp, _vp, _vp, _i, _vp, _i, _vp]),
+    "ck_moe_bias_dots": (_i, [_vp, _i64, _i, _vp, _vp, _i, _vp, _i, _vp]),
     "ck_moe_gather_rows_scaled": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i, _vp]),
     "ck_moe_combine_rows": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i, _vp]),
     "ck_moe_row_dots": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i, _vp]),
+    "ck_rmsnorm_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, ctypes.c_float, _i, _vp]),
+    "ck_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, ctypes.c_float, _i, _vp]),
     "ck_router_topk_softmax": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
-    "ck_router_topk_softmax_bwd": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
+    "ck_router_topk_softmax_bwd": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp]),
     "ck_moe_gather_rows_peer": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _i, _i64, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "ck_moe_grouped_linear_scatter_peer": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_peer_gather_scalars": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _vp]),
     "ck_peer_scatter_scalars": (_i, [_vp, _vp, _i64, _i, _vp, _i, _i64, _i, _vp, _vp]),
+    "ck_test_wait_timeout": (_i, [_i64, _vp, _vp, _vp]),
 }
 
 
@@ -102,6 +112,30 @@ def require_cuda(*tensors: torch.Tensor) -> None:
     for t in tensors:
         if t is not None and not t.is_cuda:
             raise RuntimeError("cute_kernels (B200) ops take CUDA tensors only; there is no CPU path")
+
+
+_trace_depth = 0
+
+
+class tracing:
+    """``with tracing():`` -- every op of this package goes through its opaque ``torch.library`` custom op inside the
+    block, whatever ``torch.compiler.is_compiling()`` says (a compiler backend that re-traces a captured graph with
+    fake tensors, as CuteInductor does when it hands the rewritten graph to inductor, is not "compiling" for dynamo)."""
+
+    def __enter__(self):
+        global _trace_depth
+        _trace_depth += 1
+        return self
+
+    def __exit__(self, *exc):
+        global _trace_depth
+        _trace_depth -= 1
+        return False
+
+
+def use_custom_op() -> bool:
+    """True when a call must be recorded as an opaque custom op instead of launching the kernel right away."""
+    return _trace_depth > 0 or torch.compiler.is_compiling()
 
 
 def stream_ptr() -> int:

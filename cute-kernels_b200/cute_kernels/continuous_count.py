@@ -38,5 +38,5 @@ def continuous_count_cute(x: torch.Tensor, size: int) -> torch.Tensor:
 
     x = x.contiguous()
     output = torch.empty(size, dtype=torch.uint32, device=x.device)
-    (_continuous_count_op if torch.compiler.is_compiling() else _continuous_count_impl)(x, output, size)
+    (_continuous_count_op if _lib.use_custom_op() else _continuous_count_impl)(x, output, size)
     return output

@@ -1,10 +1,13 @@
 """CuteInductor: a torch.compile backend that rewrites FX patterns into this package's kernels.
 
 Same constructor and ``compiler(gm, example_inputs)`` entry as the reference
-(cute_kernels/cute_inductor/compiler.py:18-47).  One rewrite is provided: a ``chunk(2, dim=-1)`` whose
-halves feed ``silu`` and ``mul`` becomes one ``swiglu_packed_cute`` call on the un-chunked tensor
-(cute_kernels/cute_inductor/swiglu_packed.py:16-76; the reference version calls an undefined name when
-the pattern matches, this one inserts the real function).
+(cute_kernels/cute_inductor/compiler.py:18-47), and its two rewrites:
+
+* ``replace_swiglu_unchunked``: a ``chunk(2, dim=-1)`` whose halves feed ``silu`` and ``mul`` becomes one
+  ``swiglu_packed_cute`` call on the un-chunked tensor (cute_kernels/cute_inductor/swiglu_packed.py:16-76; the
+  reference version calls an undefined name when the pattern matches, this one inserts the real function);
+* ``replace_rmsnorm``: ``torch.rms_norm(input, normalized_shape, weight, eps)`` becomes
+  ``rmsnorm_cute(x, weight, eps)`` (cute_kernels/cute_inductor/rmsnorm.py:13-35).
 """
 
 from __future__ import annotations
@@ -19,6 +22,8 @@ from torch._dynamo import lookup_backend
 from torch.fx import Node
 from torch.fx.graph_module import GraphModule
 
+from . import _lib
+from .rmsnorm import rmsnorm_cute
 from .swiglu import swiglu_packed_cute
 
 _DEBUG_CUTEINDUCTOR = os.environ.get("DEBUG_CUTEINDUCTOR", "0").lower() in ("1", "true")
@@ -76,11 +81,29 @@ def replace_swiglu_unchunked(gm: GraphModule, node: Node) -> None:
     gm.recompile()
 
 
+def replace_rmsnorm(gm: GraphModule, node: Node) -> None:
+    """``rms_norm`` over the last dimension -> ``rmsnorm_cute``.  Arguments may arrive positionally or by keyword
+    (``input``, ``normalized_shape``, ``weight``, ``eps``); a normalized_shape of more than one dimension is left alone."""
+    if not (node.op == "call_function" and node.target in (torch.rms_norm, F.rms_norm)):
+        return
+    names = ("input", "normalized_shape", "weight", "eps")
+    bound = dict(zip(names, node.args))
+    bound.update(node.kwargs)
+    shape = bound.get("normalized_shape")
+    if "input" not in bound or shape is None or len(shape) != 1:
+        return
+    with gm.graph.inserting_after(node):
+        new_node = gm.graph.call_function(rmsnorm_cute, args=(bound["input"], bound.get("weight"), bound.get("eps")))
+    node.replace_all_uses_with(new_node)
+    gm.graph.erase_node(node)
+    gm.recompile()
+
+
 class CuteInductor:
     def __init__(self, use_torch_inductor_after_cute_inductor: bool = True,
                  replace_functions: list[Callable] | None = None) -> None:
         self.use_torch_inductor_after_cute_inductor = use_torch_inductor_after_cute_inductor
-        self.replace_functions = [replace_swiglu_unchunked] if replace_functions is None else replace_functions
+        self.replace_functions = [replace_rmsnorm, replace_swiglu_unchunked] if replace_functions is None else replace_functions
 
     def compiler(self, gm: GraphModule, example_inputs: list[torch.Tensor]) -> Callable:
         if _DEBUG_CUTEINDUCTOR:
@@ -93,5 +116,8 @@ class CuteInductor:
             print("graph after cute inductor")
             gm.print_readable()
         if self.use_torch_inductor_after_cute_inductor:
-            return lookup_backend("inductor")(gm, example_inputs)
+            # inductor re-traces the rewritten graph with fake tensors: the kernels must appear as opaque custom ops
+            # (the reference wraps this call in enable_cute_tracing(), cute_inductor/compiler.py:28)
+            with _lib.tracing():
+                return lookup_backend("inductor")(gm, example_inputs)
         return gm.forward

@@ -194,13 +194,7 @@ class ExpertParallelMoE:
         dev = x.device
         flat_ids = selected_experts.reshape(-1)
         sorted_idx32, counts = self.route_fn(flat_ids, self.num_experts)
-        sorted_idx = sorted_idx32.long()
         on_gpu = dev.type == "cuda"
-        if on_gpu:  # inverse permutation: position of flat slot (t*k + j) in the sorted order
-            pos32 = torch.empty_like(sorted_idx32)
-            pos32[sorted_idx] = torch.arange(sorted_idx32.numel(), device=dev, dtype=torch.int32)
-        else:
-            tok = sorted_idx // k
 
         # per-(destination rank, local expert) counts -> what every source sends us
         send_counts = counts.to(torch.int64).view(G, epr)
@@ -214,6 +208,17 @@ class ExpertParallelMoE:
         both = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).cpu()  # the one host sync of the layer
         in_splits, out_splits = both[0].tolist(), both[1].tolist()
         n_recv = sum(out_splits)
+        # An id outside [0, num_experts) is skipped by the routing pass and leaves the tail of sorted_idx unwritten:
+        # refuse before anything indexes with it.
+        if sum(in_splits) != flat_ids.numel():
+            raise RuntimeError(f"{flat_ids.numel() - sum(in_splits)} expert ids outside [0, {self.num_experts}) reached "
+                               "the expert-parallel layer")
+        sorted_idx = sorted_idx32.long()
+        if on_gpu:  # inverse permutation: position of flat slot (t*k + j) in the sorted order
+            pos32 = torch.empty_like(sorted_idx32)
+            pos32[sorted_idx] = torch.arange(sorted_idx32.numel(), device=dev, dtype=torch.int32)
+        else:
+            tok = sorted_idx // k
 
         rows = _GatherSortedCuda.apply(x, sorted_idx32, pos32, k) if on_gpu else _GatherSorted.apply(x, tok)
         recv = _AllToAllRows.apply(rows, in_splits, out_splits, self.group)

@@ -11,9 +11,10 @@ kernels/scattermoe/triton_implementation/__init__.py:39-103); the expert computa
   backward  gather grad rows -> dgrad(down) fused with activation backward and the router-weight
             grad -> wgrad(down) -> dgrad(up) fused with the k-way sum -> wgrad(up)
 
-A gated activation that is SwiGLU (``swiglu_packed_*``) or ``torch.nn.GLU`` and no bias takes this
-fused path.  Any other activation callable (or ``add_bias=True``) runs the same grouped GEMM kernels
-un-fused, with the permutations expressed as torch indexing so autograd differentiates them.
+SwiGLU (``swiglu_packed_*``), ``torch.nn.GLU`` and -- un-gated -- ``torch.nn.GELU(approximate="tanh")`` take this
+fused path, with or without biases (``add_bias=True``: the biases are added in the GEMM epilogues, their gradients are
+column sums over each expert's rows).  Any other activation callable runs the same grouped GEMM kernels un-fused, with
+the permutations expressed as torch indexing so autograd differentiates them.
 """
 
 from __future__ import annotations
@@ -36,7 +37,7 @@ def _make_op(name: str, impl: Callable, mutates: set[str]) -> Callable:
     op = torch.library.custom_op(f"cute_kernels_b200::{name}", impl, mutates_args=mutates)
 
     def call(*args):
-        return (op if torch.compiler.is_compiling() else impl)(*args)
+        return (op if _lib.use_custom_op() else impl)(*args)
 
     call.__name__ = name
     return call
@@ -60,71 +61,103 @@ def _cast_from_f32_impl(src: torch.Tensor, dst: torch.Tensor) -> None:
     _lib.check(st, "ck_cast_from_f32")
 
 
-def _up_act_fwd_impl(xg: torch.Tensor, wfc: torch.Tensor, gate_w: torch.Tensor | None, row_map: torch.Tensor,
-                     mtile_off: torch.Tensor, act: torch.Tensor, h: torch.Tensor | None, act_kind: int) -> None:
+def _up_act_fwd_impl(xg: torch.Tensor, wfc: torch.Tensor, b_fc: torch.Tensor | None, gate_w: torch.Tensor | None,
+                     row_map: torch.Tensor, mtile_off: torch.Tensor, act: torch.Tensor, h: torch.Tensor | None,
+                     act_kind: int) -> None:
+    """``wfc`` is [E, 2I, H] for the gated activations and [E, I, H] for CK_ACT_GELU_TANH; ``act`` is [cap, I]."""
     _lib.require_cuda(xg, wfc, act)
     status = _lib.status_word(xg.device)
-    E, two_i, H = wfc.shape
-    with torch.cuda.device(xg.device), _lib.launch("up_act_fwd", 1, 2.0 * xg.size(0) * two_i * H):
-        st = _lib.lib.ck_moe_up_act_fwd(xg.data_ptr(), wfc.data_ptr(), _lib.ptr(gate_w), row_map.data_ptr(),
+    E, n_out, H = wfc.shape
+    with torch.cuda.device(xg.device), _lib.launch("up_act_fwd", 1, 2.0 * xg.size(0) * n_out * H):
+        st = _lib.lib.ck_moe_up_act_fwd(xg.data_ptr(), wfc.data_ptr(), _lib.ptr(b_fc), _lib.ptr(gate_w), row_map.data_ptr(),
                                         mtile_off.data_ptr(), act.data_ptr(), _lib.ptr(h), E, xg.size(0), H,
-                                        two_i // 2, act_kind, _lib.dtype_code(xg.dtype), status.data_ptr(),
+                                        act.size(1), act_kind, _lib.dtype_code(xg.dtype), status.data_ptr(),
                                         _lib.stream_ptr())
     _lib.check(st, "ck_moe_up_act_fwd")
 
 
-def _up_act_fwd_gather_impl(x: torch.Tensor, top_k: int, wfc: torch.Tensor, gate_w: torch.Tensor | None,
-                            row_map: torch.Tensor, mtile_off: torch.Tensor, act: torch.Tensor, h: torch.Tensor | None,
-                            act_kind: int) -> None:
+def _up_act_fwd_gather_impl(x: torch.Tensor, top_k: int, wfc: torch.Tensor, b_fc: torch.Tensor | None,
+                            gate_w: torch.Tensor | None, row_map: torch.Tensor, mtile_off: torch.Tensor, act: torch.Tensor,
+                            h: torch.Tensor | None, xg_out: torch.Tensor | None, act_kind: int) -> None:
+    """Up projection reading the routed rows of ``x`` by row index inside the GEMM; ``xg_out`` [cap, H] (optional)
+    receives the grouped copy of those rows as a by-product."""
     _lib.require_cuda(x, wfc, act)
     status = _lib.status_word(x.device)
-    E, two_i, H = wfc.shape
-    with torch.cuda.device(x.device), _lib.launch("up_act_fwd", 1, 2.0 * act.size(0) * two_i * H):
-        st = _lib.lib.ck_moe_up_act_fwd_gather(x.data_ptr(), x.size(0), top_k, wfc.data_ptr(), _lib.ptr(gate_w),
-                                               row_map.data_ptr(), mtile_off.data_ptr(), act.data_ptr(), _lib.ptr(h), E,
-                                               act.size(0), H, two_i // 2, act_kind, _lib.dtype_code(x.dtype),
-                                               status.data_ptr(), _lib.stream_ptr())
+    E, n_out, H = wfc.shape
+    with torch.cuda.device(x.device), _lib.launch("up_act_fwd", 1, 2.0 * act.size(0) * n_out * H):
+        st = _lib.lib.ck_moe_up_act_fwd_gather(x.data_ptr(), x.size(0), top_k, wfc.data_ptr(), _lib.ptr(b_fc), _lib.ptr(gate_w),
+                                               row_map.data_ptr(), mtile_off.data_ptr(), act.data_ptr(), _lib.ptr(h),
+                                               _lib.ptr(xg_out), E, act.size(0), H, act.size(1), act_kind,
+                                               _lib.dtype_code(x.dtype), status.data_ptr(), _lib.stream_ptr())
     _lib.check(st, "ck_moe_up_act_fwd_gather")
 
 
-def _down_combine_fwd_impl(act: torch.Tensor, wproj: torch.Tensor, row_map: torch.Tensor, mtile_off: torch.Tensor,
-                           out32: torch.Tensor, top_k: int) -> None:
+def _down_combine_fwd_impl(act: torch.Tensor, wproj: torch.Tensor, b_proj: torch.Tensor | None, gate_w: torch.Tensor | None,
+                           row_map: torch.Tensor, mtile_off: torch.Tensor, out32: torch.Tensor, top_k: int) -> None:
     _lib.require_cuda(act, wproj, out32)
     status = _lib.status_word(act.device)
     E, H, I = wproj.shape
     with torch.cuda.device(act.device), _lib.launch("down_combine_fwd", 1, 2.0 * act.size(0) * H * I):
-        st = _lib.lib.ck_moe_down_combine_fwd(act.data_ptr(), wproj.data_ptr(), row_map.data_ptr(),
-                                              mtile_off.data_ptr(), out32.data_ptr(), E, act.size(0), H, I, top_k,
-                                              _lib.dtype_code(act.dtype), status.data_ptr(), _lib.stream_ptr())
+        st = _lib.lib.ck_moe_down_combine_fwd(act.data_ptr(), wproj.data_ptr(), _lib.ptr(b_proj), _lib.ptr(gate_w),
+                                              row_map.data_ptr(), mtile_off.data_ptr(), out32.data_ptr(), E, act.size(0), H,
+                                              I, top_k, _lib.dtype_code(act.dtype), status.data_ptr(), _lib.stream_ptr())
     _lib.check(st, "ck_moe_down_combine_fwd")
 
 
 def _dgrad_down_impl(dyg: torch.Tensor, wproj: torch.Tensor, h: torch.Tensor, gate_w: torch.Tensor | None,
                      row_map: torch.Tensor, mtile_off: torch.Tensor, dh: torch.Tensor, dgates: torch.Tensor | None,
-                     act_kind: int) -> None:
-    _lib.require_cuda(dyg, wproj, h, dh, dgates)
+                     dgates_part: torch.Tensor | None, act_kind: int) -> None:
+    _lib.require_cuda(dyg, wproj, h, dh, dgates, dgates_part)
     status = _lib.status_word(dyg.device)
     E, H, I = wproj.shape
     with torch.cuda.device(dyg.device), _lib.launch("dgrad_down", 1, 2.0 * dyg.size(0) * H * I):
         st = _lib.lib.ck_moe_dgrad_down(dyg.data_ptr(), wproj.data_ptr(), h.data_ptr(), _lib.ptr(gate_w),
-                                        row_map.data_ptr(), mtile_off.data_ptr(), dh.data_ptr(), _lib.ptr(dgates), E,
-                                        dyg.size(0), H, I, act_kind, _lib.dtype_code(dyg.dtype), status.data_ptr(),
-                                        _lib.stream_ptr())
+                                        row_map.data_ptr(), mtile_off.data_ptr(), dh.data_ptr(), _lib.ptr(dgates),
+                                        _lib.ptr(dgates_part), E, dyg.size(0), H, I, act_kind,
+                                        _lib.dtype_code(dyg.dtype), status.data_ptr(), _lib.stream_ptr())
     _lib.check(st, "ck_moe_dgrad_down")
 
 
 def _dgrad_down_gather_impl(dy: torch.Tensor, top_k: int, wproj: torch.Tensor, h: torch.Tensor,
                             gate_w: torch.Tensor | None, row_map: torch.Tensor, mtile_off: torch.Tensor, dh: torch.Tensor,
-                            dgates: torch.Tensor | None, act_kind: int) -> None:
-    _lib.require_cuda(dy, wproj, h, dh, dgates)
+                            dgates: torch.Tensor | None, dgates_part: torch.Tensor | None, dyg_out: torch.Tensor | None,
+                            act_kind: int) -> None:
+    _lib.require_cuda(dy, wproj, h, dh, dgates, dgates_part)
     status = _lib.status_word(dy.device)
     E, H, I = wproj.shape
     with torch.cuda.device(dy.device), _lib.launch("dgrad_down", 1, 2.0 * dh.size(0) * H * I):
         st = _lib.lib.ck_moe_dgrad_down_gather(dy.data_ptr(), dy.size(0), top_k, wproj.data_ptr(), h.data_ptr(),
                                                _lib.ptr(gate_w), row_map.data_ptr(), mtile_off.data_ptr(), dh.data_ptr(),
-                                               _lib.ptr(dgates), E, dh.size(0), H, I, act_kind,
-                                               _lib.dtype_code(dy.dtype), status.data_ptr(), _lib.stream_ptr())
+                                               _lib.ptr(dgates), _lib.ptr(dgates_part), _lib.ptr(dyg_out), E, dh.size(0), H,
+                                               I, act_kind, _lib.dtype_code(dy.dtype), status.data_ptr(),
+                                               _lib.stream_ptr())
     _lib.check(st, "ck_moe_dgrad_down_gather")
+
+
+def _reduce_dgates_impl(dgates_part: torch.Tensor, row_map: torch.Tensor, padded_off: torch.Tensor, num_experts: int,
+                        dgates: torch.Tensor) -> None:
+    """dgates[row_map[p]] = sum of the parts of padded row p, added in part order (reproducible), for the padded rows
+    of the first ``num_experts`` experts (those the GEMM ran over)."""
+    _lib.require_cuda(dgates_part, row_map, dgates)
+    with torch.cuda.device(dgates.device), _lib.launch("reduce_dgates"):
+        st = _lib.lib.ck_moe_reduce_dgates(dgates_part.data_ptr(), dgates_part.size(0), dgates_part.size(1),
+                                           row_map.data_ptr(), padded_off.data_ptr(), num_experts,
+                                           dgates.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_reduce_dgates")
+
+
+@torch.compiler.assume_constant_result
+def cta_pair_kernels() -> bool:
+    """True when the grouped GEMMs run as CTA pairs (the default), False for the single-CTA flavour.  A process-level
+    setting: under torch.compile its value at trace time is baked into the graph."""
+    return bool(_lib.lib.ck_gemm_cta_pair())
+
+
+def dgates_parts(intermediate_size: int) -> int:
+    """Rows of the partial router-weight-grad buffer ``[parts, cap]`` that dgrad_down fills
+    (ck_moe_dgrad_down_parts: one part per 256-column n-tile, two with the CTA-pair kernels' two epilogue groups)."""
+    n_tiles = (intermediate_size + 255) // 256
+    return 2 * n_tiles if cta_pair_kernels() else n_tiles
 
 
 def _wgrad_gather_impl(a: torch.Tensor, a_fan: int, b: torch.Tensor, b_fan: int, row_map: torch.Tensor,
@@ -178,18 +211,39 @@ def _grouped_linear_impl(x: torch.Tensor, w: torch.Tensor, mtile_off: torch.Tens
     _lib.check(st, "ck_moe_grouped_linear")
 
 
-def _grouped_linear_scatter_impl(x: torch.Tensor, w: torch.Tensor, mtile_off: torch.Tensor, row_map: torch.Tensor,
-                                 y: torch.Tensor, trans_w: bool) -> None:
+def _grouped_linear_scatter_impl(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, gate_w: torch.Tensor | None,
+                                 mtile_off: torch.Tensor, row_map: torch.Tensor, y: torch.Tensor, trans_w: bool) -> None:
     _lib.require_cuda(x, w, y)
     status = _lib.status_word(x.device)
     E = w.size(0)
     N, K = (w.size(2), w.size(1)) if trans_w else (w.size(1), w.size(2))
     assert x.size(1) == K and y.size(1) == N
     with torch.cuda.device(x.device), _lib.launch("grouped_linear_scatter", 1, 2.0 * x.size(0) * N * K):
-        st = _lib.lib.ck_moe_grouped_linear_scatter(x.data_ptr(), w.data_ptr(), mtile_off.data_ptr(), row_map.data_ptr(),
-                                                    y.data_ptr(), E, x.size(0), N, K, int(trans_w),
-                                                    _lib.dtype_code(x.dtype), status.data_ptr(), _lib.stream_ptr())
+        st = _lib.lib.ck_moe_grouped_linear_scatter(x.data_ptr(), w.data_ptr(), _lib.ptr(bias), _lib.ptr(gate_w),
+                                                    mtile_off.data_ptr(), row_map.data_ptr(), y.data_ptr(), E, x.size(0), N, K,
+                                                    int(trans_w), _lib.dtype_code(x.dtype), status.data_ptr(),
+                                                    _lib.stream_ptr())
     _lib.check(st, "ck_moe_grouped_linear_scatter")
+
+
+def _bias_grad_impl(rows: torch.Tensor, row_map: torch.Tensor | None, gate_w: torch.Tensor | None, padded_off: torch.Tensor,
+                    out: torch.Tensor) -> None:
+    """out[e, :] = sum over expert e's padded rows of (gate_w[row_map[p]] or 1) * rows[p, :]."""
+    _lib.require_cuda(rows, padded_off, out)
+    with torch.cuda.device(rows.device), _lib.launch("bias_grad"):
+        st = _lib.lib.ck_moe_bias_grad(rows.data_ptr(), rows.size(0), rows.size(1), _lib.ptr(row_map), _lib.ptr(gate_w),
+                                       padded_off.data_ptr(), out.size(0), out.data_ptr(), _lib.dtype_code(rows.dtype),
+                                       _lib.stream_ptr())
+    _lib.check(st, "ck_moe_bias_grad")
+
+
+def _bias_dots_impl(rows: torch.Tensor, bias: torch.Tensor, padded_off: torch.Tensor, part: torch.Tensor) -> None:
+    """part[p] = rows[p, :] . bias[expert of p, :] (fp32, one more part of the router-weight-grad buffer)."""
+    _lib.require_cuda(rows, bias, padded_off, part)
+    with torch.cuda.device(rows.device), _lib.launch("bias_dots"):
+        st = _lib.lib.ck_moe_bias_dots(rows.data_ptr(), rows.size(0), rows.size(1), bias.data_ptr(), padded_off.data_ptr(),
+                                       bias.size(0), part.data_ptr(), _lib.dtype_code(rows.dtype), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_bias_dots")
 
 
 def _gather_rows_scaled_impl(src: torch.Tensor, dst: torch.Tensor, idx: torch.Tensor, coeff: torch.Tensor | None,
@@ -221,15 +275,18 @@ def _row_dots_impl(a: torch.Tensor, pos: torch.Tensor, b: torch.Tensor, dots: to
 gather_rows = _make_op("moe_gather_rows", _gather_rows_impl, {"dst"})
 cast_from_f32 = _make_op("cast_from_f32", _cast_from_f32_impl, {"dst"})
 up_act_fwd = _make_op("moe_up_act_fwd", _up_act_fwd_impl, {"act", "h"})
-up_act_fwd_gather = _make_op("moe_up_act_fwd_gather", _up_act_fwd_gather_impl, {"act", "h"})
+up_act_fwd_gather = _make_op("moe_up_act_fwd_gather", _up_act_fwd_gather_impl, {"act", "h", "xg_out"})
 down_combine_fwd = _make_op("moe_down_combine_fwd", _down_combine_fwd_impl, {"out32"})
-dgrad_down = _make_op("moe_dgrad_down", _dgrad_down_impl, {"dh", "dgates"})
-dgrad_down_gather = _make_op("moe_dgrad_down_gather", _dgrad_down_gather_impl, {"dh", "dgates"})
+dgrad_down = _make_op("moe_dgrad_down", _dgrad_down_impl, {"dh", "dgates", "dgates_part"})
+dgrad_down_gather = _make_op("moe_dgrad_down_gather", _dgrad_down_gather_impl, {"dh", "dgates", "dgates_part", "dyg_out"})
+reduce_dgates = _make_op("moe_reduce_dgates", _reduce_dgates_impl, {"dgates"})
 wgrad_gather = _make_op("moe_wgrad_gather", _wgrad_gather_impl, {"dw"})
 dgrad_up = _make_op("moe_dgrad_up", _dgrad_up_impl, {"dx32"})
 wgrad = _make_op("moe_wgrad", _wgrad_impl, {"dw"})
 grouped_linear = _make_op("moe_grouped_linear", _grouped_linear_impl, {"y"})
 grouped_linear_scatter = _make_op("moe_grouped_linear_scatter", _grouped_linear_scatter_impl, {"y"})
+bias_grad = _make_op("moe_bias_grad", _bias_grad_impl, {"out"})
+bias_dots = _make_op("moe_bias_dots", _bias_dots_impl, {"part"})
 gather_rows_scaled = _make_op("moe_gather_rows_scaled", _gather_rows_scaled_impl, {"dst"})
 combine_rows = _make_op("moe_combine_rows", _combine_rows_impl, {"out"})
 row_dots = _make_op("moe_row_dots", _row_dots_impl, {"dots"})
@@ -246,92 +303,151 @@ def _from_f32(src32: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------------
 # fused expert computation
 # ---------------------------------------------------------------------------------------------------
-# Route the permutations through TMA gather4 inside the GEMMs (no grouped copies of x / dy) instead of the
-# streaming gather kernel.  Measured on B200 (Mixtral-shaped layer, bf16): the gathered operand is fetched 512
-# bytes per TMA operation (four 128-byte swizzle rows), and the up projection drops from 1180 to 446 TFLOP/s, wgrad
-# from 1220 to 293; the separate gather costs 0.14 ms per use.  So this stays off unless CK_TMA_GATHER=1.
+# How the routed rows of x (forward) and of grad_out (backward) reach the GEMMs.
+#   "producer" (default with the CTA-pair kernels): the up projection and dgrad-down read the rows by row index with
+#              their own producer warps (cp.async into the swizzled stages) and write the grouped copy out as a
+#              by-product for the weight-gradient GEMMs; no separate permutation kernel runs.
+#   "kernel"   a streaming gather kernel builds the grouped copies first (the only choice with the single-CTA kernels
+#              when weight gradients are needed).
+#   "tma"      no grouped copies at all: the weight-gradient GEMMs gather their operand with TMA gather4 as well.
+#              Measured on B200 (Mixtral-shaped layer, bf16): gather4 moves 512 bytes per TMA operation and wgrad drops
+#              from 1220 to 293 TFLOP/s, so this stays a tested alternative (CK_TMA_GATHER=1 selects it).
 import os as _os
 
 TMA_GATHER = _os.environ.get("CK_TMA_GATHER", "0") == "1"
+GATHER_MODE = _os.environ.get("CK_GATHER_MODE", "")
+
+
+def _gather_mode() -> str:
+    if TMA_GATHER:
+        return "tma"
+    if GATHER_MODE in ("producer", "kernel", "tma"):
+        return GATHER_MODE
+    return "producer" if cta_pair_kernels() else "kernel"
+
 
 class _FusedExperts(torch.autograd.Function):
-    """y[t] = sum_j w[t, j] * W_proj[e_tj] @ act(W_fc[e_tj] @ x[t]) with saved-for-backward tensors in the
-    padded grouped layout.  Mirrors _ScatteredExperts (ops.py:143-292) for c_fc + activation + c_proj at once."""
+    """y[t] = sum_j w[t, j] * (W_proj[e_tj] @ act(W_fc[e_tj] @ x[t] + b_fc[e_tj]) + b_proj[e_tj]) with saved-for-backward
+    tensors in the padded grouped layout.  Mirrors _ScatteredExperts (ops.py:143-292) for c_fc + activation + c_proj at
+    once, with the biases of Experts_Torch (torch_implementation.py:41-44) folded into the GEMM epilogues.
+
+    ``act_kind``: CK_ACT_SWIGLU / CK_ACT_GLU (w_fc [E, 2I, H], packed [up | gate]) or CK_ACT_GELU_TANH (w_fc [E, I, H]).
+    ``deterministic``: the k rows of every token are stored un-combined ([T*k, H], each written once) and summed in a
+    fixed order by a second kernel, instead of fp32 ``red.add`` into one [T, H] buffer from the GEMM epilogue (whose
+    order of additions varies from run to run when k > 2)."""
 
     @staticmethod
-    def forward(ctx, x, router_weights, w_fc, w_proj, row_map, mtile_off, padded_off, top_k: int, act_kind: int):
+    def forward(ctx, x, router_weights, w_fc, w_proj, b_fc, b_proj, row_map, mtile_off, padded_off, top_k: int,
+                act_kind: int, deterministic: bool = False):
         T, H = x.shape
-        E, two_i, _ = w_fc.shape
-        I = two_i // 2
+        E, n_fc, _ = w_fc.shape
+        I = w_proj.size(2)
         cap = row_map.numel()
         dev, dt = x.device, x.dtype
-        need_grad = any(ctx.needs_input_grad[:4])
+        need_grad = any(ctx.needs_input_grad[:6])
+        need_xg = ctx.needs_input_grad[2]  # the weight gradient of the up projection contracts over the grouped rows
+        mode = _gather_mode()
 
         x = x.contiguous()
         gate_w = router_weights.contiguous().view(-1)
         act = torch.empty(cap, I, dtype=dt, device=dev)
-        h = torch.empty(cap, two_i, dtype=dt, device=dev) if need_grad else None
-        if TMA_GATHER:
-            # the up projection gathers the routed token rows itself (TMA gather4); the grouped copy of x is
-            # only built in backward, where the weight gradient contracts over it
-            xg = None
-            up_act_fwd_gather(x, top_k, w_fc, gate_w, row_map, mtile_off, act, h, act_kind)
-        else:
+        h = torch.empty(cap, n_fc, dtype=dt, device=dev) if need_grad else None
+        xg = None
+        if mode == "kernel":
             xg = torch.empty(cap, H, dtype=dt, device=dev)
             gather_rows(x, xg, row_map, padded_off, top_k)
-            up_act_fwd(xg, w_fc, gate_w, row_map, mtile_off, act, h, act_kind)
-        out32 = torch.zeros(T, H, dtype=torch.float32, device=dev)
-        down_combine_fwd(act, w_proj, row_map, mtile_off, out32, top_k)
-        y = _from_f32(out32, dt)
+            up_act_fwd(xg, w_fc, b_fc, gate_w, row_map, mtile_off, act, h, act_kind)
+        else:
+            if mode == "producer" and need_xg:
+                xg = torch.empty(cap, H, dtype=dt, device=dev)
+            up_act_fwd_gather(x, top_k, w_fc, b_fc, gate_w, row_map, mtile_off, act, h, xg, act_kind)
+        if deterministic:
+            rows = torch.empty(T * top_k, H, dtype=dt, device=dev)
+            grouped_linear_scatter(act, w_proj, b_proj, gate_w if b_proj is not None else None, mtile_off, row_map, rows, False)
+            y = torch.empty(T, H, dtype=dt, device=dev)
+            combine_rows(rows, None, None, y, top_k)
+        else:
+            out32 = torch.zeros(T, H, dtype=torch.float32, device=dev)
+            down_combine_fwd(act, w_proj, b_proj, gate_w if b_proj is not None else None, row_map, mtile_off, out32, top_k)
+            y = _from_f32(out32, dt)
 
         if need_grad:
-            ctx.save_for_backward(x if xg is None else xg, act, h, gate_w, w_fc, w_proj, row_map, mtile_off, padded_off)
-        ctx.x_is_grouped = xg is not None
+            ctx.save_for_backward(x, xg, act, h, gate_w, w_fc, w_proj, b_proj, row_map, mtile_off, padded_off)
+        ctx.mode = mode
         ctx.top_k = top_k
         ctx.act_kind = act_kind
-        ctx.tokens = T
+        ctx.deterministic = deterministic
+        ctx.has_b_fc = b_fc is not None
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        xg, act, h, gate_w, w_fc, w_proj, row_map, mtile_off, padded_off = ctx.saved_tensors
-        top_k, act_kind, T = ctx.top_k, ctx.act_kind, ctx.tokens
-        E, two_i, H = w_fc.shape
+        x, xg, act, h, gate_w, w_fc, w_proj, b_proj, row_map, mtile_off, padded_off = ctx.saved_tensors
+        top_k, act_kind, mode = ctx.top_k, ctx.act_kind, ctx.mode
+        T = x.size(0)
+        E, n_fc, H = w_fc.shape
+        I = w_proj.size(2)
         cap = row_map.numel()
-        dev, dt = dy.device, xg.dtype
-        need_x, need_rw, need_wfc, need_wproj = ctx.needs_input_grad[:4]
+        dev, dt = dy.device, x.dtype
+        need_x, need_rw, need_wfc, need_wproj, need_bfc, need_bproj = ctx.needs_input_grad[:6]
+        need_bfc = need_bfc and ctx.has_b_fc
+        need_bproj = need_bproj and b_proj is not None
 
         dy = dy.contiguous().to(dt)
-        dh = torch.empty(cap, two_i, dtype=dt, device=dev)
-        dgates = torch.zeros(T * top_k, dtype=torch.float32, device=dev)
-        d_wproj = d_wfc = dx = d_rw = None
-        if not ctx.x_is_grouped:
-            # every permutation is done by TMA gather inside the GEMMs: no grouped copies of x or dy exist
-            x = xg
-            dgrad_down_gather(dy, top_k, w_proj, h, gate_w, row_map, mtile_off, dh, dgates, act_kind)
-            if need_wproj:
-                d_wproj = torch.empty_like(w_proj)
-                wgrad_gather(dy, top_k, act, 0, row_map, padded_off, d_wproj)
-            if need_wfc:
-                d_wfc = torch.empty_like(w_fc)
-                wgrad_gather(dh, 0, x, top_k, row_map, padded_off, d_wfc)
-        else:
+        dh = torch.empty(cap, n_fc, dtype=dt, device=dev)
+        # router-weight grads: per-(n-tile, epilogue group) partial sums (+ one part for the bias term), added in a fixed
+        # order afterwards
+        parts = dgates_parts(I)
+        dg_part = torch.empty(parts + (1 if b_proj is not None else 0), cap, dtype=torch.float32, device=dev) if need_rw else None
+        d_wproj = d_wfc = dx = d_rw = d_bfc = d_bproj = None
+        dyg = None
+        need_dyg = need_wproj or need_bproj or (need_rw and b_proj is not None)
+        if mode == "kernel":
             dyg = torch.empty(cap, H, dtype=dt, device=dev)
             gather_rows(dy, dyg, row_map, padded_off, top_k)
-            dgrad_down(dyg, w_proj, h, gate_w, row_map, mtile_off, dh, dgates, act_kind)
-            if need_wproj:
-                d_wproj = torch.empty_like(w_proj)
+            dgrad_down(dyg, w_proj, h, gate_w, row_map, mtile_off, dh, None, dg_part, act_kind)
+        else:
+            if mode == "producer" and need_dyg:
+                dyg = torch.empty(cap, H, dtype=dt, device=dev)
+            dgrad_down_gather(dy, top_k, w_proj, h, gate_w, row_map, mtile_off, dh, None, dg_part, dyg, act_kind)
+        if dyg is None and (need_bproj or (need_rw and b_proj is not None)):
+            dyg = torch.empty(cap, H, dtype=dt, device=dev)  # "tma" mode with a bias: the bias kernels read grouped rows
+            gather_rows(dy, dyg, row_map, padded_off, top_k)
+        if need_wproj:
+            d_wproj = torch.empty_like(w_proj)
+            if dyg is not None:
                 wgrad(dyg, act, padded_off, d_wproj)
-            if need_wfc:
-                d_wfc = torch.empty_like(w_fc)
+            else:
+                wgrad_gather(dy, top_k, act, 0, row_map, padded_off, d_wproj)
+        if need_wfc:
+            d_wfc = torch.empty_like(w_fc)
+            if xg is not None:
                 wgrad(dh, xg, padded_off, d_wfc)
+            else:
+                wgrad_gather(dh, 0, x, top_k, row_map, padded_off, d_wfc)
+        if need_bfc:
+            d_bfc = torch.empty(E, n_fc, dtype=dt, device=dev)
+            bias_grad(dh, None, None, padded_off, d_bfc)
+        if need_bproj:
+            d_bproj = torch.empty(E, H, dtype=dt, device=dev)
+            bias_grad(dyg, row_map, gate_w, padded_off, d_bproj)
         if need_x:
-            dx32 = torch.zeros(T, H, dtype=torch.float32, device=dev)
-            dgrad_up(dh, w_fc, row_map, mtile_off, dx32, top_k)
-            dx = _from_f32(dx32, dt)
+            if ctx.deterministic:
+                rows = torch.empty(T * top_k, H, dtype=dt, device=dev)
+                grouped_linear_scatter(dh, w_fc, None, None, mtile_off, row_map, rows, True)
+                dx = torch.empty(T, H, dtype=dt, device=dev)
+                combine_rows(rows, None, None, dx, top_k)
+            else:
+                dx32 = torch.zeros(T, H, dtype=torch.float32, device=dev)
+                dgrad_up(dh, w_fc, row_map, mtile_off, dx32, top_k)
+                dx = _from_f32(dx32, dt)
         if need_rw:
+            if b_proj is not None:
+                bias_dots(dyg, b_proj, padded_off, dg_part[parts])
+            dgates = torch.zeros(T * top_k, dtype=torch.float32, device=dev)
+            reduce_dgates(dg_part, row_map, padded_off, E, dgates)
             d_rw = dgates.view(T, top_k).to(dt)
-        return dx, d_rw, d_wfc, d_wproj, None, None, None, None, None
+        return dx, d_rw, d_wfc, d_wproj, d_bfc, d_bproj, None, None, None, None, None, None
 
 
 class _ExpertShard(torch.autograd.Function):
@@ -346,13 +462,17 @@ class _ExpertShard(torch.autograd.Function):
         dev, dt = rows.device, rows.dtype
         need_grad = any(ctx.needs_input_grad[:3])
         rows = rows.contiguous()
-        xg = torch.empty(cap, H, dtype=dt, device=dev)
-        gather_rows(rows, xg, row_map, padded_off, 1)
         act = torch.empty(cap, two_i // 2, dtype=dt, device=dev)
         h = torch.empty(cap, two_i, dtype=dt, device=dev) if need_grad else None
-        up_act_fwd(xg, w_fc, None, row_map, mtile_off, act, h, act_kind)
+        producer = _gather_mode() == "producer" and n > 0
+        xg = torch.empty(cap, H, dtype=dt, device=dev) if (need_grad or not producer) else None
+        if producer:
+            up_act_fwd_gather(rows, 1, w_fc, None, None, row_map, mtile_off, act, h, xg, act_kind)
+        else:
+            gather_rows(rows, xg, row_map, padded_off, 1)
+            up_act_fwd(xg, w_fc, None, None, row_map, mtile_off, act, h, act_kind)
         y = torch.empty(n, H, dtype=dt, device=dev)
-        grouped_linear_scatter(act, w_proj, mtile_off, row_map, y, False)
+        grouped_linear_scatter(act, w_proj, None, None, mtile_off, row_map, y, False)
         if need_grad:
             ctx.save_for_backward(xg, act, h, w_fc, w_proj, row_map, mtile_off, padded_off)
         ctx.act_kind = act_kind
@@ -367,16 +487,19 @@ class _ExpertShard(torch.autograd.Function):
         dev, dt = dy.device, xg.dtype
         dy = dy.contiguous().to(dt)
         dyg = torch.empty(cap, H, dtype=dt, device=dev)
-        gather_rows(dy, dyg, row_map, padded_off, 1)
         dh = torch.empty(cap, two_i, dtype=dt, device=dev)
-        dgrad_down(dyg, w_proj, h, None, row_map, mtile_off, dh, None, ctx.act_kind)
+        if _gather_mode() == "producer" and ctx.rows > 0:
+            dgrad_down_gather(dy, 1, w_proj, h, None, row_map, mtile_off, dh, None, None, dyg, ctx.act_kind)
+        else:
+            gather_rows(dy, dyg, row_map, padded_off, 1)
+            dgrad_down(dyg, w_proj, h, None, row_map, mtile_off, dh, None, None, ctx.act_kind)
         d_rows = d_wfc = d_wproj = None
         if ctx.needs_input_grad[2]:
             d_wproj = torch.empty_like(w_proj)
             wgrad(dyg, act, padded_off, d_wproj)
         if ctx.needs_input_grad[0]:
             d_rows = torch.empty(ctx.rows, H, dtype=dt, device=dev)
-            grouped_linear_scatter(dh, w_fc, mtile_off, row_map, d_rows, True)
+            grouped_linear_scatter(dh, w_fc, None, None, mtile_off, row_map, d_rows, True)
         if ctx.needs_input_grad[1]:
             d_wfc = torch.empty_like(w_fc)
             wgrad(dh, xg, padded_off, d_wfc)
@@ -391,15 +514,22 @@ def expert_shard(rows: torch.Tensor, local_expert_ids: torch.Tensor, w_fc: torch
 
 
 def fused_experts(x: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor, w_fc: torch.Tensor,
-                  w_proj: torch.Tensor, top_k: int, act_kind: int = _lib.CK_ACT_SWIGLU) -> torch.Tensor:
+                  w_proj: torch.Tensor, top_k: int, act_kind: int = _lib.CK_ACT_SWIGLU, deterministic: bool = False,
+                  b_fc: torch.Tensor | None = None, b_proj: torch.Tensor | None = None) -> torch.Tensor:
     """Functional form of the fused expert path: x [T, H], router_weights [T, k] (dtype of x),
-    selected_experts [T, k] (int32/int64), w_fc [E, 2I, H] packed [up | gate], w_proj [E, H, I]."""
+    selected_experts [T, k] (int32/int64), w_fc [E, 2I, H] packed [up | gate] (or [E, I, H] with
+    ``act_kind=CK_ACT_GELU_TANH``), w_proj [E, H, I], optional biases b_fc [E, 2I or I] and b_proj [E, H].
+
+    Results are bit-reproducible from run to run for k <= 2 (two fp32 addends per element commute); for k > 2 pass
+    ``deterministic=True`` to sum the k rows of every token in a fixed order (one extra [T*k, H] round trip).
+    Router-weight and bias gradients are always summed in a fixed order."""
     E = w_fc.size(0)
     if x.size(0) == 0:
         return torch.zeros_like(x)
     r = route(selected_experts.reshape(-1), E)
-    return _FusedExperts.apply(x, router_weights, w_fc.contiguous(), w_proj.contiguous(), r.row_map, r.mtile_off,
-                               r.padded_off, top_k, act_kind)
+    return _FusedExperts.apply(x, router_weights, w_fc.contiguous(), w_proj.contiguous(),
+                               None if b_fc is None else b_fc.contiguous(), None if b_proj is None else b_proj.contiguous(),
+                               r.row_map, r.mtile_off, r.padded_off, top_k, act_kind, deterministic)
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -433,15 +563,17 @@ class _GroupedLinear(torch.autograd.Function):
 
 def _act_kind_of(activation_function: Callable, is_glu: bool) -> int | None:
     """Which fused epilogue, if any, implements ``activation_function``."""
-    if not is_glu:
-        return None
     kind = getattr(activation_function, "_ck_act_kind", None)
     if kind is not None:
         return kind
-    if getattr(activation_function, "__name__", "") in ("swiglu_packed_cute", "swiglu_packed_torch"):
-        return _lib.CK_ACT_SWIGLU
-    if isinstance(activation_function, nn.GLU) and activation_function.dim in (-1,):
-        return _lib.CK_ACT_GLU
+    if is_glu:
+        if getattr(activation_function, "__name__", "") in ("swiglu_packed_cute", "swiglu_packed_torch"):
+            return _lib.CK_ACT_SWIGLU
+        if isinstance(activation_function, nn.GLU) and activation_function.dim in (-1,):
+            return _lib.CK_ACT_GLU
+        return None
+    if isinstance(activation_function, nn.GELU) and activation_function.approximate == "tanh":
+        return _lib.CK_ACT_GELU_TANH
     return None
 
 
@@ -487,6 +619,9 @@ class MoE_Cute(nn.Module):
         is_glu: bool,
         add_bias: bool,
         std: float,
+        *,
+        check_status: bool = False,
+        deterministic: bool = False,
     ) -> None:
         super().__init__()
         self.num_experts = num_experts
@@ -500,13 +635,21 @@ class MoE_Cute(nn.Module):
                                  add_bias=add_bias, std=std)
         self.act = activation_function
         self.c_proj = Experts_Cute(num_experts, intermediate_size, hidden_size, add_bias=add_bias, std=std)
-        self._act_kind = _act_kind_of(activation_function, is_glu) if not add_bias else None
+        self._act_kind = _act_kind_of(activation_function, is_glu)
+        # True: every forward ends with one read of the device status word (a stream synchronisation) and raises when
+        # a kernel of the step flagged an out-of-range expert id, a bounded wait that ran out or inconsistent tile
+        # tables.  False (default): no synchronisation; poll cute_kernels.check_device_status() when convenient.
+        self.check_status = check_status
+        # True: the k expert outputs of a token are summed in a fixed order (see fused_experts); matters for k > 2 only
+        self.deterministic = deterministic
 
     def forward(self, hidden_states: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         original_shape = hidden_states.shape
         hidden_states = hidden_states.view(-1, self.hidden_size)
         router_logits, router_weights, selected_experts = self._compute_routing_weights(hidden_states)
         hidden_states = self._compute_experts(hidden_states, router_weights, selected_experts)
+        if self.check_status and hidden_states.is_cuda and not torch.compiler.is_compiling():
+            _lib.check_device_status(hidden_states.device)
         return hidden_states.view(original_shape), router_logits
 
     # the gate projection is a library GEMM; top-k + softmax + int32 ids run as one kernel when the router fits
@@ -529,7 +672,7 @@ class MoE_Cute(nn.Module):
                          selected_experts: torch.Tensor) -> torch.Tensor:
         if self._act_kind is not None:
             return fused_experts(hidden_states, router_weights, selected_experts, self.c_fc.weight, self.c_proj.weight,
-                                 self.top_k, self._act_kind)
+                                 self.top_k, self._act_kind, self.deterministic, self.c_fc.bias, self.c_proj.bias)
         return self._compute_experts_unfused(hidden_states, router_weights, selected_experts)
 
     def _compute_experts_unfused(self, x: torch.Tensor, router_weights: torch.Tensor,

@@ -35,7 +35,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .moe import combine_rows, dgrad_down, up_act_fwd, wgrad
+from .moe import combine_rows, cta_pair_kernels, dgates_parts, dgrad_down, reduce_dgates, up_act_fwd, wgrad
 from .routing import Routing, route
 
 
@@ -64,6 +64,29 @@ def _linear_scatter_peer(x, w, r: Routing, ptrs, S: int, trans_w: bool) -> None:
                                                          len(ptrs), S, E, x.size(0), N, K, int(trans_w),
                                                          _lib.dtype_code(x.dtype), status.data_ptr(), _lib.stream_ptr())
     _lib.check(st, "ck_moe_grouped_linear_scatter_peer")
+
+
+def _up_act_pull_peer(ptrs, S: int, fan_out: int, w_fc, gate_w, r: Routing, act, h, xg_out, act_kind: int) -> None:
+    """Up projection whose producer warps pull the routed rows from their owners (NVLink loads inside the GEMM)."""
+    status = _lib.status_word(act.device)
+    E, two_i, H = w_fc.shape
+    with torch.cuda.device(act.device), _lib.launch("up_act_fwd_peer", 1, 2.0 * act.size(0) * two_i * H):
+        st = _lib.lib.ck_moe_up_act_fwd_gather_peer(_ptr_array(ptrs), len(ptrs), S, fan_out, w_fc.data_ptr(), _lib.ptr(gate_w),
+                                                    r.row_map.data_ptr(), r.mtile_off.data_ptr(), act.data_ptr(), _lib.ptr(h),
+                                                    _lib.ptr(xg_out), E, act.size(0), H, two_i // 2, act_kind,
+                                                    _lib.dtype_code(act.dtype), status.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_up_act_fwd_gather_peer")
+
+
+def _dgrad_down_pull_peer(ptrs, S: int, fan_out: int, w_proj, h, gate_w, r: Routing, dh, dg_part, dyg_out, act_kind: int) -> None:
+    status = _lib.status_word(dh.device)
+    E, H, I = w_proj.shape
+    with torch.cuda.device(dh.device), _lib.launch("dgrad_down_peer", 1, 2.0 * dh.size(0) * H * I):
+        st = _lib.lib.ck_moe_dgrad_down_gather_peer(_ptr_array(ptrs), len(ptrs), S, fan_out, w_proj.data_ptr(), h.data_ptr(),
+                                                    _lib.ptr(gate_w), r.row_map.data_ptr(), r.mtile_off.data_ptr(), dh.data_ptr(),
+                                                    None, _lib.ptr(dg_part), _lib.ptr(dyg_out), E, dh.size(0), H, I, act_kind,
+                                                    _lib.dtype_code(dh.dtype), status.data_ptr(), _lib.stream_ptr())
+    _lib.check(st, "ck_moe_dgrad_down_gather_peer")
 
 
 def _scatter_scalars_peer(vals_by_slot, flat, n: int, ptrs, S: int) -> None:
@@ -194,6 +217,10 @@ class PeerExpertEngine:
         main.wait_event(rest_done)
         gemm(plan.mtile_rest)
 
+    # True (default with the CTA-pair kernels): the GEMMs' own producer warps pull the rows over NVLink, tile by tile,
+    # and leave a local grouped copy behind for the weight gradients.  False: a separate pull kernel runs first.
+    FUSED_PULL = True
+
     def fwd_compute(self, plan: _Plan, weights_all: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor,
                     need_grad: bool):
         """weights_all [world * S]: every rank's published router weights (indexed by global flat slot)."""
@@ -201,10 +228,14 @@ class PeerExpertEngine:
         dev, dt = b.tokens.device, b.tokens.dtype
         H = b.tokens.size(1)
         two_i = w_fc.size(1)
-        xg = torch.empty(plan.cap, H, dtype=dt, device=dev)
         act = torch.empty(plan.cap, two_i // 2, dtype=dt, device=dev)
         h = torch.empty(plan.cap, two_i, dtype=dt, device=dev) if need_grad else None
-        self._pull_then(plan, xg, lambda mt: up_act_fwd(xg, w_fc, weights_all, r.row_map, mt, act, h, self.act_kind))
+        if self.FUSED_PULL and cta_pair_kernels() and not plan.split:
+            xg = torch.empty(plan.cap, H, dtype=dt, device=dev) if need_grad else None
+            _up_act_pull_peer(b.tokens_ptrs, b.slots, b.top_k, w_fc, weights_all, r, act, h, xg, self.act_kind)
+        else:
+            xg = torch.empty(plan.cap, H, dtype=dt, device=dev)
+            self._pull_then(plan, xg, lambda mt: up_act_fwd(xg, w_fc, None, weights_all, r.row_map, mt, act, h, self.act_kind))
         _linear_scatter_peer(act, w_proj, r, b.rows_ptrs, b.slots, False)
         return xg, act, h
 
@@ -222,12 +253,19 @@ class PeerExpertEngine:
     def bwd_compute(self, plan: _Plan, saved, weights_all, w_fc, w_proj, need_wfc: bool, need_wproj: bool, need_x: bool):
         b, r = self.b, plan.routing
         xg, act, h = saved
-        dev, dt = xg.device, xg.dtype
-        dyg = torch.empty(plan.cap, xg.size(1), dtype=dt, device=dev)
+        dev, dt = act.device, act.dtype
+        H = b.tokens.size(1)
+        dyg = torch.empty(plan.cap, H, dtype=dt, device=dev)
         dh = torch.empty(plan.cap, w_fc.size(1), dtype=dt, device=dev)
-        dgates = torch.zeros(b.world * b.slots, dtype=torch.float32, device=dev)  # by global flat slot
-        self._pull_then(plan, dyg,
-                        lambda mt: dgrad_down(dyg, w_proj, h, weights_all, r.row_map, mt, dh, dgates, self.act_kind))
+        # router-weight grads by global flat slot: per-part partial sums, added in a fixed order
+        dg_part = torch.empty(dgates_parts(w_fc.size(1) // 2), plan.cap, dtype=torch.float32, device=dev)
+        if self.FUSED_PULL and cta_pair_kernels() and not plan.split:
+            _dgrad_down_pull_peer(b.tokens_ptrs, b.slots, b.top_k, w_proj, h, weights_all, r, dh, dg_part, dyg, self.act_kind)
+        else:
+            self._pull_then(plan, dyg,
+                            lambda mt: dgrad_down(dyg, w_proj, h, weights_all, r.row_map, mt, dh, None, dg_part, self.act_kind))
+        dgates = torch.zeros(b.world * b.slots, dtype=torch.float32, device=dev)
+        reduce_dgates(dg_part, r.row_map, r.padded_off, self.local_experts, dgates)
         d_wproj = d_wfc = None
         if need_wproj:
             d_wproj = torch.empty_like(w_proj)

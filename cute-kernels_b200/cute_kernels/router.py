@@ -29,10 +29,12 @@ def _fwd_impl(logits: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor, to
 
 def _bwd_impl(weights: torch.Tensor, d_weights: torch.Tensor, ids: torch.Tensor, d_logits: torch.Tensor) -> None:
     _lib.require_cuda(weights, d_weights, ids, d_logits)
+    status = _lib.status_word(weights.device)
     with torch.cuda.device(weights.device), _lib.launch("router_topk_softmax_bwd"):
         st = _lib.lib.ck_router_topk_softmax_bwd(weights.data_ptr(), d_weights.data_ptr(), ids.data_ptr(),
                                                  d_logits.data_ptr(), weights.size(0), d_logits.size(1),
-                                                 weights.size(1), _lib.dtype_code(weights.dtype), _lib.stream_ptr())
+                                                 weights.size(1), _lib.dtype_code(weights.dtype), status.data_ptr(),
+                                                 _lib.stream_ptr())
     _lib.check(st, "ck_router_topk_softmax_bwd")
 
 
@@ -41,7 +43,7 @@ _bwd_op = torch.library.custom_op("cute_kernels_b200::router_topk_softmax_bwd", 
 
 
 def _call(op, impl, *args):
-    return (op if torch.compiler.is_compiling() else impl)(*args)
+    return (op if _lib.use_custom_op() else impl)(*args)
 
 
 class _RouterTopkSoftmax(torch.autograd.Function):

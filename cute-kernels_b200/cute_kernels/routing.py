@@ -112,6 +112,6 @@ def route(ids: torch.Tensor, num_experts: int, *, with_tile_metadata: bool = Tru
     else:
         padded_off = mtile_off = row_map = None
     workspace = torch.empty(route_workspace_bytes(n, num_experts), dtype=torch.uint8, device=dev)
-    fn = _route_op if torch.compiler.is_compiling() else _route_impl
+    fn = _route_op if _lib.use_custom_op() else _route_impl
     fn(ids, num_experts, counts, excl, end, sorted_idx, sorted_expert, padded_off, mtile_off, row_map, workspace)
     return Routing(counts, excl, end, sorted_idx, sorted_expert, padded_off, mtile_off, row_map)

@@ -63,11 +63,11 @@ _swiglu_packed_backward_op = torch.library.custom_op(
 
 
 def _fwd(*args):
-    (_swiglu_forward_op if torch.compiler.is_compiling() else _swiglu_forward_impl)(*args)
+    (_swiglu_forward_op if _lib.use_custom_op() else _swiglu_forward_impl)(*args)
 
 
 def _bwd(*args):
-    (_swiglu_backward_op if torch.compiler.is_compiling() else _swiglu_backward_impl)(*args)
+    (_swiglu_backward_op if _lib.use_custom_op() else _swiglu_backward_impl)(*args)
 
 
 class _Swiglu_Cute(torch.autograd.Function):
@@ -103,7 +103,7 @@ class _SwigluPacked_Cute(torch.autograd.Function):
         cols = divide_if_divisible(x.size(-1), 2)
         output = torch.empty(*x.size()[:-1], cols, device=x.device, dtype=x.dtype)
         rows = x.numel() // (2 * cols) if cols > 0 else 0
-        fn = _swiglu_packed_forward_op if torch.compiler.is_compiling() else _swiglu_packed_forward_impl
+        fn = _swiglu_packed_forward_op if _lib.use_custom_op() else _swiglu_packed_forward_impl
         fn(x, output, rows, cols)
         return output
 
@@ -114,7 +114,7 @@ class _SwigluPacked_Cute(torch.autograd.Function):
         cols = x.size(-1) // 2
         rows = x.numel() // (2 * cols) if cols > 0 else 0
         x_grad = torch.empty_like(x)
-        fn = _swiglu_packed_backward_op if torch.compiler.is_compiling() else _swiglu_packed_backward_impl
+        fn = _swiglu_packed_backward_op if _lib.use_custom_op() else _swiglu_packed_backward_impl
         fn(x, output_grad, x_grad, rows, cols)
         return x_grad
 

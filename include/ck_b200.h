@@ -51,7 +51,10 @@ enum { CK_F32 = 0, CK_F16 = 1, CK_BF16 = 2 };
 /* fused activation of the up projection */
 enum {
     CK_ACT_SWIGLU = 0, /* up * silu(gate)     (swiglu_packed: [up | gate] along the last dim)   */
-    CK_ACT_GLU = 1     /* up * sigmoid(gate)  (torch.nn.GLU on the same packing)                 */
+    CK_ACT_GLU = 1,    /* up * sigmoid(gate)  (torch.nn.GLU on the same packing)                 */
+    CK_ACT_GELU_TANH = 2 /* un-gated: gelu(pre) with the tanh approximation (torch.nn.GELU(approximate="tanh"),
+                          * the reference tests' is_glu=False activation, tests/test_commons.py:85-86): Wfc is
+                          * [E, I, H], and h / dh are [cap, I] instead of [cap, 2I]                           */
 };
 
 #define CK_COUNT_MAX_SIZE 16384 /* same bound as kernels/continuous_count/cuda_implementation/forward.cu:12 */
@@ -105,7 +108,8 @@ CK_API int ck_route(const void *ids, int ids_is_i64, int64_t n, int E, uint32_t 
  * Same outputs, bit for bit, as ck_route.  Limits: ck_route_workspace_bytes(n, E) must not exceed
  * CK_ROUTE_STATIC_SCRATCH_BYTES (any n at E <= 256; n <= 1,212,416 ids at E = 512; n <= 606,208 at E = 1024), otherwise
  * CK_ERR_RANGE and nothing is launched.  The first call on a device looks up the array's device address
- * (make it outside stream capture).  Calls share the array: do not let two of them overlap on one GPU. */
+ * (make it outside stream capture) and keeps it for the life of the process: the cached address does not survive
+ * cudaDeviceReset.  Calls share the array: do not let two of them overlap on one GPU. */
 #define CK_ROUTE_STATIC_SCRATCH_BYTES (256 + 148 * 32 * 32 * 4)
 CK_API int64_t ck_route_static_max_bytes(void);
 CK_API int ck_route_static(const void *ids, int ids_is_i64, int64_t n, int E, uint32_t *counts,
@@ -148,43 +152,60 @@ CK_API int ck_cast_from_f32(const float *src, void *dst, int64_t n, int dtype, v
  * padded rows [128 lo, 128 hi), which lets a caller run one window while another is still being filled.
  * `tmap_cache` is reserved (pass NULL). */
 
-/* up projection + fused activation:  h[p, :] = xg[p, :] @ Wfc[e]^T  ([up | gate], 2I wide),
+/* up projection + fused activation:  h[p, :] = xg[p, :] @ Wfc[e]^T + b_fc[e]  ([up | gate], 2I wide),
  * act[p, :] = w[p] * up * silu(gate), with w[p] = gate_w[row_map[p]] (1 if gate_w is NULL).
- * Wfc: [E, 2I, H] (c_fc.weight).  h may be NULL (inference: gate/up never reach HBM). */
-CK_API int ck_moe_up_act_fwd(const void *xg, const void *wfc, const void *gate_w, const int32_t *row_map,
+ * Wfc: [E, 2I, H] (c_fc.weight); b_fc: [E, 2I] (c_fc.bias, Experts_Torch torch_implementation.py:20-22,41-44) or
+ * NULL.  h may be NULL (inference: gate/up never reach HBM).  With act_kind == CK_ACT_GELU_TANH the layer is un-gated:
+ * Wfc [E, I, H], b_fc [E, I], h[p, :] = the I pre-activations, act = w * gelu(h). */
+CK_API int ck_moe_up_act_fwd(const void *xg, const void *wfc, const void *b_fc, const void *gate_w, const int32_t *row_map,
                       const int32_t *mtile_off, void *act, void *h, int E, int64_t cap, int H, int I,
                       int act_kind, int dtype, int32_t *dev_status, void *stream);
 
-/* the same with the gather fused into the kernel: the A operand is fetched row by row from the un-permuted
- * token matrix x [tokens, H] with TMA gather4 (token of padded row p = row_map[p] / top_k), so the routed
- * rows are never materialised -- scatter2scatter with x_grouped=False (kernels.py:63-66). */
-CK_API int ck_moe_up_act_fwd_gather(const void *x, int64_t tokens, int top_k, const void *wfc, const void *gate_w,
-                                    const int32_t *row_map, const int32_t *mtile_off, void *act, void *h, int E,
-                                    int64_t cap, int H, int I, int act_kind, int dtype, int32_t *dev_status,
-                                    void *stream);
+/* the same with the gather fused into the kernel -- scatter2scatter with x_grouped=False (kernels.py:63-66): the
+ * routed rows are read from the un-permuted token matrix x [tokens, H] (token of padded row p = row_map[p] / top_k)
+ * by the GEMM's own producer and never have to exist as a grouped matrix first.  CTA-pair kernels (the default): two
+ * producer warps per CTA copy 16-byte pieces of the rows into the 128-byte-swizzled stages with cp.async; when
+ * xg_out is not NULL the first n-tile of every m-tile also stores its stages back out as the grouped copy xg_out
+ * [cap, H] (zero pad rows included) that ck_moe_wgrad contracts over later.  Single-CTA kernels
+ * (ck_set_gemm_cta_pair(0)): TMA gather4, xg_out must be NULL (CK_ERR_UNSUPPORTED otherwise). */
+CK_API int ck_moe_up_act_fwd_gather(const void *x, int64_t tokens, int top_k, const void *wfc, const void *b_fc, const void *gate_w,
+                                    const int32_t *row_map, const int32_t *mtile_off, void *act, void *h,
+                                    void *xg_out, int E, int64_t cap, int H, int I, int act_kind, int dtype,
+                                    int32_t *dev_status, void *stream);
 
 /* down projection + fused gather-back and top-k combine:
- * out32[row_map[p] / k, :] += act[p, :] @ Wproj[e]^T   (fp32 red.add into a zeroed [T, H] buffer).
- * Wproj: [E, H, I] (c_proj.weight). */
-CK_API int ck_moe_down_combine_fwd(const void *act, const void *wproj, const int32_t *row_map,
-                            const int32_t *mtile_off, float *out32, int E, int64_t cap, int H, int I,
-                            int top_k, int dtype, int32_t *dev_status, void *stream);
+ * out32[row_map[p] / k, :] += act[p, :] @ Wproj[e]^T + w[p] * b_proj[e]   (fp32 red.add into a zeroed [T, H] buffer).
+ * Wproj: [E, H, I] (c_proj.weight); b_proj: [E, H] (c_proj.bias) or NULL; gate_w as in the up projection (the
+ * activations already carry w[p], the bias term needs it here; NULL: w = 1). */
+CK_API int ck_moe_down_combine_fwd(const void *act, const void *wproj, const void *b_proj, const void *gate_w,
+                            const int32_t *row_map, const int32_t *mtile_off, float *out32, int E, int64_t cap,
+                            int H, int I, int top_k, int dtype, int32_t *dev_status, void *stream);
 
 /* dgrad of the down projection fused with the activation backward and the router-weight grad:
  *   g[p, :]   = dyg[p, :] @ Wproj[e]                      (dyg = gathered, un-weighted grad_out)
- *   dgates[row_map[p]] += sum_n a[p, n] * g[p, n],  a = up * silu(gate) recomputed from h
- *   dh[p, :]  = activation_backward(h[p, :], w[p] * g[p, :])      ([dup | dgate], 2I wide)   */
+ *   dh[p, :]  = activation_backward(h[p, :], w[p] * g[p, :])      ([dup | dgate], 2I wide)
+ *   router-weight grad of row p: sum_n a[p, n] * g[p, n],  a = up * silu(gate) recomputed from h.  Two forms:
+ *     dgates_part != NULL: every (n-tile, epilogue group) stores its partial sum into
+ *       dgates_part[part * cap + p] (fp32 [ck_moe_dgrad_down_parts(I), cap], plain stores, no initialisation
+ *       needed); ck_moe_reduce_dgates then adds the parts in a fixed order into dgates[row_map[p]] -- bit-reproducible;
+ *     dgates_part == NULL: atomicAdd into dgates[row_map[p]] (caller zeroes dgates; summation order varies).
+ *   Both pointers NULL: the router-weight grad is not produced.
+ * (the reference obtains d_gates from a bmm over the saved un-combined expert outputs, ops.py:209-214) */
 CK_API int ck_moe_dgrad_down(const void *dyg, const void *wproj, const void *h, const void *gate_w,
-                      const int32_t *row_map, const int32_t *mtile_off, void *dh, float *dgates, int E,
-                      int64_t cap, int H, int I, int act_kind, int dtype, int32_t *dev_status,
-                      void *stream);
+                      const int32_t *row_map, const int32_t *mtile_off, void *dh, float *dgates,
+                      float *dgates_part, int E, int64_t cap, int H, int I, int act_kind, int dtype,
+                      int32_t *dev_status, void *stream);
+CK_API int ck_moe_dgrad_down_parts(int I);
+CK_API int ck_moe_reduce_dgates(const float *dgates_part, int n_parts, int64_t cap, const int32_t *row_map,
+                                const int32_t *padded_off, int E, float *dgates, void *stream);
 
-/* ck_moe_dgrad_down with the grad rows gathered by TMA from the un-permuted dy [tokens, H]
- * (token of padded row p = row_map[p] / top_k) instead of a pre-gathered dyg. */
+/* ck_moe_dgrad_down with the grad rows read from the un-permuted dy [tokens, H] by the kernel's own producer
+ * (token of padded row p = row_map[p] / top_k) instead of a pre-gathered dyg; dyg_out as xg_out of
+ * ck_moe_up_act_fwd_gather (the grouped copy the weight gradient of the down projection contracts over). */
 CK_API int ck_moe_dgrad_down_gather(const void *dy, int64_t tokens, int top_k, const void *wproj, const void *h,
                                     const void *gate_w, const int32_t *row_map, const int32_t *mtile_off, void *dh,
-                                    float *dgates, int E, int64_t cap, int H, int I, int act_kind, int dtype,
-                                    int32_t *dev_status, void *stream);
+                                    float *dgates, float *dgates_part, void *dyg_out, int E, int64_t cap, int H,
+                                    int I, int act_kind, int dtype, int32_t *dev_status, void *stream);
 
 /* dgrad of the up projection fused with the k-way sum:
  *   dx32[row_map[p] / k, :] += dh[p, :] @ Wfc[e]          (fp32 red.add into a zeroed [T, H])  */
@@ -219,13 +240,26 @@ CK_API int ck_moe_grouped_linear(const void *x, const void *w, const int32_t *mt
  * value comes from the environment variable CK_GEMM_CTA_PAIR.  Takes the place of the reference's per-call
  * cutotune knobs (cute_kernels/cutotune/): there is no runtime search, only this switch. */
 CK_API int ck_set_gemm_cta_pair(int enable);
+CK_API int ck_gemm_cta_pair(void); /* the current setting */
 
-/* same as ck_moe_grouped_linear, but row p of the result is stored at y[row_map[p], :] (pad rows dropped):
+/* same as ck_moe_grouped_linear (plus an optional bias [E, N], scaled by gate_w[row_map[p]] when gate_w is given),
+ * but row p of the result is stored at y[row_map[p], :] (pad rows dropped):
  * scatter2scatter with y_grouped=False and FAN_OUT=1 (ops.py:31-78) -- used by expert-parallel shards, where
  * every routed row is produced exactly once and travels back before the combine. */
-CK_API int ck_moe_grouped_linear_scatter(const void *x, const void *w, const int32_t *mtile_off,
-                                         const int32_t *row_map, void *y, int E, int64_t cap, int N, int K,
-                                         int trans_w, int dtype, int32_t *dev_status, void *stream);
+CK_API int ck_moe_grouped_linear_scatter(const void *x, const void *w, const void *bias, const void *gate_w,
+                                         const int32_t *mtile_off, const int32_t *row_map, void *y, int E, int64_t cap,
+                                         int N, int K, int trans_w, int dtype, int32_t *dev_status, void *stream);
+
+/* Bias gradients of a layer with add_bias=True (autograd of Experts_Torch's F.linear bias, torch_implementation.py:41-44).
+ * ck_moe_bias_grad: out[e, n] = sum over the padded rows p of expert e of s(p) * rows[p, n], s(p) = gate_w[row_map[p]]
+ *   (1 when gate_w is NULL); rows [cap, N], out [E, N] in `dtype`, summed in a fixed order.  d c_fc.bias = this over dh,
+ *   d c_proj.bias = this over the gathered grad rows with the router weights.
+ * ck_moe_bias_dots: part[p] = rows[p, :] . bias[e(p), :] (fp32 [cap]): the bias term of the router-weight gradient,
+ *   laid out like one more part of the dgates_part buffer of ck_moe_dgrad_down. */
+CK_API int ck_moe_bias_grad(const void *rows, int64_t cap, int N, const int32_t *row_map, const void *gate_w,
+                            const int32_t *padded_off, int E, void *out, int dtype, void *stream);
+CK_API int ck_moe_bias_dots(const void *rows, int64_t cap, int N, const void *bias, const int32_t *padded_off, int E,
+                            float *part, int dtype, void *stream);
 
 /* ---- row permutations around the expert-parallel exchange ---------------------------------------
  * ck_moe_gather_rows_scaled: dst[j, :] = c * src[idx[j] / fan_out, :], c = coeff ? coeff[idx[j]] : 1, zeros
@@ -241,6 +275,25 @@ CK_API int ck_moe_combine_rows(const void *src, const int32_t *pos, const void *
 CK_API int ck_moe_row_dots(const void *a, const int32_t *pos, const void *b, void *dots, int64_t n, int k,
                            int64_t cols, int dtype, void *stream);
 
+/* ---- RMSNorm / fused residual-add + RMSNorm ----------------------------------------------------------
+ * Replace rmsnorm_cute and fused_residual_add_rmsnorm_cute (kernels/rmsnorm/__init__.py:12-77,
+ * kernels/fused_residual_add_rmsnorm/__init__.py:15-132: Triton forward / backward kernels) with the math of
+ * rmsnorm_torch / fused_residual_add_rmsnorm_torch (the torch_implementation.py next to each).  Rows of H
+ * contiguous elements, `rows` of them; weight [H] or NULL; all statistics in fp32.
+ * ck_rmsnorm_fwd:  a = residual ? x * multiplier + residual : x  (stored to added_out when given, else not kept);
+ *   r = rsqrt(mean(a^2) + eps), stored to inv_rms_out [rows] fp32 when given; out = a * r * weight.
+ * ck_rmsnorm_bwd:  `a` is what the forward normalised (x, or added_out); g = dy * weight;
+ *   da = r * g - a * r^3 * mean(g * a) (+ d_added when given: the gradient arriving through the residual stream);
+ *   d_residual = da (when given), dx = da * multiplier; d_weight [H] fp32 += sum over rows of dy * a * r (caller
+ *   zeroes it; atomically accumulated).  inv_rms NULL: r is recomputed from `a` (memory_efficient=True upstream).
+ * Pass multiplier = 1 where the reference passes None. */
+CK_API int ck_rmsnorm_fwd(const void *x, const void *residual, const void *weight, void *out, void *added_out,
+                          float *inv_rms_out, int64_t rows, int64_t H, float eps, float multiplier, int dtype,
+                          void *stream);
+CK_API int ck_rmsnorm_bwd(const void *a, const void *weight, const void *dy, const void *d_added, const float *inv_rms,
+                          void *dx, void *d_residual, float *d_weight, int64_t rows, int64_t H, float eps,
+                          float multiplier, int dtype, void *stream);
+
 /* ---- router tail --------------------------------------------------------------------------------
  * ck_router_topk_softmax: for each token, the k largest of its E gate logits (descending; ties to the lower
  *   expert index), weights = softmax over those k logits computed in fp32 and rounded to `dtype`, ids as int32
@@ -248,11 +301,14 @@ CK_API int ck_moe_row_dots(const void *a, const int32_t *pos, const void *b, voi
  *   (kernels/scattermoe/torch_implementation.py:122-135 with _get_topk :195-201), one launch instead of
  *   topk + softmax + type_as, and ids already in the form ck_route reads.  E <= 256, k <= 32 else CK_ERR_RANGE.
  * ck_router_topk_softmax_bwd: d_logits [tokens, E] = scatter of the softmax backward
- *   w_j * (dw_j - sum_i w_i dw_i) at ids, zeros elsewhere (what autograd derives for the same three torch ops). */
+ *   w_j * (dw_j - sum_i w_i dw_i) at ids, zeros elsewhere (what autograd derives for the same three torch ops).
+ *   An id outside [0, E) is skipped and sets CK_DEV_RANGE in *dev_status (may be NULL).
+ * NaN logits count as the greatest value (torch.topk's order), so every row yields k distinct ids in [0, E). */
 CK_API int ck_router_topk_softmax(const void *logits, void *weights, int32_t *ids, int64_t tokens, int E, int k,
                                   int dtype, void *stream);
 CK_API int ck_router_topk_softmax_bwd(const void *weights, const void *d_weights, const int32_t *ids,
-                                      void *d_logits, int64_t tokens, int E, int k, int dtype, void *stream);
+                                      void *d_logits, int64_t tokens, int E, int k, int dtype, int32_t *dev_status,
+                                      void *stream);
 
 /* ---- expert parallelism over peer memory ------------------------------------------------------------
  * No reference counterpart (the reference is single-GPU); per rank these are its `group` (ops.py:108-140) and
@@ -278,6 +334,20 @@ CK_API int ck_moe_gather_rows_peer(const void *const *peer_src, int n_peers, int
                                    const int32_t *row_map, const int32_t *padded_off, const int32_t *src_flat, int E,
                                    int64_t cap, int fan_out, int64_t cols, int64_t row_begin, int64_t row_end,
                                    int dtype, int32_t *dev_status, void *stream);
+/* ck_moe_up_act_fwd_gather / ck_moe_dgrad_down_gather with the rows living on the ranks that own them: padded row p
+ * reads row (g % S) / fan_out of peer_src[g / S], g = row_map[p] a global flat slot (the routing pass ran over all
+ * ranks' slots).  The producer warps of the GEMM issue the NVLink loads (cp.async, 16 bytes per lane) tile by tile
+ * while the tensor cores work on earlier stages; no TMA touches peer memory.  rows_out (xg_out / dyg_out) keeps the
+ * pulled rows on this GPU for the weight-gradient GEMMs, so every row crosses NVLink once.  CTA-pair kernels only. */
+CK_API int ck_moe_up_act_fwd_gather_peer(const void *const *peer_src, int n_peers, int64_t rows_per_peer, int fan_out,
+                                         const void *wfc, const void *gate_w, const int32_t *row_map,
+                                         const int32_t *mtile_off, void *act, void *h, void *xg_out, int E, int64_t cap,
+                                         int H, int I, int act_kind, int dtype, int32_t *dev_status, void *stream);
+CK_API int ck_moe_dgrad_down_gather_peer(const void *const *peer_src, int n_peers, int64_t rows_per_peer, int fan_out,
+                                         const void *wproj, const void *h, const void *gate_w, const int32_t *row_map,
+                                         const int32_t *mtile_off, void *dh, float *dgates, float *dgates_part,
+                                         void *dyg_out, int E, int64_t cap, int H, int I, int act_kind, int dtype,
+                                         int32_t *dev_status, void *stream);
 CK_API int ck_moe_grouped_linear_scatter_peer(const void *x, const void *w, const int32_t *mtile_off,
                                               const int32_t *row_map, const int32_t *dst_flat, void *const *peer_out,
                                               int n_peers, int64_t rows_per_peer, int E, int64_t cap, int N, int K,
@@ -288,6 +358,16 @@ CK_API int ck_peer_gather_scalars(const void *const *peer_src, int n_peers, int6
 CK_API int ck_peer_scatter_scalars(const void *vals, const int32_t *flat, int64_t n, int by_slot,
                                    void *const *peer_dst, int n_peers, int64_t rows_per_peer, int elem_bytes,
                                    int32_t *dev_status, void *stream);
+
+/* ---- self test of the bounded device waits -----------------------------------------------------------
+ * No reference counterpart (the reference's kernels have no device-side waits).  Every mbarrier wait of the grouped
+ * GEMMs polls with a wall-clock limit; when it runs out the CTA sets CK_DEV_TIMEOUT in *dev_status, leaves its
+ * loops, frees TMEM and returns.  ck_test_wait_timeout runs that same wait routine in a one-CTA kernel on a barrier
+ * nobody arrives at, with `limit_ns` (1 .. 100,000,000; else CK_ERR_RANGE) as the limit, so the abort path can be
+ * exercised without a broken pipeline.  result4[0], [1]: what the two waiting lanes returned (0 = gave up),
+ * result4[2]: nanoseconds the first lane waited (saturating), result4[3]: the CTA's abort flag.  The launch ends by
+ * itself after about `limit_ns`; the context stays usable. */
+CK_API int ck_test_wait_timeout(int64_t limit_ns, int32_t *result4, int32_t *dev_status, void *stream);
 
 #ifdef __cplusplus
 }

@@ -79,6 +79,29 @@ def swiglu_backward_ref(gate: torch.Tensor, up: torch.Tensor, dy: torch.Tensor) 
 
 
 # ---------------------------------------------------------------------------------------------------
+# RMSNorm
+# ---------------------------------------------------------------------------------------------------
+def rmsnorm_ref(x: torch.Tensor, weight: torch.Tensor | None, eps: float) -> torch.Tensor:
+    """kernels/rmsnorm/torch_implementation.py:9-10 (F.rms_norm over the last dimension): statistics and scaling in
+    fp32, one rounding to the input dtype at the end."""
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(dim=-1, keepdim=True) + eps)
+    if weight is not None:
+        y = y * weight.float()
+    return y.to(x.dtype)
+
+
+def fused_residual_add_rmsnorm_ref(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor | None, eps: float,
+                                   multiplier: float | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """kernels/fused_residual_add_rmsnorm/torch_implementation.py:9-20: x * multiplier (skipped for None / 1), + residual
+    (each a tensor op in the input dtype), the sum is both the new residual stream and the input of the norm."""
+    if multiplier not in (None, 1):
+        x = x * multiplier
+    x = x + residual
+    return rmsnorm_ref(x, weight, eps), x
+
+
+# ---------------------------------------------------------------------------------------------------
 # MoE expert layer
 # ---------------------------------------------------------------------------------------------------
 def routing_weights_ref(router_logits: torch.Tensor, top_k: int, out_dtype: torch.dtype):

@@ -1,8 +1,10 @@
 """Generates the golden vectors under tests/golden/ by running the REFERENCE's own torch path.
 
 Run in a container that has the reference checkout:
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference
-It imports MoE_Torch, swiglu_torch, swiglu_packed_torch and continuous_count_torch from that checkout,
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference [rmsnorm]
+(a second argument regenerates that fixture file alone)
+It imports MoE_Torch, swiglu_torch, swiglu_packed_torch, continuous_count_torch, rmsnorm_torch and
+fused_residual_add_rmsnorm_torch from that checkout,
 feeds them seeded inputs (the generators of oracle/ck_oracle.py), and stores inputs' seeds and the
 reference outputs as small .npz files.  The fixtures, not the checkout, travel with the repository.
 """
@@ -19,9 +21,10 @@ sys.path.insert(0, os.path.join(ROOT, "oracle"))
 import ck_oracle as orc  # noqa: E402
 
 
-def main(ref_path: str) -> None:
+def main(ref_path: str, only: str | None = None) -> None:
     sys.path.insert(0, ref_path)
-    from cute_kernels import MoE_Torch, continuous_count_torch, swiglu_packed_torch, swiglu_torch
+    from cute_kernels import (MoE_Torch, continuous_count_torch, fused_residual_add_rmsnorm_torch, rmsnorm_torch,
+                              swiglu_packed_torch, swiglu_torch)
 
     torch.manual_seed(0)
 
@@ -36,7 +39,8 @@ def main(ref_path: str) -> None:
         out[f"{name}_sorted_idx"] = srt.indices.numpy().astype(np.int32)
         out[f"{name}_end_off"] = t.long().bincount(minlength=E).cumsum(-1).numpy().astype(np.int32)
         out[f"{name}_meta"] = np.array([n, E, {"uniform": 0, "zipf": 1}[dist], np.dtype(dt).itemsize])
-    np.savez_compressed(os.path.join(HERE, "routing.npz"), **out)
+    if only is None:
+        np.savez_compressed(os.path.join(HERE, "routing.npz"), **out)
 
     # ---- swiglu fwd/bwd, fp32 + bf16 (tests/kernels/swiglu_test.py:33-49)
     out = {}
@@ -52,7 +56,36 @@ def main(ref_path: str) -> None:
         zp.backward(dy)
         for k, v in dict(gate=gate, up=up, dy=dy, out=z, dgate=gate.grad, dup=up.grad, packed_out=zp, packed_dx=xp.grad).items():
             out[f"{name}_{k}"] = v.detach().float().numpy()
-    np.savez_compressed(os.path.join(HERE, "swiglu.npz"), **out)
+    if only is None:
+        np.savez_compressed(os.path.join(HERE, "swiglu.npz"), **out)
+
+    # ---- rmsnorm / fused residual add + rmsnorm fwd+bwd (tests/kernels/rmsnorm_test.py:51-72,
+    #      tests/kernels/fused_residual_add_rmsnorm_test.py:45-86: eps 1e-5, loss = sum, resp. sum(2 z + 3 r))
+    out = {}
+    g = torch.Generator().manual_seed(21)
+    for name, shape, dt, has_w, mult in [("f32_w", (13, 200), torch.float32, True, 0.9), ("f32_now", (5, 33), torch.float32, False, None),
+                                         ("bf16_w", (24, 256), torch.bfloat16, True, 0.9), ("f16_w", (3, 1032), torch.float16, True, None)]:
+        x = torch.randn(shape, generator=g).to(dt).requires_grad_()
+        res = torch.randn(shape, generator=g).to(dt).requires_grad_()
+        w = torch.randn(shape[-1], generator=g).to(dt).requires_grad_() if has_w else None
+        z = rmsnorm_torch(x, w, 1e-5)
+        z.sum().backward()
+        rec = dict(x=x, res=res, z=z, dx=x.grad)
+        if has_w:
+            rec.update(w=w, dw=w.grad)
+        x2 = x.detach().clone().requires_grad_()
+        w2 = w.detach().clone().requires_grad_() if has_w else None
+        z2, r2 = fused_residual_add_rmsnorm_torch(x2, res, w2, 1e-5, mult)
+        (z2 * 2 + r2 * 3).sum().backward()
+        rec.update(fz=z2, fr=r2, fdx=x2.grad, fdres=res.grad)
+        if has_w:
+            rec.update(fdw=w2.grad)
+        for k, v in rec.items():
+            out[f"{name}_{k}"] = v.detach().float().numpy()
+        out[f"{name}_meta"] = np.array([0.0 if mult is None else mult, float(has_w)])
+    np.savez_compressed(os.path.join(HERE, "rmsnorm.npz"), **out)
+    if only == "rmsnorm":
+        return
 
     # ---- MoE fwd+bwd through MoE_Torch itself (reference module, reference routing)
     out = {}
@@ -95,11 +128,11 @@ def main(ref_path: str) -> None:
             out[f"{name}_module_logits"] = logits.numpy()
             out[f"{name}_module_gate_w"] = moe.gate.weight.detach().numpy()
     np.savez_compressed(os.path.join(HERE, "moe.npz"), **out)
-    for f in ("routing.npz", "swiglu.npz", "moe.npz"):
+    for f in ("routing.npz", "swiglu.npz", "rmsnorm.npz", "moe.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        raise SystemExit("usage: make_golden.py /path/to/reference")
-    main(sys.argv[1])
+    if len(sys.argv) not in (2, 3):
+        raise SystemExit("usage: make_golden.py /path/to/reference [rmsnorm]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

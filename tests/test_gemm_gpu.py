@@ -175,7 +175,7 @@ def test_fused_forward_pieces(dtype, act_kind, case):
 
     act = torch.full((cap, I), float("nan"), dtype=dtype, device="cuda")
     h = torch.full((cap, 2 * I), float("nan"), dtype=dtype, device="cuda")
-    up_act_fwd(xg, p["w_fc"], p["gate_w"], r.row_map, r.mtile_off, act, h, act_kind)
+    up_act_fwd(xg, p["w_fc"], None, p["gate_w"], r.row_map, r.mtile_off, act, h, act_kind)
     re = torch.from_numpy(_row_expert(ref, E)[:total])
     wf = p["w_fc"].float().cpu()
     exp_h = torch.zeros(total, 2 * I)
@@ -189,18 +189,26 @@ def test_fused_forward_pieces(dtype, act_kind, case):
     exp_act = gw[:, None] * up_ * (torch.nn.functional.silu(gate_) if act_kind == 0 else torch.sigmoid(gate_))
     torch.testing.assert_close(act[:total].float().cpu(), exp_act, **TOL[dtype])
 
-    # the TMA-gather flavour of the same kernel reads x directly: identical bits on every valid row
-    from cute_kernels.moe import up_act_fwd_gather
+    # the same kernel reading x by row index itself (cp.async producer warps on the CTA-pair kernels, TMA gather4 on the
+    # single-CTA ones): identical bits on every valid row, and the grouped copy it writes back equals the gather kernel's
+    from cute_kernels.moe import cta_pair_kernels, up_act_fwd_gather
 
     act_g = torch.full((cap, I), float("nan"), dtype=dtype, device="cuda")
     h_g = torch.full((cap, 2 * I), float("nan"), dtype=dtype, device="cuda")
-    up_act_fwd_gather(p["x"], k, p["w_fc"], p["gate_w"], r.row_map, r.mtile_off, act_g, h_g, act_kind)
+    xg_back = torch.full((cap, H), float("nan"), dtype=dtype, device="cuda") if cta_pair_kernels() else None
+    up_act_fwd_gather(p["x"], k, p["w_fc"], None, p["gate_w"], r.row_map, r.mtile_off, act_g, h_g, xg_back, act_kind)
     vrows = valid.cuda()
     assert torch.equal(act_g[:total], act[:total])  # pad rows included: they are weighted by zero
     assert torch.equal(h_g[:total][vrows], h[:total][vrows])
+    if xg_back is not None:
+        assert torch.equal(xg_back[:total], xg[:total])  # zero pad rows included
+        # and without the write-back
+        act_g2 = torch.full((cap, I), float("nan"), dtype=dtype, device="cuda")
+        up_act_fwd_gather(p["x"], k, p["w_fc"], None, p["gate_w"], r.row_map, r.mtile_off, act_g2, None, None, act_kind)
+        assert torch.equal(act_g2[:total], act[:total])
 
     out32 = torch.zeros(T, H, dtype=torch.float32, device="cuda")
-    down_combine_fwd(act, p["w_proj"], r.row_map, r.mtile_off, out32, k)
+    down_combine_fwd(act, p["w_proj"], None, None, r.row_map, r.mtile_off, out32, k)
     af = act[:total].float().cpu()
     wp = p["w_proj"].float().cpu()
     exp_out = torch.zeros(T, H)
@@ -228,7 +236,22 @@ def test_fused_backward_pieces(dtype, act_kind, case):
     h = _padded_rows(ref, 2 * I, dtype, 6)
     dh = torch.full((r.capacity, 2 * I), float("nan"), dtype=dtype, device="cuda")
     dgates = torch.zeros(T * k, dtype=torch.float32, device="cuda")
-    dgrad_down(dyg, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh, dgates, act_kind)
+    dgrad_down(dyg, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh, dgates, None, act_kind)
+    # the reproducible form of the router-weight grad: per-part partial sums, then a fixed-order reduction
+    from cute_kernels.moe import dgates_parts, reduce_dgates
+
+    dh_p = torch.full((r.capacity, 2 * I), float("nan"), dtype=dtype, device="cuda")
+    part = torch.full((dgates_parts(I), r.capacity), float("nan"), dtype=torch.float32, device="cuda")
+    dgrad_down(dyg, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh_p, None, part, act_kind)
+    dgates_p = torch.zeros(T * k, dtype=torch.float32, device="cuda")
+    reduce_dgates(part, r.row_map, r.padded_off, E, dgates_p)
+    assert torch.equal(dh_p[:total], dh[:total])
+    torch.testing.assert_close(dgates_p, dgates, rtol=1e-5, atol=1e-5 * max(1.0, float(dgates.abs().max())))
+    part2 = torch.empty_like(part)
+    dgrad_down(dyg, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh_p, None, part2, act_kind)
+    dgates_p2 = torch.zeros(T * k, dtype=torch.float32, device="cuda")
+    reduce_dgates(part2, r.row_map, r.padded_off, E, dgates_p2)
+    assert torch.equal(dgates_p2, dgates_p), "router-weight grads must be bit-reproducible"
 
     wp = p["w_proj"].float().cpu()
     g = torch.zeros(total, I)
@@ -253,19 +276,24 @@ def test_fused_backward_pieces(dtype, act_kind, case):
     tol = {k_: v * max(1.0, I**0.5 / 4) for k_, v in TOL[dtype].items()}
     torch.testing.assert_close(dgates.cpu(), exp_dg, **tol)
 
-    # the TMA-gather flavour takes the un-permuted grad rows: build dy so that its gathered rows equal dyg
-    from cute_kernels.moe import dgrad_down_gather, wgrad, wgrad_gather
+    # the same kernel reading un-permuted grad rows by row index: gather any [T, H] matrix both ways
+    from cute_kernels.moe import cta_pair_kernels, dgrad_down_gather, gather_rows, wgrad, wgrad_gather
 
-    if k == 1:
-        dy = torch.zeros(T, H, dtype=dtype, device="cuda")
-        dy[(rm[valid] // k).cuda()] = dyg[:total][valid.cuda()]
-        dh_g = torch.full((r.capacity, 2 * I), float("nan"), dtype=dtype, device="cuda")
-        dg_g = torch.zeros(T * k, dtype=torch.float32, device="cuda")
-        dgrad_down_gather(dy, k, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh_g, dg_g, act_kind)
-        assert torch.equal(dh_g[:total], dh[:total])
+    dy_any = _padded_rows(ref, H, dtype, 12)[:T].contiguous()
+    dyg_k = torch.empty(r.capacity, H, dtype=dtype, device="cuda")
+    gather_rows(dy_any, dyg_k, r.row_map, r.padded_off, k)
+    dh_k = torch.full((r.capacity, 2 * I), float("nan"), dtype=dtype, device="cuda")
+    part_k = torch.empty(dgates_parts(I), r.capacity, dtype=torch.float32, device="cuda")
+    dgrad_down(dyg_k, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh_k, None, part_k, act_kind)
+    dh_g = torch.full((r.capacity, 2 * I), float("nan"), dtype=dtype, device="cuda")
+    part_g = torch.empty(dgates_parts(I), r.capacity, dtype=torch.float32, device="cuda")
+    dyg_back = torch.full((r.capacity, H), float("nan"), dtype=dtype, device="cuda") if cta_pair_kernels() else None
+    dgrad_down_gather(dy_any, k, p["w_proj"], h, p["gate_w"], r.row_map, r.mtile_off, dh_g, None, part_g, dyg_back, act_kind)
+    assert torch.equal(dh_g[:total], dh_k[:total])
+    assert torch.equal(part_g[:, :total], part_k[:, :total])
+    if dyg_back is not None:
+        assert torch.equal(dyg_back[:total], dyg_k[:total])
     # wgrad with gathered operands against wgrad on pre-gathered copies
-    from cute_kernels.moe import gather_rows
-
     dy2 = _padded_rows(ref, H, dtype, 8)[:T].contiguous()  # any [T, H] matrix
     dyg2 = torch.empty(r.capacity, H, dtype=dtype, device="cuda")
     gather_rows(dy2, dyg2, r.row_map, r.padded_off, k)

@@ -10,11 +10,45 @@ import ck_oracle as orc
 def test_public_names_of_the_reference_surface():
     import cute_kernels as ck
 
-    for name in ("MoE_Cute", "continuous_count_cute", "swiglu_cute", "swiglu_packed_cute", "CuteInductor",
-                 "KernelBackend", "CutoTuneParameter", "set_seed", "ceil_divide"):
+    for name in ("MoE_Cute", "MoE_Torch", "MoE_Triton", "continuous_count_cute", "continuous_count_torch", "swiglu_cute",
+                 "swiglu_torch", "swiglu_packed_cute", "swiglu_packed_torch", "rmsnorm_cute", "rmsnorm_torch",
+                 "fused_residual_add_rmsnorm_cute", "fused_residual_add_rmsnorm_torch", "CuteInductor", "KernelBackend",
+                 "CutoTuneParameter", "set_seed", "ceil_divide"):
         assert hasattr(ck, name), name
     assert ck.ceil_divide(7, 2) == 4
     assert ck.KernelBackend.cuda.value == "cuda" and ck.KernelBackend.triton.value == "triton"
+    assert ck.MoE_Triton is ck.MoE_Cute
+
+
+def test_torch_named_counterparts_match_the_oracle():
+    """The eager-PyTorch functions exported under the reference's ``*_torch`` names agree with the oracle (which is
+    pinned to the reference's outputs) and share MoE_Cute's state_dict layout."""
+    import cute_kernels as ck
+
+    g = torch.Generator().manual_seed(0)
+    gate, up = torch.randn(5, 12, generator=g), torch.randn(5, 12, generator=g)
+    assert torch.equal(ck.swiglu_torch(gate, up), orc.swiglu_ref(gate, up))
+    assert torch.equal(ck.swiglu_packed_torch(torch.cat([up, gate], -1)), orc.swiglu_ref(gate, up))
+    ids = torch.randint(0, 9, (100,), generator=g)
+    assert ck.continuous_count_torch(ids, 9).tolist() == orc.continuous_count_ref(ids.numpy(), 9).tolist()
+    w = torch.randn(12, generator=g)
+    torch.testing.assert_close(ck.rmsnorm_torch(gate, w, 1e-5), orc.rmsnorm_ref(gate, w, 1e-5))
+    z, r = ck.fused_residual_add_rmsnorm_torch(gate, up, w, 1e-5, 0.9)
+    ze, r_e = orc.fused_residual_add_rmsnorm_ref(gate, up, w, 1e-5, 0.9)
+    torch.testing.assert_close(z, ze)
+    assert torch.equal(r, r_e)
+    inp = orc.gen_moe_inputs(2, T=40, H=16, I=24, E=4, k=2)
+    m = ck.MoE_Torch(4, 2, 16, 24, ck.swiglu_packed_torch, True, False, 0.02)
+    with torch.no_grad():
+        m.c_fc.weight.copy_(inp["w_fc"])
+        m.c_proj.weight.copy_(inp["w_proj"])
+    y = m._compute_experts(inp["x"], inp["router_weights"], inp["selected_experts"])
+    ref = orc.moe_experts_ref(inp["x"], inp["router_weights"], inp["selected_experts"], inp["w_fc"], inp["w_proj"], orc.swiglu_packed_ref)
+    torch.testing.assert_close(y, ref, rtol=1e-5, atol=1e-6)
+    cute = ck.MoE_Cute(4, 2, 16, 24, ck.swiglu_packed_cute, True, False, 0.02)
+    cute.load_state_dict(m.state_dict())
+    out, logits = m(inp["x"].view(2, 20, 16))
+    assert out.shape == (2, 20, 16) and logits.shape == (40, 4)
 
 
 def test_state_dict_is_interchangeable_with_the_reference_layout():
@@ -43,8 +77,10 @@ def test_fused_path_selection():
     assert mk(ck.swiglu_packed_cute, True) == 0
     assert mk(orc.swiglu_packed_ref, True) is None  # unknown callables run un-fused
     assert mk(nn.GLU(), True) == 1
-    assert mk(nn.GELU(approximate="tanh"), False) is None
-    assert mk(ck.swiglu_packed_cute, True, bias=True) is None
+    assert mk(nn.GELU(approximate="tanh"), False) == 2   # the reference tests' un-gated activation is fused too
+    assert mk(nn.GELU(), False) is None                  # exact (erf) GELU: un-fused
+    assert mk(nn.GELU(approximate="tanh"), True) is None
+    assert mk(ck.swiglu_packed_cute, True, bias=True) == 0  # biases ride in the GEMM epilogues
 
 
 def test_ops_refuse_cpu_tensors():
@@ -110,11 +146,63 @@ def test_cute_inductor_class_shell():
     import cute_kernels as ck
 
     ci = ck.CuteInductor(use_torch_inductor_after_cute_inductor=False)
-    assert ci.replace_functions == [ck.replace_swiglu_unchunked]
+    assert ci.replace_functions == [ck.replace_rmsnorm, ck.replace_swiglu_unchunked]
     gm = torch.fx.symbolic_trace(_swiglu_module)
     fwd = ci.compiler(gm, [torch.randn(2, 8)])
     assert callable(fwd)
     assert any(n.target is ck.swiglu_packed_cute for n in gm.graph.nodes)
+
+
+def test_cute_inductor_rewrites_rms_norm():
+    import cute_kernels as ck
+
+    def block(x, w):
+        return F.rms_norm(x, (x.size(-1),), weight=w, eps=1e-5) + 1.0
+
+    def two_dims(x):
+        return F.rms_norm(x, x.shape[-2:])
+
+    gm = torch.fx.symbolic_trace(lambda x, w: torch.rms_norm(x, [16], w, 1e-5) + 1.0)
+    for node in list(gm.graph.nodes):
+        ck.replace_rmsnorm(gm, node)
+    targets = [n.target for n in gm.graph.nodes if n.op == "call_function"]
+    assert ck.rmsnorm_cute in targets and torch.rms_norm not in targets
+    new = next(n for n in gm.graph.nodes if n.target is ck.rmsnorm_cute)
+    assert len(new.args) == 3 and new.args[2] == 1e-5  # (x, weight, eps): normalized_shape dropped
+
+    # through dynamo: the rewritten graph reaches this library's op, which refuses CPU tensors loudly
+    seen = []
+
+    def backend(gm, example_inputs):
+        for node in list(gm.graph.nodes):
+            ck.replace_rmsnorm(gm, node)
+        seen.extend(n.target for n in gm.graph.nodes if n.op == "call_function")
+        return gm.forward
+
+    torch._dynamo.reset()
+    f = torch.compile(block, backend=backend)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        f(torch.randn(4, 16), torch.randn(16))
+    assert ck.rmsnorm_cute in seen
+
+    gm2 = torch.fx.symbolic_trace(lambda x: torch.rms_norm(x, [4, 16]))
+    before = [n.target for n in gm2.graph.nodes]
+    for node in list(gm2.graph.nodes):
+        ck.replace_rmsnorm(gm2, node)
+    assert [n.target for n in gm2.graph.nodes] == before  # two normalized dims: left alone
+
+
+def test_cute_inductor_with_inductor_reaches_the_custom_op_on_cpu():
+    """With ``use_torch_inductor_after_cute_inductor=True`` the rewritten graph is re-traced by inductor with fake
+    tensors: the kernels must be recorded as opaque custom ops.  On a CPU tensor the compiled function then fails at
+    run time inside this library (there is no CPU path), not at trace time."""
+    import cute_kernels as ck
+
+    torch._dynamo.reset()
+    ci = ck.CuteInductor(use_torch_inductor_after_cute_inductor=True)
+    f = torch.compile(_swiglu_module, backend=ci.compiler)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        f(torch.randn(8, 16, requires_grad=True))
 
 
 def test_padded_capacity_bounds_every_routing():

@@ -110,12 +110,54 @@ def test_glu_activation_fused():
 
 
 def test_run_to_run_determinism_top2():
-    """k == 2: the fp32 combine adds two values per element, so results are bit-reproducible."""
-    inp = orc.gen_moe_inputs(3, T=512, H=256, I=256, E=8, k=2)
+    """k == 2: the fp32 combine adds two values per element, so results are bit-reproducible; the router-weight
+    gradient is summed from per-tile partial sums in a fixed order."""
+    inp = orc.gen_moe_inputs(3, T=512, H=256, I=1024, E=8, k=2)
     a = _run_fused(inp, torch.bfloat16)
     b = _run_fused(inp, torch.bfloat16)
-    for key in ("y", "dx", "d_w_fc", "d_w_proj"):
+    for key in ("y", "dx", "d_router_weights", "d_w_fc", "d_w_proj"):
         assert torch.equal(a[key], b[key]), key
+
+
+def test_deterministic_option_top8():
+    """k > 2 with ``deterministic=True``: the k rows of a token are stored un-combined and summed in a fixed order, so
+    every output is bit-reproducible; the values still match the oracle."""
+    from cute_kernels import fused_experts
+
+    cfg = dict(T=600, H=256, I=384, E=16, k=8, expert_bias=True)
+    inp = orc.gen_moe_inputs(8, **cfg)
+    outs = []
+    for _ in range(3):
+        x = inp["x"].bfloat16().cuda().requires_grad_()
+        rw = inp["router_weights"].bfloat16().cuda().requires_grad_()
+        w_fc = inp["w_fc"].bfloat16().cuda().requires_grad_()
+        w_proj = inp["w_proj"].bfloat16().cuda().requires_grad_()
+        y = fused_experts(x, rw, inp["selected_experts"].cuda(), w_fc, w_proj, 8, deterministic=True)
+        y.backward(inp["grad_out"].bfloat16().cuda())
+        outs.append(dict(y=y.detach(), dx=x.grad, d_router_weights=rw.grad, d_w_fc=w_fc.grad, d_w_proj=w_proj.grad))
+    for key in outs[0]:
+        assert torch.equal(outs[0][key], outs[1][key]) and torch.equal(outs[0][key], outs[2][key]), key
+    _compare(outs[0], orc.moe_fwd_bwd_ref(inp), torch.bfloat16, cfg["T"])
+
+
+@pytest.mark.parametrize("case", [dict(T=700, H=128, I=200, E=6, k=4), dict(T=1024, H=512, I=1408, E=16, k=8, expert_bias=True),
+                                  dict(T=130, H=72, I=64, E=3, k=1)])
+def test_gather_modes_agree(monkeypatch, case):
+    """Rows read by the GEMM's own producer warps ("producer", with the grouped copy written back for the weight
+    gradients) against rows gathered by the separate streaming kernel ("kernel"): the same bits everywhere."""
+    import cute_kernels.moe as moe
+
+    inp = orc.gen_moe_inputs(6, **case)
+    monkeypatch.setattr(moe, "GATHER_MODE", "kernel")
+    base = _run_fused(inp, torch.bfloat16)
+    monkeypatch.setattr(moe, "GATHER_MODE", "producer")
+    got = _run_fused(inp, torch.bfloat16)
+    keys = ("y", "dx", "d_router_weights", "d_w_fc", "d_w_proj") if case["k"] <= 2 else ("d_router_weights", "d_w_fc", "d_w_proj")
+    for key in keys:
+        assert torch.equal(got[key], base[key]), key
+    for key in ("y", "dx"):  # k > 2: the fp32 combine order is not fixed
+        torch.testing.assert_close(got[key].float(), base[key].float(), rtol=1e-2, atol=1e-3)
+    _compare(got, orc.moe_fwd_bwd_ref(inp), torch.bfloat16, case["T"])
 
 
 def _modules(E, k, H, I, act_cute, act_ref, is_glu, dtype, add_bias=False):
@@ -170,7 +212,8 @@ def test_reference_test_matrix(E, k, H, I, is_glu, dtype):
     x = torch.randn(H, generator=g)
     xk = x.to(dtype).cuda().requires_grad_()
     xr = x.to(dtype).float().requires_grad_()
-    y = m(xk)[0]
+    (y, _), names = _launch_names(lambda: m(xk))
+    assert "up_act_fwd" in names and "down_combine_fwd" in names, f"the module did not take the fused path: {names}"
     sel = m._compute_routing_weights(xk.detach().view(-1, H))[2].cpu()
     yr = r(xr, forced_selection=sel)[0]
     fwd = {torch.float16: 4e-3, torch.bfloat16: 2e-2, torch.float32: 6e-3}[dtype]
@@ -181,14 +224,68 @@ def test_reference_test_matrix(E, k, H, I, is_glu, dtype):
     torch.testing.assert_close(xk.grad.float().cpu(), xr.grad, atol=bwd, rtol=0)
 
 
-def test_module_with_bias_unfused():
+def _launch_names(fn):
+    from cute_kernels import _lib
+
+    _lib.launch_log.reset()
+    _lib.launch_log.record_events = True
+    try:
+        out = fn()
+        torch.cuda.synchronize()
+        return out, [e[0] for e in _lib.launch_log.events]
+    finally:
+        _lib.launch_log.record_events = False
+        _lib.launch_log.reset()
+
+
+@pytest.mark.parametrize("act", ["swiglu", "glu", "gelu_tanh"])
+@pytest.mark.parametrize("with_bias", [False, True])
+@pytest.mark.parametrize("deterministic", [False, True])
+def test_fused_activations_and_biases_against_oracle(act, with_bias, deterministic):
+    """Every fused epilogue -- gated (SwiGLU, GLU) and un-gated (GELU-tanh, the reference tests' is_glu=False
+    activation), with and without the biases of Experts_Torch -- against the fp32 oracle: outputs and every gradient,
+    the bias gradients included."""
+    from cute_kernels import fused_experts
+
+    T, H, I, E, k = 333, 128, 264, 5, 3
+    inp = orc.gen_moe_inputs(13, T=T, H=H, I=I, E=E, k=k, expert_bias=True)
+    gelu = nn.GELU(approximate="tanh")
+    glu = lambda t: t[..., : t.size(-1) // 2] * torch.sigmoid(t[..., t.size(-1) // 2 :])  # noqa: E731
+    act_fn, kind = {"swiglu": (orc.swiglu_packed_ref, 0), "glu": (glu, 1), "gelu_tanh": (gelu, 2)}[act]
+    w_fc = inp["w_fc"] if kind != 2 else inp["w_fc"][:, :I].contiguous()
+    g = torch.Generator().manual_seed(5)
+    b_fc = 0.1 * torch.randn(E, w_fc.size(1), generator=g) if with_bias else None
+    b_proj = 0.1 * torch.randn(E, H, generator=g) if with_bias else None
+
+    leaf = lambda t: None if t is None else t.clone().requires_grad_()  # noqa: E731
+    rx, rrw, rwf, rwp, rbf, rbp = map(leaf, (inp["x"], inp["router_weights"], w_fc, inp["w_proj"], b_fc, b_proj))
+    yr = orc.moe_experts_ref(rx, rrw, inp["selected_experts"], rwf, rwp, act_fn, rbf, rbp)
+    yr.backward(inp["grad_out"])
+
+    dt = torch.bfloat16
+    dev = lambda t: None if t is None else t.to(dt).cuda().requires_grad_()  # noqa: E731
+    x, rw, wf, wp, bf, bp = map(dev, (inp["x"], inp["router_weights"], w_fc, inp["w_proj"], b_fc, b_proj))
+    y, names = _launch_names(lambda: fused_experts(x, rw, inp["selected_experts"].cuda(), wf, wp, k, kind, deterministic, bf, bp))
+    assert "up_act_fwd" in names
+    y.backward(inp["grad_out"].to(dt).cuda())
+    res = dict(y=y.detach(), dx=x.grad, d_router_weights=rw.grad, d_w_fc=wf.grad, d_w_proj=wp.grad)
+    ref = dict(y=yr.detach(), dx=rx.grad, d_router_weights=rrw.grad, d_w_fc=rwf.grad, d_w_proj=rwp.grad)
+    _compare(res, ref, dt, T)
+    if with_bias:
+        tol = dict(rtol=2e-2, atol=2e-2 * max(1.0, (T / 64) ** 0.5))
+        torch.testing.assert_close(bf.grad.float().cpu(), rbf.grad, **tol)
+        torch.testing.assert_close(bp.grad.float().cpu(), rbp.grad, **tol)
+
+
+def test_module_with_bias_takes_the_fused_path():
     act = nn.GELU(approximate="tanh")
     m, r = _modules(4, 2, 128, 256, act, act, False, torch.bfloat16, add_bias=True)
     g = torch.Generator().manual_seed(1)
     x = torch.randn(200, 128, generator=g)
     xk = x.bfloat16().cuda().requires_grad_()
     xr = x.bfloat16().float().requires_grad_()
-    y = m(xk)[0]
+    (y, _), names = _launch_names(lambda: m(xk))
+    assert "up_act_fwd" in names and "grouped_linear" not in names, names
     sel = m._compute_routing_weights(xk.detach())[2].cpu()
     yr = r(xr, forced_selection=sel)[0]
     torch.testing.assert_close(y.float().cpu(), yr, rtol=2e-2, atol=2e-2)
@@ -196,6 +293,25 @@ def test_module_with_bias_unfused():
     yr.sum().backward()
     torch.testing.assert_close(xk.grad.float().cpu(), xr.grad, rtol=4e-2, atol=4e-2)
     torch.testing.assert_close(m.c_proj.bias.grad.float().cpu(), r.c_proj.bias.grad, rtol=4e-2, atol=4e-1)
+
+
+def test_arbitrary_activation_runs_unfused():
+    """An activation callable without a fused epilogue (exact GELU here) still runs, on the grouped GEMM kernels with
+    the activation in between as a torch op."""
+    act = nn.GELU()
+    m, r = _modules(4, 2, 128, 256, act, act, False, torch.bfloat16, add_bias=True)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(150, 128, generator=g)
+    xk = x.bfloat16().cuda().requires_grad_()
+    xr = x.bfloat16().float().requires_grad_()
+    (y, _), names = _launch_names(lambda: m(xk))
+    assert "grouped_linear" in names and "up_act_fwd" not in names, names
+    sel = m._compute_routing_weights(xk.detach())[2].cpu()
+    yr = r(xr, forced_selection=sel)[0]
+    torch.testing.assert_close(y.float().cpu(), yr, rtol=2e-2, atol=2e-2)
+    y.sum().backward()
+    yr.sum().backward()
+    torch.testing.assert_close(xk.grad.float().cpu(), xr.grad, rtol=4e-2, atol=4e-2)
 
 
 def test_inference_mode_skips_saved_activations():

@@ -81,3 +81,38 @@ def test_moe_module_oracle_matches_reference_module(golden_dir, name):
         y, logits = m(inp["x"])
     np.testing.assert_allclose(logits.numpy(), g[f"{name}_module_logits"], rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(y.numpy(), g[f"{name}_module_y"], rtol=1e-5, atol=2e-6)
+
+
+def _rmsnorm_case(g, name, dt):
+    t = lambda k: torch.from_numpy(g[f"{name}_{k}"]).to(dt)  # noqa: E731
+    mult, has_w = g[f"{name}_meta"]
+    return t, (None if mult == 0 else float(mult)), bool(has_w)
+
+
+@pytest.mark.parametrize("name,dt", [("f32_w", torch.float32), ("f32_now", torch.float32), ("bf16_w", torch.bfloat16),
+                                     ("f16_w", torch.float16)])
+def test_rmsnorm_oracle_matches_reference(golden_dir, name, dt):
+    """rmsnorm_torch / fused_residual_add_rmsnorm_torch of the reference, forward and autograd backward."""
+    g = np.load(os.path.join(golden_dir, "rmsnorm.npz"))
+    t, mult, has_w = _rmsnorm_case(g, name, dt)
+    x = t("x").requires_grad_()
+    w = t("w").requires_grad_() if has_w else None
+    z = orc.rmsnorm_ref(x, w, 1e-5)
+    z.sum().backward()
+    exact = dt == torch.float32
+    tol = dict(rtol=0, atol=2e-6) if exact else dict(rtol=1.6e-2, atol=1e-5)
+    assert torch.equal(z.detach(), t("z")) if not exact else torch.allclose(z.detach(), t("z"), rtol=0, atol=1e-6)
+    torch.testing.assert_close(x.grad, t("dx"), **tol)
+    if has_w:
+        torch.testing.assert_close(w.grad, t("dw"), rtol=tol["rtol"], atol=max(tol["atol"], 2e-5))
+    x2 = t("x").requires_grad_()
+    res = t("res").requires_grad_()
+    w2 = t("w").requires_grad_() if has_w else None
+    z2, r2 = orc.fused_residual_add_rmsnorm_ref(x2, res, w2, 1e-5, mult)
+    (z2 * 2 + r2 * 3).sum().backward()
+    assert torch.equal(r2.detach(), t("fr"))
+    assert torch.equal(z2.detach(), t("fz")) if not exact else torch.allclose(z2.detach(), t("fz"), rtol=0, atol=1e-6)
+    torch.testing.assert_close(x2.grad, t("fdx"), **tol)
+    torch.testing.assert_close(res.grad, t("fdres"), **tol)
+    if has_w:
+        torch.testing.assert_close(w2.grad, t("fdw"), rtol=tol["rtol"], atol=max(tol["atol"], 4e-5))

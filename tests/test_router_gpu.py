@@ -112,3 +112,58 @@ def test_moe_module_uses_int32_router():
     assert sel.dtype == torch.int32 and weights.dtype == torch.bfloat16
     y, _ = m(x)
     assert torch.isfinite(y.float()).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("E,k", [(8, 2), (64, 8), (40, 6)])
+def test_router_nan_rows_give_valid_distinct_ids(dtype, E, k):
+    """NaN logits sort as the greatest value (torch.topk's order): an all-NaN row and a partly-NaN row still give k
+    distinct ids in [0, E), and the backward pass completes without touching memory outside d_logits."""
+    from cute_kernels import router_topk_softmax
+
+    g = torch.Generator().manual_seed(E + k)
+    logits = torch.randn(9, E, generator=g)
+    logits[2] = float("nan")                       # every logit NaN
+    logits[4, 3] = float("nan")                    # one NaN: it must be picked first
+    logits[6, 1] = float("nan")
+    logits[6, E - 1] = -float("nan")               # sign bit set: still a NaN, still greatest
+    x = logits.to(dtype).cuda().requires_grad_()
+    w, ids = router_topk_softmax(x, k)
+    idc = ids.cpu().long()
+    assert ((idc >= 0) & (idc < E)).all()
+    assert (torch.sort(idc, dim=1).values.diff(dim=1) > 0).all()
+    assert idc[2].tolist() == list(range(k))       # ties between NaNs go to the lower index
+    assert idc[4, 0].item() == 3
+    assert sorted(idc[6, :2].tolist()) == [1, E - 1]
+    # rows without NaN are unaffected
+    w_ref, ids_ref = orc.routing_weights_ref(logits.to(dtype)[[0, 1, 3, 5, 7, 8]], k, dtype)
+    picked = torch.gather(logits.to(dtype)[[0, 1, 3, 5, 7, 8]], 1, idc[[0, 1, 3, 5, 7, 8]])
+    assert torch.equal(picked, torch.gather(logits.to(dtype)[[0, 1, 3, 5, 7, 8]], 1, ids_ref))
+    assert torch.isnan(w.detach().float().cpu()[2]).all()
+    w.backward(torch.ones_like(w))
+    torch.cuda.synchronize()
+    assert x.grad.shape == (9, E)
+    assert torch.isfinite(x.grad.float().cpu()[[0, 1, 3, 5, 7, 8]]).all()
+
+
+@pytest.mark.expects_dev_status
+def test_router_backward_skips_out_of_range_ids():
+    """The backward kernel never writes through an id outside [0, E): it skips the entry and raises CK_DEV_RANGE."""
+    import cute_kernels
+    from cute_kernels import _lib
+
+    T, E, k = 4, 8, 2
+    w = torch.full((T, k), 0.5, device="cuda")
+    dw = torch.ones(T, k, device="cuda")
+    ids = torch.tensor([[0, 1], [2, 0x7FFFFFFF], [-5, 3], [7, 6]], dtype=torch.int32, device="cuda")
+    guard = torch.full((T * E + 64,), 7.0, device="cuda")
+    d_logits = guard[:T * E]
+    status = _lib.status_word(torch.device("cuda", torch.cuda.current_device()))
+    st = _lib.lib.ck_router_topk_softmax_bwd(w.data_ptr(), dw.data_ptr(), ids.data_ptr(), d_logits.data_ptr(), T, E, k,
+                                             _lib.CK_F32, status.data_ptr(), _lib.stream_ptr())
+    assert st == 0
+    torch.cuda.synchronize()
+    assert (guard[T * E:] == 7.0).all()
+    with pytest.raises(RuntimeError, match="CK_DEV_RANGE"):
+        cute_kernels.check_device_status()
+    cute_kernels.check_device_status()  # cleared

@@ -40,7 +40,13 @@ def _call(static, ids, E):
               b["end"].data_ptr(), b["sidx"].data_ptr(), b["sexp"].data_ptr(), b["poff"].data_ptr(), b["moff"].data_ptr(),
               b["rmap"].data_ptr())
     if static:
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         st = _lib.lib.ck_route_static(*common, status.data_ptr(), stream)
+        torch.cuda.synchronize()
+        # every buffer above was allocated before this bracket: the entry point itself must not change the device's
+        # free memory (the first call on a device only looks up the address of the in-library array)
+        assert torch.cuda.mem_get_info()[0] == free_before, "ck_route_static changed the device's free memory"
     else:
         ws = torch.empty(_lib.lib.ck_route_workspace_bytes(ids.numel(), E), dtype=torch.uint8, device=dev)
         st = _lib.lib.ck_route(*common, ws.data_ptr(), ws.numel(), status.data_ptr(), stream)
