@@ -16,6 +16,7 @@
 // Every mbarrier wait is bounded by wall-clock time; when one runs out the CTA raises
 // CK_DEV_TIMEOUT in the caller's status word, lets in-flight copies land, frees TMEM and returns.
 #include <cuda.h>
+#include <stdio.h>
 #include <stdlib.h>
 
 #include "ck_common.cuh"
@@ -1574,7 +1575,11 @@ static int encode_map(CUtensorMap *tm, const void *base, int rank, const uint64_
                     CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-        set_last_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
+        char what[256];
+        snprintf(what, sizeof(what), "cuTensorMapEncodeTiled(base=%p rank=%d dims=%llu,%llu,%llu box=%u,%u,%u elem=%d mn=%d) -> %d",
+                 base, rank, (unsigned long long)gdims[0], (unsigned long long)gdims[1], (unsigned long long)(rank > 2 ? gdims[2] : 0),
+                 gbox[0], gbox[1], rank > 2 ? gbox[2] : 0u, int(sizeof(T)), int(mn_major), int(r));
+        set_last_cuda_error(cudaErrorInvalidValue, what);
         return CK_ERR_CUDA;
     }
     return CK_OK;

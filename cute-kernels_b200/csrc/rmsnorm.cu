@@ -15,8 +15,9 @@
 // HBM exactly once: forward 2 (4 with a residual) and backward 3 (5) elements of traffic per element.  Rows of up to
 // 1 KiB use a warp per row (shuffle reduction only), longer rows a 256-thread block per row; rows that do not fit the
 // register budget, or whose pointers / width are not 16-byte aligned, take a block-per-row kernel that re-reads the row
-// (an L2 hit) instead.  The weight gradient is accumulated per thread over the rows it visits and added to the fp32
-// d_weight with one atomic per column per block, like the reference's per-program accumulation + tl.atomic_add.
+// (an L2 hit) instead.  The weight gradient is accumulated per thread over the rows it visits (the reference's Triton kernel
+// does the same per program, then tl.atomic_add); here every block stores its sums as one row of a caller-owned fp32
+// buffer and a second small kernel adds the rows in a fixed order: no atomics, reproducible.
 #include "ck_common.cuh"
 
 namespace ck {
@@ -60,7 +61,22 @@ template <typename T>
 __device__ __forceinline__ float rounded(float v) { return DT<T>::up(DT<T>::down(v)); }
 
 // ---- forward -------------------------------------------------------------------------------------------
-// G threads per row, VPT 16-byte vectors per thread (vector j of a thread covers columns (j * G + t) * VEC ...)
+template <typename T>
+__device__ __forceinline__ void unpack_vec(const int4 &raw, float *v) {
+    const Vec16<T> &r = reinterpret_cast<const Vec16<T> &>(raw);
+#pragma unroll
+    for (int i = 0; i < Vec16<T>::N; ++i) v[i] = DT<T>::up(r.v[i]);
+}
+template <typename T>
+__device__ __forceinline__ int4 pack_vec(const float *v) {
+    Vec16<T> r;
+#pragma unroll
+    for (int i = 0; i < Vec16<T>::N; ++i) r.v[i] = DT<T>::down(v[i]);
+    return reinterpret_cast<const int4 &>(r);
+}
+
+// G threads per row, VPT 16-byte vectors per thread (vector j of a thread covers columns (j * G + t) * VEC ...).  Rows stay
+// packed in registers; the next row of the group is already in flight while the current one is reduced and written.
 template <typename T, int G, int VPT>
 __global__ void __launch_bounds__(kNormBlock)
     rmsnorm_fwd_kernel(const T *__restrict__ x, const T *__restrict__ residual, const T *__restrict__ weight, T *__restrict__ out,
@@ -70,35 +86,49 @@ __global__ void __launch_bounds__(kNormBlock)
     const int t = threadIdx.x % G;
     const int rows_per_block = kNormBlock / G;
     const int nvec = H / VEC;
-    float w[VPT][VEC];
+    const int64_t stride = int64_t(gridDim.x) * rows_per_block;
+    int4 wp[VPT];
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int c = j * G + t;
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) w[j][i] = 1.0f;
-        if (weight != nullptr && c < nvec) load_vec<T>(weight + int64_t(c) * VEC, w[j]);
+        wp[j] = make_int4(0, 0, 0, 0);
+        if (weight != nullptr && c < nvec) wp[j] = *reinterpret_cast<const int4 *>(weight + int64_t(c) * VEC);
     }
     const float inv_h = 1.0f / float(H);
-    for (int64_t row = int64_t(blockIdx.x) * rows_per_block + threadIdx.x / G; row < rows; row += int64_t(gridDim.x) * rows_per_block) {
+    int4 xp[VPT], rp[VPT];
+    auto fetch = [&](int64_t row) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = j * G + t;
+            if (row < rows && c < nvec) {
+                const int64_t off = row * int64_t(H) + int64_t(c) * VEC;
+                xp[j] = __ldcs(reinterpret_cast<const int4 *>(x + off));
+                if (residual != nullptr) rp[j] = __ldcs(reinterpret_cast<const int4 *>(residual + off));
+            }
+        }
+    };
+    int64_t row = int64_t(blockIdx.x) * rows_per_block + threadIdx.x / G;
+    fetch(row);
+    for (; row < rows; row += stride) {
         float a[VPT][VEC];
         float ss = 0.0f;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int c = j * G + t;
             if (c < nvec) {
-                const int64_t off = row * int64_t(H) + int64_t(c) * VEC;
-                load_vec<T>(x + off, a[j]);
+                unpack_vec<T>(xp[j], a[j]);
                 if (residual != nullptr) {
                     float r[VEC];
-                    load_vec<T>(residual + off, r);
+                    unpack_vec<T>(rp[j], r);
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) a[j][i] = rounded<T>(__fadd_rn(rounded<T>(__fmul_rn(a[j][i], multiplier)), r[i]));
-                    if (added != nullptr) store_vec<T>(added + off, a[j]);
+                    if (added != nullptr) store_vec<T>(added + row * int64_t(H) + int64_t(c) * VEC, a[j]);
                 }
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) ss = fmaf(a[j][i], a[j][i], ss);
             }
         }
+        fetch(row + stride);  // the next row's loads fly during the reduction and the stores below
         ss = group_sum<G>(ss, red);
         const float r = rsqrtf(ss * inv_h + eps);
         if (inv_rms != nullptr && t == 0) inv_rms[row] = r;
@@ -106,9 +136,15 @@ __global__ void __launch_bounds__(kNormBlock)
         for (int j = 0; j < VPT; ++j) {
             const int c = j * G + t;
             if (c < nvec) {
-                float y[VEC];
+                float y[VEC], w[VEC];
+                if (weight != nullptr) {
+                    unpack_vec<T>(wp[j], w);
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) y[i] = a[j][i] * r * w[j][i];
+                    for (int i = 0; i < VEC; ++i) y[i] = a[j][i] * r * w[i];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) y[i] = a[j][i] * r;
+                }
                 store_vec<T>(out + row * int64_t(H) + int64_t(c) * VEC, y);
             }
         }
@@ -146,39 +182,58 @@ __global__ void __launch_bounds__(kNormBlock)
 }
 
 // ---- backward ------------------------------------------------------------------------------------------
+// The weight gradient leaves every block as one row of dw_part [gridDim.x, H] (plain stores); rmsnorm_dw_reduce_kernel adds
+// the rows in a fixed order, so the result is reproducible and no atomics hit the same H addresses from every block.
 template <typename T, int G, int VPT>
-__global__ void __launch_bounds__(kNormBlock)
+__global__ void __launch_bounds__(kNormBlock, VPT <= 2 ? 2 : 1)
     rmsnorm_bwd_kernel(const T *__restrict__ a_in, const T *__restrict__ weight, const T *__restrict__ dy, const T *__restrict__ d_added,
-                       const float *__restrict__ inv_rms, T *__restrict__ dx, T *__restrict__ d_residual, float *__restrict__ d_weight,
+                       const float *__restrict__ inv_rms, T *__restrict__ dx, T *__restrict__ d_residual, float *__restrict__ dw_part,
                        int64_t rows, int H, float eps, float multiplier) {
     constexpr int VEC = Vec16<T>::N;
     __shared__ float red[kNormBlock / 32];
     const int t = threadIdx.x % G;
     const int rows_per_block = kNormBlock / G;
     const int nvec = H / VEC;
-    float w[VPT][VEC], dw[VPT][VEC];
+    const int64_t stride = int64_t(gridDim.x) * rows_per_block;
+    int4 wp[VPT];
+    float dw[VPT][VEC];
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
         const int c = j * G + t;
+        wp[j] = make_int4(0, 0, 0, 0);
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) { w[j][i] = 1.0f; dw[j][i] = 0.0f; }
-        if (weight != nullptr && c < nvec) load_vec<T>(weight + int64_t(c) * VEC, w[j]);
+        for (int i = 0; i < VEC; ++i) dw[j][i] = 0.0f;
+        if (weight != nullptr && c < nvec) wp[j] = *reinterpret_cast<const int4 *>(weight + int64_t(c) * VEC);
     }
     const float inv_h = 1.0f / float(H);
-    for (int64_t row = int64_t(blockIdx.x) * rows_per_block + threadIdx.x / G; row < rows; row += int64_t(gridDim.x) * rows_per_block) {
-        float a[VPT][VEC], g[VPT][VEC];
+    // rows stay packed (16 bytes per register quad) and are unpacked where they are used; two rows beyond the current one
+    // are in flight, which is what keeps enough bytes outstanding per SM at the occupancy the accumulators allow
+    int4 ap[3][VPT], gp[3][VPT];
+    auto fetch = [&](int slot, int64_t row) {
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int c = j * G + t;
+            if (row < rows && c < nvec) {
+                const int64_t off = row * int64_t(H) + int64_t(c) * VEC;
+                ap[slot][j] = __ldcs(reinterpret_cast<const int4 *>(a_in + off));
+                gp[slot][j] = __ldcs(reinterpret_cast<const int4 *>(dy + off));
+            }
+        }
+    };
+    auto process = [&](int slot, int64_t row) {
         float ss = 0.0f, dot = 0.0f;
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
             const int c = j * G + t;
             if (c < nvec) {
-                const int64_t off = row * int64_t(H) + int64_t(c) * VEC;
-                load_vec<T>(a_in + off, a[j]);
-                load_vec<T>(dy + off, g[j]);
+                float a[VEC], g[VEC], w[VEC];
+                unpack_vec<T>(ap[slot][j], a);
+                unpack_vec<T>(gp[slot][j], g);
+                if (weight != nullptr) unpack_vec<T>(wp[j], w);
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) {
-                    ss = fmaf(a[j][i], a[j][i], ss);
-                    dot = fmaf(g[j][i] * w[j][i], a[j][i], dot);
+                    ss = fmaf(a[i], a[i], ss);
+                    dot = fmaf(weight != nullptr ? g[i] * w[i] : g[i], a[i], dot);
                 }
             }
         }
@@ -196,11 +251,14 @@ __global__ void __launch_bounds__(kNormBlock)
             const int c = j * G + t;
             if (c < nvec) {
                 const int64_t off = row * int64_t(H) + int64_t(c) * VEC;
-                float da[VEC];
+                float a[VEC], g[VEC], w[VEC], da[VEC];
+                unpack_vec<T>(ap[slot][j], a);
+                unpack_vec<T>(gp[slot][j], g);
+                if (weight != nullptr) unpack_vec<T>(wp[j], w);
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) {
-                    da[i] = r * g[j][i] * w[j][i] - coef * a[j][i];
-                    dw[j][i] = fmaf(g[j][i], a[j][i] * r, dw[j][i]);
+                    da[i] = r * (weight != nullptr ? g[i] * w[i] : g[i]) - coef * a[i];
+                    dw[j][i] = fmaf(g[i], a[i] * r, dw[j][i]);
                 }
                 if (d_added != nullptr) {
                     float e[VEC];
@@ -214,40 +272,82 @@ __global__ void __launch_bounds__(kNormBlock)
                 store_vec<T>(dx + off, da);
             }
         }
+    };
+    int64_t row = int64_t(blockIdx.x) * rows_per_block + threadIdx.x / G;
+    fetch(0, row);
+    fetch(1, row + stride);
+    // the slot index must be a compile-time constant for the arrays to stay in registers: three rows per trip
+    while (row < rows) {
+        fetch(2, row + 2 * stride);
+        process(0, row);
+        row += stride;
+        if (row >= rows) break;
+        fetch(0, row + 2 * stride);
+        process(1, row);
+        row += stride;
+        if (row >= rows) break;
+        fetch(1, row + 2 * stride);
+        process(2, row);
+        row += stride;
     }
-    if (d_weight != nullptr) {
+    if (dw_part != nullptr) {
+        float *mine = dw_part + int64_t(blockIdx.x) * H;
         if constexpr (G == 32) {
-            // the warps of a block hold different rows over the same columns: add them up in shared memory first
+            // the warps of a block hold different rows over the same columns: add them up in shared memory, warp by warp
             __shared__ float acc[VPT * 32 * VEC];
-            for (int i = threadIdx.x; i < VPT * 32 * VEC; i += kNormBlock) acc[i] = 0.0f;
-            __syncthreads();
+            for (int wq = 0; wq < kNormBlock / 32; ++wq) {
+                if ((threadIdx.x >> 5) == wq) {
 #pragma unroll
-            for (int j = 0; j < VPT; ++j)
+                    for (int j = 0; j < VPT; ++j)
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) atomicAdd(&acc[(j * 32 + t) * VEC + i], dw[j][i]);
-            __syncthreads();
-            for (int i = threadIdx.x; i < VPT * 32 * VEC; i += kNormBlock)
-                if (i < H) atomicAdd(d_weight + i, acc[i]);
+                        for (int i = 0; i < VEC; ++i) {
+                            const int idx = (j * 32 + t) * VEC + i;
+                            acc[idx] = (wq == 0 ? 0.0f : acc[idx]) + dw[j][i];
+                        }
+                }
+                __syncthreads();
+            }
+            for (int i = threadIdx.x; i < H; i += kNormBlock) mine[i] = acc[i];
         } else {
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const int c = j * G + t;
                 if (c < nvec) {
-#pragma unroll
-                    for (int i = 0; i < VEC; ++i) atomicAdd(d_weight + int64_t(c) * VEC + i, dw[j][i]);
+                    *reinterpret_cast<float4 *>(mine + int64_t(c) * VEC) = make_float4(dw[j][0], dw[j][1], dw[j][2], dw[j][3]);
+                    if constexpr (VEC == 8)
+                        *reinterpret_cast<float4 *>(mine + int64_t(c) * VEC + 4) = make_float4(dw[j][4], dw[j][5], dw[j][6], dw[j][7]);
                 }
             }
         }
     }
 }
 
+// d_weight[c] = sum over the parts, in order, of dw_part[i, c], written in the weight's dtype
+template <typename T>
+__global__ void __launch_bounds__(kNormBlock) rmsnorm_dw_reduce_kernel(const float *__restrict__ dw_part, int parts, int64_t H,
+                                                                       T *__restrict__ d_weight) {
+    const int64_t c = int64_t(blockIdx.x) * kNormBlock + threadIdx.x;
+    if (c >= H) return;
+    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;  // four independent chains, combined in a fixed order
+    int i = 0;
+    for (; i + 4 <= parts; i += 4) {
+        s0 += dw_part[int64_t(i) * H + c];
+        s1 += dw_part[int64_t(i + 1) * H + c];
+        s2 += dw_part[int64_t(i + 2) * H + c];
+        s3 += dw_part[int64_t(i + 3) * H + c];
+    }
+    for (; i < parts; ++i) s0 += dw_part[int64_t(i) * H + c];
+    d_weight[c] = DT<T>::down((s0 + s1) + (s2 + s3));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kNormBlock)
     rmsnorm_bwd_generic_kernel(const T *__restrict__ a_in, const T *__restrict__ weight, const T *__restrict__ dy,
                                const T *__restrict__ d_added, const float *__restrict__ inv_rms, T *__restrict__ dx,
-                               T *__restrict__ d_residual, float *__restrict__ d_weight, int64_t rows, int64_t H, float eps,
+                               T *__restrict__ d_residual, float *__restrict__ dw_part, int64_t rows, int64_t H, float eps,
                                float multiplier) {
     __shared__ float red[kNormBlock / 32];
+    float *mine = dw_part ? dw_part + int64_t(blockIdx.x) * H : nullptr;  // zeroed by the host; each thread owns its columns
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const T *ar = a_in + row * H;
         const T *gr = dy + row * H;
@@ -275,7 +375,7 @@ __global__ void __launch_bounds__(kNormBlock)
             if (d_added) da += DT<T>::up(d_added[row * H + c]);
             if (d_residual) d_residual[row * H + c] = DT<T>::down(da);
             dx[row * H + c] = DT<T>::down(da * multiplier);
-            if (d_weight) atomicAdd(d_weight + c, g * (a * r));
+            if (mine) mine[c] += g * (a * r);
         }
     }
 }
@@ -298,13 +398,14 @@ static void launch_fwd(const void *x, const void *res, const void *w, void *out,
     rmsnorm_fwd_kernel<T, G, VPT><<<norm_grid(ceil_div64(rows, rpb), 8), kNormBlock, 0, s>>>(
         (const T *)x, (const T *)res, (const T *)w, (T *)out, (T *)added, inv, rows, H, eps, mult);
 }
+// blocks of the backward launch = rows of the weight-gradient partial buffer
+static unsigned bwd_grid(int64_t rows, int rows_per_block) { return norm_grid(ceil_div64(rows, rows_per_block), 4); }
+
 template <typename T, int G, int VPT>
 static void launch_bwd(const void *a, const void *w, const void *dy, const void *dadd, const float *inv, void *dx, void *dres,
-                       float *dw, int64_t rows, int H, float eps, float mult, cudaStream_t s) {
-    const int rpb = kNormBlock / G;
-    // fewer blocks when a weight gradient is accumulated: every block ends with one atomic per column
-    rmsnorm_bwd_kernel<T, G, VPT><<<norm_grid(ceil_div64(rows, rpb), dw ? 4 : 8), kNormBlock, 0, s>>>(
-        (const T *)a, (const T *)w, (const T *)dy, (const T *)dadd, inv, (T *)dx, (T *)dres, dw, rows, H, eps, mult);
+                       float *dw_part, int64_t rows, int H, float eps, float mult, cudaStream_t s) {
+    rmsnorm_bwd_kernel<T, G, VPT><<<bwd_grid(rows, kNormBlock / G), kNormBlock, 0, s>>>(
+        (const T *)a, (const T *)w, (const T *)dy, (const T *)dadd, inv, (T *)dx, (T *)dres, dw_part, rows, H, eps, mult);
 }
 
 // picks (G, VPT) for a row of nvec 16-byte vectors; false: use the generic kernels
@@ -337,21 +438,36 @@ static int rmsnorm_fwd_t(const void *x, const void *res, const void *w, void *ou
 }
 
 template <typename T>
-static int rmsnorm_bwd_t(const void *a, const void *w, const void *dy, const void *dadd, const float *inv, void *dx, void *dres,
-                         float *dw, int64_t rows, int64_t H, float eps, float mult, cudaStream_t s) {
+static bool bwd_vectorised(const void *a, const void *w, const void *dy, const void *dadd, const void *dx, const void *dres, int64_t H) {
     constexpr int VEC = Vec16<T>::N;
-    const bool vec_ok = H % VEC == 0 && H / VEC <= 1024 && aligned16(a) && aligned16(dy) && aligned16(dx) && (!w || aligned16(w)) &&
-                        (!dadd || aligned16(dadd)) && (!dres || aligned16(dres));
-    if (vec_ok) {
+    return H % VEC == 0 && H / VEC <= 1024 && aligned16(a) && aligned16(dy) && aligned16(dx) && (!w || aligned16(w)) &&
+           (!dadd || aligned16(dadd)) && (!dres || aligned16(dres));
+}
+// rows per block of the vectorised backward for a row of nvec vectors (a warp per row up to 128 vectors)
+static int bwd_rows_per_block(int64_t nvec) { return nvec <= 128 ? kNormBlock / 32 : 1; }
+
+template <typename T>
+static int rmsnorm_bwd_t(const void *a, const void *w, const void *dy, const void *dadd, const float *inv, void *dx, void *dres,
+                         float *dw_part, void *dw, int64_t rows, int64_t H, float eps, float mult, cudaStream_t s) {
+    constexpr int VEC = Vec16<T>::N;
+    unsigned parts;
+    if (bwd_vectorised<T>(a, w, dy, dadd, dx, dres, H)) {
         const int nvec = int(H / VEC);
-#define BWD_CALL(TT, GG, VV) launch_bwd<TT, GG, VV>(a, w, dy, dadd, inv, dx, dres, dw, rows, int(H), eps, mult, s)
+        parts = bwd_grid(rows, bwd_rows_per_block(nvec));
+#define BWD_CALL(TT, GG, VV) launch_bwd<TT, GG, VV>(a, w, dy, dadd, inv, dx, dres, dw_part, rows, int(H), eps, mult, s)
         CK_NORM_DISPATCH(T, nvec, BWD_CALL, BWD_CALL)
 #undef BWD_CALL
     } else {
-        rmsnorm_bwd_generic_kernel<T><<<norm_grid(rows, dw ? 4 : 8), kNormBlock, 0, s>>>(
-            (const T *)a, (const T *)w, (const T *)dy, (const T *)dadd, inv, (T *)dx, (T *)dres, dw, rows, H, eps, mult);
+        parts = bwd_grid(rows, 1);
+        if (dw_part) CK_CUDA_TRY(cudaMemsetAsync(dw_part, 0, size_t(parts) * size_t(H) * sizeof(float), s));
+        rmsnorm_bwd_generic_kernel<T><<<parts, kNormBlock, 0, s>>>((const T *)a, (const T *)w, (const T *)dy, (const T *)dadd, inv, (T *)dx,
+                                                                    (T *)dres, dw_part, rows, H, eps, mult);
     }
     CK_LAUNCH_CHECK("rmsnorm_bwd_kernel");
+    if (dw) {
+        rmsnorm_dw_reduce_kernel<T><<<unsigned(ceil_div64(H, kNormBlock)), kNormBlock, 0, s>>>(dw_part, int(parts), H, (T *)dw);
+        CK_LAUNCH_CHECK("rmsnorm_dw_reduce_kernel");
+    }
     return CK_OK;
 }
 
@@ -375,17 +491,29 @@ extern "C" int ck_rmsnorm_fwd(const void *x, const void *residual, const void *w
     }
 }
 
+extern "C" int64_t ck_rmsnorm_bwd_parts(int64_t rows, int64_t H) {
+    if (rows <= 0 || H <= 0) return 0;
+    // the largest grid any of the backward kernels would use for this shape (a warp per row, or a block per row)
+    const unsigned a = bwd_grid(rows, kNormBlock / 32), b = bwd_grid(rows, 1);
+    return int64_t(a > b ? a : b);
+}
+
 extern "C" int ck_rmsnorm_bwd(const void *a, const void *weight, const void *dy, const void *d_added, const float *inv_rms,
-                              void *dx, void *d_residual, float *d_weight, int64_t rows, int64_t H, float eps, float multiplier,
-                              int dtype, void *stream) {
+                              void *dx, void *d_residual, float *dw_partial, void *d_weight, int64_t rows, int64_t H, float eps,
+                              float multiplier, int dtype, void *stream) {
     if (rows < 0 || H <= 0 || H > INT32_MAX) return CK_ERR_SHAPE;
-    if (rows == 0) return CK_OK;
-    if (!a || !dy || !dx) return CK_ERR_SHAPE;
+    if (d_weight && !dw_partial) return CK_ERR_SHAPE;
     cudaStream_t s = (cudaStream_t)stream;
+    if (rows == 0) {
+        if (d_weight) CK_CUDA_TRY(cudaMemsetAsync(d_weight, 0, size_t(H) * (dtype == CK_F32 ? 4 : 2), s));
+        return CK_OK;
+    }
+    if (!a || !dy || !dx) return CK_ERR_SHAPE;
+    float *part = d_weight ? dw_partial : nullptr;
     switch (dtype) {
-        case CK_F32: return rmsnorm_bwd_t<float>(a, weight, dy, d_added, inv_rms, dx, d_residual, d_weight, rows, H, eps, multiplier, s);
-        case CK_F16: return rmsnorm_bwd_t<__half>(a, weight, dy, d_added, inv_rms, dx, d_residual, d_weight, rows, H, eps, multiplier, s);
-        case CK_BF16: return rmsnorm_bwd_t<__nv_bfloat16>(a, weight, dy, d_added, inv_rms, dx, d_residual, d_weight, rows, H, eps, multiplier, s);
+        case CK_F32: return rmsnorm_bwd_t<float>(a, weight, dy, d_added, inv_rms, dx, d_residual, part, d_weight, rows, H, eps, multiplier, s);
+        case CK_F16: return rmsnorm_bwd_t<__half>(a, weight, dy, d_added, inv_rms, dx, d_residual, part, d_weight, rows, H, eps, multiplier, s);
+        case CK_BF16: return rmsnorm_bwd_t<__nv_bfloat16>(a, weight, dy, d_added, inv_rms, dx, d_residual, part, d_weight, rows, H, eps, multiplier, s);
         default: return CK_ERR_UNSUPPORTED;
     }
 }

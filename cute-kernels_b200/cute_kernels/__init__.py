@@ -11,7 +11,8 @@ counterparts the reference exports under those names (:mod:`torch_reference`), n
 from ._lib import check_device_status
 from .continuous_count import continuous_count_cute
 from .cute_inductor import CuteInductor, replace_rmsnorm, replace_swiglu_unchunked
-from .expert_parallel import ExpertParallelMoE, gather_expert_state_dict, shard_expert_state_dict
+from .expert_parallel import (ExpertParallelMoE, balanced_expert_placement, gather_expert_state_dict,
+                              shard_expert_state_dict)
 from .kernel_backend import CutoTuneParameter, KernelBackend
 from .moe import Experts_Cute, MoE_Cute, fused_experts
 from .rmsnorm import fused_residual_add_rmsnorm_cute, rmsnorm_cute
@@ -25,7 +26,7 @@ from .utils import ceil_divide, divide_if_divisible, set_seed
 MoE_Triton = MoE_Cute  # the reference's name for its GPU implementation of the layer
 
 __all__ = [
-    "Experts_Torch", "MoE_Torch", "MoE_Triton", "continuous_count_torch", "fused_residual_add_rmsnorm_torch", "rmsnorm_torch",
+    "Experts_Torch", "MoE_Torch", "balanced_expert_placement", "MoE_Triton", "continuous_count_torch", "fused_residual_add_rmsnorm_torch", "rmsnorm_torch",
     "swiglu_packed_torch", "swiglu_torch",
     "CuteInductor", "CutoTuneParameter", "ExpertParallelMoE", "Experts_Cute", "KernelBackend", "MoE_Cute", "Routing", "ceil_divide",
     "check_device_status", "continuous_count_cute", "divide_if_divisible", "fused_experts", "gather_expert_state_dict", "padded_capacity",

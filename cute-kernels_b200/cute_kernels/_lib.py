@@ -62,7 +62,8 @@ PROTOTYPES = {
     "ck_moe_combine_rows": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i, _vp]),
     "ck_moe_row_dots": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i64, _i, _vp]),
     "ck_rmsnorm_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, ctypes.c_float, _i, _vp]),
-    "ck_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, ctypes.c_float, _i, _vp]),
+    "ck_rmsnorm_bwd_parts": (_i64, [_i64, _i64]),
+    "ck_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, ctypes.c_float, _i, _vp]),
     "ck_router_topk_softmax": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
     "ck_router_topk_softmax_bwd": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp]),
     "ck_moe_gather_rows_peer": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _i, _i64, _i, _i64, _i64, _i64, _i, _vp, _vp]),

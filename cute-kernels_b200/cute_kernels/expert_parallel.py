@@ -233,20 +233,46 @@ class ExpertParallelMoE:
         return _CombineSorted.apply(y_back, w_sorted, tok, T)
 
 
-def shard_expert_state_dict(full: dict[str, torch.Tensor], rank: int, world: int) -> dict[str, torch.Tensor]:
-    """Slices ``c_fc.*`` / ``c_proj.*`` of a full MoE state_dict to the experts rank ``rank`` owns;
-    ``gate.weight`` (the router) is replicated."""
+def balanced_expert_placement(rows_per_expert, world: int) -> list[int]:
+    """``expert_to_rank`` for ``world`` ranks with E / world experts each, balancing the rows per rank: experts in order of
+    decreasing load go to the least-loaded rank that still has a free slot (longest-processing-time-first).  The load is
+    whatever histogram the caller trusts -- a running count of routed rows per expert, typically."""
+    loads = [float(v) for v in rows_per_expert]
+    E = len(loads)
+    if E % world != 0:
+        raise ValueError("the number of experts must be divisible by the number of ranks")
+    per_rank = E // world
+    total = [0.0] * world
+    used = [0] * world
+    placement = [0] * E
+    for e in sorted(range(E), key=lambda i: (-loads[i], i)):
+        r = min((r for r in range(world) if used[r] < per_rank), key=lambda r: (total[r], r))
+        placement[e] = r
+        total[r] += loads[e]
+        used[r] += 1
+    return placement
+
+
+def shard_expert_state_dict(full: dict[str, torch.Tensor], rank: int, world: int,
+                            expert_to_rank: list[int] | None = None) -> dict[str, torch.Tensor]:
+    """Slices ``c_fc.*`` / ``c_proj.*`` of a full MoE state_dict to the experts rank ``rank`` owns (in increasing expert
+    id); ``gate.weight`` (the router) is replicated.  Default ownership: contiguous blocks of E / world experts."""
     out = {}
     for key, v in full.items():
         if key.startswith(("c_fc.", "c_proj.")):
-            epr = v.size(0) // world
-            out[key] = v[rank * epr : (rank + 1) * epr].clone()
+            if expert_to_rank is None:
+                epr = v.size(0) // world
+                out[key] = v[rank * epr : (rank + 1) * epr].clone()
+            else:
+                mine = [e for e in range(v.size(0)) if expert_to_rank[e] == rank]
+                out[key] = v[mine].clone()
         else:
             out[key] = v.clone()
     return out
 
 
-def gather_expert_state_dict(local: dict[str, torch.Tensor], group=None) -> dict[str, torch.Tensor]:
+def gather_expert_state_dict(local: dict[str, torch.Tensor], group=None,
+                             expert_to_rank: list[int] | None = None) -> dict[str, torch.Tensor]:
     """Inverse of :func:`shard_expert_state_dict`: all-gathers the expert slices into a full state_dict."""
     world = dist.get_world_size(group)
     out = {}
@@ -254,7 +280,13 @@ def gather_expert_state_dict(local: dict[str, torch.Tensor], group=None) -> dict
         if key.startswith(("c_fc.", "c_proj.")):
             parts = [torch.empty_like(v) for _ in range(world)]
             dist.all_gather(parts, v.contiguous(), group=group)
-            out[key] = torch.cat(parts, dim=0)
+            full = torch.cat(parts, dim=0)
+            if expert_to_rank is not None:
+                order = [e for r in range(world) for e in range(len(expert_to_rank)) if expert_to_rank[e] == r]
+                restored = torch.empty_like(full)
+                restored[order] = full
+                full = restored
+            out[key] = full
         else:
             out[key] = v.clone()
     return out

@@ -304,14 +304,17 @@ def _from_f32(src32: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 # fused expert computation
 # ---------------------------------------------------------------------------------------------------
 # How the routed rows of x (forward) and of grad_out (backward) reach the GEMMs.
-#   "producer" (default with the CTA-pair kernels): the up projection and dgrad-down read the rows by row index with
-#              their own producer warps (cp.async into the swizzled stages) and write the grouped copy out as a
-#              by-product for the weight-gradient GEMMs; no separate permutation kernel runs.
-#   "kernel"   a streaming gather kernel builds the grouped copies first (the only choice with the single-CTA kernels
-#              when weight gradients are needed).
+#   "kernel"   (default) a streaming gather kernel builds the grouped copies first; the GEMMs read them with tiled TMA loads.
+#   "producer" the up projection and dgrad-down read the rows by row index with their own producer warp (cp.async into
+#              the swizzled stages, CTA-pair kernels only) and write the grouped copy out as a by-product for the
+#              weight-gradient GEMMs; no separate permutation kernel runs.
 #   "tma"      no grouped copies at all: the weight-gradient GEMMs gather their operand with TMA gather4 as well.
-#              Measured on B200 (Mixtral-shaped layer, bf16): gather4 moves 512 bytes per TMA operation and wgrad drops
-#              from 1220 to 293 TFLOP/s, so this stays a tested alternative (CK_TMA_GATHER=1 selects it).
+# Measured on B200 (Mixtral-shaped layer, bf16, up projection): "kernel" 0.09 ms gather + 5.4 ms GEMM; "producer" 28.7 ms
+# (16-byte cp.async delivers about 7 GB/s per SM, a sixth of what the tensor cores consume, whether one warp or two issue
+# it, with or without the proxy fence, with a CTA- or cluster-scope acquire); "tma" 17.7 ms (gather4 moves 512 bytes per
+# TMA operation).  Every A tile is fetched once per n-tile, 56-112 times in all, so the per-byte cost of the fetch path
+# matters far more than the one extra pass of the gather kernel.  The alternatives stay selectable (CK_GATHER_MODE,
+# CK_TMA_GATHER=1) and tested.
 import os as _os
 
 TMA_GATHER = _os.environ.get("CK_TMA_GATHER", "0") == "1"
@@ -321,9 +324,11 @@ GATHER_MODE = _os.environ.get("CK_GATHER_MODE", "")
 def _gather_mode() -> str:
     if TMA_GATHER:
         return "tma"
-    if GATHER_MODE in ("producer", "kernel", "tma"):
+    if GATHER_MODE in ("kernel", "tma"):
         return GATHER_MODE
-    return "producer" if cta_pair_kernels() else "kernel"
+    if GATHER_MODE == "producer":
+        return "producer" if cta_pair_kernels() else "kernel"
+    return "kernel"
 
 
 class _FusedExperts(torch.autograd.Function):

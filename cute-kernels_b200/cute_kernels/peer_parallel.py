@@ -104,6 +104,7 @@ class PeerBuffers:
     tokens [max_tokens, H]  x in forward, dy in backward          rows [S, H]  returned expert outputs / input grads
     weights [S]             router weights, dtype of x (local)    dgates [S]   router-weight grads, fp32
     ids [S] int32           published expert ids (``num_experts`` = "no row" on the unused tail)
+    ``ids`` and ``weights`` are views into one byte buffer ``published`` (ids first), so one all-gather moves both.
     """
 
     rank: int
@@ -118,26 +119,49 @@ class PeerBuffers:
     tokens_ptrs: list[int]
     rows_ptrs: list[int]
     dgates_ptrs: list[int]
+    published: torch.Tensor | None = None  # uint8 [S * (4 + element size)]: ids | weights, when they share storage
 
     @property
     def slots(self) -> int:
         return self.max_tokens * self.top_k
 
+    def split_published(self, gathered: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """(ids_all int32 [world * S], weights_all [world * S]) from the all-gathered ``published`` buffers."""
+        S, esz = self.slots, self.weights.element_size()
+        per_rank = gathered.view(self.world, S * (4 + esz))
+        ids_all = per_rank[:, : 4 * S].contiguous().view(torch.int32).reshape(-1)
+        weights_all = per_rank[:, 4 * S:].contiguous().view(self.weights.dtype).reshape(-1)
+        return ids_all, weights_all
+
+
+def packed_publication(slots: int, dtype: torch.dtype, device: torch.device) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """(published uint8, ids int32 view, weights view): ids and router weights in one buffer, one all-gather for both."""
+    esz = torch.empty(0, dtype=dtype).element_size()
+    published = torch.empty(slots * (4 + esz), dtype=torch.uint8, device=device)
+    return published, published[: 4 * slots].view(torch.int32), published[4 * slots:].view(dtype)
+
 
 @dataclass
 class _Plan:
     routing: Routing   # all ranks' slots routed over [this rank's experts..., "not mine"]; row_map[p] = global flat slot
-    rows: int          # padded rows of the local experts (a multiple of 128, may be 0)
-    cap: int           # rows to allocate: max(rows, 128)
+    rows: int | None   # padded rows of the local experts (a multiple of 128, may be 0); None: not read back (capacity mode)
+    cap: int           # rows allocated: max(rows, 128), or the caller's capacity
     split: int         # m-tiles in the first window of the pull (0: one window)
     mtile_first: torch.Tensor | None   # mtile_off clamped to the first window / to the rest
     mtile_rest: torch.Tensor | None
+    own_map: torch.Tensor | None = None  # capacity mode: row_map[:cap] with -1 beyond the local experts' rows
 
 
 class PeerExpertEngine:
     """The per-rank phases; the caller puts a collective between them (see :class:`PeerExpertParallelMoE`)."""
 
-    def __init__(self, buffers: PeerBuffers, num_experts: int, act_kind: int = _lib.CK_ACT_SWIGLU) -> None:
+    def __init__(self, buffers: PeerBuffers, num_experts: int, act_kind: int = _lib.CK_ACT_SWIGLU,
+                 expert_to_rank: list[int] | None = None, capacity_rows: int | None = None) -> None:
+        """``expert_to_rank[e]``: the rank that owns expert e (default: contiguous blocks, rank g owns
+        [g E/G, (g+1) E/G)); every rank must own exactly E/G experts, and its weight tensors list them in increasing
+        expert id (see :func:`expert_parallel.shard_expert_state_dict`).  ``capacity_rows``: allocate this many padded
+        rows per call instead of reading the exact count back from the device (no host synchronisation in the step);
+        a call whose routing needs more rows computes nothing and raises CK_DEV_META in the device status word."""
         if num_experts % buffers.world != 0:
             raise ValueError("num_experts must be divisible by the number of ranks")
         self.b = buffers
@@ -145,6 +169,21 @@ class PeerExpertEngine:
         self.local_experts = num_experts // buffers.world
         self.act_kind = act_kind
         self._side: torch.cuda.Stream | None = None
+        if expert_to_rank is None:
+            expert_to_rank = [e // self.local_experts for e in range(num_experts)]
+        if len(expert_to_rank) != num_experts or any(expert_to_rank.count(r) != self.local_experts for r in range(buffers.world)):
+            raise ValueError("expert_to_rank must give every rank exactly num_experts / world experts")
+        self.expert_to_rank = list(expert_to_rank)
+        self.local_expert_ids = [e for e in range(num_experts) if expert_to_rank[e] == buffers.rank]
+        # global expert id -> local slot of the routing pass (0 .. E/G - 1), E/G = "not mine"; entry [num_experts] is the
+        # padding id of unused slots
+        table = [self.local_experts] * (num_experts + 1)
+        for slot, e in enumerate(self.local_expert_ids):
+            table[e] = slot
+        self._local_slot = torch.tensor(table, dtype=torch.int32, device=buffers.tokens.device)
+        if capacity_rows is not None:
+            capacity_rows = max(_lib.CK_TILE_M, -(-int(capacity_rows) // _lib.CK_TILE_M) * _lib.CK_TILE_M)
+        self.capacity_rows = capacity_rows
 
     # ---- forward -------------------------------------------------------------------------------------
     def publish(self, x: torch.Tensor, router_weights: torch.Tensor, selected_experts: torch.Tensor) -> None:
@@ -163,11 +202,22 @@ class PeerExpertEngine:
         the ids of other ranks' experts folded into a last "not mine" bin: the local experts' segments of the padded
         layout then list global flat slots, in (source rank, token) order inside every expert."""
         epr = self.local_experts
-        loc = ids_all - self.b.rank * epr
-        loc = torch.where((loc >= 0) & (loc < epr), loc, epr)
+        in_range = (ids_all >= 0) & (ids_all <= self.num_experts)
+        loc = self._local_slot[ids_all.clamp(0, self.num_experts).long()]
         r = route(loc, epr + 1)
         # ids outside [0, num_experts] would be "not mine" on every rank and their rows would never be computed
-        n_bad = ((ids_all < 0) | (ids_all > self.num_experts)).sum(dtype=torch.int32)
+        n_bad = (~in_range).sum(dtype=torch.int32)
+        if self.capacity_rows is not None:
+            # no read-back: the capacity bounds the allocation, the kernels refuse (CK_DEV_META) when the tile tables
+            # describe more rows, and bad ids raise CK_DEV_RANGE in the same status word
+            status = _lib.status_word(ids_all.device)
+            status.bitwise_or_((n_bad > 0).to(torch.int32) * _lib.CK_DEV_RANGE)
+            cap = self.capacity_rows
+            own = torch.arange(cap, device=ids_all.device, dtype=torch.int32) < r.padded_off[epr]
+            if r.row_map.numel() < cap:
+                raise RuntimeError("capacity_rows exceeds the routing pass's own bound")
+            own_map = torch.where(own, r.row_map[:cap], -1)
+            return _Plan(r, None, cap, 0, None, None, own_map)
         rows, bad = torch.stack([r.padded_off[epr], n_bad]).tolist()  # the one host sync: rows to allocate
         if bad:
             raise RuntimeError(f"{bad} expert ids outside [0, {self.num_experts}) reached the expert-parallel layer")
@@ -217,9 +267,11 @@ class PeerExpertEngine:
         main.wait_event(rest_done)
         gemm(plan.mtile_rest)
 
-    # True (default with the CTA-pair kernels): the GEMMs' own producer warps pull the rows over NVLink, tile by tile,
-    # and leave a local grouped copy behind for the weight gradients.  False: a separate pull kernel runs first.
-    FUSED_PULL = True
+    # True: the GEMMs' own producer warp pulls the rows over NVLink (cp.async by row index, CTA-pair kernels) and leaves a
+    # local grouped copy behind for the weight gradients.  False (default): a separate pull kernel runs first and the GEMM
+    # reads its output with tiled TMA loads -- an A tile is fetched once per n-tile, so pulling inside the GEMM would
+    # cross NVLink 56-112 times per row, and the cp.async path is the slower fetch path even locally.
+    FUSED_PULL = False
 
     def fwd_compute(self, plan: _Plan, weights_all: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor,
                     need_grad: bool):
@@ -270,7 +322,10 @@ class PeerExpertEngine:
         if need_wproj:
             d_wproj = torch.empty_like(w_proj)
             wgrad(dyg, act, r.padded_off, d_wproj)
-        _scatter_scalars_peer(dgates, r.row_map, plan.rows, b.dgates_ptrs, b.slots)  # local experts' rows only
+        if plan.own_map is not None:  # capacity mode: entries beyond the local experts' rows are masked to -1 (skipped)
+            _scatter_scalars_peer(dgates, plan.own_map, plan.cap, b.dgates_ptrs, b.slots)
+        else:
+            _scatter_scalars_peer(dgates, r.row_map, plan.rows, b.dgates_ptrs, b.slots)  # local experts' rows only
         if need_x:
             _linear_scatter_peer(dh, w_fc, r, b.rows_ptrs, b.slots, True)
         if need_wfc:
@@ -310,8 +365,13 @@ class _PeerExperts(torch.autograd.Function):
     def forward(ctx, x, router_weights, w_fc, w_proj, selected_experts, engine: PeerExpertEngine, exchange):
         need_grad = any(ctx.needs_input_grad[:4])
         engine.publish(x, router_weights, selected_experts)
-        ids_all = exchange.all_gather(engine.b.ids)            # also the "everything is published" ordering point
-        weights_all = exchange.all_gather(engine.b.weights)
+        if engine.b.published is not None:
+            # ids and router weights share one buffer: a single all-gather, which is also the "everything is published"
+            # ordering point
+            ids_all, weights_all = engine.b.split_published(exchange.all_gather(engine.b.published))
+        else:
+            ids_all = exchange.all_gather(engine.b.ids)
+            weights_all = exchange.all_gather(engine.b.weights)
         plan = engine.plan(ids_all)
         saved = engine.fwd_compute(plan, weights_all, w_fc, w_proj, need_grad)
         exchange.barrier()
@@ -349,11 +409,10 @@ def allocate_symmetric_buffers(max_tokens: int, hidden_size: int, top_k: int, dt
 
     tokens, tokens_ptrs = shared((max_tokens, hidden_size), dtype)
     rows, rows_ptrs = shared((S, hidden_size), dtype)
-    weights = torch.empty(S, dtype=dtype, device=device)
     dgates, dgates_ptrs = shared((S,), torch.float32)
-    ids = torch.empty(S, dtype=torch.int32, device=device)
+    published, ids, weights = packed_publication(S, dtype, device)
     return PeerBuffers(dist.get_rank(group), dist.get_world_size(group), max_tokens, top_k, tokens, rows, weights,
-                       dgates, ids, tokens_ptrs, rows_ptrs, dgates_ptrs)
+                       dgates, ids, tokens_ptrs, rows_ptrs, dgates_ptrs, published)
 
 
 class PeerExpertParallelMoE:
@@ -364,10 +423,20 @@ class PeerExpertParallelMoE:
     (forward and backward of one call must finish before the next call's forward starts, which stream order gives)."""
 
     def __init__(self, num_experts: int, top_k: int, max_tokens: int, hidden_size: int, dtype: torch.dtype, group=None,
-                 act_kind: int = _lib.CK_ACT_SWIGLU, buffers: PeerBuffers | None = None, exchange=None) -> None:
+                 act_kind: int = _lib.CK_ACT_SWIGLU, buffers: PeerBuffers | None = None, exchange=None,
+                 expert_to_rank: list[int] | None = None, capacity_factor: float | None = None) -> None:
+        """``capacity_factor``: None reads the exact number of rows this rank's experts received back from the device
+        once per call (one host synchronisation); a number allocates ``capacity_factor * max_tokens * top_k`` rows (the
+        share of a perfectly balanced routing, times the factor) plus one tile per local expert and never synchronises --
+        a batch that routes more rows to this rank is refused on the device (CK_DEV_META, see check_device_status)."""
         self.group = group if group is not None else dist.group.WORLD
         self.buffers = buffers or allocate_symmetric_buffers(max_tokens, hidden_size, top_k, dtype, self.group)
-        self.engine = PeerExpertEngine(self.buffers, num_experts, act_kind)
+        cap_rows = None
+        if capacity_factor is not None:
+            world = dist.get_world_size(self.group)
+            cap_rows = int(capacity_factor * max_tokens * top_k) + (num_experts // world) * _lib.CK_TILE_M
+            cap_rows = min(cap_rows, world * max_tokens * top_k + (num_experts // world) * _lib.CK_TILE_M)
+        self.engine = PeerExpertEngine(self.buffers, num_experts, act_kind, expert_to_rank, cap_rows)
         self.exchange = exchange or _NcclExchange(self.group, self.buffers.tokens.device)
         self.top_k = top_k
 

@@ -27,19 +27,39 @@ def _fwd_impl(x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tens
 
 def _bwd_impl(a: torch.Tensor, weight: torch.Tensor | None, output_grad: torch.Tensor, added_grad: torch.Tensor | None,
               inv_rms: torch.Tensor | None, x_grad: torch.Tensor, residual_grad: torch.Tensor | None,
-              weight_grad: torch.Tensor | None, eps: float, multiplier: float) -> None:
+              weight_grad_parts: torch.Tensor | None, weight_grad: torch.Tensor | None, eps: float, multiplier: float) -> None:
     _lib.require_cuda(a, weight, output_grad, x_grad)
     rows, H = _rows_and_hidden(a)
-    with torch.cuda.device(a.device), _lib.launch("rmsnorm_bwd"):
+    with torch.cuda.device(a.device), _lib.launch("rmsnorm_bwd", 2 if weight_grad is not None else 1):
         st = _lib.lib.ck_rmsnorm_bwd(a.data_ptr(), _lib.ptr(weight), output_grad.data_ptr(), _lib.ptr(added_grad),
-                                     _lib.ptr(inv_rms), x_grad.data_ptr(), _lib.ptr(residual_grad), _lib.ptr(weight_grad),
-                                     rows, H, eps, multiplier, _lib.dtype_code(a.dtype), _lib.stream_ptr())
+                                     _lib.ptr(inv_rms), x_grad.data_ptr(), _lib.ptr(residual_grad), _lib.ptr(weight_grad_parts),
+                                     _lib.ptr(weight_grad), rows, H, eps, multiplier, _lib.dtype_code(a.dtype), _lib.stream_ptr())
     _lib.check(st, "ck_rmsnorm_bwd")
+
+
+def weight_grad_parts(rows: int, hidden: int) -> int:
+    """Rows of the fp32 partial buffer ``[parts, hidden]`` the backward kernel writes its per-block weight-gradient sums
+    to (mirror of ck_rmsnorm_bwd_parts, kept out of ctypes so torch.compile can trace callers): the backward launches at
+    most 4 blocks per SM."""
+    if rows <= 0 or hidden <= 0:
+        return 1
+    return max(1, min(rows, 4 * _sm_count()))
+
+
+_SM_COUNT: dict[int, int] = {}
+
+
+@torch.compiler.assume_constant_result
+def _sm_count() -> int:
+    dev = torch.cuda.current_device()
+    if dev not in _SM_COUNT:
+        _SM_COUNT[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _SM_COUNT[dev]
 
 
 _fwd_op = torch.library.custom_op("cute_kernels_b200::rmsnorm_forward", _fwd_impl, mutates_args={"output", "added", "inv_rms"})
 _bwd_op = torch.library.custom_op("cute_kernels_b200::rmsnorm_backward", _bwd_impl,
-                                  mutates_args={"x_grad", "residual_grad", "weight_grad"})
+                                  mutates_args={"x_grad", "residual_grad", "weight_grad_parts", "weight_grad"})
 
 
 def _fwd(*args) -> None:
@@ -55,6 +75,14 @@ def _check_weight(x: torch.Tensor, weight: torch.Tensor | None) -> None:
         assert weight.dim() == 1, "weight should be 1D"
         assert weight.size(-1) == x.size(-1), "hidden size for x and weight tensor is different"
         assert weight.type() == x.type(), "tensors weight and y should have same dtype"
+
+
+def _weight_grad_buffers(a: torch.Tensor, weight: torch.Tensor | None):
+    """(weight_grad in the weight's dtype, fp32 partial-sum workspace) or (None, None) without a weight."""
+    if weight is None:
+        return None, None
+    rows, H = _rows_and_hidden(a)
+    return torch.empty_like(weight), torch.empty(weight_grad_parts(rows, H), H, dtype=torch.float32, device=a.device)
 
 
 class _RMSNorm_Cute(torch.autograd.Function):
@@ -77,10 +105,8 @@ class _RMSNorm_Cute(torch.autograd.Function):
     def backward(ctx, output_grad: torch.Tensor):
         x, weight, inv_rms = ctx.saved_tensors
         x_grad = torch.empty_like(x)
-        weight_grad = None if weight is None else torch.zeros_like(weight, dtype=torch.float32)
-        _bwd(x, weight, output_grad, None, inv_rms, x_grad, None, weight_grad, ctx.eps, 1.0)
-        if weight_grad is not None:
-            weight_grad = weight_grad.type_as(weight)
+        weight_grad, parts = _weight_grad_buffers(x, weight)
+        _bwd(x, weight, output_grad, None, inv_rms, x_grad, None, parts, weight_grad, ctx.eps, 1.0)
         return x_grad, weight_grad, None, None
 
 
@@ -110,10 +136,8 @@ class _FusedResidualAddRMSNorm_Cute(torch.autograd.Function):
         added, weight, inv_rms = ctx.saved_tensors
         x_grad = torch.empty_like(added)
         residual_grad = torch.empty_like(added)
-        weight_grad = None if weight is None else torch.zeros_like(weight, dtype=torch.float32)
-        _bwd(added, weight, output_grad, added_grad, inv_rms, x_grad, residual_grad, weight_grad, ctx.eps, ctx.multiplier)
-        if weight_grad is not None:
-            weight_grad = weight_grad.type_as(weight)
+        weight_grad, parts = _weight_grad_buffers(added, weight)
+        _bwd(added, weight, output_grad, added_grad, inv_rms, x_grad, residual_grad, parts, weight_grad, ctx.eps, ctx.multiplier)
         return x_grad, residual_grad, weight_grad, None, None, None
 
 

@@ -284,15 +284,19 @@ CK_API int ck_moe_row_dots(const void *a, const int32_t *pos, const void *b, voi
  *   r = rsqrt(mean(a^2) + eps), stored to inv_rms_out [rows] fp32 when given; out = a * r * weight.
  * ck_rmsnorm_bwd:  `a` is what the forward normalised (x, or added_out); g = dy * weight;
  *   da = r * g - a * r^3 * mean(g * a) (+ d_added when given: the gradient arriving through the residual stream);
- *   d_residual = da (when given), dx = da * multiplier; d_weight [H] fp32 += sum over rows of dy * a * r (caller
- *   zeroes it; atomically accumulated).  inv_rms NULL: r is recomputed from `a` (memory_efficient=True upstream).
+ *   d_residual = da (when given), dx = da * multiplier; d_weight [H] (in `dtype`, fully overwritten) = sum over rows of
+ *   dy * a * r: every block of the backward kernel stores its share as one row of dw_partial
+ *   (fp32 [ck_rmsnorm_bwd_parts(rows, H), H], caller-owned, needs no initialisation) and a second kernel adds the rows
+ *   in a fixed order -- reproducible, where the reference accumulates with tl.atomic_add.  d_weight NULL: no weight
+ *   gradient, dw_partial unused.  inv_rms NULL: r is recomputed from `a` (memory_efficient=True upstream).
  * Pass multiplier = 1 where the reference passes None. */
 CK_API int ck_rmsnorm_fwd(const void *x, const void *residual, const void *weight, void *out, void *added_out,
                           float *inv_rms_out, int64_t rows, int64_t H, float eps, float multiplier, int dtype,
                           void *stream);
+CK_API int64_t ck_rmsnorm_bwd_parts(int64_t rows, int64_t H);
 CK_API int ck_rmsnorm_bwd(const void *a, const void *weight, const void *dy, const void *d_added, const float *inv_rms,
-                          void *dx, void *d_residual, float *d_weight, int64_t rows, int64_t H, float eps,
-                          float multiplier, int dtype, void *stream);
+                          void *dx, void *d_residual, float *dw_partial, void *d_weight, int64_t rows, int64_t H,
+                          float eps, float multiplier, int dtype, void *stream);
 
 /* ---- router tail --------------------------------------------------------------------------------
  * ck_router_topk_softmax: for each token, the k largest of its E gate logits (descending; ties to the lower

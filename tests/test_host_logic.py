@@ -246,3 +246,25 @@ def test_module_traces_under_fullgraph_compile_without_graph_breaks():
         finally:
             # the refusal interrupts the traced graph inside route()'s no_grad region: restore grad mode
             torch.set_grad_enabled(True)
+
+
+def test_balanced_expert_placement_and_state_dict_round_trip():
+    import cute_kernels as ck
+    from cute_kernels.expert_parallel import shard_expert_state_dict
+
+    loads = [100, 5, 5, 5, 90, 5, 5, 80]
+    placement = ck.balanced_expert_placement(loads, 4)
+    assert sorted(placement.count(r) for r in range(4)) == [2, 2, 2, 2]
+    per_rank = [sum(l for l, r in zip(loads, placement) if r == g) for g in range(4)]
+    assert max(per_rank) == 105                      # contiguous blocks would give 105, 10, 95, 85: same bound here ...
+    assert max(per_rank) - min(per_rank) <= 100      # ... but the heavy experts land on different ranks
+    assert len({placement[0], placement[4], placement[7]}) == 3
+    skew = [64, 32, 16, 8, 4, 2, 1, 1]
+    pl = ck.balanced_expert_placement(skew, 2)
+    assert max(sum(l for l, r in zip(skew, pl) if r == g) for g in range(2)) < sum(skew[:4])
+    with pytest.raises(ValueError):
+        ck.balanced_expert_placement([1, 2, 3], 2)
+    sd = {"gate.weight": torch.zeros(8, 4), "c_fc.weight": torch.arange(8.0).view(8, 1, 1).expand(8, 2, 3).contiguous()}
+    for g in range(4):
+        local = shard_expert_state_dict(sd, g, 4, placement)
+        assert local["c_fc.weight"][:, 0, 0].tolist() == [float(e) for e in range(8) if placement[e] == g]

@@ -257,10 +257,12 @@ def test_fused_activations_and_biases_against_oracle(act, with_bias, determinist
     b_fc = 0.1 * torch.randn(E, w_fc.size(1), generator=g) if with_bias else None
     b_proj = 0.1 * torch.randn(E, H, generator=g) if with_bias else None
 
-    leaf = lambda t: None if t is None else t.clone().requires_grad_()  # noqa: E731
+    # the oracle sees the bf16-representable values the kernels get (bias gradients are short sums with cancellation:
+    # input rounding would otherwise dominate their near-zero entries)
+    leaf = lambda t: None if t is None else t.to(torch.bfloat16).float().requires_grad_()  # noqa: E731
     rx, rrw, rwf, rwp, rbf, rbp = map(leaf, (inp["x"], inp["router_weights"], w_fc, inp["w_proj"], b_fc, b_proj))
     yr = orc.moe_experts_ref(rx, rrw, inp["selected_experts"], rwf, rwp, act_fn, rbf, rbp)
-    yr.backward(inp["grad_out"])
+    yr.backward(inp["grad_out"].to(torch.bfloat16).float())
 
     dt = torch.bfloat16
     dev = lambda t: None if t is None else t.to(dt).cuda().requires_grad_()  # noqa: E731

@@ -12,18 +12,21 @@ pytestmark = pytest.mark.gpu
 
 
 def _virtual_world(world, max_tokens, H, k, dt):
-    from cute_kernels.peer_parallel import PeerBuffers
+    from cute_kernels.peer_parallel import PeerBuffers, packed_publication
 
     S = max_tokens * k
     dev = torch.device("cuda")
-    raw = [dict(tokens=torch.full((max_tokens, H), float("nan"), dtype=dt, device=dev),
-                rows=torch.full((S, H), float("nan"), dtype=dt, device=dev),
-                weights=torch.full((S,), float("nan"), dtype=dt, device=dev),
-                dgates=torch.full((S,), float("nan"), dtype=torch.float32, device=dev),
-                ids=torch.empty(S, dtype=torch.int32, device=dev)) for _ in range(world)]
+    raw = []
+    for _ in range(world):
+        published, ids, weights = packed_publication(S, dt, dev)
+        raw.append(dict(tokens=torch.full((max_tokens, H), float("nan"), dtype=dt, device=dev),
+                        rows=torch.full((S, H), float("nan"), dtype=dt, device=dev),
+                        weights=weights, dgates=torch.full((S,), float("nan"), dtype=torch.float32, device=dev),
+                        ids=ids, published=published))
     ptrs = {name: [r[name].data_ptr() for r in raw] for name in ("tokens", "rows", "dgates")}
     return [PeerBuffers(rank, world, max_tokens, k, raw[rank]["tokens"], raw[rank]["rows"], raw[rank]["weights"],
-                        raw[rank]["dgates"], raw[rank]["ids"], ptrs["tokens"], ptrs["rows"], ptrs["dgates"])
+                        raw[rank]["dgates"], raw[rank]["ids"], ptrs["tokens"], ptrs["rows"], ptrs["dgates"],
+                        raw[rank]["published"])
             for rank in range(world)]
 
 
@@ -35,6 +38,11 @@ CASES = [
     dict(world=8, E=8, k=2, T=[40] * 8, H=256, I=128, seed=4),
     dict(world=2, E=8, k=2, T=[300, 300], H=128, I=256, seed=5, min_tiles_to_split=4),   # two-window pull, small
     dict(world=2, E=4, k=2, T=[1500, 1400], H=64, I=64, seed=6, min_tiles_to_split=16),  # two-window pull, larger
+    dict(world=4, E=8, k=2, T=[130, 97, 5, 256], H=64, I=72, seed=7, fused_pull=True),   # rows pulled by the GEMM's own producer warp
+    dict(world=2, E=16, k=4, T=[257, 0], H=64, I=136, seed=8, fused_pull=True),
+    dict(world=4, E=8, k=2, T=[130, 97, 5, 256], H=64, I=72, seed=9, capacity=4.0),      # no read-back of the row count
+    dict(world=2, E=8, k=2, T=[300, 300], H=128, I=256, seed=10, capacity=1.5, placement=[1, 0, 0, 1, 1, 0, 1, 0]),
+    dict(world=4, E=16, k=4, T=[200, 190, 210, 64], H=64, I=136, seed=11, placement="balanced", expert_bias=True),
 ]
 
 
@@ -46,28 +54,40 @@ def test_peer_engine_lockstep(cfg, dt):
 
     world, E, k, H, I = cfg["world"], cfg["E"], cfg["k"], cfg["H"], cfg["I"]
     Ts = cfg["T"]
-    full = orc.gen_moe_inputs(cfg["seed"], sum(Ts), H, I, E, k, False)
+    full = orc.gen_moe_inputs(cfg["seed"], sum(Ts), H, I, E, k, cfg.get("expert_bias", False))
     ref = orc.moe_fwd_bwd_ref(full)
     epr = E // world
     starts = [sum(Ts[:r]) for r in range(world)]
     sl = [slice(starts[r], starts[r] + Ts[r]) for r in range(world)]
-    bufs = _virtual_world(world, max(max(Ts), 1), H, k, dt)
-    eng = [PeerExpertEngine(b, E) for b in bufs]
+    max_tokens = max(max(Ts), 1)
+    bufs = _virtual_world(world, max_tokens, H, k, dt)
+    placement = cfg.get("placement")
+    if placement == "balanced":  # experts spread over the ranks by the rows they receive
+        loads = torch.bincount(full["selected_experts"].reshape(-1), minlength=E).tolist()
+        placement = ck.balanced_expert_placement(loads, world)
+        per_rank = [sum(loads[e] for e in range(E) if placement[e] == r) for r in range(world)]
+        blocks = [sum(loads[r * epr:(r + 1) * epr]) for r in range(world)]
+        assert max(per_rank) <= max(blocks)
+    cap_rows = None if "capacity" not in cfg else int(cfg["capacity"] * max_tokens * k) + epr * 128
+    eng = [PeerExpertEngine(b, E, expert_to_rank=placement, capacity_rows=cap_rows) for b in bufs]
     for e in eng:
         e.MIN_TILES_TO_SPLIT = cfg.get("min_tiles_to_split", e.MIN_TILES_TO_SPLIT)
-    w_fc = [full["w_fc"][r * epr:(r + 1) * epr].to(dt).cuda().contiguous() for r in range(world)]
-    w_proj = [full["w_proj"][r * epr:(r + 1) * epr].to(dt).cuda().contiguous() for r in range(world)]
+        e.FUSED_PULL = cfg.get("fused_pull", False)
+    owned_ids = [e.local_expert_ids for e in eng]
+    w_fc = [full["w_fc"][owned_ids[r]].to(dt).cuda().contiguous() for r in range(world)]
+    w_proj = [full["w_proj"][owned_ids[r]].to(dt).cuda().contiguous() for r in range(world)]
 
     # ---- forward, phase by phase ----
     for r in range(world):
         eng[r].publish(full["x"][sl[r]].to(dt).cuda(), full["router_weights"][sl[r]].to(dt).cuda(),
                        full["selected_experts"][sl[r]].to(torch.int32).cuda())
-    ids_all = torch.cat([b.ids for b in bufs])
-    weights_all = torch.cat([b.weights for b in bufs])
+    # the all-gather of the packed (ids | weights) buffers, done by hand
+    ids_all, weights_all = bufs[0].split_published(torch.cat([b.published for b in bufs]))
+    assert torch.equal(ids_all, torch.cat([b.ids for b in bufs]))
     plans = [eng[r].plan(ids_all) for r in range(world)]
     owned = sum(int(p.routing.counts[:epr].long().sum()) for p in plans)
     assert owned == sum(Ts) * k                       # every routed row has exactly one owner
-    if cfg["seed"] >= 5:
+    if cfg["seed"] in (5, 6):
         assert all(p.split > 0 for p in plans)        # these cases exercise the overlapped two-window pull
     saved = [eng[r].fwd_compute(plans[r], weights_all, w_fc[r], w_proj[r], True) for r in range(world)]
     ys = [eng[r].fwd_finish(Ts[r]) for r in range(world)]
@@ -83,7 +103,7 @@ def test_peer_engine_lockstep(cfg, dt):
     n = sum(Ts)
     wtol = dict(rtol=tol["rtol"], atol=tol["atol"] * max(1.0, (n / 64) ** 0.5))
     for r in range(world):
-        el = slice(r * epr, (r + 1) * epr)
+        el = owned_ids[r]
         torch.testing.assert_close(ys[r].float().cpu(), ref["y"][sl[r]], **tol)
         dx, d_rw = backs[r]
         torch.testing.assert_close(dx.float().cpu(), ref["dx"][sl[r]], **tol)
