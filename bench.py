@@ -94,6 +94,31 @@ def host_info() -> tuple[int, str]:
     return os.cpu_count() or 1, model
 
 
+def bind_to_gpu_numa_node(device_index: int) -> int | None:
+    """Runs this process on the CPUs of the NUMA node the GPU hangs off, so that the pinned staging buffers it allocates
+    afterwards (first touch) and the copies it issues stay on that node's memory and PCIe root.  Reads sysfs only; returns
+    the node, or None when the topology is not exposed (single-node hosts, containers without the PCI tree)."""
+    try:
+        prop = torch.cuda.get_device_properties(device_index)
+        bdf = f"{prop.pci_domain_id:04x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus: set[int] = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 # ---------------------------------------------------------------------------------------------------
 # synthetic inputs
 # ---------------------------------------------------------------------------------------------------
@@ -232,18 +257,24 @@ def _within(got: torch.Tensor, ref: torch.Tensor, atol: float, rtol: float = 2e-
     return float((err / (atol + rtol * ref.float().abs())).max().item()), float(err.max().item())
 
 
-def parity_check(inp: dict, y: torch.Tensor, dx: torch.Tensor, w: dict, world: int, rank: int, n_tokens: int = 32) -> dict:
+def parity_check(inp: dict, y: torch.Tensor, dx: torch.Tensor, w: dict, world: int, rank: int, n_tokens: int = 32,
+                 placement: list[int] | None = None) -> dict:
     """Recomputes, in fp32 with plain torch on the GPU, what the timed step must have produced, from the same inputs:
     y and dx of ``n_tokens`` sampled tokens of this rank (each needs only its own k experts), and the first 64 rows of
     both weight gradients of this rank's first expert over the rows of ALL ranks routed to it.  Every rank builds its
-    expert weights from the same seed and shape, so expert e's weights are entry ``e % experts_per_rank`` of every
-    rank's local tensors: each rank can restate any expert without an exchange.  Tolerance: rtol 2e-2 with atol 2e-2
+    expert weights from the same seed and shape, so expert e's weights are entry ``slot[e]`` (its position among its
+    owner's experts; ``e % experts_per_rank`` for contiguous blocks) of every rank's local tensors: each rank can restate
+    any expert without an exchange.  Tolerance: rtol 2e-2 with atol 2e-2
     taken relative to the reference's RMS (outputs / input grads) or scaled by sqrt(rows / 64) (weight grads)."""
     import torch.distributed as dist
     import torch.nn.functional as F
 
     T, H, I, E, k = w["T"], w["H"], w["I"], w["E"], w["k"]
     epr = E // world
+    if placement is None:
+        placement = [e // epr for e in range(E)]
+    slot = [sum(1 for f in range(e) if placement[f] == placement[e]) for e in range(E)]  # local index at the owner
+    mine = [e for e in range(E) if placement[e] == rank]
     dev = y.device
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -260,9 +291,9 @@ def parity_check(inp: dict, y: torch.Tensor, dx: torch.Tensor, w: dict, world: i
         for j in range(k):
             for e in sel[toks, j].unique().tolist():
                 m = (sel[toks, j] == e).nonzero().squeeze(1)
-                h = F.linear(xs[m], w_fc[e % epr].float())
+                h = F.linear(xs[m], w_fc[slot[e]].float())
                 a = h[:, :I] * F.silu(h[:, I:])
-                ys = ys.index_add(0, m, F.linear(a, w_proj[e % epr].float()) * rw[toks[m], j].float().unsqueeze(1))
+                ys = ys.index_add(0, m, F.linear(a, w_proj[slot[e]].float()) * rw[toks[m], j].float().unsqueeze(1))
         ys.backward(go[toks].float())
         rms = lambda t: max(1.0, float(t.float().pow(2).mean().sqrt().item()))  # noqa: E731
         checks["y"] = _within(y[toks], ys.detach(), 2e-2 * rms(ys.detach()))
@@ -277,7 +308,7 @@ def parity_check(inp: dict, y: torch.Tensor, dx: torch.Tensor, w: dict, world: i
             return out
 
         x_all, rw_all, sel_all, go_all = gathered(x), gathered(rw), gathered(sel), gathered(go)
-        e_glob = rank * epr
+        e_glob = mine[0]
         tok_e, slot_e = (sel_all == e_glob).nonzero(as_tuple=True)
         n_e = int(tok_e.numel())
         rows = 64
@@ -327,6 +358,7 @@ def gpu_arm(args, w: dict) -> dict | None:
         raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torch.distributed.run), found WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    numa_node = bind_to_gpu_numa_node(local_rank) if world > 1 else None
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
@@ -339,15 +371,31 @@ def gpu_arm(args, w: dict) -> dict | None:
         assert E % world == 0, "experts must divide evenly across ranks"
         epr = E // world
         inp = make_device_inputs(w, device, seed=1000 + rank, experts=slice(rank * epr, (rank + 1) * epr))
-        ep, transport = None, "nccl_all_to_all"
+        ep, transport, placement = None, "nccl_all_to_all", None
         if args.ep_transport in ("auto", "peer"):
             # rows move by NVLink loads / stores issued from the permutation kernels and the GEMM epilogues
             ok = torch.ones(1, device=device)
             try:
                 from cute_kernels.peer_parallel import PeerExpertParallelMoE
 
-                ep = PeerExpertParallelMoE(E, k, T, H, torch.bfloat16, dist.group.WORLD)
-                transport = "peer_memory"
+                # balanced routing (no per-expert bias): rows per rank stay within a few percent of T * k, so a fixed
+                # capacity replaces the per-step read-back of the row count; the skewed configuration reads it back
+                # expert placement: contiguous blocks, or balanced by the rows every expert receives (all ranks' routing of
+                # this batch; a training loop would use a running histogram)
+                use_balanced = args.ep_placement == "balanced" or (args.ep_placement == "auto" and w["expert_bias"])
+                if use_balanced:
+                    from cute_kernels.expert_parallel import balanced_expert_placement
+
+                    hist = torch.bincount(inp["selected_experts"].reshape(-1).long(), minlength=E).float()
+                    dist.all_reduce(hist)
+                    placement = balanced_expert_placement(hist.tolist(), world)
+                if args.ep_capacity_factor != 0:
+                    cap_factor = args.ep_capacity_factor if args.ep_capacity_factor > 0 else None
+                else:
+                    cap_factor = None if w["expert_bias"] else 1.25
+                ep = PeerExpertParallelMoE(E, k, T, H, torch.bfloat16, dist.group.WORLD, capacity_factor=cap_factor,
+                                           expert_to_rank=placement)
+                transport = "peer_memory" + ("+balanced_placement" if placement is not None else "")
             except Exception as exc:  # symmetric memory not available on this box
                 if args.ep_transport == "peer":
                     raise
@@ -355,7 +403,7 @@ def gpu_arm(args, w: dict) -> dict | None:
                 ok.zero_()
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
             if ok.item() == 0:
-                ep, transport = None, "nccl_all_to_all"
+                ep, transport, placement = None, "nccl_all_to_all", None
         if ep is None:
             ep = ExpertParallelMoE(E, k, dist.group.WORLD)
 
@@ -484,7 +532,7 @@ def gpu_arm(args, w: dict) -> dict | None:
         zero_wgrads()
         y_chk, dx_chk = step(inp["x"], inp["router_weights"], inp["selected_experts"], inp["grad_out"])
         torch.cuda.synchronize()
-        parity = parity_check(inp, y_chk.detach(), dx_chk, w, world, rank)
+        parity = parity_check(inp, y_chk.detach(), dx_chk, w, world, rank, placement=placement if world > 1 else None)
         del y_chk, dx_chk
         zero_wgrads()
         ck.check_device_status()
@@ -554,7 +602,8 @@ def gpu_arm(args, w: dict) -> dict | None:
         "data": "synthetic",
         "config": {"workload": w["name"], "tokens_per_gpu": T, "hidden": H, "intermediate": I, "experts": E, "top_k": k,
                    "parallelism": f"ep{world}" if world > 1 else "single",
-                   **({"ep_transport": transport} if world > 1 else {}), "l2_policy": "inputs_exceed_l2",
+                   **({"ep_transport": transport, "host_numa_node_rank0": numa_node} if world > 1 else {}),
+                   "l2_policy": "inputs_exceed_l2",
                    "step": "route+gather+up_swiglu+down_combine+backward(dgrad,wgrad,swiglu_bwd,router_grad)"},
         "clocks": clocks,
         "e2e": {"value": world * T / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
@@ -591,6 +640,33 @@ def _time_each(fn, steps: int, warmup: int, flush: torch.Tensor | None) -> list[
         torch.cuda.synchronize()
         out.append(e0.elapsed_time(e1))
     return out
+
+
+def _time_kernels(fn, steps: int, warmup: int, flush: torch.Tensor | None) -> tuple[float, float]:
+    """(median device time of this library's launches inside one call of ``fn``, median time of the whole call).
+    The first is bracketed by CUDA events around each C-ABI call on the launching stream; the second also holds whatever
+    the caller's framework does around them (autograd dispatch, allocations) while the GPU waits."""
+    from cute_kernels import _lib
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    kern, whole = [], []
+    for _ in range(steps):
+        if flush is not None:
+            flush.add_(1)
+        _lib.launch_log.reset()
+        _lib.launch_log.record_events = True
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        _lib.launch_log.record_events = False
+        whole.append(e0.elapsed_time(e1))
+        kern.append(sum(a.elapsed_time(b) for _n, _w, a, b in _lib.launch_log.events))
+    _lib.launch_log.reset()
+    return statistics.median(kern), statistics.median(whole)
 
 
 def measure_c2(steps: int, warmup: int, flush: torch.Tensor, peak: float) -> dict:
@@ -656,8 +732,8 @@ def measure_rmsnorm(steps: int, warmup: int, flush: torch.Tensor, peak: float) -
     nel = rows * cols
     out = {"shape": [rows, cols]}
     with torch.no_grad():
-        f_ms = statistics.median(_time_each(lambda: ck.rmsnorm_cute(x, w, 1e-5), steps, warmup, flush))
-        ff_ms = statistics.median(_time_each(lambda: ck.fused_residual_add_rmsnorm_cute(x, res, w, 1e-5, 0.9), steps, warmup, flush))
+        f_ms = _time_kernels(lambda: ck.rmsnorm_cute(x, w, 1e-5), steps, warmup, flush)
+        ff_ms = _time_kernels(lambda: ck.fused_residual_add_rmsnorm_cute(x, res, w, 1e-5, 0.9), steps, warmup, flush)
     z = ck.rmsnorm_cute(x, w, 1e-5)
     zf, rf = ck.fused_residual_add_rmsnorm_cute(x, res, w, 1e-5, 0.9)
 
@@ -669,11 +745,13 @@ def measure_rmsnorm(steps: int, warmup: int, flush: torch.Tensor, peak: float) -
         x.grad = res.grad = w.grad = None
         torch.autograd.backward([zf, rf], [dy, dy], retain_graph=True)
 
-    b_ms = statistics.median(_time_each(bwd, steps, warmup, flush))
-    fb_ms = statistics.median(_time_each(fbwd, steps, warmup, flush))
-    for name, ms, elems in (("fwd", f_ms, 2), ("bwd", b_ms, 3), ("fused_fwd", ff_ms, 4), ("fused_bwd", fb_ms, 5)):
+    b_ms = _time_kernels(bwd, steps, warmup, flush)
+    fb_ms = _time_kernels(fbwd, steps, warmup, flush)
+    # ms / gbs / frac: the kernels' own device time; op_ms: the whole call as a user makes it (the backward goes through
+    # the autograd engine, whose dispatch leaves the GPU idle for tens of microseconds on a 100-microsecond kernel)
+    for name, (ms, op_ms), elems in (("fwd", f_ms, 2), ("bwd", b_ms, 3), ("fused_fwd", ff_ms, 4), ("fused_bwd", fb_ms, 5)):
         gbs = elems * 2.0 * nel / (ms * 1e-3) / 1e9
-        out[name] = dict(ms=ms, gbs=gbs, frac=gbs / peak, algorithmic_bytes=elems * 2 * nel)
+        out[name] = dict(ms=ms, op_ms=op_ms, gbs=gbs, frac=gbs / peak, algorithmic_bytes=elems * 2 * nel)
     return out
 
 
@@ -719,6 +797,80 @@ def measure_moe_brief(w: dict, steps: int, warmup: int, device: torch.device, pe
                 tokens_per_s=T / (ms * 1e-3), gemm_ms_per_step=gemm_ms, gemm_tflops=flops / (gemm_ms * 1e-3) / 1e12,
                 gemm_frac_of_measured_sustained=flops / (gemm_ms * 1e-3) / 1e12 / peak_tflops,
                 kernels_ms_per_step={n: round(v, 4) for n, v in sorted(per.items())})
+
+
+def gemm_cycle_profile(w: dict, device: torch.device) -> dict:
+    """Cycle accounting of the four CTA-pair GEMM launches of one layer shape, one isolated launch each.
+
+    Needs a library built with ``make -C cute-kernels_b200/csrc clean all EXTRA=-DCK_GEMM_PROFILE`` (it exports
+    ck_gemm_profile_read; the default build does not).  Per GEMM: cycles of the issuing thread per pair tile against the
+    tensor pipe's 4096 MAC/clk/SM, where the issuing and the loading warps spent their time, and how long the epilogue
+    warps were busy."""
+    import ctypes
+
+    import cute_kernels as ck
+    from cute_kernels import _lib
+    from cute_kernels.moe import dgates_parts, dgrad_down, dgrad_up, down_combine_fwd, up_act_fwd
+
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    if not hasattr(lib, "ck_gemm_profile_read"):
+        raise SystemExit("the library was not built with -DCK_GEMM_PROFILE")
+    T, H, I, E, k = w["T"], w["H"], w["I"], w["E"], w["k"]
+    dt = torch.bfloat16
+    g = torch.Generator(device=device).manual_seed(0)
+    ids = torch.randn(T, E, generator=g, device=device).topk(k, dim=-1).indices.int()
+    r = ck.route(ids.reshape(-1), E)
+    cap = r.capacity
+    rows = int((r.row_map >= 0).sum())
+    gate_w = torch.rand(T * k, generator=g, device=device).to(dt)
+    xg = torch.randn(cap, H, generator=g, device=device).to(dt)
+    w_proj = torch.empty(E, H, I, device=device, dtype=dt).normal_(0, 0.02, generator=g)
+    w_fc = torch.empty(E, 2 * I, H, device=device, dtype=dt).normal_(0, 0.02, generator=g)
+    h = torch.randn(cap, 2 * I, generator=g, device=device).to(dt)
+    dh = torch.empty(cap, 2 * I, device=device, dtype=dt)
+    act = torch.randn(cap, I, generator=g, device=device).to(dt)
+    dg_part = torch.empty(dgates_parts(I), cap, device=device, dtype=torch.float32)
+    out32 = torch.zeros(T, H, device=device, dtype=torch.float32)
+    swiglu = _lib.CK_ACT_SWIGLU
+    launches = {
+        "up_act_fwd": (lambda: up_act_fwd(xg, w_fc, None, gate_w, r.row_map, r.mtile_off, act, dh, swiglu), 2.0 * rows * H * 2 * I, H),
+        "down_combine_fwd": (lambda: down_combine_fwd(act, w_proj, None, None, r.row_map, r.mtile_off, out32, k), 2.0 * rows * H * I, I),
+        "dgrad_down": (lambda: dgrad_down(xg, w_proj, h, gate_w, r.row_map, r.mtile_off, dh, None, dg_part, swiglu), 2.0 * rows * H * I, H),
+        "dgrad_up": (lambda: dgrad_up(dh, w_fc, r.row_map, r.mtile_off, out32, k), 2.0 * rows * H * 2 * I, 2 * I),
+    }
+    slots, ctas = 16, 160
+    out = {}
+    for name, (fn, flops, K) in launches.items():
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        buf = (ctypes.c_ulonglong * (ctas * slots))()
+        if lib.ck_gemm_profile_read(buf) != 0:
+            raise SystemExit("ck_gemm_profile_read failed")
+        n_ctas = 2 * (torch.cuda.get_device_properties(device).multi_processor_count // 2)
+        rows_ = [[float(buf[c * slots + i]) for i in range(slots)] for c in range(n_ctas)]
+        lead, peer = rows_[0::2], rows_[1::2]
+        mean = lambda xs: sum(xs) / len(xs)  # noqa: E731
+        total = mean([c[2] for c in lead])
+        tiles = mean([c[3] for c in lead])
+        ideal = tiles * (K / 64.0) * 512.0  # 128 x 256 x 64 MACs per CTA and k-block at 4096 MAC/clk
+        out[name] = dict(ms=round(ms, 4), tflops=round(flops / ms / 1e9, 1), pair_tiles_per_cta_pair=round(tiles, 1),
+                         issuer_kcycles=round(total / 1e3, 1), tensor_pipe_frac_of_4096_mac_per_clk=round(ideal / total, 4),
+                         sm_mhz_during_launch=round(total / ms / 1e3, 0),
+                         issuer_wait_accumulator_frac=round(mean([c[0] / c[2] for c in lead]), 4),
+                         issuer_wait_stage_frac=round(mean([c[1] / c[2] for c in lead]), 4),
+                         issuer_stage_ready_frac=round(mean([c[8] / max(c[9], 1.0) for c in lead]), 4),
+                         producer_stage_free_frac=round(mean([c[10] / max(a[9], 1.0) for c, a in zip(peer, lead)]), 4),
+                         producer_wait_frac=round(mean([c[11] / max(c[12], 1.0) for c in peer]), 4),
+                         epilogue_busy_frac=round(mean([c[5] / c[2] for c in lead]), 4))
+    ck.check_device_status()
+    return out
 
 
 def micro_arm(args, which: str) -> dict:
@@ -774,7 +926,21 @@ def main() -> None:
     ap.add_argument("--ep-transport", default="auto", choices=["auto", "peer", "nccl"],
                     help="N > 1: rows cross GPUs by peer-memory loads/stores from the kernels (default when symmetric "
                          "memory is available) or by NCCL all-to-all")
+    ap.add_argument("--ep-placement", default="auto", choices=["auto", "block", "balanced"],
+                    help="N > 1, peer transport: experts in contiguous blocks per rank, or placed by load (longest processing "
+                         "time first); auto = balanced for the skewed configuration, blocks otherwise")
+    ap.add_argument("--ep-capacity-factor", type=float, default=0.0,
+                    help="N > 1, peer transport: rows allocated per rank = factor x tokens x top_k (no read-back of the row "
+                         "count); negative = exact read-back every step; 0 = 1.25 for balanced routing, read-back for the skewed one")
+    ap.add_argument("--gemm-cycles", action="store_true",
+                    help="profile builds of the library only: per-role cycle accounting of the grouped GEMMs (no bench line)")
     args = ap.parse_args()
+    if args.gemm_cycles:
+        torch.cuda.set_device(0)
+        w = WORKLOADS[args.workload if args.workload in WORKLOADS else "c4"]
+        print(json.dumps(dict(metric="gemm_cycle_profile", config=dict(workload=w["name"]),
+                              kernels=gemm_cycle_profile(w, torch.device("cuda", 0)))))
+        return
     if args.workload in ("c2", "c3"):
         if args.warmup < 3:
             args.warmup = 3

@@ -71,7 +71,6 @@ struct GemmParams {
     int l2_hint_a;    // ptx::L2_EVICT_* for the tiled loads of A / B (CTA-pair kernels)
     int l2_hint_b;
     uint64_t wait_limit_ns;  // bound of every mbarrier wait (0: kWaitLimitNs)
-    int dbg;                 // timing probes (CK_GEMM_DEBUG)
     // STORE with peer destinations (n_peers > 0): row row_map[p] of the result belongs to global slot
     // g = dst_flat ? dst_flat[row_map[p]] : row_map[p] and is
     // stored at peer_out[g / peer_rows] + (g % peer_rows) * N (another GPU's memory over NVLink, or this GPU's own buffer)
@@ -941,42 +940,56 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                 // aborting: give copies already in flight time to land before the CTA exits
                 for (int i = 0; i < 2000; ++i) __nanosleep(1000);
             }
-        } else if (lane == 0) {
+        } else {
+            // The whole warp runs the loop converged and one elected lane issues (uniform loop control, addresses and
+            // coordinates); the next stage's "empty" barrier is probed before this stage's loads go out.
+            const uint32_t elected = ptx::elect_one();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            bool ready = false;
+            const uint32_t empty0 = ptx::smem_u32(&ctl->empty[0]);
+            const uint32_t full0 = ptx::smem_u32(&ctl->full[0]);
             for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
                 const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
                 for (int kb = 0; kb < c.k_iters; ++kb) {
-                    if (!wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status)) { ok = false; break; }
-                    const uint32_t full = ptx::smem_u32(&ctl->full[stage]);
-                    ptx::mbar_expect_tx(full, kAStageBytes + kBStageBytes);
+                    if (!ready) {
+                        const bool w = wait_barrier(empty0 + 8u * stage, phase ^ 1u, ctl, p.dev_status);
+                        if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                    }
+                    int nstage = stage + 1;
+                    uint32_t nphase = phase;
+                    if (nstage == kStages) { nstage = 0; nphase ^= 1u; }
+                    ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(empty0 + 8u * nstage, nphase ^ 1u)) != 0;
+                    const uint32_t full = full0 + 8u * stage;
+                    ptx::mbar_expect_tx_elected(elected, full, kAStageBytes + kBStageBytes);
                     const uint32_t sa = smem_a + stage * kAStageBytes;
                     const uint32_t sb = smem_b + stage * kBStageBytes;
                     if constexpr (MODE == MODE_WGRAD) {
                         const int krow = c.k_row0 + kb * BK;
 #pragma unroll
                         for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
-                            ptx::tma_load_2d(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
+                            ptx::tma_load_2d_elected(elected, sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow);
 #pragma unroll
                         for (int j = 0; j < BN / TR::kMnBoxElems; ++j)
-                            ptx::tma_load_2d(sb + j * TR::kMnBoxBytes, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, krow);
+                            ptx::tma_load_2d_elected(elected, sb + j * TR::kMnBoxBytes, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, krow);
                     } else {
                         const int k0 = kb * BK;
-                        ptx::tma_load_2d(sa, &p.tmA, full, k0, c.m_tile * BM);
+                        ptx::tma_load_2d_elected(elected, sa, &p.tmA, full, k0, c.m_tile * BM);
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < BN / TR::kMnBoxElems; ++j)
-                                ptx::tma_load_3d(sb + j * TR::kMnBoxBytes, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, k0, c.e);
+                                ptx::tma_load_3d_elected(elected, sb + j * TR::kMnBoxBytes, &p.tmB, full, c.n_tile * BN + j * TR::kMnBoxElems, k0, c.e);
                         } else if constexpr (MODE == MODE_UP_ACT) {
                             // 128 rows of W_up followed by the matching 128 rows of W_gate
-                            ptx::tma_load_3d(sb, &p.tmB, full, k0, c.n_tile * (BN / 2), c.e);
-                            ptx::tma_load_3d(sb + kBStageBytes / 2, &p.tmB, full, k0, p.N + c.n_tile * (BN / 2), c.e);
+                            ptx::tma_load_3d_elected(elected, sb, &p.tmB, full, k0, c.n_tile * (BN / 2), c.e);
+                            ptx::tma_load_3d_elected(elected, sb + kBStageBytes / 2, &p.tmB, full, k0, p.N + c.n_tile * (BN / 2), c.e);
                         } else {
-                            ptx::tma_load_3d(sb, &p.tmB, full, k0, c.n_tile * BN, c.e);
+                            ptx::tma_load_3d_elected(elected, sb, &p.tmB, full, k0, c.n_tile * BN, c.e);
                         }
                     }
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    stage = nstage;
+                    phase = nphase;
                 }
             }
             if (!ok) {
@@ -987,36 +1000,54 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
         __syncwarp();
     } else if (warp == 1) {
         // =================================== MMA issuer =====================================
-        if (lane == 0) {
+        // The warp runs the loop converged, one elected lane issues; the next stage's barrier is probed before this
+        // stage's MMAs go out (see the CTA-pair kernel below for why the path between two k-blocks has to be short).
+        {
+            const uint32_t elected = ptx::elect_one();
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
             bool ok = true;
+            bool ready = false;
+            const uint32_t full0 = ptx::smem_u32(&ctl->full[0]);
+            const uint32_t empty0 = ptx::smem_u32(&ctl->empty[0]);
+            uint64_t adesc0, bdesc0;
+            if constexpr (A_MN) adesc0 = ptx::umma_desc_mnmajor<TR::kTf32>(smem_a, TR::kMnBoxBytes);
+            else adesc0 = ptx::umma_desc_kmajor(smem_a);
+            if constexpr (B_MN) bdesc0 = ptx::umma_desc_mnmajor<TR::kTf32>(smem_b, TR::kMnBoxBytes);
+            else bdesc0 = ptx::umma_desc_kmajor(smem_b);
+            constexpr uint32_t kAStep = A_MN ? (TR::UMMA_K * kRowBytes) >> 4 : 32u >> 4;  // per k-step, in 16-byte units
+            constexpr uint32_t kBStep = B_MN ? (TR::UMMA_K * kRowBytes) >> 4 : 32u >> 4;
             for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++it) {
                 const TileCoord c = decode_tile<MODE, BK>(p, ctl, t);
                 const int buf = it & 1;
-                if (!wait_barrier(ptx::smem_u32(&ctl->tmem_empty[buf]), ((uint32_t(it) >> 1) & 1u) ^ 1u, ctl, p.dev_status)) { ok = false; break; }
+                {
+                    const bool w = wait_barrier(ptx::smem_u32(&ctl->tmem_empty[buf]), ((uint32_t(it) >> 1) & 1u) ^ 1u, ctl, p.dev_status);
+                    if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + uint32_t(buf) * BN;
                 for (int kb = 0; kb < c.k_iters; ++kb) {
-                    if (!wait_barrier(ptx::smem_u32(&ctl->full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
-                    ptx::tc_fence_after();
-                    const uint32_t sa = smem_a + stage * kAStageBytes;
-                    const uint32_t sb = smem_b + stage * kBStageBytes;
-#pragma unroll
-                    for (int k = 0; k < TR::kSteps; ++k) {
-                        uint64_t adesc, bdesc;
-                        if constexpr (A_MN) adesc = ptx::umma_desc_mnmajor<TR::kTf32>(sa + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
-                        else adesc = ptx::umma_desc_kmajor(sa + k * 32);
-                        if constexpr (B_MN) bdesc = ptx::umma_desc_mnmajor<TR::kTf32>(sb + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
-                        else bdesc = ptx::umma_desc_kmajor(sb + k * 32);
-                        ptx::umma_ss<TR::kTf32>(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    if (!ready) {
+                        const bool w = wait_barrier(full0 + 8u * stage, phase, ctl, p.dev_status);
+                        if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
                     }
-                    ptx::tc_commit(ptx::smem_u32(&ctl->empty[stage]));  // frees the stage when these MMAs retire
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    int nstage = stage + 1;
+                    uint32_t nphase = phase;
+                    if (nstage == kStages) { nstage = 0; nphase ^= 1u; }
+                    ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(full0 + 8u * nstage, nphase)) != 0;
+                    const uint64_t adesc = adesc0 + uint64_t(uint32_t(stage) * uint32_t(kAStageBytes >> 4));
+                    const uint64_t bdesc = bdesc0 + uint64_t(uint32_t(stage) * uint32_t(kBStageBytes >> 4));
+#pragma unroll
+                    for (int k = 0; k < TR::kSteps; ++k)
+                        ptx::umma_ss_elected<TR::kTf32>(elected, d_tmem, adesc + uint64_t(k * kAStep), bdesc + uint64_t(k * kBStep), kIdesc,
+                                                        (kb | k) != 0 ? 1u : 0u);
+                    ptx::tc_commit_elected(elected, empty0 + 8u * stage);  // frees the stage when these MMAs retire
+                    stage = nstage;
+                    phase = nphase;
                 }
                 if (!ok) break;
-                ptx::tc_commit(ptx::smem_u32(&ctl->tmem_full[buf]));  // accumulator complete
+                ptx::tc_commit_elected(elected, ptx::smem_u32(&ctl->tmem_full[buf]));  // accumulator complete
             }
             if (!ok) {
                 for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -1161,6 +1192,39 @@ __device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams &p, const
     return c;
 }
 
+// Cycle accounting of the CTA-pair kernel's roles (compiled in with -DCK_GEMM_PROFILE only; `make EXTRA=-DCK_GEMM_PROFILE`).
+// Every launch overwrites one row of counters per CTA; ck_gemm_profile_read copies them out.  This is how the issue
+// loops were tuned: with the data always present (PROF_MMA_READY = PROF_KBLOCKS) and the tensor pipe still idle a sixth
+// of the time, the limit was the issuing thread's own instruction stream, not memory.
+#ifdef CK_GEMM_PROFILE
+enum {
+    PROF_MMA_WAIT_TMEM = 0,  // issuer: cycles waiting for the epilogue to free an accumulator buffer
+    PROF_MMA_WAIT_FULL,      // issuer: cycles in the blocking wait for a stage (entered only when the probe said "not yet")
+    PROF_MMA_TOTAL,          // issuer: cycles from first to last tile
+    PROF_TILES,              // pair tiles of this CTA pair
+    PROF_EPI_WAIT,           // first epilogue warp: cycles waiting for an accumulator
+    PROF_EPI_BUSY,           // first epilogue warp: cycles in the fused tail
+    PROF_EPI_LAST_WAIT,      // the same for the last epilogue warp
+    PROF_EPI_LAST_BUSY,
+    PROF_MMA_READY,          // issuer: k-blocks whose stage had already landed when the probe looked
+    PROF_KBLOCKS,            // issuer: k-blocks
+    PROF_TMA_READY,          // producer: k-blocks whose stage was already free
+    PROF_TMA_WAIT,           // producer: cycles in the blocking wait for a free stage
+    PROF_TMA_TOTAL,          // producer: cycles from first to last tile
+    kProfSlots = 16
+};
+constexpr int kProfMaxCtas = 160;
+__device__ unsigned long long g_prof[kProfMaxCtas * kProfSlots];
+#define CK_PROF(...) __VA_ARGS__
+#define PROF_T0() const long long _pt0 = clock64()
+#define PROF_ADD(var) var += clock64() - _pt0
+#define PROF_PUT(slot, v) g_prof[(blockIdx.x % kProfMaxCtas) * kProfSlots + (slot)] = (unsigned long long)(v)
+#else
+#define CK_PROF(...)
+#define PROF_T0()
+#define PROF_ADD(var)
+#define PROF_PUT(slot, v)
+#endif
 template <typename T, int MODE, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kThreads, 1)
     grouped_gemm_pair_kernel(const __grid_constant__ GemmParams p) {
@@ -1308,45 +1372,65 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kT
             if (!ok && lane == 0) {
                 for (int i = 0; i < 2000; ++i) __nanosleep(1000);
             }
-        } else if (lane == 0) {
+        } else {
+            // The whole warp runs the loop converged and one elected lane issues, so that loop control, addresses and
+            // coordinates stay warp-uniform; the next stage's "empty" barrier is probed before this stage's loads go out.
+            const uint32_t elected = ptx::elect_one();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            bool ready = false;
             const uint64_t pol_a = ptx::l2_policy(p.l2_hint_a), pol_b = ptx::l2_policy(p.l2_hint_b);
+            const uint32_t empty0 = ptx::smem_u32(&ctl->empty[0]);
+            const uint32_t full0_local = ptx::smem_u32(&ctl->full[0]);
+            const uint32_t full0 = ptx::mapa_shared(full0_local, 0);  // the leader's barriers
+            CK_PROF(long long pp_hit = 0, pp_wait = 0; const long long pp_start = clock64();)
             for (int t = pair_id; t < ntiles && ok; t += num_pairs) {
-                const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
+                TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
+                const int nb0 = c.n_tile * BN + rank * (BN / 2);  // this CTA's half of the N range
                 for (int kb = 0; kb < c.k_iters; ++kb) {
-                    if (!wait_barrier(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.dev_status)) { ok = false; break; }
-                    if (rank == 0) ptx::mbar_expect_tx(ptx::smem_u32(&ctl->full[stage]), stage_tx);
-                    const uint32_t full = ptx::mapa_shared(ptx::smem_u32(&ctl->full[stage]), 0);  // the leader's barrier
+                    CK_PROF(pp_hit += ready ? 1 : 0;)
+                    if (!ready) {
+                        PROF_T0();
+                        const bool w = wait_barrier(empty0 + 8u * stage, phase ^ 1u, ctl, p.dev_status);
+                        PROF_ADD(pp_wait);
+                        if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                    }
+                    int nstage = stage + 1;
+                    uint32_t nphase = phase;
+                    if (nstage == kNStages) { nstage = 0; nphase ^= 1u; }
+                    ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(empty0 + 8u * nstage, nphase ^ 1u)) != 0;
+                    if (rank == 0) ptx::mbar_expect_tx_elected(elected, full0_local + 8u * stage, stage_tx);
+                    const uint32_t full = full0 + 8u * stage;
                     const uint32_t sa = smem_a + stage * kAStageBytes;
                     const uint32_t sb = smem_b + stage * kBHalfStageBytes;
-                    const int nb0 = c.n_tile * BN + rank * (BN / 2);  // this CTA's half of the N range
                     if constexpr (MODE == MODE_WGRAD) {
                         const int krow = c.k_row0 + kb * BK;
 #pragma unroll
                         for (int j = 0; j < BM / TR::kMnBoxElems; ++j)
-                            ptx::tma_load_2d_pair_hint(sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow, pol_a);
+                            ptx::tma_load_2d_pair_hint_elected(elected, sa + j * TR::kMnBoxBytes, &p.tmA, full, c.m_tile * BM + j * TR::kMnBoxElems, krow, pol_a);
 #pragma unroll
                         for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
-                            ptx::tma_load_2d_pair_hint(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow, pol_b);
+                            ptx::tma_load_2d_pair_hint_elected(elected, sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, krow, pol_b);
                     } else {
                         const int k0 = kb * BK;
-                        if (!row_gather) ptx::tma_load_2d_pair_hint(sa, &p.tmA, full, k0, c.m_tile * BM, pol_a);
+                        if (!row_gather) ptx::tma_load_2d_pair_hint_elected(elected, sa, &p.tmA, full, k0, c.m_tile * BM, pol_a);
                         if constexpr (B_MN) {
 #pragma unroll
                             for (int j = 0; j < (BN / 2) / TR::kMnBoxElems; ++j)
-                                ptx::tma_load_3d_pair_hint(sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, k0, c.e, pol_b);
+                                ptx::tma_load_3d_pair_hint_elected(elected, sb + j * TR::kMnBoxBytes, &p.tmB, full, nb0 + j * TR::kMnBoxElems, k0, c.e, pol_b);
                         } else if constexpr (MODE == MODE_UP_ACT) {
                             // leader: 128 rows of W_up, peer: the matching 128 rows of W_gate
-                            ptx::tma_load_3d_pair_hint(sb, &p.tmB, full, k0, rank * p.N + c.n_tile * (BN / 2), c.e, pol_b);
+                            ptx::tma_load_3d_pair_hint_elected(elected, sb, &p.tmB, full, k0, rank * p.N + c.n_tile * (BN / 2), c.e, pol_b);
                         } else {
-                            ptx::tma_load_3d_pair_hint(sb, &p.tmB, full, k0, nb0, c.e, pol_b);
+                            ptx::tma_load_3d_pair_hint_elected(elected, sb, &p.tmB, full, k0, nb0, c.e, pol_b);
                         }
                     }
-                    if (++stage == kNStages) { stage = 0; phase ^= 1u; }
+                    stage = nstage;
+                    phase = nphase;
                 }
             }
+            CK_PROF(if (elected) { PROF_PUT(PROF_TMA_READY, pp_hit); PROF_PUT(PROF_TMA_WAIT, pp_wait); PROF_PUT(PROF_TMA_TOTAL, clock64() - pp_start); })
             if (!ok) {
                 for (int i = 0; i < 2000; ++i) __nanosleep(1000);
             }
@@ -1354,40 +1438,75 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kT
         __syncwarp();
     } else if (warp == 1) {
         // ================= MMA issuer: the leader CTA drives both tensor cores =================
-        if (lane == 0 && rank == 0) {
+        // One thread feeds the tensor cores, and the instructions it runs between the last MMA of one k-block and the first
+        // of the next are a gap in which the pipe drains (measured: 4 x 128 cycles of MMA + ~80 cycles of gap per k-block,
+        // more when epilogue warps compete for the scheduler's issue slots).  The loop therefore keeps that path short: the
+        // next stage's barrier is probed (non-blocking) BEFORE this stage's MMAs are issued, so the probe's latency hides
+        // behind them and the blocking wait is only entered when the data really is late; operand descriptors advance by
+        // constant adds; no tcgen05 fence sits between TMA-filled stages (the mbarrier orders the async-proxy writes).
+        if (rank == 0) {
+            // the whole warp runs the loop converged (uniform control and descriptor arithmetic); one elected lane issues
+            const uint32_t elected = ptx::elect_one();
             int stage = 0;
             uint32_t phase = 0;
             int it = 0;
             bool ok = true;
+            CK_PROF(long long prof_a = 0, prof_b = 0, prof_hit = 0, prof_n = 0; const long long prof_start = clock64();)
+            const uint32_t full0 = ptx::smem_u32(&ctl->full[0]);
+            const uint32_t empty0 = ptx::smem_u32(&ctl->empty[0]);
+            // descriptors of stage 0, k-step 0; a stage further adds (stage bytes >> 4) to the low word
+            uint64_t adesc0, bdesc0;
+            if constexpr (A_MN) adesc0 = ptx::umma_desc_mnmajor<TR::kTf32>(smem_a, TR::kMnBoxBytes);
+            else adesc0 = ptx::umma_desc_kmajor(smem_a);
+            if constexpr (B_MN) bdesc0 = ptx::umma_desc_mnmajor<TR::kTf32>(smem_b, TR::kMnBoxBytes);
+            else bdesc0 = ptx::umma_desc_kmajor(smem_b);
+            constexpr uint32_t kAStep = A_MN ? (TR::UMMA_K * kRowBytes) >> 4 : 32u >> 4;  // per k-step, in 16-byte units
+            constexpr uint32_t kBStep = B_MN ? (TR::UMMA_K * kRowBytes) >> 4 : 32u >> 4;
+            auto probe = [&](int st, uint32_t ph) -> bool {
+                // rows written by the other CTA's row-gather warps are released at cluster scope
+                const bool r = row_gather ? ptx::mbar_test_wait_cluster(full0 + 8u * st, ph) : ptx::mbar_test_wait(full0 + 8u * st, ph);
+                return __all_sync(0xffffffffu, r) != 0;  // one answer for the warp
+            };
+            bool ready = false;
             for (int t = pair_id; t < ntiles && ok; t += num_pairs, ++it) {
                 const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, 0);
                 const int buf = it & 1;
-                if (!wait_barrier(ptx::smem_u32(&ctl->tmem_empty[buf]), ((uint32_t(it) >> 1) & 1u) ^ 1u, ctl, p.dev_status)) { ok = false; break; }
+                { PROF_T0();
+                const bool w = wait_barrier(ptx::smem_u32(&ctl->tmem_empty[buf]), ((uint32_t(it) >> 1) & 1u) ^ 1u, ctl, p.dev_status);
+                PROF_ADD(prof_a);
+                if (!__all_sync(0xffffffffu, w)) { ok = false; break; } }
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + uint32_t(buf) * BN;
                 for (int kb = 0; kb < c.k_iters; ++kb) {
-                    // rows written by the other CTA's row-gather warps are released at cluster scope
-                    if (p.dbg & 1) {
-                        if (!wait_barrier(ptx::smem_u32(&ctl->full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
-                    } else if (!wait_barrier<false, true>(ptx::smem_u32(&ctl->full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
-                    ptx::tc_fence_after();
-                    const uint32_t sa = smem_a + stage * kAStageBytes;
-                    const uint32_t sb = smem_b + stage * kBHalfStageBytes;
-#pragma unroll
-                    for (int k = 0; k < TR::kSteps; ++k) {
-                        uint64_t adesc, bdesc;
-                        if constexpr (A_MN) adesc = ptx::umma_desc_mnmajor<TR::kTf32>(sa + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
-                        else adesc = ptx::umma_desc_kmajor(sa + k * 32);
-                        if constexpr (B_MN) bdesc = ptx::umma_desc_mnmajor<TR::kTf32>(sb + k * TR::UMMA_K * kRowBytes, TR::kMnBoxBytes);
-                        else bdesc = ptx::umma_desc_kmajor(sb + k * 32);
-                        ptx::umma_ss_pair<TR::kTf32>(d_tmem, adesc, bdesc, kIdesc, (kb | k) != 0 ? 1u : 0u);
+                    CK_PROF(prof_hit += ready ? 1 : 0; ++prof_n;)
+                    if (!ready) {
+                        PROF_T0();
+                        const bool w = row_gather ? wait_barrier<false, true>(full0 + 8u * stage, phase, ctl, p.dev_status)
+                                                  : wait_barrier<false, false>(full0 + 8u * stage, phase, ctl, p.dev_status);
+                        PROF_ADD(prof_b);
+                        if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
                     }
-                    ptx::tc_commit_pair(ptx::smem_u32(&ctl->empty[stage]), 3);  // frees the stage in both CTAs
-                    if (++stage == kNStages) { stage = 0; phase ^= 1u; }
+                    int nstage = stage + 1;
+                    uint32_t nphase = phase;
+                    if (nstage == kNStages) { nstage = 0; nphase ^= 1u; }
+                    ready = probe(nstage, nphase);  // consumed in the next iteration (possibly of the next tile)
+                    const uint64_t adesc = adesc0 + uint64_t(uint32_t(stage) * uint32_t(kAStageBytes >> 4));
+                    const uint64_t bdesc = bdesc0 + uint64_t(uint32_t(stage) * uint32_t(kBHalfStageBytes >> 4));
+#pragma unroll
+                    for (int k = 0; k < TR::kSteps; ++k)
+                        ptx::umma_ss_pair_elected<TR::kTf32>(elected, d_tmem, adesc + uint64_t(k * kAStep), bdesc + uint64_t(k * kBStep), kIdesc,
+                                                             (kb | k) != 0 ? 1u : 0u);
+                    ptx::tc_commit_pair_elected(elected, empty0 + 8u * stage, 3);  // frees the stage in both CTAs
+                    stage = nstage;
+                    phase = nphase;
                 }
                 if (!ok) break;
-                ptx::tc_commit_pair(ptx::smem_u32(&ctl->tmem_full[buf]), 3);  // accumulators of both CTAs complete
+                ptx::tc_commit_pair_elected(elected, ptx::smem_u32(&ctl->tmem_full[buf]), 3);  // accumulators of both CTAs complete
             }
+            CK_PROF(if (elected) {
+                PROF_PUT(PROF_MMA_WAIT_TMEM, prof_a); PROF_PUT(PROF_MMA_WAIT_FULL, prof_b); PROF_PUT(PROF_MMA_TOTAL, clock64() - prof_start);
+                PROF_PUT(PROF_TILES, it); PROF_PUT(PROF_MMA_READY, prof_hit); PROF_PUT(PROF_KBLOCKS, prof_n);
+            })
             if (!ok) {
                 for (int i = 0; i < 2000; ++i) __nanosleep(1000);
             }
@@ -1444,9 +1563,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kT
                             const bool live = v >= 0 && in_k;
                             const T *base = reinterpret_cast<const T *>(p.n_src_peers > 0 ? p.peer_src[live ? (v >> kPeerRowBits) : 0] : p.a_src);
                             const int64_t row = live ? int64_t(v & ((1 << kPeerRowBits) - 1)) : 0;
-                            if ((p.dbg & 8) && (i & 1)) continue;
-                            if (p.dbg & 4) ptx::cp_async_16_full(dst, base + row * int64_t(p.K) + (live ? col : 0));
-                            else
                             ptx::cp_async_16(dst, base + row * int64_t(p.K) + (live ? col : 0), live ? 16u : 0u);  // 0 bytes read: zero fill
                         }
                         ptx::cp_async_mbar_arrive_noinc(ptx::smem_u32(&ctl->a_full[stage]));
@@ -1464,10 +1580,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kT
                     const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
                     const bool store_tile = store_rows && c.valid && c.n_tile == 0;
                     for (int kb = 0; kb < c.k_iters; ++kb) {
-                        if (p.dbg & 16) {
-                            if (!wait_barrier(ptx::smem_u32(&ctl->a_full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
-                        } else if (!wait_barrier<true>(ptx::smem_u32(&ctl->a_full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
-                        if (!(p.dbg & 2)) ptx::fence_proxy_async();
+                        if (!wait_barrier<true>(ptx::smem_u32(&ctl->a_full[stage]), phase, ctl, p.dev_status)) { ok = false; break; }
+                        ptx::fence_proxy_async();
                         if (store_tile) {
                             ptx::tma_store_2d(&p.tmOut, smem_a + stage * kAStageBytes, kb * BK, c.m_tile * BM);
                             ptx::bulk_commit_group();
@@ -1501,19 +1615,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kT
         constexpr int kColsPerGroup = kCols / CFG::kEpiGroups;
         int it = 0;
         bool ok = true;
+        CK_PROF(long long prof_w = 0, prof_e = 0;)
         for (int t = pair_id; t < ntiles && ok; t += num_pairs, ++it) {
             const TileCoord c = decode_pair_tile<MODE, BK>(p, ctl, t, rank);
             const int buf = it & 1;
+            { PROF_T0();
             if (!wait_barrier<true>(ptx::smem_u32(&ctl->tmem_full[buf]), (uint32_t(it) >> 1) & 1u, ctl, p.dev_status)) { ok = false; break; }
+            PROF_ADD(prof_w); }
             ptx::tc_fence_after();
             const uint32_t tbase = tmem_base + uint32_t(buf) * BN + (uint32_t(quarter * 32) << 16);
+            { PROF_T0();
             if (c.valid)
                 epilogue_tile<T, MODE, CFG::kPitch>(p, c, tbase, row_in_tile, es, group * kColsPerGroup, (group + 1) * kColsPerGroup,
                                                     c.n_tile * CFG::kEpiGroups + group);
+            PROF_ADD(prof_e); }
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(buf ? leader_empty1 : leader_empty0);
         }
+        CK_PROF(if (lane == 0 && ew == 0) { PROF_PUT(PROF_EPI_WAIT, prof_w); PROF_PUT(PROF_EPI_BUSY, prof_e); }
+                if (lane == 0 && ew == CFG::kEpiWarpsTotal - 1) { PROF_PUT(PROF_EPI_LAST_WAIT, prof_w); PROF_PUT(PROF_EPI_LAST_BUSY, prof_e); })
         if (MODE == MODE_STORE && p.n_peers > 0) __threadfence_system();  // stores to other GPUs land before the kernel ends
     }
 
@@ -1606,11 +1727,6 @@ static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t stream) {
     } else {
         p.l2_hint_a = (p.K <= 8192) ? ptx::L2_EVICT_LAST : ptx::L2_EVICT_NORMAL;
         p.l2_hint_b = ptx::L2_EVICT_NORMAL;
-    }
-    {
-        static int dbg = -1;
-        if (dbg < 0) { const char *e = getenv("CK_GEMM_DEBUG"); dbg = e ? atoi(e) : 0; }
-        p.dbg = dbg;
     }
     if (use_cta_pair()) {
         auto kern2 = grouped_gemm_pair_kernel<T, MODE, B_MN>;
@@ -1999,6 +2115,14 @@ extern "C" int ck_test_wait_timeout(int64_t limit_ns, int32_t *result4, int32_t 
     return CK_OK;
 }
 
+#ifdef CK_GEMM_PROFILE
+// Profile builds only: copies the last launch's counters, [160 CTAs][16 slots] of uint64, to `host` (synchronises the device).
+extern "C" __attribute__((visibility("default"))) int ck_gemm_profile_read(unsigned long long *host) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(host, g_prof, sizeof(g_prof));
+    return e == cudaSuccess ? CK_OK : CK_ERR_CUDA;
+}
+#endif
 extern "C" int ck_gemm_cta_pair(void) { return use_cta_pair() ? 1 : 0; }
 
 extern "C" int ck_set_gemm_cta_pair(int enable) {

@@ -35,6 +35,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// non-blocking probe of a phase (try_wait may suspend the thread for a while; this never does)
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_test_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // acquire at cluster scope: pairs with mbarrier.arrive.release.cluster from the other CTA of a pair
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -93,9 +120,6 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint3
 // arrival is counted against the barrier's initial count (.noinc)
 __device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async_16_full(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -294,6 +318,145 @@ __device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t adesc, ui
             "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
             "}\n" ::"r"(d_tmem),
             "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+
+// Predicated forms for a converged producer / issuer warp: only the lane with `elected` != 0 issues.
+__device__ __forceinline__ void tma_load_2d_elected(uint32_t elected, uint32_t dst, const CUtensorMap *tm, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "{\n"
+        ".reg .pred q;\n"
+        "setp.ne.b32 q, %5, 0;\n"
+        "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        "}\n" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(c0), "r"(c1), "r"(elected)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_elected(uint32_t elected, uint32_t dst, const CUtensorMap *tm, uint32_t bar, int c0, int c1,
+                                                    int c2) {
+    asm volatile(
+        "{\n"
+        ".reg .pred q;\n"
+        "setp.ne.b32 q, %6, 0;\n"
+        "@q cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+        "}\n" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(elected)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_elected(uint32_t elected, uint32_t bar) {
+    asm volatile(
+        "{\n"
+        ".reg .pred q;\n"
+        "setp.ne.b32 q, %1, 0;\n"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+        "}\n" ::"r"(bar),
+        "r"(elected)
+        : "memory");
+}
+template <bool KIND_TF32>
+__device__ __forceinline__ void umma_ss_elected(uint32_t elected, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate) {
+    if constexpr (KIND_TF32) {
+        asm volatile(
+            "{\n"
+            ".reg .pred p, q;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "setp.ne.b32 q, %5, 0;\n"
+            "@q tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(elected)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n"
+            ".reg .pred p, q;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "setp.ne.b32 q, %5, 0;\n"
+            "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(elected)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void mbar_expect_tx_elected(uint32_t elected, uint32_t bar, uint32_t bytes) {
+    asm volatile(
+        "{\n"
+        ".reg .pred q;\n"
+        "setp.ne.b32 q, %2, 0;\n"
+        "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n"
+        "}\n" ::"r"(bar),
+        "r"(bytes), "r"(elected)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair_hint_elected(uint32_t elected, uint32_t dst, const CUtensorMap *tm, uint32_t bar_cluster,
+                                                              int c0, int c1, uint64_t pol) {
+    asm volatile(
+        "{\n"
+        ".reg .pred q;\n"
+        "setp.ne.b32 q, %6, 0;\n"
+        "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;\n"
+        "}\n" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar_cluster), "r"(c0), "r"(c1), "l"(pol), "r"(elected)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair_hint_elected(uint32_t elected, uint32_t dst, const CUtensorMap *tm, uint32_t bar_cluster,
+                                                              int c0, int c1, int c2, uint64_t pol) {
+    asm volatile(
+        "{\n"
+        ".reg .pred q;\n"
+        "setp.ne.b32 q, %7, 0;\n"
+        "@q cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;\n"
+        "}\n" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2), "l"(pol), "r"(elected)
+        : "memory");
+}
+// One lane of a converged warp, the same lane on every call (nonzero in that lane only).
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t is_elected;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(is_elected));
+    return is_elected;
+}
+// The same two operations issued by the lane with `elected` != 0 while the whole warp runs the surrounding loop converged
+// (loop control and descriptor arithmetic stay warp-uniform).
+__device__ __forceinline__ void tc_commit_pair_elected(uint32_t elected, uint32_t bar, uint16_t mask) {
+    asm volatile(
+        "{\n"
+        ".reg .pred q;\n"
+        "setp.ne.b32 q, %2, 0;\n"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+        "}\n" ::"r"(bar),
+        "h"(mask), "r"(elected)
+        : "memory");
+}
+template <bool KIND_TF32>
+__device__ __forceinline__ void umma_ss_pair_elected(uint32_t elected, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                     uint32_t accumulate) {
+    if constexpr (KIND_TF32) {
+        asm volatile(
+            "{\n"
+            ".reg .pred p, q;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "setp.ne.b32 q, %5, 0;\n"
+            "@q tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(elected)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n"
+            ".reg .pred p, q;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "setp.ne.b32 q, %5, 0;\n"
+            "@q tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(elected)
             : "memory");
     }
 }

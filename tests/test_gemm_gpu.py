@@ -322,6 +322,66 @@ def test_fused_backward_pieces(dtype, act_kind, case):
     torch.testing.assert_close(dx32.cpu(), exp_dx, **tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_swiglu_epilogues_on_the_negative_gate_tail(dtype):
+    """Gates in [-12, -3]: the 16-bit epilogues compute sigmoid(x) = 0.5 + 0.5 tanh.approx(x / 2), whose absolute error
+    (about 2.4e-4 on the sigmoid) is a large RELATIVE error where silu is tiny.  Forward and backward must stay within
+    rtol 2e-2 plus an explicit absolute 4e-3 (|gate| * 2.4e-4 * |up| <= 12 * 2.4e-4 * |up|) of the exact fp32 formulas."""
+    from cute_kernels.moe import dgrad_down, gather_rows, up_act_fwd
+
+    counts, H, I, k = [130, 70, 0, 56], 64, 128, 2
+    p = _moe_problem(counts, H, I, k, dtype, seed=3)
+    r, ref, E, T = p["r"], p["ref"], p["E"], p["T"]
+    total = int(ref["padded_off"][-1])
+    rm = torch.from_numpy(ref["row_map"][:total].astype(np.int64))
+    valid = rm >= 0
+    tol = dict(rtol=2e-2, atol=4e-3)
+
+    # forward: feature 0 of every token is 1 and W_gate reads only that feature, so gate[j] = -g_j exactly
+    x = p["x"].clone()
+    x[:, 0] = 1.0
+    g_j = torch.linspace(3.0, 12.0, I)
+    w_fc = p["w_fc"].clone()
+    w_fc[:, I:, :] = 0
+    w_fc[:, I:, 0] = (-g_j).to(dtype).cuda()
+    xg = torch.empty(r.capacity, H, dtype=dtype, device="cuda")
+    gather_rows(x, xg, r.row_map, r.padded_off, k)
+    act = torch.full((r.capacity, I), float("nan"), dtype=dtype, device="cuda")
+    h = torch.full((r.capacity, 2 * I), float("nan"), dtype=dtype, device="cuda")
+    up_act_fwd(xg, w_fc, None, p["gate_w"], r.row_map, r.mtile_off, act, h, 0)
+    hf = h[:total].float().cpu()
+    assert hf[valid][:, I:].max() <= -2.9 and hf[valid][:, I:].min() >= -12.1
+    gw = torch.zeros(total)
+    gw[valid] = p["gate_w"].float().cpu()[rm[valid]]
+    exp_act = gw[:, None] * hf[:, :I] * torch.nn.functional.silu(hf[:, I:])  # from the kernel's own saved pre-activations
+    torch.testing.assert_close(act[:total].float().cpu()[valid], exp_act[valid], **tol)
+
+    # backward: saved pre-activations with the gate half in [-12, -3]
+    re = torch.from_numpy(_row_expert(ref, E)[:total])
+    dyg = _padded_rows(ref, H, dtype, 5)
+    hb = _padded_rows(ref, 2 * I, dtype, 6)
+    gen = torch.Generator().manual_seed(7)
+    gates = -(3.0 + 9.0 * torch.rand(r.capacity, I, generator=gen))
+    gates[torch.from_numpy(ref["row_map"] < 0)] = 0
+    hb[:, I:] = gates.to(dtype).cuda()
+    dh = torch.full((r.capacity, 2 * I), float("nan"), dtype=dtype, device="cuda")
+    dgates = torch.zeros(T * k, dtype=torch.float32, device="cuda")
+    dgrad_down(dyg, p["w_proj"], hb, p["gate_w"], r.row_map, r.mtile_off, dh, dgates, None, 0)
+    wp = p["w_proj"].float().cpu()
+    g = torch.zeros(total, I)
+    for e in range(E):
+        rows = re == e
+        g[rows] = dyg[:total].float().cpu()[rows] @ wp[e]
+    hbf = hb[:total].float().cpu()
+    up_, gate_ = hbf[:, :I], hbf[:, I:]
+    s = torch.sigmoid(gate_)
+    exp_dh = torch.cat([gw[:, None] * g * gate_ * s, gw[:, None] * g * up_ * (s + gate_ * s * (1 - s))], dim=1)
+    torch.testing.assert_close(dh[:total].float().cpu(), exp_dh, **tol)
+    exp_dg = torch.zeros(T * k)
+    exp_dg[rm[valid]] = (up_ * gate_ * s * g).sum(-1)[valid]
+    torch.testing.assert_close(dgates.cpu(), exp_dg, rtol=2e-2, atol=4e-3 * I**0.5)
+
+
 def test_bad_arguments_are_rejected():
     from cute_kernels import _lib
 
