@@ -41,6 +41,7 @@ WORKLOADS = {
     "c4s": dict(name="c4_slice_moe_fwd_bwd", T=2048, H=4096, I=14336, E=4, k=2, expert_bias=False),
     "c1": dict(name="c1_small_moe_fwd_bwd", T=512, H=256, I=512, E=8, k=2, expert_bias=False),
 }
+COMBINE_ROWS = {"auto": None, "red": False, "rows": True}  # --combine -> fused_experts(deterministic=...)
 METRIC = "moe_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 # DRAM bytes (read + write) per launch of each GEMM family on the full c4 workload, from a one-pass ncu capture of this
@@ -378,8 +379,8 @@ def gpu_arm(args, w: dict) -> dict | None:
             try:
                 from cute_kernels.peer_parallel import PeerExpertParallelMoE
 
-                # balanced routing (no per-expert bias): rows per rank stay within a few percent of T * k, so a fixed
-                # capacity replaces the per-step read-back of the row count; the skewed configuration reads it back
+                # rows to allocate per step: read back from the device (default; measured equal or faster at 2 GPUs), or a
+                # fixed capacity with no read-back
                 # expert placement: contiguous blocks, or balanced by the rows every expert receives (all ranks' routing of
                 # this batch; a training loop would use a running histogram)
                 use_balanced = args.ep_placement == "balanced" or (args.ep_placement == "auto" and w["expert_bias"])
@@ -389,13 +390,14 @@ def gpu_arm(args, w: dict) -> dict | None:
                     hist = torch.bincount(inp["selected_experts"].reshape(-1).long(), minlength=E).float()
                     dist.all_reduce(hist)
                     placement = balanced_expert_placement(hist.tolist(), world)
-                if args.ep_capacity_factor != 0:
-                    cap_factor = args.ep_capacity_factor if args.ep_capacity_factor > 0 else None
-                else:
-                    cap_factor = None if w["expert_bias"] else 1.25
+                cap_factor = args.ep_capacity_factor if args.ep_capacity_factor > 0 else None
                 ep = PeerExpertParallelMoE(E, k, T, H, torch.bfloat16, dist.group.WORLD, capacity_factor=cap_factor,
                                            expert_to_rank=placement)
-                transport = "peer_memory" + ("+balanced_placement" if placement is not None else "")
+                if args.ep_overlap == "off":
+                    ep.engine.MIN_TILES_TO_SPLIT = None
+                ep.engine.PULL_SMS = args.ep_pull_sms
+                transport = ("peer_memory" + ("+balanced_placement" if placement is not None else "") +
+                             (f"+pull_overlapped_on_{args.ep_pull_sms}_sms" if args.ep_overlap == "on" else ""))
             except Exception as exc:  # symmetric memory not available on this box
                 if args.ep_transport == "peer":
                     raise
@@ -419,7 +421,7 @@ def gpu_arm(args, w: dict) -> dict | None:
         def step(x, rw, sel, grad_out):
             x = x.detach().requires_grad_()
             rw = rw.detach().requires_grad_()
-            y = ck.fused_experts(x, rw, sel, inp["w_fc"], inp["w_proj"], k)
+            y = ck.fused_experts(x, rw, sel, inp["w_fc"], inp["w_proj"], k, deterministic=COMBINE_ROWS.get(args.combine))
             y.backward(grad_out)
             return y, x.grad
 
@@ -491,9 +493,15 @@ def gpu_arm(args, w: dict) -> dict | None:
             ev.record(h2d_stream)
         return dev, ev
 
+    step_marks: list = []  # CK_BENCH_DEBUG: one event per end-to-end step, printed as per-step milliseconds on stderr
+
     def e2e_loop(n_steps: int) -> None:
         pending = stage_in()
         for i in range(n_steps):
+            if os.environ.get("CK_BENCH_DEBUG"):
+                ev_dbg = torch.cuda.Event(enable_timing=True)
+                ev_dbg.record(main_stream)
+                step_marks.append((time.perf_counter(), ev_dbg))
             dev, ev = pending
             if i + 1 < n_steps:
                 pending = stage_in()
@@ -522,6 +530,10 @@ def gpu_arm(args, w: dict) -> dict | None:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item()) / args.steps
+    if step_marks and rank == 0:
+        marks = step_marks[-args.steps:]
+        print("[bench] e2e step starts, device ms: " + " ".join(f"{marks[0][1].elapsed_time(m[1]):.1f}" for m in marks) +
+              " | host ms: " + " ".join(f"{(m[0] - marks[0][0]) * 1e3:.1f}" for m in marks), file=sys.stderr)
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = 2 * T * H * 2
     ck.check_device_status()
@@ -929,9 +941,16 @@ def main() -> None:
     ap.add_argument("--ep-placement", default="auto", choices=["auto", "block", "balanced"],
                     help="N > 1, peer transport: experts in contiguous blocks per rank, or placed by load (longest processing "
                          "time first); auto = balanced for the skewed configuration, blocks otherwise")
+    ap.add_argument("--combine", default="auto", choices=["auto", "red", "rows"],
+                    help="N = 1: how the k expert outputs of a token are summed: fp32 red.add from the GEMM epilogue, or rows "
+                         "stored once and summed in slot order by a second kernel; auto = the library's choice")
+    ap.add_argument("--ep-overlap", default="on", choices=["on", "off"],
+                    help="N > 1, peer transport: pull most of the routed rows over NVLink while the GEMM already runs on the "
+                         "first quarter of them (the GEMM leaves --ep-pull-sms SMs to the pull)")
+    ap.add_argument("--ep-pull-sms", type=int, default=16)
     ap.add_argument("--ep-capacity-factor", type=float, default=0.0,
-                    help="N > 1, peer transport: rows allocated per rank = factor x tokens x top_k (no read-back of the row "
-                         "count); negative = exact read-back every step; 0 = 1.25 for balanced routing, read-back for the skewed one")
+                    help="N > 1, peer transport: rows allocated per rank = factor x tokens x top_k with no read-back of the row "
+                         "count; 0 (default) = read the exact count back every step")
     ap.add_argument("--gemm-cycles", action="store_true",
                     help="profile builds of the library only: per-role cycle accounting of the grouped GEMMs (no bench line)")
     args = ap.parse_args()

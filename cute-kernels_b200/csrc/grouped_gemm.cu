@@ -1716,6 +1716,19 @@ static bool use_cta_pair() {
     return g_cta_pair != 0;
 }
 
+// SMs the persistent GEMM grids may occupy (0 = all of them); initial value from CK_GEMM_SMS.  A smaller budget leaves
+// SMs free for kernels of other streams (row pulls over NVLink, collectives) to run beside a GEMM instead of in its tail.
+static int g_sm_budget = -1;
+static int gemm_sms() {
+    if (g_sm_budget < 0) {
+        const char *e = getenv("CK_GEMM_SMS");
+        g_sm_budget = e ? atoi(e) : 0;
+        if (g_sm_budget < 0) g_sm_budget = 0;
+    }
+    const int all = num_sms();
+    return (g_sm_budget > 0 && g_sm_budget < all) ? g_sm_budget : all;
+}
+
 template <typename T, int MODE, bool B_MN>
 static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t stream) {
     // L2 policy of the operand loads.  Inside an expert the tiles run with one dimension fastest: the panels along it
@@ -1733,7 +1746,7 @@ static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t stream) {
         constexpr size_t smem_bytes = pair_smem_bytes<T, MODE>();
         static_assert(smem_bytes <= 227 * 1024, "the CTA-pair kernel's shared memory exceeds what one CTA may own");
         CK_CUDA_TRY(cudaFuncSetAttribute(kern2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-        int64_t pairs = num_sms() / 2;
+        int64_t pairs = gemm_sms() / 2;
         if (pairs > max_tiles) pairs = max_tiles;  // upper bound: a pair tile covers at least one single tile
         if (pairs < 1) return CK_OK;
         kern2<<<dim3((unsigned)(2 * pairs)), PairCfg<T, MODE>::kThreads, smem_bytes, stream>>>(p);
@@ -1742,7 +1755,7 @@ static int launch_gemm(GemmParams &p, int64_t max_tiles, cudaStream_t stream) {
     }
     auto kern = grouped_gemm_kernel<T, MODE, B_MN>;
     CK_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes));
-    int64_t grid = num_sms();
+    int64_t grid = gemm_sms();
     if (grid > max_tiles) grid = max_tiles;
     if (grid < 1) return CK_OK;
     kern<<<dim3((unsigned)grid), kGemmThreads, kGemmSmemBytes, stream>>>(p);
@@ -2124,6 +2137,14 @@ extern "C" __attribute__((visibility("default"))) int ck_gemm_profile_read(unsig
 }
 #endif
 extern "C" int ck_gemm_cta_pair(void) { return use_cta_pair() ? 1 : 0; }
+
+extern "C" int ck_gemm_sm_budget(void) { return gemm_sms(); }
+
+extern "C" int ck_set_gemm_sm_budget(int sms) {
+    const int prev = gemm_sms();
+    g_sm_budget = sms > 0 ? sms : 0;
+    return prev;
+}
 
 extern "C" int ck_set_gemm_cta_pair(int enable) {
     const int prev = use_cta_pair() ? 1 : 0;

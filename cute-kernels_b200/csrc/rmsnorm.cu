@@ -184,8 +184,10 @@ __global__ void __launch_bounds__(kNormBlock)
 // ---- backward ------------------------------------------------------------------------------------------
 // The weight gradient leaves every block as one row of dw_part [gridDim.x, H] (plain stores); rmsnorm_dw_reduce_kernel adds
 // the rows in a fixed order, so the result is reproducible and no atomics hit the same H addresses from every block.
-template <typename T, int G, int VPT>
-__global__ void __launch_bounds__(kNormBlock, VPT <= 2 ? 2 : 1)
+// ADDED: a gradient arrives through the residual stream too (d_added); its rows are prefetched with the others, which takes
+// the registers of a second resident block.
+template <typename T, int G, int VPT, bool ADDED>
+__global__ void __launch_bounds__(kNormBlock, (VPT <= 2 && !ADDED) ? 2 : 1)
     rmsnorm_bwd_kernel(const T *__restrict__ a_in, const T *__restrict__ weight, const T *__restrict__ dy, const T *__restrict__ d_added,
                        const float *__restrict__ inv_rms, T *__restrict__ dx, T *__restrict__ d_residual, float *__restrict__ dw_part,
                        int64_t rows, int H, float eps, float multiplier) {
@@ -208,7 +210,7 @@ __global__ void __launch_bounds__(kNormBlock, VPT <= 2 ? 2 : 1)
     const float inv_h = 1.0f / float(H);
     // rows stay packed (16 bytes per register quad) and are unpacked where they are used; two rows beyond the current one
     // are in flight, which is what keeps enough bytes outstanding per SM at the occupancy the accumulators allow
-    int4 ap[3][VPT], gp[3][VPT];
+    int4 ap[3][VPT], gp[3][VPT], ep[3][ADDED ? VPT : 1];
     auto fetch = [&](int slot, int64_t row) {
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
@@ -217,6 +219,7 @@ __global__ void __launch_bounds__(kNormBlock, VPT <= 2 ? 2 : 1)
                 const int64_t off = row * int64_t(H) + int64_t(c) * VEC;
                 ap[slot][j] = __ldcs(reinterpret_cast<const int4 *>(a_in + off));
                 gp[slot][j] = __ldcs(reinterpret_cast<const int4 *>(dy + off));
+                if constexpr (ADDED) ep[slot][j] = __ldcs(reinterpret_cast<const int4 *>(d_added + off));
             }
         }
     };
@@ -260,9 +263,9 @@ __global__ void __launch_bounds__(kNormBlock, VPT <= 2 ? 2 : 1)
                     da[i] = r * (weight != nullptr ? g[i] * w[i] : g[i]) - coef * a[i];
                     dw[j][i] = fmaf(g[i], a[i] * r, dw[j][i]);
                 }
-                if (d_added != nullptr) {
+                if constexpr (ADDED) {
                     float e[VEC];
-                    load_vec<T>(d_added + off, e);
+                    unpack_vec<T>(ep[slot][j], e);
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) da[i] += e[i];
                 }
@@ -322,22 +325,38 @@ __global__ void __launch_bounds__(kNormBlock, VPT <= 2 ? 2 : 1)
     }
 }
 
-// d_weight[c] = sum over the parts, in order, of dw_part[i, c], written in the weight's dtype
+// d_weight[c] = sum over the parts of dw_part[i, c], written in the weight's dtype.  A block owns 32 columns; its eight
+// warps take the parts i = warp, warp + 8, ... with eight loads in flight each (the rows were just written: L2 hits, and
+// a single chain per column would be latency bound: hundreds of parts times an L2 round trip), then the eight partial sums
+// are added in warp order.  The order of every addition is fixed by the code: reproducible.
+constexpr int kDwCols = 32;
 template <typename T>
 __global__ void __launch_bounds__(kNormBlock) rmsnorm_dw_reduce_kernel(const float *__restrict__ dw_part, int parts, int64_t H,
                                                                        T *__restrict__ d_weight) {
-    const int64_t c = int64_t(blockIdx.x) * kNormBlock + threadIdx.x;
-    if (c >= H) return;
-    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;  // four independent chains, combined in a fixed order
-    int i = 0;
-    for (; i + 4 <= parts; i += 4) {
-        s0 += dw_part[int64_t(i) * H + c];
-        s1 += dw_part[int64_t(i + 1) * H + c];
-        s2 += dw_part[int64_t(i + 2) * H + c];
-        s3 += dw_part[int64_t(i + 3) * H + c];
+    constexpr int kLanes = kNormBlock / kDwCols;  // 8 part lanes
+    __shared__ float acc[kLanes][kDwCols];
+    const int col = threadIdx.x % kDwCols, lane = threadIdx.x / kDwCols;
+    const int64_t c = int64_t(blockIdx.x) * kDwCols + col;
+    float s[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) s[u] = 0.0f;
+    if (c < H) {
+        for (int i = lane; i < parts; i += 8 * kLanes) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int q = i + u * kLanes;
+                if (q < parts) s[u] += dw_part[int64_t(q) * H + c];
+            }
+        }
     }
-    for (; i < parts; ++i) s0 += dw_part[int64_t(i) * H + c];
-    d_weight[c] = DT<T>::down((s0 + s1) + (s2 + s3));
+    acc[lane][col] = ((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]));
+    __syncthreads();
+    if (lane == 0 && c < H) {
+        float total = acc[0][col];
+#pragma unroll
+        for (int l = 1; l < kLanes; ++l) total += acc[l][col];
+        d_weight[c] = DT<T>::down(total);
+    }
 }
 
 template <typename T>
@@ -398,14 +417,33 @@ static void launch_fwd(const void *x, const void *res, const void *w, void *out,
     rmsnorm_fwd_kernel<T, G, VPT><<<norm_grid(ceil_div64(rows, rpb), 8), kNormBlock, 0, s>>>(
         (const T *)x, (const T *)res, (const T *)w, (T *)out, (T *)added, inv, rows, H, eps, mult);
 }
-// blocks of the backward launch = rows of the weight-gradient partial buffer
-static unsigned bwd_grid(int64_t rows, int rows_per_block) { return norm_grid(ceil_div64(rows, rows_per_block), 4); }
+// blocks of the backward launch = rows of the weight-gradient partial buffer: at most kBwdBlocksPerSm per SM
+constexpr int kBwdBlocksPerSm = 4;
+static unsigned bwd_grid(int64_t rows, int rows_per_block, int blocks_per_sm = kBwdBlocksPerSm) {
+    return norm_grid(ceil_div64(rows, rows_per_block), blocks_per_sm);
+}
 
-template <typename T, int G, int VPT>
-static void launch_bwd(const void *a, const void *w, const void *dy, const void *dadd, const float *inv, void *dx, void *dres,
-                       float *dw_part, int64_t rows, int H, float eps, float mult, cudaStream_t s) {
-    rmsnorm_bwd_kernel<T, G, VPT><<<bwd_grid(rows, kNormBlock / G), kNormBlock, 0, s>>>(
+// The grid is exactly what is resident at once (every block then walks the same number of rows: no second, ragged wave,
+// and no more partial weight-gradient rows than needed); returns the number of blocks launched.
+template <typename T, int G, int VPT, bool ADDED>
+static unsigned launch_bwd_t(const void *a, const void *w, const void *dy, const void *dadd, const float *inv, void *dx, void *dres,
+                           float *dw_part, int64_t rows, int H, float eps, float mult, cudaStream_t s) {
+    static int resident = 0;  // blocks of this instantiation per SM
+    if (resident == 0) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, rmsnorm_bwd_kernel<T, G, VPT, ADDED>, kNormBlock, 0) != cudaSuccess || n < 1) n = 1;
+        resident = n > kBwdBlocksPerSm ? kBwdBlocksPerSm : n;
+    }
+    const unsigned grid = bwd_grid(rows, kNormBlock / G, resident);
+    rmsnorm_bwd_kernel<T, G, VPT, ADDED><<<grid, kNormBlock, 0, s>>>(
         (const T *)a, (const T *)w, (const T *)dy, (const T *)dadd, inv, (T *)dx, (T *)dres, dw_part, rows, H, eps, mult);
+    return grid;
+}
+template <typename T, int G, int VPT>
+static unsigned launch_bwd(const void *a, const void *w, const void *dy, const void *dadd, const float *inv, void *dx, void *dres,
+                           float *dw_part, int64_t rows, int H, float eps, float mult, cudaStream_t s) {
+    return dadd ? launch_bwd_t<T, G, VPT, true>(a, w, dy, dadd, inv, dx, dres, dw_part, rows, H, eps, mult, s)
+                : launch_bwd_t<T, G, VPT, false>(a, w, dy, dadd, inv, dx, dres, dw_part, rows, H, eps, mult, s);
 }
 
 // picks (G, VPT) for a row of nvec 16-byte vectors; false: use the generic kernels
@@ -443,9 +481,6 @@ static bool bwd_vectorised(const void *a, const void *w, const void *dy, const v
     return H % VEC == 0 && H / VEC <= 1024 && aligned16(a) && aligned16(dy) && aligned16(dx) && (!w || aligned16(w)) &&
            (!dadd || aligned16(dadd)) && (!dres || aligned16(dres));
 }
-// rows per block of the vectorised backward for a row of nvec vectors (a warp per row up to 128 vectors)
-static int bwd_rows_per_block(int64_t nvec) { return nvec <= 128 ? kNormBlock / 32 : 1; }
-
 template <typename T>
 static int rmsnorm_bwd_t(const void *a, const void *w, const void *dy, const void *dadd, const float *inv, void *dx, void *dres,
                          float *dw_part, void *dw, int64_t rows, int64_t H, float eps, float mult, cudaStream_t s) {
@@ -453,8 +488,8 @@ static int rmsnorm_bwd_t(const void *a, const void *w, const void *dy, const voi
     unsigned parts;
     if (bwd_vectorised<T>(a, w, dy, dadd, dx, dres, H)) {
         const int nvec = int(H / VEC);
-        parts = bwd_grid(rows, bwd_rows_per_block(nvec));
-#define BWD_CALL(TT, GG, VV) launch_bwd<TT, GG, VV>(a, w, dy, dadd, inv, dx, dres, dw_part, rows, int(H), eps, mult, s)
+        parts = 0;
+#define BWD_CALL(TT, GG, VV) parts = launch_bwd<TT, GG, VV>(a, w, dy, dadd, inv, dx, dres, dw_part, rows, int(H), eps, mult, s)
         CK_NORM_DISPATCH(T, nvec, BWD_CALL, BWD_CALL)
 #undef BWD_CALL
     } else {
@@ -465,7 +500,7 @@ static int rmsnorm_bwd_t(const void *a, const void *w, const void *dy, const voi
     }
     CK_LAUNCH_CHECK("rmsnorm_bwd_kernel");
     if (dw) {
-        rmsnorm_dw_reduce_kernel<T><<<unsigned(ceil_div64(H, kNormBlock)), kNormBlock, 0, s>>>(dw_part, int(parts), H, (T *)dw);
+        rmsnorm_dw_reduce_kernel<T><<<unsigned(ceil_div64(H, kDwCols)), kNormBlock, 0, s>>>(dw_part, int(parts), H, (T *)dw);
         CK_LAUNCH_CHECK("rmsnorm_dw_reduce_kernel");
     }
     return CK_OK;

@@ -55,6 +55,8 @@ PROTOTYPES = {
     "ck_moe_grouped_linear": (_i, [_vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_set_gemm_cta_pair": (_i, [_i]),
     "ck_gemm_cta_pair": (_i, []),
+    "ck_set_gemm_sm_budget": (_i, [_i]),
+    "ck_gemm_sm_budget": (_i, []),
     "ck_moe_grouped_linear_scatter": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_moe_bias_grad": (_i, [_vp, _i64, _i, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "ck_moe_bias_dots": (_i, [_vp, _i64, _i, _vp, _vp, _i, _vp, _i, _vp]),
@@ -173,6 +175,23 @@ def check_device_status(device: torch.device | None = None) -> None:
                               (CK_DEV_TIMEOUT, "CK_DEV_TIMEOUT (a bounded device wait ran out)"),
                               (CK_DEV_META, "CK_DEV_META (tile metadata exceeds the allocated rows)")) if v & bit]
     raise RuntimeError("device status: " + ", ".join(names))
+
+
+class gemm_sm_budget:
+    """``with gemm_sm_budget(n):`` -- grouped GEMMs launched inside the block occupy at most ``n`` SMs (0 = all), leaving the
+    rest to kernels of other streams.  The budget is read when a GEMM is launched, so it only has to cover the launch call;
+    it is process-wide (see ck_set_gemm_sm_budget), so do not launch GEMMs from other threads meanwhile."""
+
+    def __init__(self, sms: int) -> None:
+        self.sms, self.prev = int(sms), 0
+
+    def __enter__(self):
+        self.prev = lib.ck_set_gemm_sm_budget(self.sms)
+        return self
+
+    def __exit__(self, *exc):
+        lib.ck_set_gemm_sm_budget(self.prev)
+        return False
 
 
 # ---- launch accounting ------------------------------------------------------------------------------

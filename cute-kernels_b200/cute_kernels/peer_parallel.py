@@ -230,13 +230,15 @@ class PeerExpertEngine:
         rest = r.mtile_off.clamp(min=split) if split else None
         return _Plan(r, rows, max(rows, _lib.CK_TILE_M), split, first, rest)
 
-    # Off by default.  Measured on B200: the pull and the persistent GEMM never become resident on an SM together, in
-    # either launch order (tried 128-thread blocks, at most two per SM, the GEMM's shared-memory carve-out, a high-priority
-    # side stream, a GEMM with 32 KiB less shared memory, the one-CTA GEMM flavour): the second window only runs while the
-    # first GEMM drains, and nothing is hidden.  The GEMM's epilogue warps hold 218-255 registers per thread, which
-    # leaves at most one 64-register warp's worth free in the scheduler partitions that host two of them.  Set to a tile
-    # count (e.g. 16) to run the two-window schedule anyway.
-    MIN_TILES_TO_SPLIT: int | None = None
+    # Two-window schedule: the first quarter of the padded rows is pulled, then the rest is pulled on a side stream WHILE the
+    # GEMM runs on the first window.  A pull kernel never becomes resident on an SM that hosts a persistent GEMM CTA (its warps
+    # hold the whole register file; tried 128-thread blocks, the shared-memory carve-out, a high-priority stream, the one-CTA
+    # flavour: the later kernel always started in the earlier one's tail), so the first-window GEMM is launched on
+    # ``SMS - PULL_SMS`` SMs and the pull gets the rest.  That costs the GEMM next to nothing: the layer runs under the
+    # board's power cap, and a GEMM on 132 of 148 SMs settles at a higher clock (measured on the Mixtral-shaped layer:
+    # 29.02 ms per step on 148 SMs, 29.14 ms on 132, 29.91 ms on 120).  Set MIN_TILES_TO_SPLIT to None for one window.
+    MIN_TILES_TO_SPLIT: int | None = 16
+    PULL_SMS = 16
 
     def _side_stream(self) -> torch.cuda.Stream:
         if self._side is None:
@@ -256,8 +258,10 @@ class PeerExpertEngine:
         _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, 0, edge)
         first_done = torch.cuda.Event()
         first_done.record(main)
-        # the GEMM on the first window is enqueued before the second pull, which waits only for the first pull
-        gemm(plan.mtile_first)
+        # the GEMM on the first window is enqueued before the second pull, which waits only for the first pull; it leaves
+        # PULL_SMS SMs to that pull
+        with _lib.gemm_sm_budget(max(2, _lib.lib.ck_gemm_sm_budget() - self.PULL_SMS)):
+            gemm(plan.mtile_first)
         side.wait_event(first_done)
         with torch.cuda.stream(side):
             _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, edge, plan.cap)

@@ -241,6 +241,12 @@ CK_API int ck_moe_grouped_linear(const void *x, const void *w, const int32_t *mt
  * cutotune knobs (cute_kernels/cutotune/): there is no runtime search, only this switch. */
 CK_API int ck_set_gemm_cta_pair(int enable);
 CK_API int ck_gemm_cta_pair(void); /* the current setting */
+/* SMs the persistent grouped-GEMM grids may occupy: `sms` <= 0 or >= the device's SM count means all of them (the default;
+ * CK_GEMM_SMS in the environment sets the initial value).  A smaller budget leaves SMs free so that kernels launched on
+ * other streams (row pulls over NVLink, collectives) run beside a GEMM instead of in its tail.  Process-wide, like
+ * ck_set_gemm_cta_pair; returns the previous budget.  No counterpart in the reference (its GEMMs are not persistent). */
+CK_API int ck_set_gemm_sm_budget(int sms);
+CK_API int ck_gemm_sm_budget(void); /* SMs in use by the next launch on the current device */
 
 /* same as ck_moe_grouped_linear (plus an optional bias [E, N], scaled by gate_w[row_map[p]] when gate_w is given),
  * but row p of the result is stored at y[row_map[p], :] (pad rows dropped):

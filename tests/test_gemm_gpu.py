@@ -382,6 +382,31 @@ def test_swiglu_epilogues_on_the_negative_gate_tail(dtype):
     torch.testing.assert_close(dgates.cpu(), exp_dg, rtol=2e-2, atol=4e-3 * I**0.5)
 
 
+def test_sm_budget_changes_the_grid_not_the_result():
+    """A grouped GEMM confined to a few SMs (so that another stream's kernels can run beside it) writes the same bits."""
+    from cute_kernels import _lib
+    from cute_kernels.moe import grouped_linear
+
+    counts, K, N = [700, 900, 0, 131], 512, 1024
+    E = len(counts)
+    ids, r, ref = _routing(counts, 1)
+    x = _padded_rows(ref, K, torch.bfloat16, 1)
+    g = torch.Generator().manual_seed(2)
+    w = torch.randn(E, N, K, generator=g).mul(0.1).bfloat16().cuda()
+    full = torch.empty(x.size(0), N, dtype=torch.bfloat16, device="cuda")
+    grouped_linear(x, w, r.mtile_off, full, False)
+    total = int(ref["padded_off"][-1])
+    all_sms = _lib.lib.ck_gemm_sm_budget()
+    assert all_sms == torch.cuda.get_device_properties(0).multi_processor_count
+    for sms in (2, 6, all_sms - 16):
+        y = torch.full_like(full, float("nan"))
+        with _lib.gemm_sm_budget(sms):
+            assert _lib.lib.ck_gemm_sm_budget() == sms
+            grouped_linear(x, w, r.mtile_off, y, False)
+        assert _lib.lib.ck_gemm_sm_budget() == all_sms
+        assert torch.equal(y[:total].view(torch.int16), full[:total].view(torch.int16))
+
+
 def test_bad_arguments_are_rejected():
     from cute_kernels import _lib
 
