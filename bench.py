@@ -473,6 +473,15 @@ def gpu_arm(args, w: dict) -> dict | None:
     ms_total = float(t.item())
     ms_per_step = ms_total / args.steps
     value = world * T / (ms_per_step * 1e-3)
+    # every rank's own GEMM time per step: the ranks meet at four collectives per step, so the slowest GPU under the power
+    # cap sets the pace of all of them
+    rank_gemm_ms = None
+    if world > 1:
+        mine = torch.tensor([sum(sum(ts) for n, ts in per_kernel.items() if n in GEMM_KERNELS) / args.steps], device=device,
+                            dtype=torch.float64)
+        allr = torch.empty(world, device=device, dtype=torch.float64)
+        dist.all_gather_into_tensor(allr, mine)
+        rank_gemm_ms = [round(v, 3) for v in allr.tolist()]
 
     # ---- end to end: pinned host buffers in, results out, inside the timed region ------------------------
     host = {n: inp[n].cpu().pin_memory() for n in ("x", "router_weights", "selected_experts", "grad_out")}
@@ -537,6 +546,25 @@ def gpu_arm(args, w: dict) -> dict | None:
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = 2 * T * H * 2
     ck.check_device_status()
+    # the same copies with no compute at all, every rank at once: what the host side (PCIe, host memory, IOMMU) allows
+    y_dev = torch.empty(T, H, dtype=torch.bfloat16, device=device)
+    barrier()
+    e0.record()
+    for _ in range(4):
+        with torch.cuda.stream(h2d_stream):
+            keep = [v.to(device, non_blocking=True) for v in host.values()]
+        with torch.cuda.stream(d2h_stream):
+            y_host.copy_(y_dev, non_blocking=True)
+            dx_host.copy_(y_dev, non_blocking=True)
+        main_stream.wait_stream(h2d_stream)
+        main_stream.wait_stream(d2h_stream)
+    e1.record()
+    barrier()
+    del keep
+    t = torch.tensor([e0.elapsed_time(e1)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    copies_alone_ms = float(t.item()) / 4
 
     # ---- parity of this very configuration, untimed: one more step on the resident inputs, checked in fp32 ----------
     parity = None
@@ -619,10 +647,12 @@ def gpu_arm(args, w: dict) -> dict | None:
                    "step": "route+gather+up_swiglu+down_combine+backward(dgrad,wgrad,swiglu_bwd,router_grad)"},
         "clocks": clocks,
         "e2e": {"value": world * T / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h},
+                "d2h_bytes_per_step": d2h, "copies_alone_ms_per_step": round(copies_alone_ms, 3)},
         "gpu_launches": launches,
         "roofline": roofline,
     }
+    if rank_gemm_ms is not None:
+        line["rank_gemm_ms_per_step"] = rank_gemm_ms
     if parity is not None:
         line["parity"] = parity
     if aux is not None:

@@ -76,6 +76,19 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
     return __fdividef(1.0f, 1.0f + __expf(-x));
 }
 
+// ---- router ordering ----------------------------------------------------------------------------
+// Total order on the logits: the key of a float grows with its value, every NaN maps to the largest key (torch.topk
+// treats NaN as the greatest value) and -0.0 equals +0.0.  With (key, expert) compared lexicographically every lane of a
+// butterfly reduction arrives at the same winner, whatever the row holds.
+__device__ __forceinline__ uint32_t order_key(float v) {
+    if (v != v) return 0xffffffffu;
+    const uint32_t b = __float_as_uint(v + 0.0f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
+}
+
 __host__ __device__ __forceinline__ int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 }  // namespace ck

@@ -25,7 +25,8 @@
 namespace ck {
 
 enum { MODE_STORE = 0, MODE_UP_ACT = 1, MODE_SCATTER_ADD = 2, MODE_ACT_BWD = 3, MODE_WGRAD = 4,
-       MODE_UP_ACT1 = 5, MODE_ACT1_BWD = 6 };  // 5, 6: the un-gated up projection (one pre-activation per output) and its backward
+       MODE_UP_ACT1 = 5, MODE_ACT1_BWD = 6,  // 5, 6: the un-gated up projection (one pre-activation per output) and its backward
+       MODE_ROUTER = 7 };                    // gate projection with the router tail (top-k, softmax, int32 ids) in the epilogue
 
 constexpr int BM = 128;
 constexpr int BN = 256;
@@ -41,13 +42,14 @@ constexpr int kMaxSchedExperts = CK_ROUTE_MAX_EXPERTS;
 struct GemmParams {
     CUtensorMap tmA;
     CUtensorMap tmB;
-    const int32_t *mtile_off;   // [E+1] (all modes but WGRAD)
+    const int32_t *mtile_off;   // [E+1] (all modes but WGRAD); NULL: one group of m_tiles_w m-tiles (E must be 1)
     const int32_t *padded_off;  // [E+1] (WGRAD)
     const int32_t *row_map;     // [cap]
     const void *gate_w;         // router weights, flat [T*k], dtype T (may be NULL)
     const void *h_in;           // ACT_BWD: saved [cap, 2I] pre-activation
     void *out0;                 // STORE/WGRAD: y | UP_ACT: act | ACT_BWD: dh
-    void *out1;                 // UP_ACT: h (may be NULL)
+    void *out1;                 // UP_ACT: h (may be NULL) | ROUTER: router weights [tokens, top_k]
+    int32_t *ids_out;           // ROUTER: expert ids [tokens, top_k]
     float *out32;               // SCATTER_ADD target [T, N]
     const void *bias;           // per-expert bias of the GEMM's output features, [E, bias_ld] of T (may be NULL):
                                 //   UP_ACT: [up | gate] packed, bias_ld = 2I; UP_ACT1: bias_ld = I; STORE / SCATTER_ADD: bias_ld = N,
@@ -483,7 +485,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
     const int lane = row_in_tile & 31;
     const int row0 = row_in_tile - lane;  // first tile row of this warp
     using RP = RowPass<T>;
-    static_assert(PITCH >= RP::kWords + 4 || MODE == MODE_SCATTER_ADD, "stage rows too narrow for this dtype");
+    static_assert(PITCH >= RP::kWords + 4 || MODE == MODE_SCATTER_ADD || MODE == MODE_ROUTER, "stage rows too narrow for this dtype");
 
     if constexpr (MODE == MODE_STORE || MODE == MODE_WGRAD) {
         // per-row destination: grouped row, scattered row (row_map) or a row of dW[e]
@@ -743,6 +745,66 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const TileCoo
                 __syncwarp();
             }
         }
+    } else if constexpr (MODE == MODE_ROUTER) {
+        // Gate projection of the router: the accumulator row IS the token's logits (N = number of experts <= 256).  The
+        // thread rounds them to the tensor dtype (what the reference's F.linear returns and what top-k then sees), writes
+        // them out, keeps the k largest in a sorted register list (total order of order_key: NaN greatest, ties to the lower
+        // expert index, as torch.topk / the stand-alone router kernel), and finishes with softmax over the k kept logits.
+        constexpr int kMaxK = 8;
+        const int64_t token = int64_t(c.m_tile) * BM + row_in_tile;
+        const bool live = token < p.M;
+        uint32_t tk[kMaxK];
+        int te[kMaxK];
+#pragma unroll
+        for (int j = 0; j < kMaxK; ++j) { tk[j] = 0u; te[j] = 0; }  // real keys are >= 0x007fffff (-inf)
+        T *logits = reinterpret_cast<T *>(p.out0) + token * int64_t(p.N);
+#pragma unroll 1
+        for (int cc = cc_begin; cc < cc_end; cc += 32) {
+            if (cc >= p.N) break;
+            uint32_t r[32];
+            ptx::tmem_ld32(tbase + cc, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i0 = 0; i0 < 32; i0 += 8) {
+                if (cc + i0 >= p.N) break;  // N is a multiple of 8
+                float v8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v8[i] = DT<T>::up(DT<T>::down(__uint_as_float(r[i0 + i])));
+                if (live) store8<T>(logits + cc + i0, v8);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t key = order_key(v8[i]);
+                    const int e = cc + i0 + i;
+                    // branch-free insertion into the descending list; equal keys stay behind earlier (lower) experts
+#pragma unroll
+                    for (int j = kMaxK - 1; j >= 0; --j) {
+                        const bool before_prev = j > 0 && key > tk[j - 1];
+                        const bool before_cur = key > tk[j];
+                        tk[j] = before_prev ? tk[j - 1] : (before_cur ? key : tk[j]);
+                        te[j] = before_prev ? te[j - 1] : (before_cur ? e : te[j]);
+                    }
+                }
+            }
+        }
+        if (live) {
+            const float vmax = key_value(tk[0]);
+            float ex[kMaxK];
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kMaxK; ++j) {
+                ex[j] = j < p.top_k ? expf(key_value(tk[j]) - vmax) : 0.0f;
+                sum += ex[j];
+            }
+            T *wout = reinterpret_cast<T *>(p.out1) + token * int64_t(p.top_k);
+            int32_t *iout = p.ids_out + token * int64_t(p.top_k);
+#pragma unroll
+            for (int j = 0; j < kMaxK; ++j) {
+                if (j < p.top_k) {
+                    wout[j] = DT<T>::down(ex[j] / sum);
+                    iout[j] = te[j];
+                }
+            }
+        }
     } else if constexpr (MODE == MODE_ACT1_BWD) {
         // backward of the above: g = dy W_proj (accumulator), d_pre = w * g * gelu'(pre), router-weight grad = sum gelu(pre) * g
         const int64_t prow0 = int64_t(c.m_tile) * BM + row0;
@@ -834,7 +896,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
     }
     {
         const int32_t *src = (MODE == MODE_WGRAD) ? p.padded_off : p.mtile_off;
-        for (int i = threadIdx.x; i <= p.E; i += kGemmThreads) ctl->sched[i] = src[i];
+        for (int i = threadIdx.x; i <= p.E; i += kGemmThreads) ctl->sched[i] = src ? src[i] : (i == 0 ? 0 : p.m_tiles_w);
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -1279,7 +1341,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kT
     }
     {
         const int32_t *src = (MODE == MODE_WGRAD) ? p.padded_off : p.mtile_off;
-        for (int i = threadIdx.x; i <= p.E; i += CFG::kThreads) ctl->sched[i] = src[i];
+        for (int i = threadIdx.x; i <= p.E; i += CFG::kThreads) ctl->sched[i] = src ? src[i] : (i == 0 ? 0 : p.m_tiles_w);
     }
     __syncthreads();
     if (MODE != MODE_WGRAD && threadIdx.x == 0) {
@@ -1993,6 +2055,25 @@ static int grouped_linear_t(const void *x, const void *w, const int32_t *mtile_o
     return launch_gemm<T, MODE_STORE, false>(p, (cap / BM) * p.n_tiles, stream);
 }
 
+// ---- gate projection + router tail ---------------------------------------------------------------------------
+// logits[t, :] = x[t, :] @ gate_w^T (rounded to T), top-k / softmax / ids from the epilogue.  The tokens are one group of
+// ceil(tokens / 128) m-tiles (no routing tables needed yet: this IS the step that produces the expert ids); rows past
+// `tokens` in the last tile are zero-filled by TMA and never written.
+template <typename T>
+static int router_gate_t(const void *x, const void *gate_w, void *logits, void *weights, int32_t *ids, int64_t tokens, int H,
+                         int E, int top_k, int32_t *dev_status, cudaStream_t stream) {
+    GemmParams p = {};
+    const int64_t m_tiles = (tokens + BM - 1) / BM;
+    p.cap = m_tiles * BM;
+    int rc;
+    if ((rc = map_a_kmajor<T>(&p.tmA, x, tokens, H)) != CK_OK) return rc;
+    if ((rc = map_w_kmajor<T>(&p.tmB, gate_w, 1, E, H, use_cta_pair() ? BN / 2 : BN)) != CK_OK) return rc;
+    p.mtile_off = nullptr; p.m_tiles_w = int(m_tiles);
+    p.out0 = logits; p.out1 = weights; p.ids_out = ids; p.dev_status = dev_status;
+    p.E = 1; p.n_tiles = 1; p.N = E; p.K = H; p.M = int(tokens); p.top_k = top_k;
+    return launch_gemm<T, MODE_ROUTER, false>(p, m_tiles, stream);
+}
+
 // ---- bias gradients (layers with add_bias=True) -------------------------------------------------------------
 // out[e, n] = sum over the padded rows p of expert e of scale(p) * rows[p, n], scale(p) = gate_w[row_map[p]] (1 without
 // gate_w; pad rows are zero).  One block per (expert, 256-column slab): the eight warps take every eighth row, each lane
@@ -2279,6 +2360,16 @@ extern "C" int ck_moe_grouped_linear_scatter(const void *x, const void *w, const
     if (!x || !w || !mtile_off || !row_map || !y || E <= 0 || E > kMaxSchedExperts || !dims_ok(cap, N, K)) return CK_ERR_SHAPE;
     CK_DISPATCH_DTYPE(dtype, (grouped_linear_t<T>(x, w, mtile_off, row_map, y, E, cap, N, K, trans_w, dev_status, (cudaStream_t)stream,
                                                   nullptr, nullptr, 0, 0, bias, gate_w)));
+}
+
+extern "C" int ck_router_gate_topk_softmax(const void *x, const void *gate_w, void *logits, void *weights, int32_t *ids,
+                                           int64_t tokens, int H, int E, int top_k, int dtype, int32_t *dev_status, void *stream) {
+    if (tokens < 0 || H <= 0 || H % 8 != 0 || E <= 0 || E % 8 != 0 || E > BN || top_k <= 0 || top_k > 8 || top_k > E) return CK_ERR_SHAPE;
+    if (tokens > INT32_MAX - BM) return CK_ERR_SHAPE;
+    if (tokens == 0) return CK_OK;
+    if (!x || !gate_w || !logits || !weights || !ids) return CK_ERR_SHAPE;
+    if (dtype == CK_F32) return CK_ERR_UNSUPPORTED;  // fp32 logits would come out of a TF32 product: not what top-k should see
+    CK_DISPATCH_DTYPE(dtype, (router_gate_t<T>(x, gate_w, logits, weights, ids, tokens, H, E, top_k, dev_status, (cudaStream_t)stream)));
 }
 
 extern "C" int ck_moe_bias_grad(const void *rows, int64_t cap, int N, const int32_t *row_map, const void *gate_w,

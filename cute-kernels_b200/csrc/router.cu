@@ -13,18 +13,6 @@ constexpr int kRouterMaxExperts = 256;
 constexpr int kRouterMaxK = 32;
 constexpr int kRouterThreads = 256;
 
-// Total order on the logits: the key of a float grows with its value, every NaN maps to the largest key (torch.topk
-// treats NaN as the greatest value) and -0.0 equals +0.0.  With (key, expert) compared lexicographically every lane of a
-// butterfly reduction arrives at the same winner, whatever the row holds.
-__device__ __forceinline__ uint32_t order_key(float v) {
-    if (v != v) return 0xffffffffu;
-    const uint32_t b = __float_as_uint(v + 0.0f);
-    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-}
-__device__ __forceinline__ float key_value(uint32_t key) {
-    return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kRouterThreads)
     router_topk_softmax_kernel(const T *__restrict__ logits, T *__restrict__ weights, int32_t *__restrict__ ids,

@@ -16,7 +16,7 @@ from .expert_parallel import (ExpertParallelMoE, balanced_expert_placement, gath
 from .kernel_backend import CutoTuneParameter, KernelBackend
 from .moe import Experts_Cute, MoE_Cute, fused_experts
 from .rmsnorm import fused_residual_add_rmsnorm_cute, rmsnorm_cute
-from .router import router_topk_softmax
+from .router import router_gate_topk_softmax, router_topk_softmax
 from .routing import Routing, padded_capacity, route
 from .swiglu import swiglu_cute, swiglu_packed_cute
 from .torch_reference import (Experts_Torch, MoE_Torch, continuous_count_torch, fused_residual_add_rmsnorm_torch,
@@ -30,5 +30,5 @@ __all__ = [
     "swiglu_packed_torch", "swiglu_torch",
     "CuteInductor", "CutoTuneParameter", "ExpertParallelMoE", "Experts_Cute", "KernelBackend", "MoE_Cute", "Routing", "ceil_divide",
     "check_device_status", "continuous_count_cute", "divide_if_divisible", "fused_experts", "gather_expert_state_dict", "padded_capacity",
-    "fused_residual_add_rmsnorm_cute", "replace_rmsnorm", "replace_swiglu_unchunked", "rmsnorm_cute", "route", "router_topk_softmax", "set_seed", "shard_expert_state_dict", "swiglu_cute", "swiglu_packed_cute",
+    "fused_residual_add_rmsnorm_cute", "replace_rmsnorm", "replace_swiglu_unchunked", "rmsnorm_cute", "route", "router_gate_topk_softmax", "router_topk_softmax", "set_seed", "shard_expert_state_dict", "swiglu_cute", "swiglu_packed_cute",
 ]

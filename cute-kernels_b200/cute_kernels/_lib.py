@@ -68,6 +68,7 @@ PROTOTYPES = {
     "ck_rmsnorm_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, ctypes.c_float, ctypes.c_float, _i, _vp]),
     "ck_router_topk_softmax": (_i, [_vp, _vp, _vp, _i64, _i, _i, _i, _vp]),
     "ck_router_topk_softmax_bwd": (_i, [_vp, _vp, _vp, _vp, _i64, _i, _i, _i, _vp, _vp]),
+    "ck_router_gate_topk_softmax": (_i, [_vp, _vp, _vp, _vp, _vp, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_moe_gather_rows_peer": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _i, _i64, _i, _i64, _i64, _i64, _i, _vp, _vp]),
     "ck_moe_grouped_linear_scatter_peer": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i64, _i, _i64, _i, _i, _i, _i, _vp, _vp]),
     "ck_peer_gather_scalars": (_i, [_vp, _i, _i64, _vp, _i64, _vp, _i, _vp, _vp]),

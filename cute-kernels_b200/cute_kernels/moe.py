@@ -653,6 +653,8 @@ class MoE_Cute(nn.Module):
         self.check_status = check_status
         # how the k expert outputs of a token are summed (see fused_experts): None = in a fixed order for k > 2
         self.deterministic = deterministic
+        # False: keep the gate projection a library GEMM (its logits then match F.linear bit for bit)
+        self.fuse_router = True
 
     def forward(self, hidden_states: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         original_shape = hidden_states.shape
@@ -663,9 +665,12 @@ class MoE_Cute(nn.Module):
             _lib.check_device_status(hidden_states.device)
         return hidden_states.view(original_shape), router_logits
 
-    # the gate projection is a library GEMM; top-k + softmax + int32 ids run as one kernel when the router fits
-    # it (up to 256 experts), else as the reference's three torch ops
+    # 16-bit tensors, up to 256 experts, k <= 8: the gate projection runs on the tensor cores with top-k + softmax + int32
+    # ids in its epilogue (one launch).  Otherwise the gate projection is a library GEMM and top-k + softmax + ids run as
+    # one kernel when the router fits it, else as the reference's three torch ops.
     def _compute_routing_weights(self, hidden_states: torch.Tensor):
+        if self.fuse_router and _router.fused_gate_supported(hidden_states, self.gate.weight, self.top_k):
+            return _router.router_gate_topk_softmax(hidden_states, self.gate.weight, self.top_k)
         router_logits = self.gate(hidden_states)
         if router_logits.is_cuda and _router.supported(self.num_experts, self.top_k):
             router_weights, selected_experts = _router.router_topk_softmax(router_logits, self.top_k)

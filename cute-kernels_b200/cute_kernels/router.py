@@ -4,7 +4,8 @@ The reference runs ``topk`` (``max`` when k == 1), ``softmax(.float())`` and ``t
 and hands an int64 ``selected_experts`` to the expert path
 (kernels/scattermoe/torch_implementation.py:122-135,195-201).  ``router_topk_softmax`` computes the same
 ``(router_weights, selected_experts)`` pair in one launch and keeps the ids int32, the form the routing kernels
-read.  The gate projection itself stays ``nn.Linear`` (a library GEMM).  Differentiable in the logits: the
+read.  ``router_gate_topk_softmax`` goes one step further and runs the gate projection itself on the tensor cores with
+this tail in the GEMM epilogue (16-bit dtypes, up to 256 experts, k <= 8).  Differentiable in the logits: the
 backward kernel scatters the softmax gradient of the k selected logits into a zero ``[T, E]`` tensor, which is
 what autograd derives for the three torch ops.
 """
@@ -67,6 +68,77 @@ class _RouterTopkSoftmax(torch.autograd.Function):
         if weights.size(0):
             _call(_bwd_op, _bwd_impl, weights, d_weights.contiguous(), ids, d_logits)
         return d_logits, None
+
+
+# ---- gate projection + router tail in one tensor-core launch ---------------------------------------------
+FUSED_MAX_TOP_K = 8
+
+
+def _gate_fwd_impl(x: torch.Tensor, gate_w: torch.Tensor, logits: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor,
+                   top_k: int) -> None:
+    _lib.require_cuda(x, gate_w, logits, weights, ids)
+    status = _lib.status_word(x.device)
+    T, H = x.shape
+    E = gate_w.size(0)
+    with torch.cuda.device(x.device), _lib.launch("router_gate_topk_softmax", 1, 2.0 * T * H * E):
+        st = _lib.lib.ck_router_gate_topk_softmax(x.data_ptr(), gate_w.data_ptr(), logits.data_ptr(), weights.data_ptr(),
+                                                  ids.data_ptr(), T, H, E, top_k, _lib.dtype_code(x.dtype), status.data_ptr(),
+                                                  _lib.stream_ptr())
+    _lib.check(st, "ck_router_gate_topk_softmax")
+
+
+_gate_fwd_op = torch.library.custom_op("cute_kernels_b200::router_gate_topk_softmax", _gate_fwd_impl,
+                                       mutates_args={"logits", "weights", "ids"})
+
+
+class _GateRouter(torch.autograd.Function):
+    """(logits, weights, ids) = router(x @ gate_w^T).  Backward: the softmax / top-k scatter kernel gives the gradient that
+    reaches the logits through the weights; added to whatever arrives on the logits themselves (auxiliary losses), it goes
+    through the two library GEMMs of a linear layer."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, gate_w: torch.Tensor, top_k: int):
+        x = x.contiguous()
+        gate_w = gate_w.contiguous()
+        T, E = x.size(0), gate_w.size(0)
+        logits = torch.empty(T, E, dtype=x.dtype, device=x.device)
+        weights = torch.empty(T, top_k, dtype=x.dtype, device=x.device)
+        ids = torch.empty(T, top_k, dtype=torch.int32, device=x.device)
+        if T:
+            _call(_gate_fwd_op, _gate_fwd_impl, x, gate_w, logits, weights, ids, top_k)
+        ctx.save_for_backward(x, gate_w, weights, ids)
+        ctx.mark_non_differentiable(ids)
+        return logits, weights, ids
+
+    @staticmethod
+    def backward(ctx, d_logits_direct, d_weights, _d_ids):
+        x, gate_w, weights, ids = ctx.saved_tensors
+        T, E = x.size(0), gate_w.size(0)
+        d_logits = torch.zeros(T, E, dtype=x.dtype, device=x.device)
+        if T and d_weights is not None:
+            _call(_bwd_op, _bwd_impl, weights, d_weights.contiguous().to(weights.dtype), ids, d_logits)
+        if d_logits_direct is not None:
+            d_logits = d_logits + d_logits_direct
+        dx = d_logits @ gate_w if ctx.needs_input_grad[0] else None
+        dw = d_logits.t() @ x if ctx.needs_input_grad[1] else None
+        return dx, dw, None
+
+
+def fused_gate_supported(x: torch.Tensor, gate_w: torch.Tensor, top_k: int) -> bool:
+    E, H = gate_w.shape
+    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and gate_w.dtype == x.dtype and H % 8 == 0 and E % 8 == 0
+            and E <= MAX_EXPERTS and 0 < top_k <= min(FUSED_MAX_TOP_K, E))
+
+
+def router_gate_topk_softmax(x: torch.Tensor, gate_w: torch.Tensor, top_k: int):
+    """``(router_logits [T, E], router_weights [T, k], selected_experts [T, k] int32)`` from tokens ``x [T, H]`` and the gate
+    weight ``[E, H]`` in one tensor-core launch: the gate projection with the top-k / softmax / ids in its epilogue.
+    16-bit dtypes, ``H % 8 == 0``, ``E % 8 == 0``, ``E <= 256``, ``k <= 8`` (see :func:`fused_gate_supported`)."""
+    if x.dim() != 2 or gate_w.dim() != 2 or x.size(1) != gate_w.size(1):
+        raise ValueError("x must be [tokens, H] and gate_w [experts, H]")
+    if not fused_gate_supported(x, gate_w, top_k):
+        raise ValueError("shape / dtype outside the fused router's range; use gate(x) + router_topk_softmax")
+    return _GateRouter.apply(x, gate_w, top_k)
 
 
 def supported(num_experts: int, top_k: int) -> bool:

@@ -320,6 +320,18 @@ CK_API int ck_router_topk_softmax_bwd(const void *weights, const void *d_weights
                                       void *d_logits, int64_t tokens, int E, int k, int dtype, int32_t *dev_status,
                                       void *stream);
 
+/* ck_router_gate_topk_softmax: the gate projection and the router tail in ONE tcgen05 launch.
+ *   logits[t, :] = x[t, :] @ gate_w^T  (x [tokens, H], gate_w [E, H], fp32 accumulation, rounded to `dtype`: what
+ *   F.linear returns), written out because the module returns them, and -- from the same accumulator row, in the GEMM
+ *   epilogue -- weights [tokens, k] and ids [tokens, k] exactly as ck_router_topk_softmax computes them from those rounded
+ *   logits.  Replaces self.gate(x) + topk + softmax + type_as (torch_implementation.py:122-135,195-201): the [tokens, E]
+ *   logits are not re-read and no int64 ids exist.  H % 8 == 0, E % 8 == 0, E <= 256, k <= 8 and k <= E, 16-bit dtypes
+ *   (CK_ERR_UNSUPPORTED for fp32: its logits would come out of a TF32 product); other shapes take the two-step path.
+ *   The backward is ck_router_topk_softmax_bwd followed by the two library GEMMs of a linear layer. */
+CK_API int ck_router_gate_topk_softmax(const void *x, const void *gate_w, void *logits, void *weights, int32_t *ids,
+                                       int64_t tokens, int H, int E, int top_k, int dtype, int32_t *dev_status,
+                                       void *stream);
+
 /* ---- expert parallelism over peer memory ------------------------------------------------------------
  * No reference counterpart (the reference is single-GPU); per rank these are its `group` (ops.py:108-140) and
  * `scatter2scatter` with y_grouped=False (ops.py:31-78) with the other side of the permutation living on another

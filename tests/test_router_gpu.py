@@ -167,3 +167,87 @@ def test_router_backward_skips_out_of_range_ids():
     with pytest.raises(RuntimeError, match="CK_DEV_RANGE"):
         cute_kernels.check_device_status()
     cute_kernels.check_device_status()  # cleared
+
+
+# ---- gate projection + router tail in one tensor-core launch ---------------------------------------------------
+@pytest.mark.parametrize("flavour", ["cta_pair", "single_cta"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,H,E,k", [(1, 64, 8, 2), (130, 256, 8, 2), (1000, 512, 64, 8), (257, 128, 40, 6), (512, 1024, 256, 8),
+                                     (384, 72, 8, 1)])
+def test_fused_gate_router_matches_linear_plus_router(flavour, dtype, T, H, E, k):
+    """logits = F.linear(x, w) within one rounding of the 16-bit type (fp32 accumulation in a different order); weights and
+    ids are EXACTLY what the stand-alone router kernel gives on the fused kernel's own logits."""
+    from cute_kernels import _lib, router_gate_topk_softmax, router_topk_softmax
+
+    prev = _lib.lib.ck_set_gemm_cta_pair(1 if flavour == "cta_pair" else 0)
+    try:
+        g = torch.Generator().manual_seed(T + E)
+        x = torch.randn(T, H, generator=g).to(dtype).cuda()
+        w = (torch.randn(E, H, generator=g) / H**0.5).to(dtype).cuda()
+        logits = torch.full((T, E), float("nan"), dtype=dtype, device="cuda")
+        logits, weights, ids = router_gate_topk_softmax(x, w, k)
+        ref = x.float() @ w.float().t()
+        torch.testing.assert_close(logits.float(), ref, rtol=2 ** -7 if dtype == torch.bfloat16 else 2 ** -10, atol=1e-3)
+        w2, ids2 = router_topk_softmax(logits, k)
+        assert torch.equal(ids, ids2)
+        assert torch.equal(weights.view(torch.int16), w2.view(torch.int16))
+        assert ids.dtype == torch.int32 and int(ids.min()) >= 0 and int(ids.max()) < E
+        import cute_kernels
+
+        cute_kernels.check_device_status()
+    finally:
+        _lib.lib.ck_set_gemm_cta_pair(prev)
+
+
+def test_fused_gate_router_gradients_match_autograd():
+    from cute_kernels import router_gate_topk_softmax
+
+    T, H, E, k = 300, 256, 16, 4
+    g = torch.Generator().manual_seed(5)
+    x0 = torch.randn(T, H, generator=g).bfloat16().cuda()
+    w0 = (torch.randn(E, H, generator=g) / H**0.5).bfloat16().cuda()
+    d_w = torch.randn(T, k, generator=g).bfloat16().cuda()
+    d_l = torch.randn(T, E, generator=g).bfloat16().cuda()
+    x, w = x0.clone().requires_grad_(), w0.clone().requires_grad_()
+    logits, weights, ids = router_gate_topk_softmax(x, w, k)
+    torch.autograd.backward([logits, weights], [d_l, d_w])
+    # the same computation with torch ops on the same selection
+    xr, wr = x0.float().requires_grad_(), w0.float().requires_grad_()
+    lr = xr @ wr.t()
+    wr_sel = torch.softmax(lr.gather(1, ids.long()), dim=-1)
+    torch.autograd.backward([lr, wr_sel], [d_l.float(), d_w.float()])
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(w.grad.float(), wr.grad, rtol=3e-2, atol=3e-2 * T**0.5 / 4)
+
+
+def test_fused_gate_router_rejects_what_it_cannot_do_and_module_uses_it():
+    from cute_kernels import MoE_Cute, _lib, router_gate_topk_softmax
+    from cute_kernels.router import fused_gate_supported
+    from cute_kernels.swiglu import swiglu_packed_cute
+
+    x = torch.randn(16, 64, device="cuda")
+    assert not fused_gate_supported(x, torch.randn(8, 64, device="cuda"), 2)              # fp32: two-step path
+    assert not fused_gate_supported(x.bfloat16(), torch.randn(12, 64, device="cuda").bfloat16(), 2)  # E % 8 != 0
+    assert not fused_gate_supported(x.bfloat16(), torch.randn(16, 64, device="cuda").bfloat16(), 9)  # k > 8
+    with pytest.raises(ValueError):
+        router_gate_topk_softmax(x, torch.randn(8, 64, device="cuda"), 2)
+    torch.manual_seed(0)
+    m = MoE_Cute(num_experts=8, num_experts_per_tok=2, hidden_size=128, intermediate_size=128,
+                 activation_function=swiglu_packed_cute, is_glu=True, add_bias=False, std=0.02).cuda().bfloat16()
+    xb = torch.randn(200, 128, device="cuda", dtype=torch.bfloat16)
+    _lib.launch_log.reset()
+    _lib.launch_log.record_events = True
+    try:
+        logits, weights, sel = m._compute_routing_weights(xb)
+        names = [e[0] for e in _lib.launch_log.events]
+    finally:
+        _lib.launch_log.record_events = False
+        _lib.launch_log.reset()
+    assert names == ["router_gate_topk_softmax"]
+    m.fuse_router = False
+    l2, w2, s2 = m._compute_routing_weights(xb)
+    torch.testing.assert_close(logits.float(), l2.float(), rtol=2 ** -7, atol=1e-3)
+    same = (sel == s2).all(dim=1)
+    assert same.float().mean() > 0.98  # a logit that rounds differently may swap two near-equal experts
+    assert torch.equal(weights[same].view(torch.int16), w2[same].view(torch.int16)) or \
+        torch.allclose(weights[same].float(), w2[same].float(), atol=2e-2)
