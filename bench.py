@@ -937,6 +937,17 @@ def micro_arm(args, which: str) -> dict:
                                   traffic=None, algorithmic_bytes=results["algorithmic_bytes"]["route"],
                                   peak_source=f"hbm_gbs of {peaks['source']}"),
                     detail=results)
+    elif which == "rmsnorm":
+        sampler.mark_begin()
+        results = measure_rmsnorm(args.steps, args.warmup, flush, peak)
+        sampler.mark_end()
+        head = results["bwd"]
+        line = dict(metric="rmsnorm_bwd_hbm_gb_per_s", value=head["gbs"], unit="GB/s", ms_per_step=head["ms"],
+                    config=dict(workload="rmsnorm_fwd_bwd", shape=results["shape"], l2_policy="l2_flushed_between_launches"),
+                    roofline=dict(bound="hbm", kernel="rmsnorm_bwd_kernel<bf16> + rmsnorm_dw_reduce_kernel", achieved=head["gbs"],
+                                  peak=peak, unit="GB/s", frac=head["frac"], traffic=None,
+                                  algorithmic_bytes=head["algorithmic_bytes"], peak_source=f"hbm_gbs of {peaks['source']}"),
+                    detail=results)
     else:
         sampler.mark_begin()
         results = measure_c3(args.steps, args.warmup, flush, peak)
@@ -961,7 +972,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c2", "c3"])
+    ap.add_argument("--workload", default="c4", choices=sorted(WORKLOADS) + ["c2", "c3", "rmsnorm"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the untimed fp32 parity check of the timed configuration")
     ap.add_argument("--no-aux", action="store_true", help="N = 1: skip the routing / SwiGLU / fine-grained-layer figures")
@@ -990,7 +1001,7 @@ def main() -> None:
         print(json.dumps(dict(metric="gemm_cycle_profile", config=dict(workload=w["name"]),
                               kernels=gemm_cycle_profile(w, torch.device("cuda", 0)))))
         return
-    if args.workload in ("c2", "c3"):
+    if args.workload in ("c2", "c3", "rmsnorm"):
         if args.warmup < 3:
             args.warmup = 3
         print(json.dumps(micro_arm(args, args.workload)))

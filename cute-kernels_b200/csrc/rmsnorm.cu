@@ -210,7 +210,11 @@ __global__ void __launch_bounds__(kNormBlock, (VPT <= 2 && !ADDED) ? 2 : 1)
     const float inv_h = 1.0f / float(H);
     // rows stay packed (16 bytes per register quad) and are unpacked where they are used; two rows beyond the current one
     // are in flight, which is what keeps enough bytes outstanding per SM at the occupancy the accumulators allow
-    int4 ap[3][VPT], gp[3][VPT], ep[3][ADDED ? VPT : 1];
+    // rows in flight per thread group: the current one and two more.  Measured on [16384, 4096] bf16: two in flight with three
+    // resident blocks (80 registers, spills) 132 us; keeping g * w unpacked across the reduction (spills at 128 registers)
+    // 134 us; this form 102 us.  The kernel issues 58 % of its slots at a quarter of the warp slots: instruction bound.
+    constexpr int kSlots = 3;
+    int4 ap[kSlots][VPT], gp[kSlots][VPT], ep[kSlots][ADDED ? VPT : 1];
     auto fetch = [&](int slot, int64_t row) {
 #pragma unroll
         for (int j = 0; j < VPT; ++j) {
@@ -278,20 +282,32 @@ __global__ void __launch_bounds__(kNormBlock, (VPT <= 2 && !ADDED) ? 2 : 1)
     };
     int64_t row = int64_t(blockIdx.x) * rows_per_block + threadIdx.x / G;
     fetch(0, row);
-    fetch(1, row + stride);
-    // the slot index must be a compile-time constant for the arrays to stay in registers: three rows per trip
-    while (row < rows) {
-        fetch(2, row + 2 * stride);
-        process(0, row);
-        row += stride;
-        if (row >= rows) break;
-        fetch(0, row + 2 * stride);
-        process(1, row);
-        row += stride;
-        if (row >= rows) break;
-        fetch(1, row + 2 * stride);
-        process(2, row);
-        row += stride;
+    // the slot index must be a compile-time constant for the arrays to stay in registers: kSlots rows per trip
+    if constexpr (kSlots == 3) {
+        fetch(1, row + stride);
+        while (row < rows) {
+            fetch(2, row + 2 * stride);
+            process(0, row);
+            row += stride;
+            if (row >= rows) break;
+            fetch(0, row + 2 * stride);
+            process(1, row);
+            row += stride;
+            if (row >= rows) break;
+            fetch(1, row + 2 * stride);
+            process(2, row);
+            row += stride;
+        }
+    } else {
+        while (row < rows) {
+            fetch(1, row + stride);
+            process(0, row);
+            row += stride;
+            if (row >= rows) break;
+            fetch(0, row + stride);
+            process(1, row);
+            row += stride;
+        }
     }
     if (dw_part != nullptr) {
         float *mine = dw_part + int64_t(blockIdx.x) * H;
@@ -325,37 +341,39 @@ __global__ void __launch_bounds__(kNormBlock, (VPT <= 2 && !ADDED) ? 2 : 1)
     }
 }
 
-// d_weight[c] = sum over the parts of dw_part[i, c], written in the weight's dtype.  A block owns 32 columns; its eight
-// warps take the parts i = warp, warp + 8, ... with eight loads in flight each (the rows were just written: L2 hits, and
-// a single chain per column would be latency bound: hundreds of parts times an L2 round trip), then the eight partial sums
-// are added in warp order.  The order of every addition is fixed by the code: reproducible.
-constexpr int kDwCols = 32;
+// d_weight[c] = sum over the parts of dw_part[i, c], written in the weight's dtype.  A block owns 8 columns (one 32-byte
+// sector per part row); its 32 part lanes take the parts i = lane, lane + 32, ... with all of their loads in flight at once
+// (the rows were just written: L2 hits, and a single chain per column would cost hundreds of L2 round trips), then the 32
+// partial sums are added in lane order.  The order of every addition is fixed by the code: reproducible.
+constexpr int kDwCols = 8;
 template <typename T>
 __global__ void __launch_bounds__(kNormBlock) rmsnorm_dw_reduce_kernel(const float *__restrict__ dw_part, int parts, int64_t H,
                                                                        T *__restrict__ d_weight) {
-    constexpr int kLanes = kNormBlock / kDwCols;  // 8 part lanes
-    __shared__ float acc[kLanes][kDwCols];
+    constexpr int kLanes = kNormBlock / kDwCols;  // 32 part lanes
+    constexpr int kUnroll = 16;                   // up to 16 x 32 = 512 parts per pass
+    __shared__ float acc[kLanes][kDwCols + 1];
     const int col = threadIdx.x % kDwCols, lane = threadIdx.x / kDwCols;
     const int64_t c = int64_t(blockIdx.x) * kDwCols + col;
-    float s[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) s[u] = 0.0f;
+    float total = 0.0f;
     if (c < H) {
-        for (int i = lane; i < parts; i += 8 * kLanes) {
+        for (int base = lane; base < parts; base += kUnroll * kLanes) {
+            float v[kUnroll];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int q = i + u * kLanes;
-                if (q < parts) s[u] += dw_part[int64_t(q) * H + c];
+            for (int u = 0; u < kUnroll; ++u) {
+                const int q = base + u * kLanes;
+                v[u] = q < parts ? dw_part[int64_t(q) * H + c] : 0.0f;
             }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) total += v[u];
         }
     }
-    acc[lane][col] = ((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]));
+    acc[lane][col] = total;
     __syncthreads();
     if (lane == 0 && c < H) {
-        float total = acc[0][col];
+        float sum = acc[0][col];
 #pragma unroll
-        for (int l = 1; l < kLanes; ++l) total += acc[l][col];
-        d_weight[c] = DT<T>::down(total);
+        for (int l = 1; l < kLanes; ++l) sum += acc[l][col];
+        d_weight[c] = DT<T>::down(sum);
     }
 }
 
