@@ -407,7 +407,8 @@ def gpu_arm(args, w: dict) -> dict | None:
             if ok.item() == 0:
                 ep, transport, placement = None, "nccl_all_to_all", None
         if ep is None:
-            ep = ExpertParallelMoE(E, k, dist.group.WORLD)
+            ep = ExpertParallelMoE(E, k, dist.group.WORLD, chunks=args.ep_chunks)
+            transport = "nccl_all_to_all" + (f"+{args.ep_chunks}_chunks_on_side_streams" if args.ep_chunks > 1 else "")
 
         def step(x, rw, sel, grad_out):
             x = x.detach().requires_grad_()
@@ -989,6 +990,10 @@ def main() -> None:
                     help="N > 1, peer transport: pull most of the routed rows over NVLink while the GEMM already runs on the "
                          "first quarter of them (the GEMM leaves --ep-pull-sms SMs to the pull)")
     ap.add_argument("--ep-pull-sms", type=int, default=16)
+    ap.add_argument("--ep-chunks", type=int, default=1,
+                    help="N > 1, NCCL transport: token chunks pipelined on side streams (all-to-all of one chunk overlaps the "
+                         "GEMMs of another); 1 = no overlap.  Measured at 2 GPUs: 2 chunks 30.36 -> 30.02 ms per step on the "
+                         "Mixtral-shaped layer, 20.1 -> 22.9 ms on the 64-expert one (twice the launches, half-size GEMMs)")
     ap.add_argument("--ep-capacity-factor", type=float, default=0.0,
                     help="N > 1, peer transport: rows allocated per rank = factor x tokens x top_k with no read-back of the row "
                          "count; 0 (default) = read the exact count back every step")

@@ -17,7 +17,13 @@ batch.  Rank g owns experts [g*E/G, (g+1)*E/G) and only those slices of ``c_fc.w
   backward  the mirror image; every exchange step is an autograd function whose backward is the
             reverse exchange.
 
-Receive sizes are data dependent: one device-to-host read of the count matrix per call.
+Overlap (``chunks`` > 1, GPUs): the local tokens are cut into chunks that run the whole pipeline on streams of their own, so
+the all-to-all of one chunk travels while the grouped GEMMs of another compute, forward and backward (autograd replays every
+op on the stream it ran on).  The persistent GEMM grids own every SM they run on, so the layer lowers their SM budget by
+``comm_sms`` for the process (ck_set_gemm_sm_budget): NCCL's kernels then find free SMs instead of waiting for a GEMM's tail.
+Under the board's power cap the narrower GEMMs settle at a higher clock and lose next to nothing.
+
+Receive sizes are data dependent: one device-to-host read of the count matrix per call (per chunk).
 ``expert_fn`` / ``route_fn`` are injectable so the permutation and exchange logic can run on CPU ranks
 (gloo) with a CPU expert function in tests.
 """
@@ -175,7 +181,10 @@ class ExpertParallelMoE:
     w_fc_local [E/G, 2I, H], w_proj_local [E/G, H, I]: this rank's experts."""
 
     def __init__(self, num_experts: int, top_k: int, group=None, act_kind: int = 0,
-                 expert_fn: Callable | None = None, route_fn: Callable | None = None) -> None:
+                 expert_fn: Callable | None = None, route_fn: Callable | None = None, chunks: int = 1,
+                 comm_sms: int = 16) -> None:
+        """``chunks``: token chunks pipelined on their own streams (1 = everything on the caller's stream); with more than
+        one chunk the grouped GEMMs of this PROCESS leave ``comm_sms`` SMs free from now on, for the collectives' kernels."""
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -187,8 +196,40 @@ class ExpertParallelMoE:
         self.act_kind = act_kind
         self.expert_fn = expert_fn or _default_expert_fn
         self.route_fn = route_fn or _default_route
+        self.chunks = max(1, int(chunks))
+        self._streams: list = []
+        if self.chunks > 1 and torch.cuda.is_available():
+            from . import _lib
+
+            all_sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+            _lib.lib.ck_set_gemm_sm_budget(max(2, all_sms - int(comm_sms)))
 
     def __call__(self, x, router_weights, selected_experts, w_fc_local, w_proj_local):
+        """Runs the layer; with ``chunks`` > 1 on CUDA tensors, chunk by chunk on side streams (see the module docstring)."""
+        T = x.size(0)
+        if self.chunks == 1 or not x.is_cuda or T < 2 * self.chunks:
+            return self._run(x, router_weights, selected_experts, w_fc_local, w_proj_local)
+        if not self._streams:
+            self._streams = [torch.cuda.Stream(device=x.device) for _ in range(self.chunks)]
+        main = torch.cuda.current_stream()
+        ready = main.record_event()
+        bounds = [T * c // self.chunks for c in range(self.chunks + 1)]
+        outs = []
+        for c, st in enumerate(self._streams):
+            sl = slice(bounds[c], bounds[c + 1])
+            st.wait_event(ready)
+            with torch.cuda.stream(st):
+                y_c = self._run(x[sl], router_weights[sl], selected_experts[sl], w_fc_local, w_proj_local)
+            outs.append(y_c)
+        for t in (x, router_weights, selected_experts, w_fc_local, w_proj_local):
+            for st in self._streams:
+                t.record_stream(st)
+        for y_c, st in zip(outs, self._streams):
+            main.wait_stream(st)
+            y_c.record_stream(main)
+        return torch.cat(outs, dim=0)
+
+    def _run(self, x, router_weights, selected_experts, w_fc_local, w_proj_local):
         G, epr, k = self.world, self.local_experts, self.top_k
         T = x.size(0)
         dev = x.device

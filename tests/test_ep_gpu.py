@@ -43,7 +43,7 @@ def _worker(rank, world, port, cfg, out_dir):
 
             ep = PeerExpertParallelMoE(E, k, T + 7, cfg["H"], dt, None)   # buffers larger than the batch
         else:
-            ep = ExpertParallelMoE(E, k, None)
+            ep = ExpertParallelMoE(E, k, None, chunks=cfg.get("chunks", 1))
         y = ep(x, rw, full["selected_experts"][sl].cuda(), w_fc, w_proj)
         y.backward(full["grad_out"][sl].to(dt).cuda())
         torch.cuda.synchronize()
@@ -57,6 +57,8 @@ def _worker(rank, world, port, cfg, out_dir):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("cfg", [dict(E=8, k=2, T=300, H=128, I=256, expert_bias=False, seed=0),
                                  dict(E=16, k=4, T=257, H=64, I=72, expert_bias=True, seed=1),
+                                 dict(E=8, k=2, T=300, H=128, I=256, expert_bias=False, seed=0, chunks=2),
+                                 dict(E=16, k=4, T=257, H=64, I=72, expert_bias=True, seed=1, chunks=3),
                                  dict(E=8, k=2, T=300, H=128, I=256, expert_bias=False, seed=0, transport="peer"),
                                  dict(E=2, k=1, T=513, H=256, I=128, expert_bias=True, seed=2, transport="peer")])
 def test_expert_parallel_two_gpus(tmp_path, cfg):
