@@ -41,4 +41,4 @@ extern "C" const char *ck_status_string(int status) {
 
 extern "C" const char *ck_last_cuda_error(void) { return ck::g_last_error; }
 
-extern "C" int ck_abi_version(void) { return 2; }
+extern "C" int ck_abi_version(void) { return 3; }
