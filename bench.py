@@ -44,33 +44,6 @@ WORKLOADS = {
 COMBINE_ROWS = {"auto": None, "red": False, "rows": True}  # --combine -> fused_experts(deterministic=...)
 METRIC = "moe_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
-# DRAM bytes (read + write) per launch of each GEMM family on the full c4 workload, from a one-pass ncu capture of this
-# command (dram__bytes_read.sum + dram__bytes_write.sum; wgrad = mean of its two launches).  The figures belong to the
-# kernel source they were captured from: "gemm_source_sha16" is the sha256 prefix of csrc/grouped_gemm.cu at capture
-# time, and a different source makes ``roofline.traffic`` null instead of quoting a stale capture.
-MEASURED_DRAM_TRAFFIC = {
-    "c4_mixtral_moe_fwd_bwd": {"gemm_source_sha16": "", "up_act_fwd": 5910e6, "down_combine_fwd": 6276e6,
-                               "dgrad_down": 6500e6, "wgrad": 3686e6, "dgrad_up": 13209e6},
-}
-
-
-def gemm_source_sha16() -> str:
-    import hashlib
-
-    try:
-        with open(os.path.join(ROOT, "cute-kernels_b200", "csrc", "grouped_gemm.cu"), "rb") as f:
-            return hashlib.sha256(f.read()).hexdigest()[:16]
-    except OSError:
-        return "unknown"
-
-
-def measured_traffic(workload: str, kernel: str):
-    t = MEASURED_DRAM_TRAFFIC.get(workload)
-    if not t or t.get("gemm_source_sha16") != gemm_source_sha16():
-        return None
-    return t.get(kernel)
-
-
 GEMM_KERNELS = ("up_act_fwd", "down_combine_fwd", "dgrad_down", "dgrad_up", "wgrad", "grouped_linear",
                 "grouped_linear_scatter", "grouped_linear_scatter_peer", "up_act_fwd_peer", "dgrad_down_peer")
 
@@ -606,8 +579,8 @@ def gpu_arm(args, w: dict) -> dict | None:
         bound="tensor",
         kernel=f"{'grouped_gemm_pair_kernel' if os.environ.get('CK_GEMM_CTA_PAIR', '1') != '0' else 'grouped_gemm_kernel'}<bf16> ({dom})", achieved=kernels[dom]["tflops"], peak=peak,
         unit="TFLOP/s", frac=kernels[dom]["tflops"] / peak,
-        traffic=(measured_traffic(w["name"], dom) if world == 1 else None),
-        traffic_unit="bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture)",
+        traffic=None,  # DRAM bytes per launch need an ncu capture of this very build; a constant here would go stale
+        traffic_unit="bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum)",
         peak_source=f"bf16_tflops_sustained of {peaks['source']}",
         all_gemms=dict(ms_per_step=gemm_ms, tflops=gemm_flops / (gemm_ms * 1e-3) / 1e12,
                        frac_of_measured_sustained=gemm_flops / (gemm_ms * 1e-3) / 1e12 / peak,
