@@ -1201,7 +1201,7 @@ struct SmemCtlPairT {
     volatile int abort_flag;
     uint64_t wait_limit_ns;
     int32_t sched[kMaxSchedExperts + 1];   // m-tile offsets (or padded row offsets for WGRAD)
-    int32_t psched[kMaxSchedExperts + 1];  // pair-tile offsets per expert
+    int32_t psched[kMaxSchedExperts + 1];  // pair-tile offsets per expert; WGRAD: experts in the order their tiles are handed out
     int32_t gather_src[BM];                // row-indexed A producer: source of every row of the current tile
 };
 
@@ -1218,8 +1218,9 @@ __device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams &p, const
     if constexpr (MODE == MODE_WGRAD) {
         const int mpairs = (p.m_tiles_w + 1) >> 1;
         const int per_e = mpairs * p.n_tiles;
-        c.e = t / per_e;
-        const int local = t - c.e * per_e;
+        const int slot = t / per_e;
+        c.e = ctl->psched[slot];
+        const int local = t - slot * per_e;
         int pm;
         if (p.n_fastest) {
             pm = local / p.n_tiles;
@@ -1350,6 +1351,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kT
         for (int e = 0; e < p.E; ++e) {
             acc += (ctl->sched[e + 1] - ctl->sched[e] + 1) >> 1;
             ctl->psched[e + 1] = acc;
+        }
+    }
+    if constexpr (MODE == MODE_WGRAD) {
+        // A weight-gradient tile costs as many k-blocks as its expert has rows, and the tiles go to the CTA pairs round robin:
+        // handing out the experts with the most rows first (ties by index) evens out the pairs' totals under skewed routing
+        // (64 experts, top-8, biased router: heaviest pair 1.12 x the mean in expert order, 1.05-1.07 x in this order).
+        // Up to kLptMaxExperts experts (one thread ranks one expert against all others); more experts keep their order.
+        constexpr int kLptMaxExperts = 128;
+        for (int e = threadIdx.x; e < p.E; e += CFG::kThreads) {
+            int pos = e;
+            if (p.E <= kLptMaxExperts) {
+                const int rows = ctl->sched[e + 1] - ctl->sched[e];
+                pos = 0;
+                for (int f = 0; f < p.E; ++f) {
+                    const int rf = ctl->sched[f + 1] - ctl->sched[f];
+                    pos += (rf > rows || (rf == rows && f < e)) ? 1 : 0;
+                }
+            }
+            ctl->psched[pos] = e;
         }
     }
     ptx::tc_fence_before();
