@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-@pytest.mark.parametrize("T,k,H", [(1, 1, 8), (33, 2, 64), (257, 8, 136), (1000, 4, 512)])
+@pytest.mark.parametrize("T,k,H", [(1, 1, 8), (33, 2, 64), (257, 8, 136), (1000, 4, 512), (65, 6, 2056), (40, 3, 4096)])
 def test_gather_combine_dots(dtype, T, k, H):
     from cute_kernels.moe import combine_rows, gather_rows_scaled, row_dots
 
@@ -45,6 +45,15 @@ def test_gather_combine_dots(dtype, T, k, H):
     torch.testing.assert_close(out.float(), exp, **tol)
     combine_rows(src, pos, None, out, k)
     torch.testing.assert_close(out.float(), src.float()[pos.long()].view(T, k, H).sum(1), **tol)
+    # no position table: the k rows of token t are rows t*k .. t*k+k-1; a missing row (-1) contributes nothing
+    combine_rows(src, None, None, out, k)
+    torch.testing.assert_close(out.float(), src.float().view(T, k, H).sum(1), **tol)
+    pos2 = pos.clone()
+    pos2[::k] = -1
+    combine_rows(src, pos2, None, out, k)
+    keep = torch.ones(T, k, 1)
+    keep[:, 0] = 0
+    torch.testing.assert_close(out.float().cpu(), (src.float().cpu()[pos.long().cpu()].view(T, k, H) * keep).sum(1), **tol)
 
     dots = torch.empty(T * k, dtype=dtype, device="cuda")
     row_dots(src, pos, x, dots, k)
