@@ -146,9 +146,9 @@ class _Plan:
     routing: Routing   # all ranks' slots routed over [this rank's experts..., "not mine"]; row_map[p] = global flat slot
     rows: int | None   # padded rows of the local experts (a multiple of 128, may be 0); None: not read back (capacity mode)
     cap: int           # rows allocated: max(rows, 128), or the caller's capacity
-    split: int         # m-tiles in the first window of the pull (0: one window)
-    mtile_first: torch.Tensor | None   # mtile_off clamped to the first window / to the rest
-    mtile_rest: torch.Tensor | None
+    split: int         # number of pull windows beyond the first (0: one window)
+    edges: list[int] | None            # window w covers the m-tiles [edges[w], edges[w + 1])
+    mtile_windows: list[torch.Tensor] | None  # mtile_off clamped to each window
     own_map: torch.Tensor | None = None  # capacity mode: row_map[:cap] with -1 beyond the local experts' rows
 
 
@@ -221,17 +221,24 @@ class PeerExpertEngine:
         rows, bad = torch.stack([r.padded_off[epr], n_bad]).tolist()  # the one host sync: rows to allocate
         if bad:
             raise RuntimeError(f"{bad} expert ids outside [0, {self.num_experts}) reached the expert-parallel layer")
-        # Optional: two windows of the padded rows, the second pulled on a side stream while the GEMM runs on the first.
+        # Windows of the padded rows: window w + 1 is pulled on a side stream while the GEMM runs on window w.
         tiles = rows // _lib.CK_TILE_M
-        split = 0
+        edges = None
         if self.MIN_TILES_TO_SPLIT is not None and tiles >= self.MIN_TILES_TO_SPLIT:
-            split = min(tiles - 2, max(2, (tiles // 4 + 1) & ~1))  # a quarter of the rows, whole CTA pairs
-        first = r.mtile_off.clamp(max=split) if split else None
-        rest = r.mtile_off.clamp(min=split) if split else None
-        return _Plan(r, rows, max(rows, _lib.CK_TILE_M), split, first, rest)
+            n_win = max(2, min(self.PULL_WINDOWS, tiles // max(2, self.MIN_TILES_TO_SPLIT // 2)))
+            if n_win == 2:  # a quarter first (the exposed pull), the rest beside its GEMM
+                edges = [0, min(tiles - 2, max(2, (tiles // 4 + 1) & ~1)), tiles]
+            else:           # equal shares, whole CTA pairs
+                edges = sorted({min(tiles, ((tiles * w // n_win) + 1) & ~1) for w in range(n_win)} | {0, tiles})
+            if len(edges) < 3:
+                edges = None
+        windows = None
+        if edges is not None:
+            windows = [r.mtile_off.clamp(min=a, max=b) for a, b in zip(edges[:-1], edges[1:])]
+        return _Plan(r, rows, max(rows, _lib.CK_TILE_M), 0 if edges is None else len(edges) - 2, edges, windows)
 
-    # Two-window schedule: the first quarter of the padded rows is pulled, then the rest is pulled on a side stream WHILE the
-    # GEMM runs on the first window.  A pull kernel never becomes resident on an SM that hosts a persistent GEMM CTA (its warps
+    # Windowed schedule: the padded rows are cut into PULL_WINDOWS windows; the first is pulled, then window w + 1 is pulled on a
+    # side stream WHILE the GEMM runs on window w (only the first pull is exposed).  A pull kernel never becomes resident on an SM that hosts a persistent GEMM CTA (its warps
     # hold the whole register file; tried 128-thread blocks, the shared-memory carve-out, a high-priority stream, the one-CTA
     # flavour: the later kernel always started in the earlier one's tail), so the first-window GEMM is launched on
     # ``SMS - PULL_SMS`` SMs and the pull gets the rest.  That costs the GEMM next to nothing: the layer runs under the
@@ -239,6 +246,10 @@ class PeerExpertEngine:
     # 29.02 ms per step on 148 SMs, 29.14 ms on 132, 29.91 ms on 120).  Set MIN_TILES_TO_SPLIT to None for one window.
     MIN_TILES_TO_SPLIT: int | None = 16
     PULL_SMS = 16
+    # Two windows: a quarter of the rows, then the rest.  Four equal windows were measured at 4 GPUs: the 64-expert layer
+    # 16.18 against 16.20 ms per step (what the extra windows hide, 1.5 ms, the four narrower GEMM launches give back: the
+    # ranks' GEMM time rose from 12.7 to 13.9 ms), the 8-expert layer within the spread between runs.
+    PULL_WINDOWS = 2
 
     def _side_stream(self) -> torch.cuda.Stream:
         if self._side is None:
@@ -254,22 +265,32 @@ class PeerExpertEngine:
             gemm(r.mtile_off)
             return
         main, side = torch.cuda.current_stream(), self._side_stream()
-        edge = plan.split * _lib.CK_TILE_M
-        _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, 0, edge)
+        rows = [e * _lib.CK_TILE_M for e in plan.edges]
+        rows[-1] = plan.cap
+        n_win = len(plan.mtile_windows)
+        _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, rows[0], rows[1])
         first_done = torch.cuda.Event()
         first_done.record(main)
-        # the GEMM on the first window is enqueued before the second pull, which waits only for the first pull; it leaves
-        # PULL_SMS SMs to that pull
-        with _lib.gemm_sm_budget(max(2, _lib.lib.ck_gemm_sm_budget() - self.PULL_SMS)):
-            gemm(plan.mtile_first)
+        # the later windows are pulled back to back on the side stream, after the first pull (which keeps the whole machine)
         side.wait_event(first_done)
+        landed = []
         with torch.cuda.stream(side):
-            _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, edge, plan.cap)
-            rest_done = torch.cuda.Event()
-            rest_done.record(side)
+            for w in range(1, n_win):
+                _gather_rows_peer(b.tokens_ptrs, b.slots, dst, r, self.local_experts, b.top_k, rows[w], rows[w + 1])
+                ev = torch.cuda.Event()
+                ev.record(side)
+                landed.append(ev)
         dst.record_stream(side)
-        main.wait_event(rest_done)
-        gemm(plan.mtile_rest)
+        # the GEMM of every window but the last runs beside a pull: it leaves PULL_SMS SMs to it
+        narrow = max(2, _lib.lib.ck_gemm_sm_budget() - self.PULL_SMS)
+        for w in range(n_win):
+            if w > 0:
+                main.wait_event(landed[w - 1])
+            if w + 1 < n_win:
+                with _lib.gemm_sm_budget(narrow):
+                    gemm(plan.mtile_windows[w])
+            else:
+                gemm(plan.mtile_windows[w])
 
     # True: the GEMMs' own producer warp pulls the rows over NVLink (cp.async by row index, CTA-pair kernels) and leaves a
     # local grouped copy behind for the weight gradients.  False (default): a separate pull kernel runs first and the GEMM
