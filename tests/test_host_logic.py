@@ -268,3 +268,24 @@ def test_balanced_expert_placement_and_state_dict_round_trip():
     for g in range(4):
         local = shard_expert_state_dict(sd, g, 4, placement)
         assert local["c_fc.weight"][:, 0, 0].tolist() == [float(e) for e in range(8) if placement[e] == g]
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` needs no GPU: it times the CPU port on a bounded sample and prints one JSON line with the
+    keys the GPU arm's line carries."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, check=True).stdout.strip().splitlines()
+    assert len(out) == 1
+    line = json.loads(out[0])
+    assert line["impl"] == "reference" and line["metric"] == "moe_fwd_bwd_tokens_per_s" and line["unit"] == "tokens/s"
+    assert line["higher_is_better"] is True and line["steps"] == 1 and line["value"] > 0
+    assert line["config"]["workload"] == "c4_mixtral_moe_fwd_bwd"
+    cpu = line["cpu_baseline"]
+    assert cpu["kind"] == "port" and cpu["cores"] >= 1 and cpu["value"] == line["value"] and "sample" in cpu
+    assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}

@@ -251,3 +251,30 @@ def test_fused_gate_router_rejects_what_it_cannot_do_and_module_uses_it():
     assert same.float().mean() > 0.98  # a logit that rounds differently may swap two near-equal experts
     assert torch.equal(weights[same].view(torch.int16), w2[same].view(torch.int16)) or \
         torch.allclose(weights[same].float(), w2[same].float(), atol=2e-2)
+
+
+def test_fused_gate_router_nan_tokens_give_valid_distinct_ids():
+    """A token of NaNs gives NaN logits: they sort as the greatest value, the ids stay distinct and inside [0, E), the
+    weights are NaN like torch.softmax's, and the other tokens are untouched."""
+    from cute_kernels import router_gate_topk_softmax, router_topk_softmax
+
+    T, H, E, k = 200, 128, 16, 4
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(T, H, generator=g).bfloat16().cuda()
+    w = (torch.randn(E, H, generator=g) / H**0.5).bfloat16().cuda()
+    ref_l, ref_w, ref_i = router_gate_topk_softmax(x, w, k)
+    x2 = x.clone()
+    x2[7] = float("nan")
+    x2[130, :5] = float("nan")
+    logits, weights, ids = router_gate_topk_softmax(x2, w, k)
+    for t in (7, 130):
+        assert torch.isnan(logits[t].float()).all()
+        row = ids[t].tolist()
+        assert len(set(row)) == k and all(0 <= e < E for e in row)
+        assert row == list(range(k))  # all keys equal: ties go to the lower expert index
+        assert torch.isnan(weights[t].float()).all()
+    keep = torch.ones(T, dtype=torch.bool, device="cuda")
+    keep[[7, 130]] = False
+    assert torch.equal(ids[keep], ref_i[keep]) and torch.equal(weights[keep].view(torch.int16), ref_w[keep].view(torch.int16))
+    w2, i2 = router_topk_softmax(logits, k)
+    assert torch.equal(i2, ids)
