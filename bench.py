@@ -826,7 +826,7 @@ def gemm_cycle_profile(w: dict, device: torch.device) -> dict:
 
     import cute_kernels as ck
     from cute_kernels import _lib
-    from cute_kernels.moe import dgates_parts, dgrad_down, dgrad_up, down_combine_fwd, up_act_fwd
+    from cute_kernels.moe import dgates_parts, dgrad_down, dgrad_up, down_combine_fwd, up_act_fwd, wgrad
 
     lib = ctypes.CDLL(_lib.LIB_PATH)
     if not hasattr(lib, "ck_gemm_profile_read"):
@@ -838,6 +838,7 @@ def gemm_cycle_profile(w: dict, device: torch.device) -> dict:
     r = ck.route(ids.reshape(-1), E)
     cap = r.capacity
     rows = int((r.row_map >= 0).sum())
+    padded_rows = int(r.padded_off[E].item())
     gate_w = torch.rand(T * k, generator=g, device=device).to(dt)
     xg = torch.randn(cap, H, generator=g, device=device).to(dt)
     w_proj = torch.empty(E, H, I, device=device, dtype=dt).normal_(0, 0.02, generator=g)
@@ -847,12 +848,17 @@ def gemm_cycle_profile(w: dict, device: torch.device) -> dict:
     act = torch.randn(cap, I, generator=g, device=device).to(dt)
     dg_part = torch.empty(dgates_parts(I), cap, device=device, dtype=torch.float32)
     out32 = torch.zeros(T, H, device=device, dtype=torch.float32)
+    dw_proj = torch.empty(E, H, I, device=device, dtype=dt)
+    dw_fc = torch.empty(E, 2 * I, H, device=device, dtype=dt)
     swiglu = _lib.CK_ACT_SWIGLU
     launches = {
         "up_act_fwd": (lambda: up_act_fwd(xg, w_fc, None, gate_w, r.row_map, r.mtile_off, act, dh, swiglu), 2.0 * rows * H * 2 * I, H),
         "down_combine_fwd": (lambda: down_combine_fwd(act, w_proj, None, None, r.row_map, r.mtile_off, out32, k), 2.0 * rows * H * I, I),
         "dgrad_down": (lambda: dgrad_down(xg, w_proj, h, gate_w, r.row_map, r.mtile_off, dh, None, dg_part, swiglu), 2.0 * rows * H * I, H),
         "dgrad_up": (lambda: dgrad_up(dh, w_fc, r.row_map, r.mtile_off, out32, k), 2.0 * rows * H * 2 * I, 2 * I),
+        # weight gradients contract over an expert's padded rows: K = padded rows / experts on average
+        "wgrad_c_proj": (lambda: wgrad(xg, act, r.padded_off, dw_proj), 2.0 * rows * H * I, padded_rows / E),
+        "wgrad_c_fc": (lambda: wgrad(dh, xg, r.padded_off, dw_fc), 2.0 * rows * H * 2 * I, padded_rows / E),
     }
     slots, ctas = 16, 160
     out = {}
