@@ -1,20 +1,26 @@
 // Grouped GEMMs of the MoE expert path on tcgen05 tensor cores.
 //
-// One persistent, warp-specialised kernel template covers the five GEMMs of a forward + backward
-// pass.  Rows of every activation matrix live in the "padded grouped" layout produced by ck_route:
-// the rows routed to expert e occupy [padded_off[e], padded_off[e+1]), a multiple of 128 rows, pad
-// rows are zero.  A 128-row tile therefore belongs to exactly one expert and needs no row masks on
-// the operand side.
+// One persistent, warp-specialised kernel template covers the GEMMs of a forward + backward pass (and the router's gate
+// projection).  Rows of every activation matrix live in the "padded grouped" layout produced by ck_route: the rows routed
+// to expert e occupy [padded_off[e], padded_off[e+1]), a multiple of 128 rows, pad rows are zero.  A 128-row tile therefore
+// belongs to exactly one expert and needs no row masks on the operand side.
 //
-//   CTA (192 threads, one per SM, 128x256 output tile, fp32 accumulators in TMEM, double buffered)
-//     warp 0     : TMA producer  -- global -> 128B-swizzled shared memory, 4-stage mbarrier ring
-//     warp 1     : MMA issuer    -- tcgen05.mma (cta_group::1, M=128, N=256, K=32 bytes per instruction)
-//     warps 2..5 : epilogue      -- tcgen05.ld of the finished accumulator + the fused tail:
-//                                   activation, SwiGLU backward, router-weight grad, scatter-add
-//                                   combine, or a plain store (wgrad / generic grouped linear)
+// Two flavours of the same design (ck_set_gemm_cta_pair):
+//   CTA pair (default)  clusters of two CTAs share a 256 x 256 tile: each owns 128 rows and loads half of the B tile, one
+//                       tcgen05.mma.cta_group::2 issued by the leader reads both halves; 6-stage ring of 32 KiB per CTA
+//   single CTA          128 x 256 tile, cta_group::1, 4 stages of 48 KiB
+// Warp roles (one CTA per SM, fp32 accumulators in TMEM, 2 x 256 columns, double buffered):
+//     TMA producer   global -> 128B-swizzled shared memory through an mbarrier ring
+//     MMA issuer     tcgen05.mma, 32 bytes of K per instruction, commits free the stages / publish the accumulators
+//     epilogue       one or two groups of four warps: tcgen05.ld of the finished accumulator + the fused tail (activation,
+//                    activation backward, router-weight grad, scatter-add combine, router top-k, or a plain / scattered /
+//                    peer-memory store)
+// The producer and issuer loops are run by their whole warp, converged, with one elected lane issuing the predicated
+// TMA / MMA / commit instructions, and each probes the next stage's barrier before it issues the current stage's work:
+// a single thread's instruction stream between two k-blocks is otherwise what the tensor pipe waits for.
 //
-// Every mbarrier wait is bounded by wall-clock time; when one runs out the CTA raises
-// CK_DEV_TIMEOUT in the caller's status word, lets in-flight copies land, frees TMEM and returns.
+// Every mbarrier wait is bounded by wall-clock time; when one runs out the CTA raises CK_DEV_TIMEOUT in the caller's
+// status word, lets in-flight copies land, frees TMEM and returns.
 #include <cuda.h>
 #include <stdio.h>
 #include <stdlib.h>
