@@ -56,6 +56,11 @@ struct GemmParams {
     void *out0;                 // STORE/WGRAD: y | UP_ACT: act | ACT_BWD: dh
     void *out1;                 // UP_ACT: h (may be NULL) | ROUTER: router weights [tokens, top_k]
     int32_t *ids_out;           // ROUTER: expert ids [tokens, top_k]
+    // ROUTER: rows of the gate weight each TMA box of B holds (the boxes cover only rows that exist: a box that hangs over the
+    // end of the tensor is filled row by row at a fraction of the normal rate).  CTA pair: the leader's box (rows 0 ..) and the
+    // second CTA's (rows 128 .., tensor map tmOut; 0 = no load); single CTA: one box of b_rows_lead rows.
+    int b_rows_lead;
+    int b_rows_peer;
     float *out32;               // SCATTER_ADD target [T, N]
     const void *bias;           // per-expert bias of the GEMM's output features, [E, bias_ld] of T (may be NULL):
                                 //   UP_ACT: [up | gate] packed, bias_ld = 2I; UP_ACT1: bias_ld = I; STORE / SCATTER_ADD: bias_ld = N,
@@ -1030,7 +1035,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
                     if (nstage == kStages) { nstage = 0; nphase ^= 1u; }
                     ready = __all_sync(0xffffffffu, ptx::mbar_test_wait(empty0 + 8u * nstage, nphase ^ 1u)) != 0;
                     const uint32_t full = full0 + 8u * stage;
-                    ptx::mbar_expect_tx_elected(elected, full, kAStageBytes + kBStageBytes);
+                    ptx::mbar_expect_tx_elected(elected, full,
+                                                MODE == MODE_ROUTER ? kAStageBytes + uint32_t(p.b_rows_lead) * kRowBytes : kAStageBytes + kBStageBytes);
                     const uint32_t sa = smem_a + stage * kAStageBytes;
                     const uint32_t sb = smem_b + stage * kBStageBytes;
                     if constexpr (MODE == MODE_WGRAD) {
@@ -1321,7 +1327,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kT
     // A rows copied in by warps 2 and 3 (cp.async by row index) instead of a tiled TMA load
     const bool row_gather = CFG::kCanGather && p.gather_fan > 0;
     // transaction bytes per stage on the leader's barrier: both CTAs' TMA loads
-    const uint32_t stage_tx = row_gather ? 2u * kBHalfStageBytes : 2u * (kAStageBytes + kBHalfStageBytes);
+    const uint32_t stage_tx = MODE == MODE_ROUTER ? 2u * kAStageBytes + uint32_t(p.b_rows_lead + p.b_rows_peer) * kRowBytes
+                              : row_gather     ? 2u * kBHalfStageBytes
+                                               : 2u * (kAStageBytes + kBHalfStageBytes);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kNStages; ++s) {
@@ -1510,6 +1518,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<T, MODE>::kT
                         } else if constexpr (MODE == MODE_UP_ACT) {
                             // leader: 128 rows of W_up, peer: the matching 128 rows of W_gate
                             ptx::tma_load_3d_pair_hint_elected(elected, sb, &p.tmB, full, k0, rank * p.N + c.n_tile * (BN / 2), c.e, pol_b);
+                        } else if constexpr (MODE == MODE_ROUTER) {
+                            // only the rows of the gate weight that exist; the rest of the B tile feeds accumulator columns nobody reads
+                            if (rank == 0) ptx::tma_load_3d_pair_hint_elected(elected, sb, &p.tmB, full, k0, 0, 0, pol_b);
+                            else if (p.b_rows_peer > 0) ptx::tma_load_3d_pair_hint_elected(elected, sb, &p.tmOut, full, k0, BN / 2, 0, pol_b);
                         } else {
                             ptx::tma_load_3d_pair_hint_elected(elected, sb, &p.tmB, full, k0, nb0, c.e, pol_b);
                         }
@@ -2093,7 +2105,15 @@ static int router_gate_t(const void *x, const void *gate_w, void *logits, void *
     p.cap = m_tiles * BM;
     int rc;
     if ((rc = map_a_kmajor<T>(&p.tmA, x, tokens, H)) != CK_OK) return rc;
-    if ((rc = map_w_kmajor<T>(&p.tmB, gate_w, 1, E, H, use_cta_pair() ? BN / 2 : BN)) != CK_OK) return rc;
+    if (use_cta_pair()) {
+        p.b_rows_lead = E < BN / 2 ? E : BN / 2;
+        p.b_rows_peer = E > BN / 2 ? E - BN / 2 : 0;
+        if ((rc = map_w_kmajor<T>(&p.tmB, gate_w, 1, E, H, p.b_rows_lead)) != CK_OK) return rc;
+        if (p.b_rows_peer > 0 && (rc = map_w_kmajor<T>(&p.tmOut, gate_w, 1, E, H, p.b_rows_peer)) != CK_OK) return rc;
+    } else {
+        p.b_rows_lead = E;
+        if ((rc = map_w_kmajor<T>(&p.tmB, gate_w, 1, E, H, E)) != CK_OK) return rc;
+    }
     p.mtile_off = nullptr; p.m_tiles_w = int(m_tiles);
     p.out0 = logits; p.out1 = weights; p.ids_out = ids; p.dev_status = dev_status;
     p.E = 1; p.n_tiles = 1; p.N = E; p.K = H; p.M = int(tokens); p.top_k = top_k;
