@@ -826,7 +826,8 @@ def gemm_cycle_profile(w: dict, device: torch.device) -> dict:
 
     import cute_kernels as ck
     from cute_kernels import _lib
-    from cute_kernels.moe import dgates_parts, dgrad_down, dgrad_up, down_combine_fwd, up_act_fwd, wgrad
+    from cute_kernels.moe import (dgates_parts, dgrad_down, dgrad_up, down_combine_fwd, grouped_linear_scatter, up_act_fwd,
+                                  wgrad)
 
     lib = ctypes.CDLL(_lib.LIB_PATH)
     if not hasattr(lib, "ck_gemm_profile_read"):
@@ -850,12 +851,16 @@ def gemm_cycle_profile(w: dict, device: torch.device) -> dict:
     out32 = torch.zeros(T, H, device=device, dtype=torch.float32)
     dw_proj = torch.empty(E, H, I, device=device, dtype=dt)
     dw_fc = torch.empty(E, 2 * I, H, device=device, dtype=dt)
+    rows_h = torch.empty(T * k, H, device=device, dtype=dt)  # per-(token, slot) result rows of the row-store flavour
     swiglu = _lib.CK_ACT_SWIGLU
     launches = {
         "up_act_fwd": (lambda: up_act_fwd(xg, w_fc, None, gate_w, r.row_map, r.mtile_off, act, dh, swiglu), 2.0 * rows * H * 2 * I, H),
         "down_combine_fwd": (lambda: down_combine_fwd(act, w_proj, None, None, r.row_map, r.mtile_off, out32, k), 2.0 * rows * H * I, I),
         "dgrad_down": (lambda: dgrad_down(xg, w_proj, h, gate_w, r.row_map, r.mtile_off, dh, None, dg_part, swiglu), 2.0 * rows * H * I, H),
         "dgrad_up": (lambda: dgrad_up(dh, w_fc, r.row_map, r.mtile_off, out32, k), 2.0 * rows * H * 2 * I, 2 * I),
+        # the deterministic flavour (default for top-k > 2): rows stored by row_map, summed per token by a second kernel
+        "down_row_store": (lambda: grouped_linear_scatter(act, w_proj, None, None, r.mtile_off, r.row_map, rows_h, False), 2.0 * rows * H * I, I),
+        "dgrad_up_row_store": (lambda: grouped_linear_scatter(dh, w_fc, None, None, r.mtile_off, r.row_map, rows_h, True), 2.0 * rows * H * 2 * I, 2 * I),
         # weight gradients contract over an expert's padded rows: K = padded rows / experts on average
         "wgrad_c_proj": (lambda: wgrad(xg, act, r.padded_off, dw_proj), 2.0 * rows * H * I, padded_rows / E),
         "wgrad_c_fc": (lambda: wgrad(dh, xg, r.padded_off, dw_fc), 2.0 * rows * H * 2 * I, padded_rows / E),

@@ -1183,19 +1183,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) grouped_gemm_kernel(const __g
 #ifndef CK_PAIR_STAGES
 #define CK_PAIR_STAGES 6
 #endif
+#ifndef CK_STORE_TWO_GROUPS
+#define CK_STORE_TWO_GROUPS 1
+#endif
 constexpr int kBHalfStageBytes = kBStageBytes / 2;  // 16 KiB
 
 template <typename T, int MODE>
 struct PairCfg {
     static constexpr bool kHeavyEpilogue = (MODE == MODE_UP_ACT || MODE == MODE_ACT_BWD || MODE == MODE_UP_ACT1 || MODE == MODE_ACT1_BWD);
-    static constexpr int kEpiGroups = kHeavyEpilogue ? 2 : 1;
+    // The plain row store is light per element, but with a short contraction (K of a fine-grained expert: 22 k-blocks) four
+    // warps need longer for a tile's 128 x 256 results than the tensor pipe needs for the next tile: it gets eight as well.
+    static constexpr bool kTwoGroups = kHeavyEpilogue || (CK_STORE_TWO_GROUPS && MODE == MODE_STORE);
+    static constexpr int kEpiGroups = kTwoGroups ? 2 : 1;
     static constexpr int kEpiWarpsTotal = 4 * kEpiGroups;
     static constexpr int kThreads = 128 + 32 * kEpiWarpsTotal;
     // words per row of an epilogue warp's stage: 32 fp32 payload words, or 16 for rows of 16-bit results
     static constexpr int kPitch = (sizeof(T) == 4 || MODE == MODE_SCATTER_ADD) ? kStagePitchWords : kStagePitchWords16;
     static constexpr int kEpiBytes = kEpiWarpsTotal * (32 * kPitch * 4 + 32 * 4);
     // fp32 tensors with two epilogue groups need the wide stages for eight warps: one pipeline stage less
-    static constexpr int kStages = (kHeavyEpilogue && sizeof(T) == 4) ? CK_PAIR_STAGES - 1 : CK_PAIR_STAGES;
+    static constexpr int kStages = (kTwoGroups && sizeof(T) == 4) ? CK_PAIR_STAGES - 1 : CK_PAIR_STAGES;
     static constexpr bool kCanGather = kHeavyEpilogue;
     // registers per thread after the hand-over (two epilogue groups only): 128 x 80 + 256 x 208 <= 384 x 168
     static constexpr int kRegsControl = 80;
