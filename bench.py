@@ -816,7 +816,8 @@ def measure_moe_brief(w: dict, steps: int, warmup: int, device: torch.device, pe
 
 
 def gemm_cycle_profile(w: dict, device: torch.device) -> dict:
-    """Cycle accounting of the four CTA-pair GEMM launches of one layer shape, one isolated launch each.
+    """Cycle accounting of the CTA-pair GEMM launches of one layer shape (both combine flavours of the down projection and of
+    dgrad-up, and the two weight gradients), one isolated launch each.
 
     Needs a library built with ``make -C cute-kernels_b200/csrc clean all EXTRA=-DCK_GEMM_PROFILE`` (it exports
     ck_gemm_profile_read; the default build does not).  Per GEMM: cycles of the issuing thread per pair tile against the
