@@ -17,6 +17,13 @@ __device__ __forceinline__ void ld16f(const T *p, float (&v)[Vec16<T>::N]) {
     for (int i = 0; i < Vec16<T>::N; ++i) v[i] = DT<T>::up(r.v[i]);
 }
 template <typename T>
+__device__ __forceinline__ void up16f(const int4 &raw, float (&v)[Vec16<T>::N]) {  // 16 bytes already in registers
+    Vec16<T> r;
+    *reinterpret_cast<int4 *>(&r) = raw;
+#pragma unroll
+    for (int i = 0; i < Vec16<T>::N; ++i) v[i] = DT<T>::up(r.v[i]);
+}
+template <typename T>
 __device__ __forceinline__ void st16f(T *p, const float (&v)[Vec16<T>::N]) {
     Vec16<T> r;
 #pragma unroll
@@ -52,6 +59,12 @@ __global__ void __launch_bounds__(kRowThreads)
 }
 
 // out[t, :] = sum_{j<k} (w ? w[t*k+j] : 1) * src[pos[t*k+j], :]
+// The k rows are fetched kCombineBatch at a time, all loads of a batch issued before the first is used (one dependent
+// pos -> row load per thread in flight leaves the copy latency bound); the sum keeps the order j = 0 .. k-1.
+#ifndef CK_COMBINE_BATCH
+#define CK_COMBINE_BATCH 4
+#endif
+constexpr int kCombineBatch = CK_COMBINE_BATCH;
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
     combine_rows_kernel(const T *__restrict__ src, const int32_t *__restrict__ pos, const T *__restrict__ w,
@@ -64,15 +77,33 @@ __global__ void __launch_bounds__(kRowThreads)
         float acc[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) acc[i] = 0.0f;
-        for (int j = 0; j < k; ++j) {
-            const int64_t f = t * k + j;
-            const int64_t r = pos ? int64_t(pos[f]) : f;  // pos == NULL: the k rows of token t are rows t*k .. t*k+k-1
-            if (r < 0) continue;
-            float x[VEC];
-            ld16f(src + r * (vpr * VEC) + c, x);
-            const float wj = w ? DT<T>::up(w[f]) : 1.0f;
+        for (int j0 = 0; j0 < k; j0 += kCombineBatch) {
+            int64_t r[kCombineBatch];
+            float wj[kCombineBatch];
+            int4 raw[kCombineBatch];
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) acc[i] = fmaf(wj, x[i], acc[i]);
+            for (int u = 0; u < kCombineBatch; ++u) {
+                const int64_t f = t * k + j0 + u;
+                r[u] = -1;  // pos == NULL: the k rows of token t are rows t*k .. t*k+k-1
+                if (j0 + u < k) r[u] = pos ? int64_t(pos[f]) : f;
+            }
+#pragma unroll
+            for (int u = 0; u < kCombineBatch; ++u) {
+                raw[u] = make_int4(0, 0, 0, 0);
+                wj[u] = 0.0f;
+                if (r[u] >= 0) {
+                    raw[u] = __ldg(reinterpret_cast<const int4 *>(src + r[u] * (vpr * VEC) + c));
+                    wj[u] = w ? DT<T>::up(w[t * k + j0 + u]) : 1.0f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kCombineBatch; ++u) {
+                if (r[u] < 0) continue;  // an absent row adds nothing (not even a signed zero)
+                float x[VEC];
+                up16f<T>(raw[u], x);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] = fmaf(wj[u], x[i], acc[i]);
+            }
         }
         st16f(out + v * VEC, acc);
     }
